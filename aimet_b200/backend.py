@@ -1,0 +1,374 @@
+"""The ``b200`` quantization backend.
+
+This module satisfies aimet_torch's ``_QuantizationBackendProtocol``
+(quantization/affine/backends/utils.py:16-44): three callables ``quantize``,
+``dequantize`` and ``quantize_dequantize`` with the reference's argument meaning, validation
+errors and dtype rules (quantization/affine/backends/torch_builtins.py:119-302, 537-571),
+executed by the sm_100a kernels behind the C ABI.  Register it with
+``aimet_b200.register_backend()`` and select it with
+``aimet_torch.quantization.set_backend("b200")``.
+
+CUDA tensors only: a CPU tensor raises ``RuntimeError`` (there is no fallback path).
+"""
+
+from __future__ import annotations
+
+import functools
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import lib
+
+__all__ = ["quantize", "dequantize", "quantize_dequantize"]
+
+_MANTISSA_BITS = {
+    torch.float32: 23,
+    torch.float16: 10,
+    torch.bfloat16: 7,
+    torch.float64: 52,
+}
+
+
+# ---------------------------------------------------------------------------
+# dtype rules (torch_builtins.py:49-116)
+# ---------------------------------------------------------------------------
+def _is_value_representable(dtype: torch.dtype, value: int) -> bool:
+    """An integer is exact in ``dtype`` iff the span between its highest and lowest set bit
+    fits in the mantissa (and it is within range)."""
+    if dtype not in _MANTISSA_BITS:
+        raise ValueError(f"Expected dtype to be one of float32, float16, bfloat16, or float64; got {dtype}")
+    finfo = torch.finfo(dtype)
+    if not finfo.min <= value <= finfo.max:
+        return False
+    mag = abs(int(value))
+    if mag == 0:
+        return True
+    msb = mag.bit_length() - 1
+    lsb = (mag & -mag).bit_length() - 1
+    return msb - lsb <= _MANTISSA_BITS[dtype]
+
+
+@functools.lru_cache(None)
+def _is_grid_representable(dtype: torch.dtype, qmin: int, qmax: int) -> bool:
+    return all(_is_value_representable(dtype, v) for v in (qmax, qmax - 1, qmin + 1, qmin))
+
+
+def _is_numerically_stable(dtype: torch.dtype, qmin: int, qmax: int) -> bool:
+    if not _is_grid_representable(dtype, qmin, qmax):
+        return False
+    if qmin == qmax:
+        return True
+    return not torch.finfo(dtype).eps > 0.25 / (qmax - qmin)
+
+
+def _internal_dtype(dtype: torch.dtype, qmin: int, qmax: int) -> torch.dtype:
+    if _is_numerically_stable(dtype, qmin, qmax):
+        return dtype
+    if _is_numerically_stable(torch.float32, qmin, qmax):
+        return torch.float32
+    return torch.float64
+
+
+# ---------------------------------------------------------------------------
+# validation (torch_builtins.py:119-162)
+# ---------------------------------------------------------------------------
+def _is_expandable(src: Sequence[int], dst: Sequence[int]) -> bool:
+    if len(src) > len(dst):
+        return False
+    return all(s in (1, d) for s, d in zip(reversed(src), reversed(dst)))
+
+
+def _validate(tensor, scale, offset, qmin=None, qmax=None, block_size=None):
+    for name, t in (("input", tensor), ("scale", scale), ("offset", offset)):
+        if not isinstance(t, torch.Tensor):
+            raise TypeError(f"{name} must be a torch.Tensor, got {type(t)}")
+    if not tensor.is_cuda:
+        raise RuntimeError(
+            "aimet_b200 runs on CUDA tensors only (got a tensor on "
+            f"'{tensor.device}'); there is no CPU fallback in this backend."
+        )
+    if scale.device != tensor.device or offset.device != tensor.device:
+        raise RuntimeError(
+            "Expected all tensors to be on the same device, but found input on "
+            f"{tensor.device}, scale on {scale.device} and offset on {offset.device}"
+        )
+    if block_size is not None:
+        if len(scale.shape) != len(block_size):
+            raise RuntimeError(
+                f"Length of scale shape {scale.shape} must equal length of block size {block_size}"
+            )
+        if len(tensor.shape) < len(scale.shape):
+            raise RuntimeError(
+                f"Input shape {tuple(tensor.shape)} must have at least as many dimensions as "
+                f"scale shape {tuple(scale.shape)}."
+            )
+        for i in range(1, len(block_size) + 1):
+            if block_size[-i] == -1:
+                if scale.shape[-i] == 0 or tensor.shape[-i] % scale.shape[-i] != 0:
+                    raise RuntimeError(
+                        f"Each tensor dimension size for tensor shape {tensor.shape} must divide "
+                        f"evenly with corresponding scale dimension value for scale shape {scale.shape}"
+                    )
+            elif block_size[-i] * scale.shape[-i] != tensor.shape[-i]:
+                raise RuntimeError(
+                    f"Each tensor dimension size for tensor shape {tensor.shape} must equal the "
+                    f"corresponding scale dimension size * block size for scale shape {scale.shape} "
+                    f"and block size {block_size}"
+                )
+    elif not _is_expandable(scale.shape, tensor.shape):
+        msg = f"Scale of shape {scale.shape} cannot be expanded like input tensor of shape {tensor.shape}. "
+        if tensor.numel() == 0:
+            msg += "Detected that the tensor is empty; check that the input tensor is the intended one."
+        raise RuntimeError(msg)
+    if qmin is not None and qmax is not None and qmin > qmax:
+        raise RuntimeError(f"qmin ({qmin}) must be smaller than or equal to qmax ({qmax})")
+
+
+# ---------------------------------------------------------------------------
+# layout: which run of coordinates along each dim shares one parameter
+# ---------------------------------------------------------------------------
+def _param_blocks(shape: Sequence[int], pshape: Sequence[int], block_size) -> Tuple[int, ...]:
+    """Elements per parameter along each tensor dim (parameter shape right-aligned)."""
+    nd = len(shape)
+    pad = nd - len(pshape)
+    blocks = []
+    for k in range(nd):
+        if k < pad:
+            blocks.append(shape[k])
+            continue
+        p = pshape[k - pad]
+        if block_size is None:
+            blocks.append(shape[k] if p == 1 else 1)
+        else:
+            b = block_size[k - pad]
+            blocks.append(shape[k] // p if b == -1 else b)
+    return tuple(int(max(b, 1)) for b in blocks)
+
+
+def _dense_perm(t: torch.Tensor) -> Optional[Tuple[int, ...]]:
+    """Permutation of dims under which ``t`` is row-major contiguous, else None."""
+    if t.is_contiguous():
+        return tuple(range(t.dim()))
+    perm = tuple(sorted(range(t.dim()), key=lambda k: (-t.stride(k), k)))
+    if t.permute(perm).is_contiguous():
+        return perm
+    return None
+
+
+class _Plan:
+    """Everything the C ABI needs to know about one call, derived once in forward."""
+
+    __slots__ = ("perm", "layout", "io", "ct", "pt", "pshape", "upcast")
+
+    def __init__(self, perm, layout, io, ct, pt, pshape, upcast):
+        self.perm, self.layout, self.io, self.ct, self.pt = perm, layout, io, ct, pt
+        self.pshape, self.upcast = pshape, upcast
+
+
+def _prepare(tensor, scale, offset, block_size, internal_dtype):
+    """Returns (x_dense_view, plan).  ``x_dense_view`` is a contiguous permuted view (or copy)."""
+    pshape = torch.broadcast_shapes(scale.shape, offset.shape)
+    perm = None if block_size else _dense_perm(tensor)
+    if perm is None:
+        x = tensor.contiguous()
+        perm = tuple(range(tensor.dim()))
+    else:
+        x = tensor.permute(perm)
+    blocks = _param_blocks(tensor.shape, pshape, block_size)
+    if list(perm) != list(range(tensor.dim())):
+        # parameters follow the logical dim order; only a permutation that keeps the parameter
+        # array row-major can be described to the kernels, otherwise densify the input
+        pdims = [k for k in perm if tensor.shape[k] // blocks[k] > 1]
+        if pdims != sorted(pdims):
+            x = tensor.contiguous()
+            perm = tuple(range(tensor.dim()))
+    size_p = [tensor.shape[k] for k in perm]
+    block_p = [blocks[k] for k in perm]
+
+    io_dtype = x.dtype
+    upcast = False
+    if io_dtype not in _lib.DTYPE_CODE:
+        raise RuntimeError(f"aimet_b200 supports float16, bfloat16, float32 and float64 inputs; got {io_dtype}")
+    if internal_dtype == torch.float64 and io_dtype in (torch.float16, torch.bfloat16):
+        x = x.to(torch.float32)
+        io_dtype = torch.float32
+        upcast = True
+    elif internal_dtype == torch.float32 and io_dtype == torch.float64:
+        internal_dtype = torch.float64
+    pt = torch.float64 if internal_dtype == torch.float64 else torch.float32
+    plan = _Plan(
+        perm,
+        _lib.make_layout(size_p, block_p),
+        _lib.DTYPE_CODE[io_dtype],
+        _lib.DTYPE_CODE[internal_dtype],
+        pt,
+        tuple(pshape),
+        upcast,
+    )
+    return x, plan
+
+
+def _params(scale, offset, plan: _Plan):
+    s = scale.detach().expand(plan.pshape).to(plan.pt).contiguous()
+    o = offset.detach().expand(plan.pshape).to(plan.pt).contiguous()
+    return s, o
+
+
+def _restore(y_dense: torch.Tensor, plan: _Plan, like: torch.Tensor) -> torch.Tensor:
+    """Undo the dense permutation and the optional upcast."""
+    if plan.upcast:
+        y_dense = y_dense.to(like.dtype)
+    inv = [0] * len(plan.perm)
+    for i, k in enumerate(plan.perm):
+        inv[k] = i
+    return y_dense.permute(inv) if list(inv) != sorted(inv) else y_dense
+
+
+_OPS_FWD = {
+    "q": lib.aimet_b200_quantize,
+    "dq": lib.aimet_b200_dequantize,
+    "qdq": lib.aimet_b200_quantize_dequantize,
+}
+
+
+class _AffineFunction(torch.autograd.Function):
+    """Forward and backward of the three affine functionals through the C ABI.
+
+    Gradients follow QuantizeFunc / DequantizeFunc / QuantDequantFunc.backward
+    (torch_builtins.py:637-659, 689-701, 772-831); scale and offset gradients come back already
+    reduced to the parameter shape.
+    """
+
+    @staticmethod
+    def forward(ctx, tensor, scale, offset, op, qmin, qmax, zps, block_size, internal_dtype):
+        x, plan = _prepare(tensor, scale, offset, block_size, internal_dtype)
+        s, o = _params(scale, offset, plan)
+        y = torch.empty_like(x, memory_format=torch.contiguous_format)
+        if x.numel() > 0:
+            with torch.cuda.device(x.device):
+                st = _lib.stream_ptr(x.device)
+                if op == "q":
+                    rc = lib.aimet_b200_quantize(x.data_ptr(), y.data_ptr(), s.data_ptr(), o.data_ptr(),
+                                                 plan.layout, plan.io, plan.ct, _lib.DTYPE_CODE[plan.pt],
+                                                 qmin, qmax, st)
+                elif op == "dq":
+                    rc = lib.aimet_b200_dequantize(x.data_ptr(), y.data_ptr(), s.data_ptr(), o.data_ptr(),
+                                                   plan.layout, plan.io, plan.ct, _lib.DTYPE_CODE[plan.pt], st)
+                else:
+                    rc = lib.aimet_b200_quantize_dequantize(x.data_ptr(), y.data_ptr(), s.data_ptr(),
+                                                            o.data_ptr(), plan.layout, plan.io, plan.ct,
+                                                            _lib.DTYPE_CODE[plan.pt], qmin, qmax, float(zps), st)
+            _lib.check(rc)
+        ctx.plan = plan
+        ctx.op, ctx.qmin, ctx.qmax, ctx.zps = op, qmin, qmax, float(zps)
+        ctx.in_dtype = tensor.dtype
+        ctx.scale_meta = (scale.shape, scale.dtype)
+        ctx.offset_meta = (offset.shape, offset.dtype)
+        if any(ctx.needs_input_grad[:3]):
+            ctx.save_for_backward(x, s, o)
+        return _restore(y, plan, tensor)
+
+    @staticmethod
+    def backward(ctx, grad):
+        x, s, o = ctx.saved_tensors
+        plan: _Plan = ctx.plan
+        need_x, need_s, need_o = ctx.needs_input_grad[:3]
+        g = grad.permute(plan.perm).to(x.dtype).contiguous()
+        gx = torch.empty_like(x) if need_x else None
+        gs = torch.empty(plan.pshape, dtype=plan.pt, device=x.device) if need_s else None
+        go = torch.empty(plan.pshape, dtype=plan.pt, device=x.device) if need_o else None
+        if x.numel() == 0:
+            if gs is not None:
+                gs.zero_()
+            if go is not None:
+                go.zero_()
+        else:
+            with torch.cuda.device(x.device):
+                nbytes = lib.aimet_b200_backward_scratch_bytes(plan.layout, plan.io)
+                _lib.check(nbytes)
+                scratch = _lib.scratch.get(x.device, nbytes) if (need_s or need_o) else None
+                st = _lib.stream_ptr(x.device)
+                common = (x.data_ptr(), g.data_ptr(), s.data_ptr(), o.data_ptr(), plan.layout, plan.io,
+                          plan.ct, _lib.DTYPE_CODE[plan.pt])
+                tail = (_lib.ptr(gx), _lib.ptr(gs), _lib.ptr(go), _lib.ptr(scratch),
+                        0 if scratch is None else scratch.numel(), st)
+                if ctx.op == "q":
+                    rc = lib.aimet_b200_quantize_backward(*common, ctx.qmin, ctx.qmax, *tail)
+                elif ctx.op == "dq":
+                    rc = lib.aimet_b200_dequantize_backward(*common, *tail)
+                else:
+                    rc = lib.aimet_b200_quantize_dequantize_backward(*common, ctx.qmin, ctx.qmax, ctx.zps, *tail)
+            _lib.check(rc)
+        if gx is not None:
+            gx = _restore(gx, plan, grad).to(ctx.in_dtype)
+        if gs is not None:
+            gs = gs.sum_to_size(ctx.scale_meta[0]).to(ctx.scale_meta[1])
+        if go is not None:
+            go = go.sum_to_size(ctx.offset_meta[0]).to(ctx.offset_meta[1])
+        return gx, gs, go, None, None, None, None, None, None
+
+
+def _normalize_block_size(block_size) -> Optional[Tuple[int, ...]]:
+    if block_size is None:
+        return None
+    block_size = tuple(int(b) for b in block_size)
+    return block_size or None
+
+
+def quantize(
+    input: torch.Tensor,  # pylint: disable=redefined-builtin
+    scale: torch.Tensor,
+    offset: torch.Tensor,
+    qmin: int,
+    qmax: int,
+    block_size: Optional[List] = None,
+) -> torch.Tensor:
+    """``clamp(round(input / scale) - offset, qmin, qmax)`` as float-valued integer codes in
+    ``input.dtype`` (torch_builtins.py:166-212)."""
+    block_size = _normalize_block_size(block_size)
+    _validate(input, scale, offset, qmin, qmax, block_size)
+    qmin, qmax = int(qmin), int(qmax)
+    if not _is_grid_representable(input.dtype, qmin, qmax):
+        raise RuntimeError(f"{input.dtype} is unable to represent quantized output of range [{qmin}, {qmax}].")
+    internal = _internal_dtype(input.dtype, qmin, qmax)
+    return _AffineFunction.apply(input, scale, offset, "q", qmin, qmax, 0.0, block_size, internal)
+
+
+def dequantize(
+    input: torch.Tensor,  # pylint: disable=redefined-builtin
+    scale: torch.Tensor,
+    offset: torch.Tensor,
+    block_size: Optional[List] = None,
+) -> torch.Tensor:
+    """``(input + offset) * scale`` evaluated in ``input.dtype`` (torch_builtins.py:537-571)."""
+    block_size = _normalize_block_size(block_size)
+    _validate(input, scale, offset, block_size=block_size)
+    return _AffineFunction.apply(input, scale, offset, "dq", 0, 0, 0.0, block_size, input.dtype)
+
+
+def quantize_dequantize(
+    input: torch.Tensor,  # pylint: disable=redefined-builtin
+    scale: torch.Tensor,
+    offset: torch.Tensor,
+    qmin: int,
+    qmax: int,
+    block_size: Optional[List] = None,
+    zero_point_shift: float = 0.0,
+) -> torch.Tensor:
+    """Fake-quantization ``(clamp(round(input / scale - zps) - offset, qmin, qmax) + offset + zps) * scale``
+    with straight-through gradients (torch_builtins.py:216-302).
+
+    Every mode -- with or without gradients -- evaluates the ``QuantDequantFunc`` arithmetic (true
+    division, round-half-to-even) in the reference's internal dtype.
+    """
+    if torch.onnx.is_in_onnx_export():
+        return input
+    block_size = _normalize_block_size(block_size)
+    _validate(input, scale, offset, qmin, qmax, block_size)
+    qmin, qmax = int(qmin), int(qmax)
+    internal = _internal_dtype(input.dtype, qmin, qmax)
+    if not _is_grid_representable(internal, qmin, qmax):
+        raise RuntimeError(f"{internal} is unable to represent quantized output of range [{qmin}, {qmax}].")
+    return _AffineFunction.apply(input, scale, offset, "qdq", qmin, qmax, zero_point_shift or 0.0, block_size, internal)

@@ -1,0 +1,636 @@
+// Calibration statistics: single-pass min/max, shared-memory histograms with
+// the exact torch.histc binning rule, and the SQNR candidate sweep over a
+// histogram.  Follows quantization/encoding_analyzer.py of the reference:
+// _MinMaxObserver (:69-118), _HistogramObserver (:121-338) and
+// _LpNormEncodingAnalyzer._estimate_clip_and_quant_noise (:822-899).
+#include <math.h>
+
+#include "common.cuh"
+
+namespace ab {
+namespace {
+
+// ---------------------------------------------------------------------------
+// min / max
+// ---------------------------------------------------------------------------
+template <typename T> struct MinMax {
+    T lo, hi;
+};
+
+// torch.amin / amax semantics: NaN wins.
+template <typename T> __device__ __forceinline__ void mm_update(MinMax<T> &m, T v, bool finite_only) {
+    if (finite_only) {
+        if (!isfinite(v)) return;
+        m.lo = v < m.lo ? v : m.lo;
+        m.hi = v > m.hi ? v : m.hi;
+    } else {
+        // once NaN, comparisons keep it: (v < NaN) is false and v != v picks up new NaNs
+        m.lo = (v < m.lo || v != v) ? v : m.lo;
+        m.hi = (v > m.hi || v != v) ? v : m.hi;
+    }
+}
+template <typename T> __device__ __forceinline__ void mm_merge(MinMax<T> &m, T lo, T hi) {
+    m.lo = (lo < m.lo || lo != lo) ? lo : m.lo;
+    m.hi = (hi > m.hi || hi != hi) ? hi : m.hi;
+}
+template <typename T> __device__ __forceinline__ MinMax<T> mm_init() {
+    MinMax<T> m;
+    m.lo = (T)INFINITY;
+    m.hi = (T)-INFINITY;
+    return m;
+}
+
+template <int IO> struct StatT { using T = float; };
+template <> struct StatT<AB_F64> { using T = double; };
+
+template <typename T, typename E> __device__ __forceinline__ T stat_load(E v) { return (T)to_f32(v); }
+template <> __device__ __forceinline__ double stat_load<double, double>(double v) { return v; }
+
+template <typename E> __device__ __forceinline__ E stat_store(double v);
+template <> __device__ __forceinline__ float stat_store<float>(double v) { return (float)v; }
+template <> __device__ __forceinline__ double stat_store<double>(double v) { return v; }
+template <> __device__ __forceinline__ __half stat_store<__half>(double v) { return __float2half_rn((float)v); }
+template <> __device__ __forceinline__ __nv_bfloat16 stat_store<__nv_bfloat16>(double v) {
+    return __float2bfloat16_rn((float)v);
+}
+
+struct MinMaxArgs {
+    const void *x;
+    void *min_out, *max_out;  // io dtype, direct mode
+    double *partial;          // [npartial][2]
+    ChanMap cm;
+    int64_t seg_len, nseg, nchunk;
+    int group, direct;
+    int64_t rows, row_len, rows_per_tile;
+    int finite_only;
+};
+
+template <int IO, bool VECT> __global__ void __launch_bounds__(kThreads) k_minmax_seg(MinMaxArgs a) {
+    using E = typename Elem<IO>::type;
+    using T = typename StatT<IO>::T;
+    constexpr int VEC = VECT ? 16 / (int)sizeof(E) : 1;
+    const E *__restrict__ xp = static_cast<const E *>(a.x);
+    const int G = a.group;
+    const int64_t s = (int64_t)blockIdx.x * (kThreads / G) + threadIdx.x / G;
+    const int lane = threadIdx.x % G;
+    const bool valid = s < a.nseg;
+    MinMax<T> m = mm_init<T>();
+    int64_t param = 0;
+    if (valid) {
+        const int64_t ts = s / a.nchunk;
+        const int64_t k = s - ts * a.nchunk;
+        const int64_t start = ts * a.cm.I + k * a.seg_len;
+        int64_t len = a.cm.I - k * a.seg_len;
+        if (len > a.seg_len) len = a.seg_len;
+        param = a.cm.C == 1 ? 0 : (a.cm.wrap ? ts % a.cm.C : ts);
+        const int64_t nv = len / VEC, v0 = start / VEC;
+        for (int64_t v = lane; v < nv; v += 2 * (int64_t)G) {
+            const bool hb = v + G < nv;
+            if (VECT) {
+                Vec16<E> xa = reinterpret_cast<const Vec16<E> *>(xp)[v0 + v], xb;
+                if (hb) xb = reinterpret_cast<const Vec16<E> *>(xp)[v0 + v + G];
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) mm_update(m, stat_load<T, E>(xa.v[i]), a.finite_only);
+                if (hb) {
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) mm_update(m, stat_load<T, E>(xb.v[i]), a.finite_only);
+                }
+            } else {
+                mm_update(m, stat_load<T, E>(xp[v0 + v]), a.finite_only);
+                if (hb) mm_update(m, stat_load<T, E>(xp[v0 + v + G]), a.finite_only);
+            }
+        }
+    }
+    const int span = G < 32 ? G : 32;
+    for (int o = span >> 1; o > 0; o >>= 1) {
+        T lo = __shfl_xor_sync(0xffffffffu, m.lo, o);
+        T hi = __shfl_xor_sync(0xffffffffu, m.hi, o);
+        mm_merge(m, lo, hi);
+    }
+    if (G > 32) {
+        __shared__ double sh[2][kThreads / 32];
+        const int warp = threadIdx.x >> 5;
+        if ((threadIdx.x & 31) == 0) {
+            sh[0][warp] = (double)m.lo;
+            sh[1][warp] = (double)m.hi;
+        }
+        __syncthreads();
+        if (lane == 0) {
+            const int w0 = (threadIdx.x / G) * (G / 32);
+            for (int w = 1; w < G / 32; ++w) mm_merge(m, (T)sh[0][w0 + w], (T)sh[1][w0 + w]);
+        }
+    }
+    if (valid && lane == 0) {
+        if (a.direct) {
+            static_cast<E *>(a.min_out)[param] = stat_store<E>((double)m.lo);
+            static_cast<E *>(a.max_out)[param] = stat_store<E>((double)m.hi);
+        } else {
+            a.partial[2 * s] = (double)m.lo;
+            a.partial[2 * s + 1] = (double)m.hi;
+        }
+    }
+}
+
+template <int IO, bool VECT> __global__ void __launch_bounds__(kThreads) k_minmax_col(MinMaxArgs a) {
+    using E = typename Elem<IO>::type;
+    using T = typename StatT<IO>::T;
+    constexpr int VEC = VECT ? 16 / (int)sizeof(E) : 1;
+    const E *__restrict__ xp = static_cast<const E *>(a.x);
+    const int64_t cv = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    const int64_t ncv = a.row_len / VEC;
+    if (cv >= ncv) return;
+    const int64_t r0 = (int64_t)blockIdx.y * a.rows_per_tile;
+    int64_t r1 = r0 + a.rows_per_tile;
+    if (r1 > a.rows) r1 = a.rows;
+    MinMax<T> m[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) m[i] = mm_init<T>();
+    for (int64_t r = r0; r < r1; r += 2) {
+        const bool hb = r + 1 < r1;
+        Vec16<E> xa, xb;
+        if (VECT) {
+            xa = reinterpret_cast<const Vec16<E> *>(xp)[r * ncv + cv];
+            if (hb) xb = reinterpret_cast<const Vec16<E> *>(xp)[(r + 1) * ncv + cv];
+        } else {
+            xa.v[0] = xp[r * ncv + cv];
+            if (hb) xb.v[0] = xp[(r + 1) * ncv + cv];
+        }
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) mm_update(m[i], stat_load<T, E>(xa.v[i]), a.finite_only);
+        if (hb) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) mm_update(m[i], stat_load<T, E>(xb.v[i]), a.finite_only);
+        }
+    }
+    double *out = a.partial + 2 * ((int64_t)blockIdx.y * a.row_len + cv * VEC);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        out[2 * i] = (double)m[i].lo;
+        out[2 * i + 1] = (double)m[i].hi;
+    }
+}
+
+struct MinMaxFinishArgs {
+    const double *partial;
+    void *min_out, *max_out;
+    int64_t nparam, na, sa, sc, nb;
+};
+
+template <int IO> __global__ void __launch_bounds__(kThreads) k_minmax_finish(MinMaxFinishArgs a) {
+    using E = typename Elem<IO>::type;
+    const int64_t c = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (c >= a.nparam) return;
+    MinMax<double> m = mm_init<double>();
+    const int64_t n = a.na * a.nb;
+    for (int64_t t = lane; t < n; t += 32) {
+        const int64_t ia = t / a.nb, ib = t - ia * a.nb;
+        const double *p = a.partial + 2 * (ia * a.sa + c * a.sc + ib);
+        mm_merge(m, p[0], p[1]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        double lo = __shfl_xor_sync(0xffffffffu, m.lo, o);
+        double hi = __shfl_xor_sync(0xffffffffu, m.hi, o);
+        mm_merge(m, lo, hi);
+    }
+    if (lane == 0) {
+        static_cast<E *>(a.min_out)[c] = stat_store<E>(m.lo);
+        static_cast<E *>(a.max_out)[c] = stat_store<E>(m.hi);
+    }
+}
+
+template <int IO>
+int launch_minmax(const void *x, const Canon &canon, int finite_only, void *min_out, void *max_out,
+                  void *scratch, int64_t scratch_bytes, cudaStream_t stream) {
+    const ReducePlan p = plan_reduce(canon, IO, aligned16(x));
+    if (p.mode == ReducePlan::GEN)
+        return fail(AB_ERR_UNSUPPORTED, "statistics need a layout that reduces to (outer, channel, inner)");
+    const int64_t need = p.npartial * 2 * (int64_t)sizeof(double);
+    if (need > 0 && (!scratch || scratch_bytes < need))
+        return fail(AB_ERR_SCRATCH, "min/max needs %lld bytes of scratch, got %lld", (long long)need,
+                    (long long)scratch_bytes);
+    MinMaxArgs a;
+    a.x = x;
+    a.min_out = min_out;
+    a.max_out = max_out;
+    a.partial = static_cast<double *>(scratch);
+    a.cm = make_chan_map(canon);
+    a.seg_len = p.seg_len;
+    a.nseg = p.nseg;
+    a.nchunk = p.nchunk;
+    a.group = p.group;
+    a.direct = p.direct;
+    a.rows = canon.O;
+    a.row_len = canon.C * canon.I;
+    a.rows_per_tile = p.rows_per_tile;
+    a.finite_only = finite_only;
+    if (p.mode == ReducePlan::SEG) {
+        const int gpc = kThreads / p.group;
+        const int64_t grid = (p.nseg + gpc - 1) / gpc;
+        if (grid > 2147483647LL) return fail(AB_ERR_UNSUPPORTED, "tensor too large for one launch");
+        if (p.vect)
+            k_minmax_seg<IO, true><<<(unsigned)grid, kThreads, 0, stream>>>(a);
+        else
+            k_minmax_seg<IO, false><<<(unsigned)grid, kThreads, 0, stream>>>(a);
+    } else {
+        const int v = p.vect ? 16 / dtype_size(IO) : 1;
+        const int64_t gx = (a.row_len / v + kThreads - 1) / kThreads;
+        dim3 grid((unsigned)gx, (unsigned)p.row_tiles);
+        if (p.vect)
+            k_minmax_col<IO, true><<<grid, kThreads, 0, stream>>>(a);
+        else
+            k_minmax_col<IO, false><<<grid, kThreads, 0, stream>>>(a);
+    }
+    AB_LAUNCH_OK();
+    if (p.npartial > 0) {
+        MinMaxFinishArgs f{a.partial, min_out, max_out, canon.nparam, p.na, p.sa, p.sc, p.nb};
+        const int64_t grid = (canon.nparam * 32 + kThreads - 1) / kThreads;
+        k_minmax_finish<IO><<<(unsigned)grid, kThreads, 0, stream>>>(f);
+        AB_LAUNCH_OK();
+    }
+    return AB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// histogram
+// ---------------------------------------------------------------------------
+constexpr int kHistUnroll = 4;
+
+struct HistArgs {
+    const void *x;
+    const float *lo, *hi, *below, *above;
+    unsigned long long *counts;  // [C][num_bins]
+    double *mm_partial;          // [C][tiles][2] or NULL
+    int64_t O, C, I;
+    int64_t chan_elems;          // O * I
+    int64_t tile_elems;          // elements of one channel handled by one CTA (multiple of 16)
+    int num_bins;
+    int tiles;                   // CTAs per channel
+};
+
+// torch.histc's bin of v over [lo, hi] (CPU and CUDA kernels agree):
+//   bin = (int)((v - lo) * num_bins / (hi - lo)), with v == hi folded into the last bin.
+__device__ __forceinline__ int histc_bin(float v, float lo, float range, float nbins_f, int nbins) {
+    int b = __float2int_rz(__fdiv_rn(__fmul_rn(__fsub_rn(v, lo), nbins_f), range));
+    return b >= nbins ? nbins - 1 : b;
+}
+
+// One CTA bins one tile of one channel into a shared-memory histogram.  Values
+// of a calibration batch pile up in a handful of bins, so a warp whose lanes all
+// hit the same bin issues a single shared-memory atomic.
+template <int IO, bool VECT> __global__ void __launch_bounds__(kThreads) k_histogram(HistArgs a) {
+    using E = typename Elem<IO>::type;
+    constexpr int VEC = VECT ? 16 / (int)sizeof(E) : 1;
+    extern __shared__ unsigned int sh_hist[];
+    __shared__ unsigned long long sh_edge[2];
+    __shared__ float sh_mm[2][kThreads / 32];
+
+    const int64_t c = blockIdx.y;
+    const int tile = blockIdx.x;
+    for (int b = threadIdx.x; b < a.num_bins; b += kThreads) sh_hist[b] = 0;
+    if (threadIdx.x < 2) sh_edge[threadIdx.x] = 0;
+    __syncthreads();
+
+    const float lo = a.lo[c], hi = a.hi[c];
+    const float range = __fsub_rn(hi, lo);
+    const float nbf = (float)a.num_bins;
+    const float below = a.below[c], above = a.above[c];
+    const E *__restrict__ xp = static_cast<const E *>(a.x);
+
+    const int64_t e0 = (int64_t)tile * a.tile_elems;
+    int64_t e1 = e0 + a.tile_elems;
+    if (e1 > a.chan_elems) e1 = a.chan_elems;
+
+    unsigned int n_below = 0, n_above = 0;
+    float fmin_ = INFINITY, fmax_ = -INFINITY;
+    const bool want_mm = a.mm_partial != nullptr;
+    const unsigned full = 0xffffffffu;
+    const int lane = threadIdx.x & 31;
+
+    auto consume = [&](float v, int &run_bin, unsigned int &run_cnt) {
+        if (v < below) ++n_below;
+        if (v > above) ++n_above;
+        if (want_mm && isfinite(v)) {
+            fmin_ = fminf(fmin_, v);
+            fmax_ = fmaxf(fmax_, v);
+        }
+        if (v >= lo && v <= hi) {
+            const int b = histc_bin(v, lo, range, nbf, a.num_bins);
+            if (b == run_bin) {
+                ++run_cnt;
+            } else {
+                if (run_cnt) atomicAdd(&sh_hist[run_bin], run_cnt);
+                run_bin = b;
+                run_cnt = 1;
+            }
+        }
+    };
+
+    // element index within the channel -> address: (o * C + c) * I + i
+    const bool flat = (a.C == 1);
+    const int64_t nvec = (e1 - e0) / VEC;  // tiles and runs are multiples of VEC when VECT
+    // the trip count is the same for every thread of the CTA: the warp-wide votes below need all lanes
+    for (int64_t base = 0; base < nvec; base += kThreads * kHistUnroll) {
+        const int64_t v0 = base + threadIdx.x;
+        Vec16<E> xv[kHistUnroll];
+        bool ok[kHistUnroll];
+#pragma unroll
+        for (int u = 0; u < kHistUnroll; ++u) {
+            const int64_t v = v0 + (int64_t)u * kThreads;
+            ok[u] = v < nvec;
+            if (ok[u]) {
+                const int64_t e = e0 + v * VEC;
+                int64_t addr;
+                if (flat) {
+                    addr = e;
+                } else {
+                    const int64_t o = e / a.I, i = e - o * a.I;
+                    addr = (o * a.C + c) * a.I + i;
+                }
+                if (VECT)
+                    xv[u] = *reinterpret_cast<const Vec16<E> *>(xp + addr);
+                else
+                    xv[u].v[0] = xp[addr];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kHistUnroll; ++u) {
+            int run_bin = -1;
+            unsigned int run_cnt = 0;
+            if (ok[u]) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) consume(to_f32(xv[u].v[i]), run_bin, run_cnt);
+            }
+            // warp-uniform fast path: every lane ended on the same bin
+            const int b0 = __shfl_sync(full, run_bin, 0);
+            if (__all_sync(full, run_bin == b0)) {
+                const unsigned int tot = __reduce_add_sync(full, run_cnt);
+                if (lane == 0 && tot) atomicAdd(&sh_hist[b0], tot);
+            } else if (run_cnt) {
+                atomicAdd(&sh_hist[run_bin], run_cnt);
+            }
+        }
+    }
+
+    // below / above counts
+    n_below = __reduce_add_sync(full, n_below);
+    n_above = __reduce_add_sync(full, n_above);
+    if (lane == 0) {
+        if (n_below) atomicAdd(&sh_edge[0], (unsigned long long)n_below);
+        if (n_above) atomicAdd(&sh_edge[1], (unsigned long long)n_above);
+    }
+    if (want_mm) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            fmin_ = fminf(fmin_, __shfl_xor_sync(full, fmin_, o));
+            fmax_ = fmaxf(fmax_, __shfl_xor_sync(full, fmax_, o));
+        }
+        if (lane == 0) {
+            sh_mm[0][threadIdx.x >> 5] = fmin_;
+            sh_mm[1][threadIdx.x >> 5] = fmax_;
+        }
+    }
+    __syncthreads();
+    unsigned long long *out = a.counts + c * (int64_t)a.num_bins;
+    for (int b = threadIdx.x; b < a.num_bins; b += kThreads) {
+        unsigned long long n = sh_hist[b];
+        if (b == 0) n += sh_edge[0];
+        if (b == a.num_bins - 1) n += sh_edge[1];
+        if (n) atomicAdd(out + b, n);
+    }
+    if (want_mm && threadIdx.x == 0) {
+        float mn = sh_mm[0][0], mx = sh_mm[1][0];
+        for (int w = 1; w < kThreads / 32; ++w) {
+            mn = fminf(mn, sh_mm[0][w]);
+            mx = fmaxf(mx, sh_mm[1][w]);
+        }
+        double *p = a.mm_partial + 2 * (c * (int64_t)a.tiles + tile);
+        p[0] = (double)mn;
+        p[1] = (double)mx;
+    }
+}
+
+template <int IO>
+int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const float *lo, const float *hi,
+                     const float *below, const float *above, int64_t *counts, void *fin_min, void *fin_max,
+                     void *scratch, int64_t scratch_bytes, cudaStream_t stream) {
+    if (!canon.oci)
+        return fail(AB_ERR_UNSUPPORTED, "statistics need a layout that reduces to (outer, channel, inner)");
+    if (canon.C > 65535) return fail(AB_ERR_UNSUPPORTED, "at most 65535 histograms per call, got %lld", (long long)canon.C);
+    const int vecw = 16 / dtype_size(IO);
+    const bool vect = aligned16(x) && (canon.I % vecw == 0);
+    const int v = vect ? vecw : 1;
+    const int64_t chan_elems = canon.O * canon.I;
+    const int64_t grain = (int64_t)kThreads * kHistUnroll * v;  // elements per CTA sweep
+    int64_t tiles = ((int64_t)sm_count() * 8 + canon.C - 1) / canon.C;
+    const int64_t max_tiles = (chan_elems + grain - 1) / grain;
+    if (tiles > max_tiles) tiles = max_tiles;
+    if (tiles < 1) tiles = 1;
+    int64_t tile_elems = (chan_elems + tiles - 1) / tiles;
+    tile_elems = ((tile_elems + 15) / 16) * 16;
+    tiles = (chan_elems + tile_elems - 1) / tile_elems;
+
+    const bool want_mm = fin_min && fin_max;
+    const int64_t need = want_mm ? canon.C * tiles * 2 * (int64_t)sizeof(double) : 0;
+    if (need > 0 && (!scratch || scratch_bytes < need))
+        return fail(AB_ERR_SCRATCH, "histogram needs %lld bytes of scratch, got %lld", (long long)need,
+                    (long long)scratch_bytes);
+
+    AB_CUDA_OK(cudaMemsetAsync(counts, 0, sizeof(int64_t) * canon.C * (int64_t)num_bins, stream));
+    HistArgs a;
+    a.x = x;
+    a.lo = lo;
+    a.hi = hi;
+    a.below = below;
+    a.above = above;
+    a.counts = reinterpret_cast<unsigned long long *>(counts);
+    a.mm_partial = want_mm ? static_cast<double *>(scratch) : nullptr;
+    a.O = canon.O;
+    a.C = canon.C;
+    a.I = canon.I;
+    a.chan_elems = chan_elems;
+    a.tile_elems = tile_elems;
+    a.num_bins = num_bins;
+    a.tiles = (int)tiles;
+    dim3 grid((unsigned)tiles, (unsigned)canon.C);
+    const size_t smem = sizeof(unsigned int) * (size_t)num_bins;
+    if (vect)
+        k_histogram<IO, true><<<grid, kThreads, smem, stream>>>(a);
+    else
+        k_histogram<IO, false><<<grid, kThreads, smem, stream>>>(a);
+    AB_LAUNCH_OK();
+    if (want_mm) {
+        MinMaxFinishArgs f{a.mm_partial, fin_min, fin_max, canon.C, 1, 0, tiles, tiles};
+        const int64_t g = (canon.C * 32 + kThreads - 1) / kThreads;
+        k_minmax_finish<IO><<<(unsigned)g, kThreads, 0, stream>>>(f);
+        AB_LAUNCH_OK();
+    }
+    return AB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// SQNR sweep: noise of every (delta, offset) candidate against a histogram
+// ---------------------------------------------------------------------------
+struct SweepArgs {
+    const float *hist, *edge0, *width, *deltas, *offsets;
+    int offsets_per_hist;
+    int num_bins, num_cand;
+    float num_steps, gamma;
+    int use_gamma;
+    float *noise;
+};
+
+constexpr int kSweepThreads = 128;
+
+__global__ void __launch_bounds__(kSweepThreads) k_sqnr_sweep(SweepArgs a) {
+    const int cand = blockIdx.x, h = blockIdx.y;
+    const float delta = a.deltas[(int64_t)h * a.num_cand + cand];
+    const float offset = a.offsets[(a.offsets_per_hist ? (int64_t)h * a.num_cand : 0) + cand];
+    const float width = a.width[h];
+    const float mid0 = __fadd_rn(a.edge0[h], __fdiv_rn(width, 2.0f));
+    const float *hist = a.hist + (int64_t)h * a.num_bins;
+    double acc = 0.0;
+    for (int b = threadIdx.x; b < a.num_bins; b += kSweepThreads) {
+        const float mid = __fadd_rn(mid0, __fmul_rn(width, (float)b));
+        float q = rintf(__fsub_rn(__fdiv_rn(mid, delta), offset));
+        const bool clipped = (q < 0.0f) || (q > a.num_steps);
+        q = clamp_nan(q, 0.0f, a.num_steps);
+        q = __fmul_rn(__fadd_rn(q, offset), delta);
+        float err = fabsf(__fsub_rn(q, mid));
+        err = __fmul_rn(__fmul_rn(err, err), hist[b]);
+        if (a.use_gamma && clipped) err = __fmul_rn(err, a.gamma);
+        acc += (double)err;
+    }
+    acc = warp_sum(acc);
+    __shared__ double sh[kSweepThreads / 32];
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0;
+        for (int w = 0; w < kSweepThreads / 32; ++w) t += sh[w];
+        a.noise[(int64_t)h * a.num_cand + cand] = (float)t;
+    }
+}
+
+__global__ void __launch_bounds__(kSweepThreads) k_argmin(const float *noise, int num_cand, int *best) {
+    const int h = blockIdx.x;
+    const float *n = noise + (int64_t)h * num_cand;
+    float bv = INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < num_cand; i += kSweepThreads) {
+        const float v = n[i];
+        if (v < bv || (v == bv && i < bi)) {
+            bv = v;
+            bi = i;
+        }
+    }
+    __shared__ float sv[kSweepThreads];
+    __shared__ int si[kSweepThreads];
+    sv[threadIdx.x] = bv;
+    si[threadIdx.x] = bi;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int t = 1; t < kSweepThreads; ++t) {
+            const float v = sv[t];
+            const int i = si[t];
+            if (i == 0x7fffffff) continue;
+            if (bi == 0x7fffffff || v < bv || (v == bv && i < bi)) {
+                bv = v;
+                bi = i;
+            }
+        }
+        best[h] = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
+}  // namespace
+}  // namespace ab
+
+extern "C" int64_t aimet_b200_stats_scratch_bytes(const ab_layout *layout, int io_dtype) {
+    ab::Canon canon;
+    int rc = ab::canonicalize(layout, &canon);
+    if (rc != AB_OK) return rc;
+    if (ab::dtype_size(io_dtype) == 0) return ab::fail(AB_ERR_INVALID, "unknown io_dtype %d", io_dtype);
+    if (canon.numel == 0 || !canon.oci) return 0;
+    const ab::ReducePlan pa = ab::plan_reduce(canon, io_dtype, true);
+    const ab::ReducePlan pb = ab::plan_reduce(canon, io_dtype, false);
+    int64_t n = pa.npartial > pb.npartial ? pa.npartial : pb.npartial;
+    // histogram min/max partials: at most 8 * SMs tiles in total, plus one per channel
+    const int64_t hist = (int64_t)ab::sm_count() * 8 + 2 * canon.C;
+    if (hist > n) n = hist;
+    return n * 2 * (int64_t)sizeof(double);
+}
+
+extern "C" int aimet_b200_minmax(const void *x, const ab_layout *layout, int io_dtype, int finite_only,
+                                 void *min_out, void *max_out, void *scratch, int64_t scratch_bytes,
+                                 void *stream) {
+    ab::Canon canon;
+    int rc = ab::canonicalize(layout, &canon);
+    if (rc != AB_OK) return rc;
+    if (canon.numel == 0) return ab::fail(AB_ERR_INVALID, "min/max of an empty tensor is undefined");
+    if (!x || !min_out || !max_out) return ab::fail(AB_ERR_INVALID, "x, min_out and max_out must not be NULL");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (io_dtype) {
+        case AB_F32: return ab::launch_minmax<AB_F32>(x, canon, finite_only, min_out, max_out, scratch, scratch_bytes, st);
+        case AB_F16: return ab::launch_minmax<AB_F16>(x, canon, finite_only, min_out, max_out, scratch, scratch_bytes, st);
+        case AB_BF16: return ab::launch_minmax<AB_BF16>(x, canon, finite_only, min_out, max_out, scratch, scratch_bytes, st);
+        case AB_F64: return ab::launch_minmax<AB_F64>(x, canon, finite_only, min_out, max_out, scratch, scratch_bytes, st);
+    }
+    return ab::fail(AB_ERR_INVALID, "unknown io_dtype %d", io_dtype);
+}
+
+extern "C" int aimet_b200_histogram(const void *x, const ab_layout *layout, int io_dtype, int32_t num_bins,
+                                    const float *lo, const float *hi, const float *below,
+                                    const float *above, int64_t *counts, void *fin_min, void *fin_max,
+                                    void *scratch, int64_t scratch_bytes, void *stream) {
+    ab::Canon canon;
+    int rc = ab::canonicalize(layout, &canon);
+    if (rc != AB_OK) return rc;
+    if (num_bins <= 0 || num_bins > 8192)
+        return ab::fail(AB_ERR_UNSUPPORTED, "num_bins must be in [1, 8192], got %d", num_bins);
+    if (canon.numel == 0) return ab::fail(AB_ERR_INVALID, "histogram of an empty tensor is undefined");
+    if (!x || !lo || !hi || !below || !above || !counts)
+        return ab::fail(AB_ERR_INVALID, "x, lo, hi, below, above and counts must not be NULL");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (io_dtype) {
+        case AB_F32:
+            return ab::launch_histogram<AB_F32>(x, canon, num_bins, lo, hi, below, above, counts, fin_min, fin_max, scratch, scratch_bytes, st);
+        case AB_F16:
+            return ab::launch_histogram<AB_F16>(x, canon, num_bins, lo, hi, below, above, counts, fin_min, fin_max, scratch, scratch_bytes, st);
+        case AB_BF16:
+            return ab::launch_histogram<AB_BF16>(x, canon, num_bins, lo, hi, below, above, counts, fin_min, fin_max, scratch, scratch_bytes, st);
+    }
+    return ab::fail(AB_ERR_UNSUPPORTED, "histogram supports float32, float16 and bfloat16 inputs");
+}
+
+extern "C" int aimet_b200_sqnr_sweep(const float *hist, const float *edge0, const float *width,
+                                     const float *deltas, const float *offsets, int32_t offsets_per_hist,
+                                     int32_t num_hist, int32_t num_bins, int32_t num_cand, double num_steps,
+                                     double gamma, float *noise_out, int32_t *best_out, void *stream) {
+    if (num_hist <= 0 || num_bins <= 0 || num_cand <= 0)
+        return ab::fail(AB_ERR_INVALID, "num_hist, num_bins and num_cand must be positive");
+    if (num_hist > 65535) return ab::fail(AB_ERR_UNSUPPORTED, "at most 65535 histograms per call");
+    if (!hist || !edge0 || !width || !deltas || !offsets || !noise_out || !best_out)
+        return ab::fail(AB_ERR_INVALID, "NULL pointer argument");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    ab::SweepArgs a;
+    a.hist = hist;
+    a.edge0 = edge0;
+    a.width = width;
+    a.deltas = deltas;
+    a.offsets = offsets;
+    a.offsets_per_hist = offsets_per_hist;
+    a.num_bins = num_bins;
+    a.num_cand = num_cand;
+    a.num_steps = (float)num_steps;
+    a.gamma = (float)gamma;
+    a.use_gamma = gamma != 1.0;
+    a.noise = noise_out;
+    dim3 grid((unsigned)num_cand, (unsigned)num_hist);
+    ab::k_sqnr_sweep<<<grid, ab::kSweepThreads, 0, st>>>(a);
+    AB_LAUNCH_OK();
+    ab::k_argmin<<<(unsigned)num_hist, ab::kSweepThreads, 0, st>>>(noise_out, num_cand, best_out);
+    AB_LAUNCH_OK();
+    return AB_OK;
+}

@@ -1,0 +1,183 @@
+/*
+ * aimet_b200 -- C ABI of the sm_100a quantization-simulation kernels.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the CUDA
+ * stream it is given (a cudaStream_t passed as void*), never synchronises and
+ * never allocates: outputs and scratch buffers are owned by the caller.  Every
+ * function returns AB_OK (0) or a negative AB_ERR_* code; the message for the
+ * last error of the calling thread is returned by aimet_b200_last_error().
+ *
+ * The citations name the aimet_torch interface each entry point stands behind
+ * (paths relative to TrainingExtensions/torch/src/python/aimet_torch/).
+ */
+#ifndef AIMET_B200_H
+#define AIMET_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AB_OK 0
+#define AB_ERR_INVALID (-1)     /* bad argument (shape, dtype, null pointer) */
+#define AB_ERR_UNSUPPORTED (-2) /* valid request this build has no kernel for */
+#define AB_ERR_CUDA (-3)        /* a CUDA runtime call failed */
+#define AB_ERR_SCRATCH (-4)     /* caller-provided scratch buffer is too small */
+#define AB_ERR_DEVICE (-5)      /* a kernel reported a device-side time-out */
+
+/* element types of tensors crossing the boundary */
+#define AB_F32 0
+#define AB_F16 1
+#define AB_BF16 2
+#define AB_F64 3
+
+#define AB_MAX_DIMS 8
+
+/*
+ * How a row-major contiguous tensor maps onto its encoding parameters.
+ * Along dim k every run of block[k] consecutive coordinates shares one
+ * (scale, offset) pair: block[k] == size[k] broadcasts the parameter over the
+ * dim, block[k] == 1 is per-channel, anything between is blockwise.  The
+ * parameter arrays are row-major contiguous of shape size[k] / block[k].
+ * (quantization/affine/backends/torch_builtins.py:119-162, 283-289 define the
+ * same mapping through reshape + interleave.)
+ */
+typedef struct ab_layout {
+    int32_t ndim;
+    int32_t reserved;
+    int64_t size[AB_MAX_DIMS];
+    int64_t block[AB_MAX_DIMS];
+} ab_layout;
+
+int aimet_b200_version(void);
+const char *aimet_b200_last_error(void);
+
+/* ------------------------------------------------------------------------- *
+ * Affine functionals.
+ *   io_dtype       element type of x / y / grad tensors
+ *   compute_dtype  the reference's "internal dtype": AB_F16 / AB_BF16 round
+ *                  after every arithmetic step exactly like the aten chain the
+ *                  reference runs in that dtype (torch_builtins.py:99-116, 268-300)
+ *   param_dtype    element type of scale / offset / grad_scale / grad_offset
+ *                  (AB_F32 or AB_F64)
+ * ------------------------------------------------------------------------- */
+
+/* out = clamp(round(x / scale) - offset, qmin, qmax)
+ * replaces backends.quantize (quantization/affine/backends/utils.py:17-25,
+ * torch_builtins.py:166-212, QuantizeFunc.forward :588-633) */
+int aimet_b200_quantize(const void *x, void *y, const void *scale, const void *offset,
+                        const ab_layout *layout, int io_dtype, int compute_dtype, int param_dtype,
+                        int64_t qmin, int64_t qmax, void *stream);
+
+/* out = (x + offset) * scale
+ * replaces backends.dequantize (backends/utils.py:27-33, torch_builtins.py:537-571,
+ * DequantizeFunc.forward :666-685) */
+int aimet_b200_dequantize(const void *x, void *y, const void *scale, const void *offset,
+                          const ab_layout *layout, int io_dtype, int compute_dtype, int param_dtype,
+                          void *stream);
+
+/* out = (clamp(round(x / scale - zps) - offset, qmin, qmax) + offset + zps) * scale
+ * replaces backends.quantize_dequantize (backends/utils.py:35-44,
+ * torch_builtins.py:216-302, QuantDequantFunc.forward :705-770) */
+int aimet_b200_quantize_dequantize(const void *x, void *y, const void *scale, const void *offset,
+                                   const ab_layout *layout, int io_dtype, int compute_dtype,
+                                   int param_dtype, int64_t qmin, int64_t qmax,
+                                   double zero_point_shift, void *stream);
+
+/* Bytes of scratch the three backward entry points need for this layout. */
+int64_t aimet_b200_backward_scratch_bytes(const ab_layout *layout, int io_dtype);
+
+/* Backward passes.  grad_x / grad_scale / grad_offset may each be NULL when the
+ * gradient is not wanted.  grad_scale / grad_offset have the parameters' shape
+ * (the reference returns full-size tensors that autograd sums down to that
+ * shape; the reduction is done here, deterministically).
+ * QuantDequantFunc.backward (torch_builtins.py:772-831) */
+int aimet_b200_quantize_dequantize_backward(const void *x, const void *grad_y, const void *scale,
+                                            const void *offset, const ab_layout *layout,
+                                            int io_dtype, int compute_dtype, int param_dtype,
+                                            int64_t qmin, int64_t qmax, double zero_point_shift,
+                                            void *grad_x, void *grad_scale, void *grad_offset,
+                                            void *scratch, int64_t scratch_bytes, void *stream);
+/* QuantizeFunc.backward (torch_builtins.py:637-659) */
+int aimet_b200_quantize_backward(const void *x, const void *grad_y, const void *scale,
+                                 const void *offset, const ab_layout *layout, int io_dtype,
+                                 int compute_dtype, int param_dtype, int64_t qmin, int64_t qmax,
+                                 void *grad_x, void *grad_scale, void *grad_offset, void *scratch,
+                                 int64_t scratch_bytes, void *stream);
+/* DequantizeFunc.backward (torch_builtins.py:689-701) */
+int aimet_b200_dequantize_backward(const void *x, const void *grad_y, const void *scale,
+                                   const void *offset, const ab_layout *layout, int io_dtype,
+                                   int compute_dtype, int param_dtype, void *grad_x,
+                                   void *grad_scale, void *grad_offset, void *scratch,
+                                   int64_t scratch_bytes, void *stream);
+
+/* ------------------------------------------------------------------------- *
+ * Calibration statistics.  The layout must reduce to (outer, channel, inner):
+ * one statistic per parameter element, taken over everything that shares it.
+ * ------------------------------------------------------------------------- */
+
+int64_t aimet_b200_stats_scratch_bytes(const ab_layout *layout, int io_dtype);
+
+/* min_out[c], max_out[c] in io_dtype.
+ * finite_only == 0: torch.amin / torch.amax semantics, NaN propagates
+ *   (_MinMaxObserver.collect_stats, quantization/encoding_analyzer.py:80-93)
+ * finite_only == 1: +-inf and NaN are skipped; a slice with no finite value
+ *   yields (+inf, -inf) (_HistogramObserver._get_min_max, :213-219) */
+int aimet_b200_minmax(const void *x, const ab_layout *layout, int io_dtype, int finite_only,
+                      void *min_out, void *max_out, void *scratch, int64_t scratch_bytes,
+                      void *stream);
+
+/* counts[c][b] (int64, overwritten): torch.histc binning of float(x) over
+ * [lo[c], hi[c]], i.e. bin = (int)((x - lo) * num_bins / (hi - lo)) with x == hi
+ * in the last bin and values outside [lo, hi] or NaN ignored; then the number of
+ * x < below[c] is added to bin 0 and the number of x > above[c] to the last
+ * bin, the comparison being made in io_dtype as the reference's tensor
+ * comparison does.  lo / hi / below / above are float32[C].
+ * (_HistogramObserver.collect_stats / merge_stats, encoding_analyzer.py:194-209, 313-323)
+ * If fin_min / fin_max are non-NULL the finite-only min / max of each slice is
+ * produced by the same pass (io_dtype, needs scratch as for aimet_b200_minmax). */
+int aimet_b200_histogram(const void *x, const ab_layout *layout, int io_dtype, int32_t num_bins,
+                         const float *lo, const float *hi, const float *below, const float *above,
+                         int64_t *counts, void *fin_min, void *fin_max, void *scratch,
+                         int64_t scratch_bytes, void *stream);
+
+/* Expected clipping + rounding noise of every (delta, offset) candidate against
+ * a histogram, and the arg-min per histogram.
+ *   hist        float32 [H][num_bins]
+ *   edge0/width float32 [H]: first bin edge and bin width (bin_edges[1]-bin_edges[0])
+ *   deltas      float32 [H][num_cand]
+ *   offsets     float32 [H][num_cand] or, if offsets_per_hist == 0, [num_cand]
+ *   noise_out   float32 [H][num_cand]
+ *   best_out    int32   [H]  (lowest index among equal minima)
+ * _LpNormEncodingAnalyzer._estimate_clip_and_quant_noise / _select_best_candidates
+ * (encoding_analyzer.py:822-899) with p = 2 */
+int aimet_b200_sqnr_sweep(const float *hist, const float *edge0, const float *width,
+                          const float *deltas, const float *offsets, int32_t offsets_per_hist,
+                          int32_t num_hist, int32_t num_bins, int32_t num_cand, double num_steps,
+                          double gamma, float *noise_out, int32_t *best_out, void *stream);
+
+/* ------------------------------------------------------------------------- *
+ * SeqMSE reconstruction loss of a Linear layer for all candidates at once:
+ *   out[c][n][0] = sum_m f(x[m,:] . w[n,:],  xq[m,:] . wq[c][n,:])
+ * with f = squared difference (loss_kind 0), absolute difference (1), or, for
+ * loss_kind 2, out[c][n][0] = sum of squared differences and out[c][n][1] = sum
+ * of squares of the second product (what neg_sqnr needs).
+ *   x, xq  [M][K] row-major, io_dtype AB_BF16 or AB_F16;  w [N][K];  wq [C][N][K]
+ *   out    float32 [C][N][2]
+ *   lowp_epilogue != 0 rounds both products, their difference and f() to io_dtype
+ *   the way the reference's half-precision aten chain does.
+ * SequentialMse._compute_linear_loss (seq_mse.py:403-482) for num_blocks == 1.
+ * The contraction runs on the 5th-generation tensor cores (tcgen05, TMEM
+ * accumulators, TMA-fed operands).  status is a device int32 the kernel sets to
+ * non-zero if one of its bounded waits gives up. */
+int64_t aimet_b200_seqmse_scratch_bytes(int64_t M, int64_t N, int64_t K, int32_t num_cand);
+int aimet_b200_seqmse_linear_loss(const void *x, const void *xq, const void *w, const void *wq,
+                                  int64_t M, int64_t N, int64_t K, int32_t num_cand, int io_dtype,
+                                  int loss_kind, int lowp_epilogue, float *out, int32_t *status,
+                                  void *scratch, int64_t scratch_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AIMET_B200_H */

@@ -1,0 +1,183 @@
+"""CUDA affine functionals (through the C ABI) against the golden fixtures and the CPU oracle."""
+
+import pytest
+import torch
+
+from conftest import assert_same, load_golden
+from oracle import affine as O
+
+pytestmark = pytest.mark.gpu
+
+CASES = load_golden("affine_cases.pt")
+VECTORS = load_golden("backend_vectors.pt")
+
+
+def _backend():
+    from aimet_b200 import backend
+
+    return backend
+
+
+def _ulp_close(a, b, dtype, ulps=1):
+    """|a - b| <= ulps * ulp(dtype) relative to the larger magnitude."""
+    a, b = a.double().cpu(), b.double().cpu()
+    eps = torch.finfo(dtype).eps
+    tol = ulps * eps * torch.maximum(a.abs(), b.abs()) + 1e-30
+    return bool(((a - b).abs() <= tol).all())
+
+
+def _check_param_grad(got, want, internal_dtype, what):
+    """Scale / offset gradients are sums: the reduction order differs from torch's, so they are
+    compared within 1e-5 relative (float32 / float64 internal dtype) or one unit in the last
+    place of the 16-bit internal dtype the reference sums in."""
+    assert got.shape == want.shape and got.dtype == want.dtype, what
+    if internal_dtype in (torch.float16, torch.bfloat16):
+        assert _ulp_close(got, want, internal_dtype, ulps=1), what
+    else:
+        scale = want.double().abs().max().clamp_min(1e-30)
+        err = (got.double().cpu() - want.double()).abs().max()
+        assert err <= 1e-5 * scale, f"{what}: max abs err {err} vs scale {scale}"
+
+
+def _run(fn, x, grad, scale, offset, *args):
+    xi = x.clone().cuda().requires_grad_(True)
+    s = scale.clone().cuda().requires_grad_(True)
+    o = offset.clone().cuda().requires_grad_(True)
+    y = fn(xi, s, o, *args)
+    y.backward(grad.cuda())
+    torch.cuda.synchronize()
+    return y.detach(), xi.grad, s.grad, o.grad
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_quantize_dequantize_golden(name):
+    c = CASES[name]
+    B = _backend()
+    idt = O.internal_dtype(c["dtype"], c["qmin"], c["qmax"])
+    y, gx, gs, go = _run(B.quantize_dequantize, c["x"], c["grad"], c["scale"], c["offset"], c["qmin"], c["qmax"],
+                         c["block_size"], c["zero_point_shift"])
+    assert_same(y, c["qdq"], "qdq")          # bit-exact (north-star allows 1 ulp)
+    assert_same(gx, c["qdq_gx"], "grad_x")   # bit-exact
+    _check_param_grad(gs, c["qdq_gs"], idt, "grad_scale")
+    _check_param_grad(go, c["qdq_go"], idt, "grad_offset")
+
+
+@pytest.mark.parametrize("name", sorted(n for n, c in CASES.items() if "q" in c))
+def test_quantize_and_dequantize_golden(name):
+    c = CASES[name]
+    B = _backend()
+    idt = O.internal_dtype(c["dtype"], c["qmin"], c["qmax"])
+    q, gx, gs, go = _run(B.quantize, c["x"], c["grad"], c["scale"], c["offset"], c["qmin"], c["qmax"], c["block_size"])
+    assert_same(q, c["q"], "codes")  # integer codes: bit-exact
+    assert_same(gx, c["q_gx"], "q grad_x")
+    _check_param_grad(gs, c["q_gs"], idt, "q grad_scale")
+    _check_param_grad(go, c["q_go"], idt, "q grad_offset")
+    dq, gx, gs, go = _run(B.dequantize, c["q"], c["grad"], c["scale"], c["offset"], c["block_size"])
+    assert_same(dq, c["dq"], "dq")
+    assert_same(gx, c["dq_gx"], "dq grad_x")
+    _check_param_grad(gs, c["dq_gs"], c["dtype"], "dq grad_scale")
+    _check_param_grad(go, c["dq_go"], c["dtype"], "dq grad_offset")
+
+
+@pytest.mark.parametrize("name", sorted(VECTORS))
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_known_answer_vectors(name, dtype):
+    v = VECTORS[name]
+    if dtype != torch.float32 and not name.startswith("bfloat16_compat"):
+        pytest.skip("inputs of this set are not exact in 16-bit floats")
+    B = _backend()
+    x = v["tensor"].to(dtype).cuda().requires_grad_(True)
+    scale, offset = v["delta"].to(dtype).cuda(), v["offset"].to(dtype).cuda()
+    q = B.quantize(x.detach(), scale, offset, v["qmin"], v["qmax"])
+    assert torch.equal(q.cpu(), v["tensor_q"].to(dtype))
+    assert torch.equal(B.dequantize(q, scale, offset).cpu(), v["tensor_qdq"].to(dtype))
+    y = B.quantize_dequantize(x, scale, offset, v["qmin"], v["qmax"])
+    assert torch.equal(y.detach().cpu(), v["tensor_qdq"].to(dtype))
+    y.backward(torch.ones_like(y))
+    assert torch.equal(x.grad.cpu(), (~v["mask"]).to(dtype))
+
+
+# ---- larger shapes against the oracle: every kernel variant (vector / scalar, segment / column /
+# ---- chunked / general) gets exercised -------------------------------------------------------
+ORACLE_CASES = [
+    # dtype, shape, pshape, block, qmin, qmax, zps
+    (torch.float32, (512, 1024), (), None, 0, 255, 0.0),            # chunked per-tensor
+    (torch.float32, (1, 100003), (), None, 0, 255, 0.0),            # scalar path, chunked
+    (torch.bfloat16, (300, 4096), (300, 1), None, -128, 127, 0.0),  # one CTA per row
+    (torch.bfloat16, (64, 20480), (64, 1), None, -128, 127, 0.0),   # chunked rows
+    (torch.bfloat16, (128, 4096), (128, 64), (1, 64), -8, 7, 0.0),  # blockwise int4, bf16 internal
+    (torch.float16, (128, 1024), (128, 16), (1, 64), -8, 7, 0.0),
+    (torch.float32, (64, 96, 14, 14), (96, 1, 1), None, 0, 255, 0.0),  # NCHW per-channel: seg + partials
+    (torch.float32, (8, 32, 3, 3), (32, 1, 1), None, 0, 255, 0.0),     # small inner: column mode
+    (torch.bfloat16, (4096, 520), (520,), None, 0, 255, 0.0),          # channel-last: column mode
+    (torch.float32, (1000, 77), (77,), None, -8, 7, 0.5),              # scalar column mode + zps
+    (torch.float32, (48, 64), (6, 8), (8, 8), 0, 15, 0.0),             # 2-d blocks: general path
+    (torch.bfloat16, (6, 40, 50), (3, 1, 5), (2, -1, 10), -8, 7, 0.0),
+]
+
+
+@pytest.mark.parametrize("case", ORACLE_CASES, ids=lambda c: f"{str(c[0])[6:]}-{'x'.join(map(str, c[1]))}-p{'x'.join(map(str, c[2]))}")
+def test_quantize_dequantize_vs_oracle(case):
+    dtype, shape, pshape, block, qmin, qmax, zps = case
+    B = _backend()
+    g = torch.Generator().manual_seed(hash(shape) % 10000)
+    x = (torch.randn(shape, generator=g) * (1 + 5 * (torch.rand(shape, generator=g) < 0.01))).to(dtype)
+    grad = torch.randn(shape, generator=g).to(dtype)
+    scale = (4.0 / (qmax - qmin)) * (0.5 + torch.rand(pshape, generator=g))
+    offset = torch.round(-(qmax - qmin) * (0.3 + 0.4 * torch.rand(pshape, generator=g))) - qmin
+    idt = O.internal_dtype(dtype, qmin, qmax)
+    y, gx, gs, go = _run(B.quantize_dequantize, x, grad, scale, offset, qmin, qmax, block, zps)
+    assert_same(y, O.quantize_dequantize(x, scale, offset, qmin, qmax, block, zps), "qdq")
+    ogx, ogs, ogo = O.quantize_dequantize_backward(x, grad, scale, offset, qmin, qmax, block, zps)
+    assert_same(gx, ogx, "grad_x")
+    _check_param_grad(gs, ogs, idt, "grad_scale")
+    _check_param_grad(go, ogo, idt, "grad_offset")
+    # deterministic: a second run is bit-identical
+    y2, gx2, gs2, go2 = _run(B.quantize_dequantize, x, grad, scale, offset, qmin, qmax, block, zps)
+    assert torch.equal(gs, gs2) and torch.equal(go, go2) and torch.equal(gx, gx2)
+
+
+def test_memory_format_and_strides():
+    B = _backend()
+    x = torch.randn(4, 8, 6, 6).cuda().to(memory_format=torch.channels_last)
+    scale = (torch.rand(8, 1, 1) * 0.05 + 0.01).cuda()
+    offset = torch.zeros(8, 1, 1).cuda()
+    y = B.quantize_dequantize(x, scale, offset, -128, 127)
+    assert y.is_contiguous(memory_format=torch.channels_last)
+    assert_same(y, O.quantize_dequantize(x.cpu(), scale.cpu(), offset.cpu(), -128, 127), "channels_last")
+    xt = torch.randn(33, 20).cuda().t()  # transposed view
+    y = B.quantize_dequantize(xt, torch.tensor(0.02).cuda(), torch.tensor(0.0).cuda(), -128, 127)
+    assert_same(y, O.quantize_dequantize(xt.cpu(), torch.tensor(0.02), torch.tensor(0.0), -128, 127), "transposed")
+    xs = torch.randn(16, 40).cuda()[:, ::2]  # not dense
+    y = B.quantize_dequantize(xs, torch.tensor(0.02).cuda(), torch.tensor(0.0).cuda(), -128, 127)
+    assert_same(y, O.quantize_dequantize(xs.cpu(), torch.tensor(0.02), torch.tensor(0.0), -128, 127), "strided")
+
+
+def test_special_values_and_empty():
+    B = _backend()
+    x = torch.tensor([float("nan"), float("inf"), -float("inf"), 0.0, -0.0, 1e30, -1e-30, 0.25]).cuda()
+    s, o = torch.tensor(0.5).cuda(), torch.tensor(-3.0).cuda()
+    assert_same(B.quantize_dequantize(x, s, o, 0, 15), O.quantize_dequantize(x.cpu(), s.cpu(), o.cpu(), 0, 15), "special")
+    assert_same(B.quantize(x, s, o, 0, 15), O.quantize(x.cpu(), s.cpu(), o.cpu(), 0, 15), "special codes")
+    e = torch.empty(0, 4).cuda()
+    assert B.quantize_dequantize(e, s, o, 0, 15).shape == (0, 4)
+
+
+def test_error_contracts():
+    B = _backend()
+    x = torch.randn(4, 6).cuda()
+    s, o = torch.ones(()).cuda(), torch.zeros(()).cuda()
+    with pytest.raises(RuntimeError):
+        B.quantize_dequantize(x.cpu(), s.cpu(), o.cpu(), 0, 15)      # no CPU path
+    with pytest.raises(RuntimeError):
+        B.quantize_dequantize(x, torch.ones(5).cuda(), torch.zeros(5).cuda(), 0, 15)  # not broadcastable
+    with pytest.raises(RuntimeError):
+        B.quantize_dequantize(x, torch.ones(2, 4, 6).cuda(), torch.zeros(2, 4, 6).cuda(), 0, 15)  # inverse broadcast
+    with pytest.raises(RuntimeError):
+        B.quantize_dequantize(x, s, o, 16, 15)                        # qmin > qmax
+    with pytest.raises(RuntimeError):
+        B.quantize_dequantize(x, s.cpu(), o, 0, 15)                   # devices differ
+    with pytest.raises(RuntimeError):
+        B.quantize_dequantize(x, torch.ones(2, 2).cuda(), torch.zeros(2, 2).cuda(), 0, 15, block_size=(2, 2))
+    with pytest.raises(RuntimeError):
+        B.quantize(x.to(torch.bfloat16), s, o, 0, 2**16 - 1)           # grid not representable in bf16
