@@ -16,15 +16,38 @@ enum { OP_Q = 0, OP_DQ = 1, OP_QDQ = 2 };
 constexpr int kFwdUnroll = 4;       // 16-byte vectors in flight per thread, forward
 
 // ---------------------------------------------------------------------------
-// per-parameter values, rounded to the internal dtype once
+// The quantization grid in the register type, plus facts about it that hold for
+// the whole launch.
+// ---------------------------------------------------------------------------
+template <typename T> struct Grid {
+    T qmin, qmax, zps;
+    int has_zps;
+    // 16-bit internal dtypes only: qmin-1 and qmax+1 are exact in that dtype, so
+    // re-rounding an integer difference cannot move it across a grid boundary
+    int exact_edges;
+};
+
+// ---------------------------------------------------------------------------
+// Per-parameter values, rounded to the internal dtype once per 16-byte vector
+// (or per element where neighbouring elements use different parameters).
 // ---------------------------------------------------------------------------
 template <int CT> struct Enc {
     using T = typename Arith<CT>::T;
     T s, o;
+    T r;     // correctly rounded 1 / s (float arithmetic only)
+    T back;  // what is added back after clamping: o, or o + zero_point_shift
+    T lo, hi;  // o + qmin, o + qmax in the internal dtype (backward clamp bounds)
+    // float arithmetic: s is a normal number of moderate magnitude and the clamp
+    // bounds are small integers, so x / s can be formed from r with an exact
+    // remainder correction and rounding can use the 2^23 trick
+    bool fast;
+    // 16-bit internal dtype: integer sums around this offset are exact
+    bool exact_int;
 };
 
 template <int CT>
-__device__ __forceinline__ Enc<CT> load_enc(const ParamPtr &scale, const ParamPtr &offset, int64_t p) {
+__device__ __forceinline__ Enc<CT> load_enc(const ParamPtr &scale, const ParamPtr &offset, int64_t p,
+                                            const Grid<typename Arith<CT>::T> &g) {
     using A = Arith<CT>;
     using T = typename A::T;
     Enc<CT> e;
@@ -35,13 +58,69 @@ __device__ __forceinline__ Enc<CT> load_enc(const ParamPtr &scale, const ParamPt
         e.s = A::rnd((T)__ldg(static_cast<const float *>(scale.p) + p));
         e.o = A::rnd((T)__ldg(static_cast<const float *>(offset.p) + p));
     }
+    e.back = g.has_zps ? A::rnd(op_add(e.o, g.zps)) : e.o;
+    e.lo = A::rnd(op_add(e.o, g.qmin));
+    e.hi = A::rnd(op_add(e.o, g.qmax));
+    e.r = (T)0;
+    e.fast = false;
+    e.exact_int = false;
+    if (CT != AB_F64) {
+        const float as = fabsf((float)e.s);
+        const float bound = fmaxf(fabsf((float)e.lo), fabsf((float)e.hi));
+        e.fast = (as > 7.888609e-31f) && (as < 1.2676506e30f) && (bound < 4194304.0f);  // 2^-100, 2^100, 2^22
+        e.r = (T)__frcp_rn((float)e.s);
+        // all integers up to 2^(mantissa+1) are exact: 256 for bfloat16, 2048 for float16
+        const float lim = CT == AB_BF16 ? 256.0f : 2048.0f;
+        e.exact_int = g.exact_edges && bound <= lim && fabsf((float)e.o) <= lim && (float)e.o == rintf((float)e.o);
+    }
     return e;
 }
 
-template <typename T> struct Grid {  // quantization grid, in the register type
-    T qmin, qmax, zps;
-    int has_zps;
-};
+// x / s, correctly rounded.  With r = RN(1/s): q0 = RN(x*r) is within one ulp,
+// the remainder x - q0*s is exact in an fma, and RN(q0 + rem*r) is the correctly
+// rounded quotient (Markstein).  Infinities, NaN and absurd magnitudes take the
+// IEEE division instruction.
+template <int CT>
+__device__ __forceinline__ typename Arith<CT>::T div_scale(typename Arith<CT>::T x, const Enc<CT> &e) {
+    return op_div(x, e.s);
+}
+__device__ __forceinline__ float div_scale_f32(float x, float sc, float r, bool fast) {
+    if (!fast) return __fdiv_rn(x, sc);
+    const float q0 = __fmul_rn(x, r);
+    float rem = __fmaf_rn(-q0, sc, x);
+    // +-inf, NaN and quotients beyond 2^100 keep q0 (the remainder would be NaN);
+    // such quotients are far outside any grid, so their last bit is immaterial
+    rem = fabsf(q0) < 1.2676506e30f ? rem : 0.0f;
+    return __fmaf_rn(rem, r, q0);
+}
+template <> __device__ __forceinline__ float div_scale<AB_F32>(float x, const Enc<AB_F32> &e) { return div_scale_f32(x, e.s, e.r, e.fast); }
+template <> __device__ __forceinline__ float div_scale<AB_BF16>(float x, const Enc<AB_BF16> &e) { return div_scale_f32(x, e.s, e.r, e.fast); }
+template <> __device__ __forceinline__ float div_scale<AB_F16>(float x, const Enc<AB_F16> &e) { return div_scale_f32(x, e.s, e.r, e.fast); }
+
+// Round half to even.  In float, (|v| + 2^23) - 2^23 is exact rounding for
+// |v| < 2^23; larger magnitudes stay far outside any grid whose clamp bounds are
+// below 2^22 (Enc::fast), which is all the callers need of them.
+template <int CT>
+__device__ __forceinline__ typename Arith<CT>::T round_even(typename Arith<CT>::T v, const Enc<CT> &e) {
+    return op_rint(v);
+}
+__device__ __forceinline__ float round_even_f32(float v, bool fast) {
+    if (!fast) return rintf(v);
+    const float r = __fsub_rn(__fadd_rn(fabsf(v), 8388608.0f), 8388608.0f);
+    return copysignf(r, v);
+}
+template <> __device__ __forceinline__ float round_even<AB_F32>(float v, const Enc<AB_F32> &e) { return round_even_f32(v, e.fast); }
+template <> __device__ __forceinline__ float round_even<AB_BF16>(float v, const Enc<AB_BF16> &e) { return round_even_f32(v, e.fast); }
+template <> __device__ __forceinline__ float round_even<AB_F16>(float v, const Enc<AB_F16> &e) { return round_even_f32(v, e.fast); }
+
+// torch.clamp semantics (NaN propagates) in two instructions
+__device__ __forceinline__ float clamp_prop(float v, float lo, float hi) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(v), "f"(lo));
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(r), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ double clamp_prop(double v, double lo, double hi) { return clamp_nan(v, lo, hi); }
 
 // ---------------------------------------------------------------------------
 // forward element functions
@@ -55,22 +134,23 @@ __device__ __forceinline__ typename Arith<CT>::T fwd_elem(typename Arith<CT>::T 
         T t = A::rnd(op_add(x, e.o));
         return A::rnd(op_mul(t, e.s));
     }
-    T t = A::rnd(op_div(x, e.s));
+    T t = A::rnd(div_scale<CT>(x, e));
     if (OP == OP_QDQ && g.has_zps) t = A::rnd(op_sub(t, g.zps));
-    t = op_rint(t);
-    t = A::rnd(op_sub(t, e.o));
-    t = clamp_nan(t, g.qmin, g.qmax);
+    t = round_even<CT>(t, e);
+    t = op_sub(t, e.o);
+    if (!e.exact_int) t = A::rnd(t);
+    t = clamp_prop(t, g.qmin, g.qmax);
     if (OP == OP_Q) return t;
-    T back = g.has_zps ? A::rnd(op_add(e.o, g.zps)) : e.o;
-    t = A::rnd(op_add(t, back));
+    t = op_add(t, e.back);
+    if (!e.exact_int || g.has_zps) t = A::rnd(t);
     return A::rnd(op_mul(t, e.s));
 }
 
 // ---------------------------------------------------------------------------
-// backward element functions: returns input gradient, adds this element's
-// contribution to the scale / offset gradient accumulators
+// backward element functions: returns the input gradient and this element's
+// contribution to the scale / offset gradients
 // ---------------------------------------------------------------------------
-template <int CT, int OP>
+template <int CT, int OP, bool WANT_O>
 __device__ __forceinline__ typename Arith<CT>::T bwd_elem(typename Arith<CT>::T x,
                                                           typename Arith<CT>::T gy, const Enc<CT> &e,
                                                           const Grid<typename Arith<CT>::T> &g,
@@ -78,36 +158,120 @@ __device__ __forceinline__ typename Arith<CT>::T bwd_elem(typename Arith<CT>::T 
                                                           typename Arith<CT>::T &dofs) {
     using A = Arith<CT>;
     using T = typename A::T;
+    dofs = (T)0;
     if (OP == OP_DQ) {
         T dx = A::rnd(op_mul(gy, e.s));
         ds = A::rnd(op_mul(gy, A::rnd(op_add(x, e.o))));
-        dofs = dx;
+        if (WANT_O) dofs = dx;
         return dx;
     }
     if (OP == OP_Q) {
-        T xs = A::rnd(op_div(x, e.s));
-        T t = A::rnd(op_sub(op_rint(xs), e.o));
+        T xs = A::rnd(div_scale<CT>(x, e));
+        T t = A::rnd(op_sub(round_even<CT>(xs, e), e.o));
         bool in = (t >= g.qmin) && (t <= g.qmax);
         T mg = op_mul(gy, in ? (T)1 : (T)0);
         T dx = A::rnd(op_div(mg, e.s));
         ds = A::rnd(op_mul(-dx, xs));
-        dofs = -mg;
+        if (WANT_O) dofs = -mg;
         return dx;
     }
     // OP_QDQ
-    T xs = A::rnd(op_div(x, e.s));
+    T xs = A::rnd(div_scale<CT>(x, e));
     if (g.has_zps) xs = A::rnd(op_sub(xs, g.zps));
-    T xr = op_rint(xs);
-    T t = A::rnd(op_sub(xr, e.o));
+    T xr = round_even<CT>(xs, e);
+    T t = op_sub(xr, e.o);
+    if (!e.exact_int) t = A::rnd(t);
     bool in = (g.qmin <= t) && (t <= g.qmax);
-    T err = A::rnd(op_sub(xr, xs));
-    T lo = A::rnd(op_add(e.o, g.qmin));
-    T hi = A::rnd(op_add(e.o, g.qmax));
-    T xc = clamp_nan(xr, lo, hi);
+    // xr - xs needs no re-rounding: its bits are a subset of the fraction bits of xs
+    T err = op_sub(xr, xs);
+    T xc = clamp_prop(xr, e.lo, e.hi);
     if (g.has_zps) xc = A::rnd(op_add(xc, g.zps));
     ds = A::rnd(op_mul(gy, in ? err : xc));
-    dofs = in ? (T)0 : A::rnd(op_mul(gy, e.s));
+    if (WANT_O) dofs = in ? (T)0 : A::rnd(op_mul(gy, e.s));
     return in ? gy : (T)0;
+}
+
+// ---------------------------------------------------------------------------
+// Two elements at a time (same parameter): identical arithmetic to fwd_elem /
+// bwd_elem with the re-roundings to a 16-bit internal dtype done pairwise.
+// ---------------------------------------------------------------------------
+template <int CT, int OP>
+__device__ __forceinline__ void fwd_pair(typename Arith<CT>::T &a, typename Arith<CT>::T &b, const Enc<CT> &e,
+                                         const Grid<typename Arith<CT>::T> &g) {
+    using A = Arith<CT>;
+    if (OP != OP_QDQ) {
+        a = fwd_elem<CT, OP>(a, e, g);
+        b = fwd_elem<CT, OP>(b, e, g);
+        return;
+    }
+    a = div_scale<CT>(a, e);
+    b = div_scale<CT>(b, e);
+    A::rnd2(a, b);
+    if (g.has_zps) {
+        a = op_sub(a, g.zps);
+        b = op_sub(b, g.zps);
+        A::rnd2(a, b);
+    }
+    a = op_sub(round_even<CT>(a, e), e.o);
+    b = op_sub(round_even<CT>(b, e), e.o);
+    if (!e.exact_int) A::rnd2(a, b);
+    a = op_add(clamp_prop(a, g.qmin, g.qmax), e.back);
+    b = op_add(clamp_prop(b, g.qmin, g.qmax), e.back);
+    if (!e.exact_int || g.has_zps) A::rnd2(a, b);
+    // the product is re-rounded by the store conversion when the output dtype is
+    // the internal dtype; VecCvt::pack does that rounding
+    a = op_mul(a, e.s);
+    b = op_mul(b, e.s);
+}
+
+template <int CT, int OP, bool WANT_O>
+__device__ __forceinline__ void bwd_pair(typename Arith<CT>::T &xa, typename Arith<CT>::T &xb,
+                                         typename Arith<CT>::T ga, typename Arith<CT>::T gb, const Enc<CT> &e,
+                                         const Grid<typename Arith<CT>::T> &g, typename Arith<CT>::T &acc_s,
+                                         typename Arith<CT>::T &acc_o) {
+    using A = Arith<CT>;
+    using T = typename A::T;
+    if (OP != OP_QDQ) {
+        T ds, dofs;
+        xa = bwd_elem<CT, OP, WANT_O>(xa, ga, e, g, ds, dofs);
+        acc_s += ds;
+        acc_o += dofs;
+        xb = bwd_elem<CT, OP, WANT_O>(xb, gb, e, g, ds, dofs);
+        acc_s += ds;
+        acc_o += dofs;
+        return;
+    }
+    T sa = div_scale<CT>(xa, e), sb = div_scale<CT>(xb, e);
+    A::rnd2(sa, sb);
+    if (g.has_zps) {
+        sa = op_sub(sa, g.zps);
+        sb = op_sub(sb, g.zps);
+        A::rnd2(sa, sb);
+    }
+    const T ra = round_even<CT>(sa, e), rb = round_even<CT>(sb, e);
+    T ta = op_sub(ra, e.o), tb = op_sub(rb, e.o);
+    if (!e.exact_int) A::rnd2(ta, tb);
+    const bool ina = (g.qmin <= ta) && (ta <= g.qmax);
+    const bool inb = (g.qmin <= tb) && (tb <= g.qmax);
+    T ca = clamp_prop(ra, e.lo, e.hi), cb = clamp_prop(rb, e.lo, e.hi);
+    if (g.has_zps) {
+        ca = op_add(ca, g.zps);
+        cb = op_add(cb, g.zps);
+        A::rnd2(ca, cb);
+    }
+    T da = op_mul(ga, ina ? op_sub(ra, sa) : ca);
+    T db = op_mul(gb, inb ? op_sub(rb, sb) : cb);
+    A::rnd2(da, db);
+    acc_s += da;
+    acc_s += db;
+    if (WANT_O) {
+        T oa = op_mul(ga, e.s), ob = op_mul(gb, e.s);
+        A::rnd2(oa, ob);
+        acc_o += ina ? (T)0 : oa;
+        acc_o += inb ? (T)0 : ob;
+    }
+    xa = ina ? ga : (T)0;
+    xb = inb ? gb : (T)0;
 }
 
 // ---------------------------------------------------------------------------
@@ -120,6 +284,7 @@ struct FwdArgs {
     int64_t numel;
     ChanMap cm;
     double qmin, qmax, zps;
+    int exact_edges;
 };
 
 template <int IO, int CT, int OP, bool VECT>
@@ -129,14 +294,14 @@ __global__ void __launch_bounds__(kThreads) k_fwd_oci(FwdArgs a) {
     using T = typename A::T;
     using C = Cvt<T, E>;
     constexpr int VEC = VECT ? 16 / (int)sizeof(E) : 1;
-    const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0};
+    const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0, a.exact_edges};
     const int64_t nvec = a.numel / VEC;
     const bool uniform = (a.cm.I % VEC) == 0;
     const E *__restrict__ xp = static_cast<const E *>(a.x);
     E *__restrict__ yp = static_cast<E *>(a.y);
 
     const int64_t base = (int64_t)blockIdx.x * (kThreads * kFwdUnroll) + threadIdx.x;
-    if (VECT) {
+    if constexpr (VECT) {
         Vec16<E> xv[kFwdUnroll];
 #pragma unroll
         for (int u = 0; u < kFwdUnroll; ++u) {
@@ -149,13 +314,17 @@ __global__ void __launch_bounds__(kThreads) k_fwd_oci(FwdArgs a) {
             if (v >= nvec) continue;
             Vec16<E> yv;
             if (uniform) {
-                Enc<CT> e = load_enc<CT>(a.scale, a.offset, a.cm.of(v * VEC));
+                const Enc<CT> e = load_enc<CT>(a.scale, a.offset, a.cm.of(v * VEC), g);
+                constexpr int NV = 16 / (int)sizeof(E);
+                T f[NV];
+                VecCvt<T, E>::unpack(xv[u], f);
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) yv.v[i] = C::store(fwd_elem<CT, OP>(C::load(xv[u].v[i]), e, g));
+                for (int i = 0; i + 1 < NV; i += 2) fwd_pair<CT, OP>(f[i], f[i + 1], e, g);
+                VecCvt<T, E>::pack(f, yv);
             } else {
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) {
-                    Enc<CT> e = load_enc<CT>(a.scale, a.offset, a.cm.of(v * VEC + i));
+                    Enc<CT> e = load_enc<CT>(a.scale, a.offset, a.cm.of(v * VEC + i), g);
                     yv.v[i] = C::store(fwd_elem<CT, OP>(C::load(xv[u].v[i]), e, g));
                 }
             }
@@ -166,7 +335,7 @@ __global__ void __launch_bounds__(kThreads) k_fwd_oci(FwdArgs a) {
         for (int u = 0; u < kFwdUnroll; ++u) {
             int64_t v = base + (int64_t)u * kThreads;
             if (v >= nvec) continue;
-            Enc<CT> e = load_enc<CT>(a.scale, a.offset, a.cm.of(v));
+            Enc<CT> e = load_enc<CT>(a.scale, a.offset, a.cm.of(v), g);
             yp[v] = C::store(fwd_elem<CT, OP>(C::load(xp[v]), e, g));
         }
     }
@@ -179,6 +348,7 @@ struct FwdGenArgs {
     int64_t numel;
     GenMap gm;
     double qmin, qmax, zps;
+    int exact_edges;
 };
 
 template <int IO, int CT, int OP>
@@ -187,12 +357,12 @@ __global__ void __launch_bounds__(kThreads) k_fwd_gen(FwdGenArgs a) {
     using A = Arith<CT>;
     using T = typename A::T;
     using C = Cvt<T, E>;
-    const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0};
+    const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0, a.exact_edges};
     const E *__restrict__ xp = static_cast<const E *>(a.x);
     E *__restrict__ yp = static_cast<E *>(a.y);
     const int64_t stride = (int64_t)gridDim.x * kThreads;
     for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < a.numel; i += stride) {
-        Enc<CT> e = load_enc<CT>(a.scale, a.offset, a.gm.of(i));
+        Enc<CT> e = load_enc<CT>(a.scale, a.offset, a.gm.of(i), g);
         yp[i] = C::store(fwd_elem<CT, OP>(C::load(xp[i]), e, g));
     }
 }
@@ -217,6 +387,7 @@ struct BwdArgs {
     // column mode
     int64_t rows, row_len, rows_per_tile;
     double qmin, qmax, zps;
+    int exact_edges;
 };
 
 template <int CT> __device__ __forceinline__ double finalize(double v) {
@@ -227,14 +398,14 @@ template <int CT> __device__ __forceinline__ double finalize(double v) {
 
 // One group of `group` threads per pseudo-segment; a pseudo-segment is a
 // contiguous run of elements that share one parameter.
-template <int IO, int CT, int OP, bool VECT>
+template <int IO, int CT, int OP, bool VECT, bool WANT_O>
 __global__ void __launch_bounds__(kThreads) k_bwd_seg(BwdArgs a) {
     using E = typename Elem<IO>::type;
     using A = Arith<CT>;
     using T = typename A::T;
     using C = Cvt<T, E>;
     constexpr int VEC = VECT ? 16 / (int)sizeof(E) : 1;
-    const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0};
+    const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0, a.exact_edges};
     const E *__restrict__ xp = static_cast<const E *>(a.x);
     const E *__restrict__ gp = static_cast<const E *>(a.gy);
     E *__restrict__ dxp = static_cast<E *>(a.gx);
@@ -255,46 +426,50 @@ __global__ void __launch_bounds__(kThreads) k_bwd_seg(BwdArgs a) {
         if (len > a.seg_len) len = a.seg_len;
         param = a.cm.wrap ? ts % a.cm.C : ts;
         if (a.cm.C == 1) param = 0;
-        const Enc<CT> e = load_enc<CT>(a.scale, a.offset, param);
+        const Enc<CT> e = load_enc<CT>(a.scale, a.offset, param, g);
         const int64_t nv = len / VEC;
         const int64_t v0 = start / VEC;
         for (int64_t v = lane; v < nv; v += 2 * (int64_t)G) {
             const int64_t va = v0 + v, vb = va + G;
             const bool hb = v + G < nv;
-            if (VECT) {
-                Vec16<E> xa, ga, xb, gb, da, db;
+            if constexpr (VECT) {
+                constexpr int NV = 16 / (int)sizeof(E);
+                Vec16<E> xa, ga, xb, gb;
                 xa = reinterpret_cast<const Vec16<E> *>(xp)[va];
                 ga = reinterpret_cast<const Vec16<E> *>(gp)[va];
                 if (hb) {
                     xb = reinterpret_cast<const Vec16<E> *>(xp)[vb];
                     gb = reinterpret_cast<const Vec16<E> *>(gp)[vb];
                 }
+                T fx[NV], fg[NV];
+                VecCvt<T, E>::unpack(xa, fx);
+                VecCvt<T, E>::unpack(ga, fg);
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) {
-                    T ds, dofs;
-                    da.v[i] = C::store(bwd_elem<CT, OP>(C::load(xa.v[i]), C::load(ga.v[i]), e, g, ds, dofs));
-                    acc_s += ds;
-                    acc_o += dofs;
+                for (int i = 0; i + 1 < NV; i += 2)
+                    bwd_pair<CT, OP, WANT_O>(fx[i], fx[i + 1], fg[i], fg[i + 1], e, g, acc_s, acc_o);
+                if (dxp) {
+                    VecCvt<T, E>::pack(fx, xa);
+                    reinterpret_cast<Vec16<E> *>(dxp)[va] = xa;
                 }
-                if (dxp) reinterpret_cast<Vec16<E> *>(dxp)[va] = da;
                 if (hb) {
+                    VecCvt<T, E>::unpack(xb, fx);
+                    VecCvt<T, E>::unpack(gb, fg);
 #pragma unroll
-                    for (int i = 0; i < VEC; ++i) {
-                        T ds, dofs;
-                        db.v[i] = C::store(bwd_elem<CT, OP>(C::load(xb.v[i]), C::load(gb.v[i]), e, g, ds, dofs));
-                        acc_s += ds;
-                        acc_o += dofs;
+                    for (int i = 0; i + 1 < NV; i += 2)
+                        bwd_pair<CT, OP, WANT_O>(fx[i], fx[i + 1], fg[i], fg[i + 1], e, g, acc_s, acc_o);
+                    if (dxp) {
+                        VecCvt<T, E>::pack(fx, xb);
+                        reinterpret_cast<Vec16<E> *>(dxp)[vb] = xb;
                     }
-                    if (dxp) reinterpret_cast<Vec16<E> *>(dxp)[vb] = db;
                 }
             } else {
                 T ds, dofs;
-                T dx = bwd_elem<CT, OP>(C::load(xp[va]), C::load(gp[va]), e, g, ds, dofs);
+                T dx = bwd_elem<CT, OP, WANT_O>(C::load(xp[va]), C::load(gp[va]), e, g, ds, dofs);
                 acc_s += ds;
                 acc_o += dofs;
                 if (dxp) dxp[va] = C::store(dx);
                 if (hb) {
-                    dx = bwd_elem<CT, OP>(C::load(xp[vb]), C::load(gp[vb]), e, g, ds, dofs);
+                    dx = bwd_elem<CT, OP, WANT_O>(C::load(xp[vb]), C::load(gp[vb]), e, g, ds, dofs);
                     acc_s += ds;
                     acc_o += dofs;
                     if (dxp) dxp[vb] = C::store(dx);
@@ -342,14 +517,14 @@ __global__ void __launch_bounds__(kThreads) k_bwd_seg(BwdArgs a) {
 // Column mode for small inner extents under a large outer dim: the tensor is a
 // (rows, row_len) matrix whose columns each belong to one parameter; a thread
 // owns one 16-byte column group and walks down a tile of rows.
-template <int IO, int CT, int OP, bool VECT>
+template <int IO, int CT, int OP, bool VECT, bool WANT_O>
 __global__ void __launch_bounds__(kThreads) k_bwd_col(BwdArgs a) {
     using E = typename Elem<IO>::type;
     using A = Arith<CT>;
     using T = typename A::T;
     using C = Cvt<T, E>;
     constexpr int VEC = VECT ? 16 / (int)sizeof(E) : 1;
-    const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0};
+    const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0, a.exact_edges};
     const E *__restrict__ xp = static_cast<const E *>(a.x);
     const E *__restrict__ gp = static_cast<const E *>(a.gy);
     E *__restrict__ dxp = static_cast<E *>(a.gx);
@@ -366,7 +541,7 @@ __global__ void __launch_bounds__(kThreads) k_bwd_col(BwdArgs a) {
     for (int i = 0; i < VEC; ++i) {
         int64_t col = cv * VEC + i;
         int64_t p = a.cm.C == 1 ? 0 : (a.cm.shift >= 0 ? (col >> a.cm.shift) : col / a.cm.I);
-        e[i] = load_enc<CT>(a.scale, a.offset, p);
+        e[i] = load_enc<CT>(a.scale, a.offset, p, g);
     }
     T acc_s[VEC], acc_o[VEC];
 #pragma unroll
@@ -394,7 +569,7 @@ __global__ void __launch_bounds__(kThreads) k_bwd_col(BwdArgs a) {
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
             T ds, dofs;
-            da.v[i] = C::store(bwd_elem<CT, OP>(C::load(xa.v[i]), C::load(ga.v[i]), e[i], g, ds, dofs));
+            da.v[i] = C::store(bwd_elem<CT, OP, WANT_O>(C::load(xa.v[i]), C::load(ga.v[i]), e[i], g, ds, dofs));
             acc_s[i] += ds;
             acc_o[i] += dofs;
         }
@@ -402,7 +577,7 @@ __global__ void __launch_bounds__(kThreads) k_bwd_col(BwdArgs a) {
 #pragma unroll
             for (int i = 0; i < VEC; ++i) {
                 T ds, dofs;
-                db.v[i] = C::store(bwd_elem<CT, OP>(C::load(xb.v[i]), C::load(gb.v[i]), e[i], g, ds, dofs));
+                db.v[i] = C::store(bwd_elem<CT, OP, WANT_O>(C::load(xb.v[i]), C::load(gb.v[i]), e[i], g, ds, dofs));
                 acc_s[i] += ds;
                 acc_o[i] += dofs;
             }
@@ -434,13 +609,15 @@ struct FinishArgs {
     int64_t nparam, na, sa, sc, nb;
 };
 
-template <int CT> __global__ void __launch_bounds__(kThreads) k_bwd_finish(FinishArgs a) {
-    const int64_t c = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+template <int CT, bool PER_CTA> __global__ void __launch_bounds__(kThreads) k_bwd_finish(FinishArgs a) {
+    // PER_CTA: one CTA per parameter (many partials each); else one warp per parameter
+    const int64_t c = PER_CTA ? (int64_t)blockIdx.x : (((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5);
     const int lane = threadIdx.x & 31;
     if (c >= a.nparam) return;
     double rs = 0, ro = 0;
     const int64_t n = a.na * a.nb;
-    for (int64_t t = lane; t < n; t += 32) {
+    const int step = PER_CTA ? kThreads : 32;
+    for (int64_t t = PER_CTA ? threadIdx.x : lane; t < n; t += step) {
         const int64_t ia = t / a.nb, ib = t - ia * a.nb;
         const double *p = a.partial + 2 * (ia * a.sa + c * a.sc + ib);
         rs += p[0];
@@ -448,6 +625,20 @@ template <int CT> __global__ void __launch_bounds__(kThreads) k_bwd_finish(Finis
     }
     rs = warp_sum(rs);
     ro = warp_sum(ro);
+    if (PER_CTA) {
+        __shared__ double sh[2][kThreads / 32];
+        if (lane == 0) {
+            sh[0][threadIdx.x >> 5] = rs;
+            sh[1][threadIdx.x >> 5] = ro;
+        }
+        __syncthreads();
+        if (threadIdx.x != 0) return;
+        rs = ro = 0;
+        for (int w = 0; w < kThreads / 32; ++w) {
+            rs += sh[0][w];
+            ro += sh[1][w];
+        }
+    }
     if (lane == 0) {
         if (a.gs.p) a.gs.put(c, finalize<CT>(rs));
         if (a.go.p) a.go.put(c, finalize<CT>(ro));
@@ -468,15 +659,16 @@ struct BwdGenArgs {
     int64_t estride[AB_MAX_DIMS];  // element stride of dim k
     int64_t box;                   // elements per parameter
     double qmin, qmax, zps;
+    int exact_edges;
 };
 
-template <int IO, int CT, int OP>
+template <int IO, int CT, int OP, bool WANT_O>
 __global__ void __launch_bounds__(kThreads) k_bwd_gen(BwdGenArgs a) {
     using E = typename Elem<IO>::type;
     using A = Arith<CT>;
     using T = typename A::T;
     using C = Cvt<T, E>;
-    const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0};
+    const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0, a.exact_edges};
     const E *__restrict__ xp = static_cast<const E *>(a.x);
     const E *__restrict__ gp = static_cast<const E *>(a.gy);
     E *__restrict__ dxp = static_cast<E *>(a.gx);
@@ -489,7 +681,7 @@ __global__ void __launch_bounds__(kThreads) k_bwd_gen(BwdGenArgs a) {
             rem /= a.nblk[k];
             base += pc * a.block[k] * a.estride[k];
         }
-        const Enc<CT> e = load_enc<CT>(a.scale, a.offset, p);
+        const Enc<CT> e = load_enc<CT>(a.scale, a.offset, p, g);
         T acc_s = 0, acc_o = 0;
         for (int64_t t = lane; t < a.box; t += 32) {
             int64_t off = base, r = t;
@@ -499,7 +691,7 @@ __global__ void __launch_bounds__(kThreads) k_bwd_gen(BwdGenArgs a) {
                 off += c * a.estride[k];
             }
             T ds, dofs;
-            T dx = bwd_elem<CT, OP>(C::load(xp[off]), C::load(gp[off]), e, g, ds, dofs);
+            T dx = bwd_elem<CT, OP, WANT_O>(C::load(xp[off]), C::load(gp[off]), e, g, ds, dofs);
             acc_s += ds;
             acc_o += dofs;
             if (dxp) dxp[off] = C::store(dx);
@@ -517,6 +709,20 @@ __global__ void __launch_bounds__(kThreads) k_bwd_gen(BwdGenArgs a) {
 // ---------------------------------------------------------------------------
 using BwdPlan = ReducePlan;
 inline BwdPlan plan_backward(const Canon &c, int io_dtype, bool ptr_aligned) { return plan_reduce(c, io_dtype, ptr_aligned); }
+
+// qmin-1 and qmax+1 are exactly representable in the 16-bit internal dtype
+bool fits_significand(int64_t v, int bits) {
+    if (v < 0) v = -v;
+    if (v == 0) return true;
+    while ((v & 1) == 0) v >>= 1;
+    return v < ((int64_t)1 << bits);
+}
+int exact_edges(int ct, int64_t qmin, int64_t qmax) {
+    const int bits = ct == AB_BF16 ? 8 : (ct == AB_F16 ? 11 : 0);
+    if (bits == 0) return 0;
+    if (qmax > 60000 || qmin < -60000) return 0;
+    return fits_significand(qmin - 1, bits) && fits_significand(qmax + 1, bits);
+}
 
 struct Call {
     int op;
@@ -558,6 +764,7 @@ template <int IO, int CT, int OP> int launch_forward(const Call &c, const Canon 
         a.qmin = (double)c.qmin;
         a.qmax = (double)c.qmax;
         a.zps = c.zps;
+        a.exact_edges = exact_edges(CT, c.qmin, c.qmax);
         const bool vect = aligned16(c.x) && aligned16(c.y) && (canon.numel % vecw == 0);
         const int64_t nvec = vect ? canon.numel / vecw : canon.numel;
         const int64_t per_cta = (int64_t)kThreads * kFwdUnroll;
@@ -578,6 +785,7 @@ template <int IO, int CT, int OP> int launch_forward(const Call &c, const Canon 
         a.qmin = (double)c.qmin;
         a.qmax = (double)c.qmax;
         a.zps = c.zps;
+        a.exact_edges = exact_edges(CT, c.qmin, c.qmax);
         int64_t grid = (canon.numel + kThreads - 1) / kThreads;
         const int64_t cap = (int64_t)sm_count() * 16;
         if (grid > cap) grid = cap;
@@ -621,10 +829,14 @@ template <int IO, int CT, int OP> int launch_backward(const Call &c, const Canon
         a.qmin = (double)c.qmin;
         a.qmax = (double)c.qmax;
         a.zps = c.zps;
+        a.exact_edges = exact_edges(CT, c.qmin, c.qmax);
         int64_t grid = (canon.nparam * 32 + kThreads - 1) / kThreads;
         const int64_t cap = (int64_t)sm_count() * 16;
         if (grid > cap) grid = cap;
-        k_bwd_gen<IO, CT, OP><<<(unsigned)grid, kThreads, 0, c.stream>>>(a);
+        if (c.go)
+            k_bwd_gen<IO, CT, OP, true><<<(unsigned)grid, kThreads, 0, c.stream>>>(a);
+        else
+            k_bwd_gen<IO, CT, OP, false><<<(unsigned)grid, kThreads, 0, c.stream>>>(a);
         AB_LAUNCH_OK();
         return AB_OK;
     }
@@ -658,24 +870,33 @@ template <int IO, int CT, int OP> int launch_backward(const Call &c, const Canon
     a.qmin = (double)c.qmin;
     a.qmax = (double)c.qmax;
     a.zps = c.zps;
+    a.exact_edges = exact_edges(CT, c.qmin, c.qmax);
 
     if (p.mode == BwdPlan::SEG) {
         const int gpc = kThreads / p.group;
         const int64_t grid = (p.nseg + gpc - 1) / gpc;
         if (grid > 2147483647LL) return fail(AB_ERR_UNSUPPORTED, "tensor too large for one launch");
-        if (p.vect)
-            k_bwd_seg<IO, CT, OP, true><<<(unsigned)grid, kThreads, 0, c.stream>>>(a);
+        if (p.vect && c.go)
+            k_bwd_seg<IO, CT, OP, true, true><<<(unsigned)grid, kThreads, 0, c.stream>>>(a);
+        else if (p.vect)
+            k_bwd_seg<IO, CT, OP, true, false><<<(unsigned)grid, kThreads, 0, c.stream>>>(a);
+        else if (c.go)
+            k_bwd_seg<IO, CT, OP, false, true><<<(unsigned)grid, kThreads, 0, c.stream>>>(a);
         else
-            k_bwd_seg<IO, CT, OP, false><<<(unsigned)grid, kThreads, 0, c.stream>>>(a);
+            k_bwd_seg<IO, CT, OP, false, false><<<(unsigned)grid, kThreads, 0, c.stream>>>(a);
     } else {
         const int v = p.vect ? 16 / dtype_size(IO) : 1;
         const int64_t gx = (a.row_len / v + kThreads - 1) / kThreads;
         if (gx > 2147483647LL) return fail(AB_ERR_UNSUPPORTED, "tensor too large for one launch");
         dim3 grid((unsigned)gx, (unsigned)p.row_tiles);
-        if (p.vect)
-            k_bwd_col<IO, CT, OP, true><<<grid, kThreads, 0, c.stream>>>(a);
+        if (p.vect && c.go)
+            k_bwd_col<IO, CT, OP, true, true><<<grid, kThreads, 0, c.stream>>>(a);
+        else if (p.vect)
+            k_bwd_col<IO, CT, OP, true, false><<<grid, kThreads, 0, c.stream>>>(a);
+        else if (c.go)
+            k_bwd_col<IO, CT, OP, false, true><<<grid, kThreads, 0, c.stream>>>(a);
         else
-            k_bwd_col<IO, CT, OP, false><<<grid, kThreads, 0, c.stream>>>(a);
+            k_bwd_col<IO, CT, OP, false, false><<<grid, kThreads, 0, c.stream>>>(a);
     }
     AB_LAUNCH_OK();
     if (need > 0) {
@@ -688,8 +909,12 @@ template <int IO, int CT, int OP> int launch_backward(const Call &c, const Canon
         f.sa = p.sa;
         f.sc = p.sc;
         f.nb = p.nb;
-        const int64_t grid = (canon.nparam * 32 + kThreads - 1) / kThreads;
-        k_bwd_finish<CT><<<(unsigned)grid, kThreads, 0, c.stream>>>(f);
+        if (p.na * p.nb > 256) {
+            k_bwd_finish<CT, true><<<(unsigned)canon.nparam, kThreads, 0, c.stream>>>(f);
+        } else {
+            const int64_t grid = (canon.nparam * 32 + kThreads - 1) / kThreads;
+            k_bwd_finish<CT, false><<<(unsigned)grid, kThreads, 0, c.stream>>>(f);
+        }
         AB_LAUNCH_OK();
     }
     return AB_OK;

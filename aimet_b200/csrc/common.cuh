@@ -90,21 +90,37 @@ __device__ __forceinline__ double to_f64(double v) { return v; }
 // ---------------------------------------------------------------------------
 template <int CT> struct Arith;
 
+// rnd2() rounds two values at once: the packed float->16-bit conversion is one
+// instruction on the ALU pipe, whereas the scalar conversion goes through the
+// quarter-rate conversion unit.
 template <> struct Arith<AB_F32> {
     using T = float;
     static __device__ __forceinline__ T rnd(T v) { return v; }
+    static __device__ __forceinline__ void rnd2(T &, T &) {}
 };
 template <> struct Arith<AB_BF16> {
     using T = float;
     static __device__ __forceinline__ T rnd(T v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+    static __device__ __forceinline__ void rnd2(T &a, T &b) {
+        const __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
+        const uint32_t w = *reinterpret_cast<const uint32_t *>(&p);
+        a = __uint_as_float(w << 16);
+        b = __uint_as_float(w & 0xffff0000u);
+    }
 };
 template <> struct Arith<AB_F16> {
     using T = float;
     static __device__ __forceinline__ T rnd(T v) { return __half2float(__float2half_rn(v)); }
+    static __device__ __forceinline__ void rnd2(T &a, T &b) {
+        const float2 f = __half22float2(__floats2half2_rn(a, b));
+        a = f.x;
+        b = f.y;
+    }
 };
 template <> struct Arith<AB_F64> {
     using T = double;
     static __device__ __forceinline__ T rnd(T v) { return v; }
+    static __device__ __forceinline__ void rnd2(T &, T &) {}
 };
 
 __device__ __forceinline__ float op_add(float a, float b) { return __fadd_rn(a, b); }
@@ -151,6 +167,52 @@ template <> struct Cvt<double, double> {
 template <typename E> struct alignas(16) Vec16 {
     static constexpr int N = 16 / sizeof(E);
     E v[N];
+};
+
+// whole-vector conversions between a 16-byte vector and register values
+template <typename T, typename E> struct VecCvt {
+    static constexpr int N = 16 / sizeof(E);
+    static __device__ __forceinline__ void unpack(const Vec16<E> &v, T (&out)[N]) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) out[i] = Cvt<T, E>::load(v.v[i]);
+    }
+    static __device__ __forceinline__ void pack(const T (&in)[N], Vec16<E> &v) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) v.v[i] = Cvt<T, E>::store(in[i]);
+    }
+};
+template <> struct VecCvt<float, __nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void unpack(const Vec16<__nv_bfloat16> &v, float (&out)[8]) {
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            out[2 * i] = __uint_as_float(w[i] << 16);
+            out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ void pack(const float (&in)[8], Vec16<__nv_bfloat16> &v) {
+        __nv_bfloat162 *p = reinterpret_cast<__nv_bfloat162 *>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(in[2 * i], in[2 * i + 1]);
+    }
+};
+template <> struct VecCvt<float, __half> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void unpack(const Vec16<__half> &v, float (&out)[8]) {
+        const __half2 *p = reinterpret_cast<const __half2 *>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(p[i]);
+            out[2 * i] = f.x;
+            out[2 * i + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void pack(const float (&in)[8], Vec16<__half> &v) {
+        __half2 *p = reinterpret_cast<__half2 *>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) p[i] = __floats2half2_rn(in[2 * i], in[2 * i + 1]);
+    }
 };
 
 // parameter (scale / offset / grad) access: float32 or float64 arrays

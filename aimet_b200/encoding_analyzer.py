@@ -1,0 +1,637 @@
+"""Encoding analyzers on the B200 statistics kernels.
+
+Host-side mirror of aimet_torch's ``quantization/encoding_analyzer.py``: the same class names,
+constructor arguments, statistics containers and error behaviour (``_MinMaxObserver`` :69-118,
+``_HistogramObserver`` :121-338, ``EncodingAnalyzer`` :341-394, ``MinMaxEncodingAnalyzer``
+:397-481, ``PercentileEncodingAnalyzer`` :537-650, ``SqnrEncodingAnalyzer`` :902-953,
+``TfEnhancedEncodingAnalyzer`` :956-1002), so an instance can be passed as ``encoding_analyzer=``
+to a quantizer.  Every pass over the observed tensor is a CUDA kernel behind the C ABI
+(min/max, histogram, SQNR sweep); what remains in PyTorch is O(bins) bookkeeping on device
+tensors.  All histograms of an observer are kept as one batched tensor and handled at once.
+"""
+
+from __future__ import annotations
+
+import math
+from collections.abc import Sequence as _SequenceABC
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import lib
+from .backend import _dense_perm, _param_blocks
+
+__all__ = [
+    "StatisticsNotFoundError",
+    "EncodingAnalyzer",
+    "MinMaxEncodingAnalyzer",
+    "PercentileEncodingAnalyzer",
+    "SqnrEncodingAnalyzer",
+    "TfEnhancedEncodingAnalyzer",
+]
+
+
+class StatisticsNotFoundError(RuntimeError):
+    """compute_encodings() was called before any statistics were observed (aimet_torch/utils.py:1257)."""
+
+
+def _get_minimum_scale(num_steps) -> float:
+    """Largest s <= float32 eps whose grid still spans [-0.005, 0.005] (_aimet_common/quantsim.py:537-559)."""
+    return min(float(np.finfo(np.float32).eps), 0.01 / num_steps)
+
+
+@dataclass
+class _MinMaxRange:
+    min: Optional[torch.Tensor] = None
+    max: Optional[torch.Tensor] = None
+
+
+@dataclass
+class _Histogram:
+    histogram: torch.Tensor = None
+    bin_edges: torch.Tensor = None
+    min: Optional[torch.Tensor] = None
+    max: Optional[torch.Tensor] = None
+
+
+class _HistogramList(_SequenceABC):
+    """``List[_Histogram]`` view over batched tensors ``[H, bins]`` / ``[H, bins+1]`` / ``[H]``."""
+
+    def __init__(self, histogram, bin_edges, min, max):  # pylint: disable=redefined-builtin
+        self.histogram, self.bin_edges, self.min, self.max = histogram, bin_edges, min, max
+
+    def __len__(self):
+        return self.histogram.shape[0]
+
+    def __getitem__(self, i):
+        if isinstance(i, slice):
+            return _HistogramList(self.histogram[i], self.bin_edges[i], self.min[i], self.max[i])
+        if i < 0:
+            i += len(self)
+        if not 0 <= i < len(self):
+            raise IndexError(i)
+        return _Histogram(self.histogram[i], self.bin_edges[i], self.min[i], self.max[i])
+
+    @staticmethod
+    def from_stats(stats) -> "_HistogramList":
+        if isinstance(stats, _HistogramList):
+            return stats
+        return _HistogramList(
+            torch.stack([s.histogram for s in stats]),
+            torch.stack([s.bin_edges for s in stats]),
+            torch.stack([s.min for s in stats]),
+            torch.stack([s.max for s in stats]),
+        )
+
+
+# --------------------------------------------------------------------------------------------
+# kernel plumbing
+# --------------------------------------------------------------------------------------------
+def _check_input(x: torch.Tensor) -> torch.Tensor:
+    if not isinstance(x, torch.Tensor):
+        raise TypeError(f"expected a torch.Tensor, got {type(x)}")
+    if not x.is_cuda:
+        raise RuntimeError(
+            f"aimet_b200 analyzers observe CUDA tensors only (got '{x.device}'); there is no CPU fallback."
+        )
+    if x.dtype not in _lib.DTYPE_CODE:
+        raise RuntimeError(f"unsupported dtype {x.dtype}")
+    return x.detach()
+
+
+def _is_reducible(src_shape, target_shape) -> bool:
+    if len(target_shape) > len(src_shape):
+        return False
+    return all(t in (1, s) for s, t in zip(reversed(src_shape), reversed(target_shape)))
+
+
+class _StatLayout:
+    """Dense view of an observed tensor plus the layout that maps it onto ``shape`` statistics."""
+
+    def __init__(self, x: torch.Tensor, shape: Tuple[int, ...], block_size):
+        if block_size is not None:
+            if len(block_size) != len(shape) or len(shape) > x.dim():
+                raise RuntimeError(f"Shape {shape} / block size {block_size} is incompatible with input of shape {tuple(x.shape)}")
+            for k in range(1, len(shape) + 1):
+                b, s, d = block_size[-k], shape[-k], x.shape[-k]
+                if (b == -1 and (s == 0 or d % s != 0)) or (b != -1 and b * s != d):
+                    raise RuntimeError(
+                        f"Input of shape {list(x.shape)} can't be reduced to shape {list(shape)} with block size {block_size}"
+                    )
+        elif not _is_reducible(x.shape, shape):
+            raise RuntimeError(f"Input of shape {list(x.shape)} can't be reduced to shape {list(shape)}")
+        blocks = _param_blocks(x.shape, shape, block_size)
+        perm = _dense_perm(x)
+        if perm is not None and list(perm) != list(range(x.dim())):
+            pdims = [k for k in perm if x.shape[k] // blocks[k] > 1]
+            if pdims != sorted(pdims):
+                perm = None
+        if perm is None:
+            x = x.contiguous()
+            perm = tuple(range(x.dim()))
+        self.x = x.permute(perm)
+        self.size = [x.shape[k] for k in perm]
+        self.block = [blocks[k] for k in perm]
+        self.layout = _lib.make_layout(self.size, self.block)
+        self.count = int(np.prod(shape, dtype=np.int64)) if len(shape) else 1
+        self.io = _lib.DTYPE_CODE[self.x.dtype]
+
+    def densify(self):
+        """Fallback for layouts the kernels cannot walk in place: copy to [count, rest]."""
+        x, size, block = self.x, self.size, self.block
+        view = []
+        for s, b in zip(size, block):
+            view.extend((s // b, b))
+        x = x.reshape(view)
+        nd = len(size)
+        x = x.permute(*range(0, 2 * nd, 2), *range(1, 2 * nd, 2)).reshape(self.count, -1).contiguous()
+        self.x = x
+        self.size, self.block = list(x.shape), [1, x.shape[1]]
+        self.layout = _lib.make_layout(self.size, self.block)
+
+
+def _run_minmax(lay: _StatLayout, finite_only: bool):
+    x = lay.x
+    mn = torch.empty(lay.count, dtype=x.dtype, device=x.device)
+    mx = torch.empty(lay.count, dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        nbytes = lib.aimet_b200_stats_scratch_bytes(lay.layout, lay.io)
+        _lib.check(nbytes)
+        scratch = _lib.scratch.get(x.device, nbytes)
+        rc = lib.aimet_b200_minmax(x.data_ptr(), lay.layout, lay.io, int(finite_only), mn.data_ptr(), mx.data_ptr(),
+                                   _lib.ptr(scratch), 0 if scratch is None else scratch.numel(),
+                                   _lib.stream_ptr(x.device))
+    _lib.check(rc)
+    return mn, mx
+
+
+def _minmax(lay: _StatLayout, finite_only: bool):
+    try:
+        return _run_minmax(lay, finite_only)
+    except NotImplementedError:
+        lay.densify()
+        return _run_minmax(lay, finite_only)
+
+
+def _run_histogram(lay: _StatLayout, num_bins: int, lo, hi, below, above):
+    x = lay.x
+    counts = torch.empty((lay.count, num_bins), dtype=torch.int64, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib.aimet_b200_histogram(x.data_ptr(), lay.layout, lay.io, num_bins, lo.data_ptr(), hi.data_ptr(),
+                                      below.data_ptr(), above.data_ptr(), counts.data_ptr(), None, None, None, 0,
+                                      _lib.stream_ptr(x.device))
+    _lib.check(rc)
+    return counts
+
+
+def _histogram(lay: _StatLayout, num_bins: int, lo: torch.Tensor, hi: torch.Tensor) -> torch.Tensor:
+    """float32 [count, num_bins] histogram of the observed tensor over [lo, hi] per statistic, values
+    below / above the range (including -inf / +inf) added to the first / last bin.  The outlier
+    comparison happens in the observed tensor's dtype, like the reference's ``input < edge``."""
+    if lay.x.dtype == torch.float64:
+        lay.x = lay.x.to(torch.float32)
+        lay.io = _lib.AB_F32
+    lo = lo.to(torch.float32).contiguous()
+    hi = hi.to(torch.float32).contiguous()
+    below = lo.to(lay.x.dtype).to(torch.float32)
+    above = hi.to(lay.x.dtype).to(torch.float32)
+    try:
+        counts = _run_histogram(lay, num_bins, lo, hi, below, above)
+    except NotImplementedError:
+        lay.densify()
+        counts = _run_histogram(lay, num_bins, lo, hi, below, above)
+    return counts.to(torch.float32)
+
+
+# --------------------------------------------------------------------------------------------
+# observers
+# --------------------------------------------------------------------------------------------
+class _Observer:
+    def __init__(self, shape, block_size=None):
+        if isinstance(shape, int):
+            shape = (shape,)
+        self.shape = tuple(shape)
+        self.block_size = tuple(block_size) if block_size is not None else None
+
+
+class _MinMaxObserver(_Observer):
+    """Running elementwise min / max of everything observed (encoding_analyzer.py:69-118)."""
+
+    def __init__(self, shape, block_size=None):
+        super().__init__(shape, block_size)
+        self.stats = _MinMaxRange()
+
+    @torch.no_grad()
+    def collect_stats(self, input_tensor: torch.Tensor) -> _MinMaxRange:
+        x = _check_input(input_tensor)
+        if x.numel() == 0:
+            raise RuntimeError("cannot collect statistics of an empty tensor")
+        mn, mx = _minmax(_StatLayout(x, self.shape, self.block_size), finite_only=False)
+        return _MinMaxRange(mn.view(self.shape), mx.view(self.shape))
+
+    @torch.no_grad()
+    def merge_stats(self, stats: _MinMaxRange):
+        new_min, new_max = self.stats.min, self.stats.max
+        if stats.min is not None:
+            new_min = stats.min.clone() if new_min is None else torch.minimum(new_min, stats.min)
+        if stats.max is not None:
+            new_max = stats.max.clone() if new_max is None else torch.maximum(new_max, stats.max)
+        self.stats = _MinMaxRange(new_min, new_max)
+
+    def reset_stats(self):
+        self.stats = _MinMaxRange()
+
+    def get_stats(self) -> _MinMaxRange:
+        return self.stats
+
+
+class _HistogramObserver(_Observer):
+    """One ``num_bins`` histogram per element of ``shape`` (encoding_analyzer.py:121-338)."""
+
+    def __init__(self, shape, *, block_size=None, num_bins: int, growth_limit: Optional[float] = None):
+        super().__init__(shape, block_size)
+        self.num_bins = num_bins
+        self.num_histograms = int(np.prod(self.shape, dtype=np.int64)) if len(self.shape) else 1
+        if growth_limit is None:
+            growth_limit = float("inf")
+        if growth_limit < 1.0:
+            raise RuntimeError(f"Growth limit must be at least 1.0. Got {growth_limit}")
+        self.growth_limit = growth_limit
+        self._state: Optional[_HistogramList] = None
+        self._histogram_range_limit = None
+
+    def _create_bin_edges(self, min_val: torch.Tensor, max_val: torch.Tensor) -> torch.Tensor:
+        """[H, bins + 1] edges; a degenerate range is widened by 0.5 each side (:221-229)."""
+        same = min_val == max_val
+        lo = torch.where(same, min_val - 0.5, min_val).float()
+        hi = torch.where(same, max_val + 0.5, max_val).float()
+        step = (hi - lo) / self.num_bins
+        ticks = torch.arange(0, self.num_bins + 1, device=min_val.device)
+        return ticks[None, :] * step[:, None] + lo[:, None]
+
+    @torch.no_grad()
+    def collect_stats(self, input_tensor: torch.Tensor) -> _HistogramList:
+        x = _check_input(input_tensor)
+        if x.numel() == 0:
+            raise RuntimeError("cannot collect statistics of an empty tensor")
+        lay = _StatLayout(x, self.shape, self.block_size)
+        mn, mx = _minmax(lay, finite_only=True)
+        edges = self._create_bin_edges(mn, mx)
+        hist = _histogram(lay, self.num_bins, edges[:, 0], edges[:, -1])
+        return _HistogramList(hist, edges, mn, mx)
+
+    def _bin_index(self, width, base, data):
+        idx = ((data - base[:, None]) / width[:, None]).to(torch.int32)
+        return idx.clamp(max=self.num_bins - 1)
+
+    @torch.no_grad()
+    def merge_stats(self, new_stats_list, input_tensor: torch.Tensor):
+        new = _HistogramList.from_stats(new_stats_list)
+        n = self.num_bins
+        if self._state is None:
+            self._state = new
+            e0, e1 = new.bin_edges[:, 0], new.bin_edges[:, -1]
+            span = e1 - e0
+            self._histogram_range_limit = torch.stack(
+                (e0 - span * self.growth_limit / 2, e1 + span * self.growth_limit / 2), dim=1
+            )
+            return
+        cur = self._state
+        lim = self._histogram_range_limit
+        umin = new.min.clamp(lim[:, 0], cur.bin_edges[:, 0])
+        umax = new.max.clamp(cur.bin_edges[:, -1], lim[:, 1])
+        keep = (umin == cur.min) & (umax == cur.max)  # the current range already covers the batch
+
+        # move the accumulated counts into the bins of the new range; a source bin that straddles a
+        # destination edge is split proportionally and rounded (:274-310)
+        dw = (umax - umin) / n
+        sw = cur.bin_edges[:, 1] - cur.bin_edges[:, 0]
+        src = cur.bin_edges[:, :-1]
+        d1 = self._bin_index(dw, umin, src)
+        d1_end = umin[:, None] + dw[:, None] * (d1 + 1)
+        first = torch.minimum(torch.round(((d1_end - src) / sw[:, None]) * cur.histogram), cur.histogram)
+        d2 = self._bin_index(dw, umin, src + dw[:, None])
+        rest = cur.histogram - first
+        split = first < cur.histogram
+        live = ~keep[:, None]
+        rows = torch.arange(len(cur), device=umin.device)[:, None] * n
+        carry = torch.zeros(len(cur) * n, dtype=cur.histogram.dtype, device=umin.device)
+        carry.index_add_(0, (rows + d1.clamp(0, n - 1)).flatten(), torch.where(live, first, 0.0).flatten())
+        carry.index_add_(0, (rows + d2.clamp(0, n - 1)).flatten(), torch.where(live & split, rest, 0.0).flatten())
+        carry = torch.where(keep[:, None], cur.histogram, carry.view(len(cur), n))
+
+        x = _check_input(input_tensor)
+        lay = _StatLayout(x, self.shape, self.block_size)
+        hist = _histogram(lay, n, umin, umax)
+        hist += carry
+        self._state = _HistogramList(hist, self._create_bin_edges(umin, umax), umin, umax)
+
+    def reset_stats(self):
+        self._state = None
+        self._histogram_range_limit = None
+
+    @property
+    def stats(self):
+        return self.get_stats()
+
+    def get_stats(self):
+        if self._state is None:
+            return [_Histogram() for _ in range(self.num_histograms)]
+        return self._state
+
+
+# --------------------------------------------------------------------------------------------
+# analyzers
+# --------------------------------------------------------------------------------------------
+class EncodingAnalyzer:
+    """Gathers statistics of observed tensors and turns them into an encoding range (:341-394)."""
+
+    def __init__(self, observer: _Observer):
+        self.observer = observer
+
+    @torch.no_grad()
+    def update_stats(self, input_tensor: torch.Tensor):
+        new_stats = self.observer.collect_stats(input_tensor)
+        self.observer.merge_stats(new_stats)
+        return new_stats
+
+    def reset_stats(self):
+        self.observer.reset_stats()
+
+    def compute_encodings(self, num_steps: int, is_symmetric: bool):
+        return self.compute_encodings_from_stats(self.observer.get_stats(), num_steps, is_symmetric)
+
+    def compute_dynamic_encodings(self, input_tensor: torch.Tensor, num_steps: int, is_symmetric: bool):
+        return self.compute_encodings_from_stats(self.observer.collect_stats(input_tensor), num_steps, is_symmetric)
+
+    def compute_encodings_from_stats(self, stats, num_steps: int, is_symmetric: bool):
+        raise NotImplementedError
+
+
+def _check_num_steps(num_steps):
+    if num_steps <= 0:
+        raise ValueError("The number of quantization bins cannot be less than or equal to 0.")
+
+
+class MinMaxEncodingAnalyzer(EncodingAnalyzer):
+    """Range = [min(input), max(input)], made to contain zero and at least ``minimum_scale`` wide,
+    fitted to a symmetric grid on request (:397-481)."""
+
+    def __init__(self, shape, block_size=None):
+        super().__init__(_MinMaxObserver(shape, block_size))
+
+    @torch.no_grad()
+    def compute_encodings_from_stats(self, stats: _MinMaxRange, num_steps: int, is_symmetric: bool):
+        _check_num_steps(num_steps)
+        if stats.min is None or stats.max is None:
+            raise StatisticsNotFoundError("No statistics present to compute encodings.")
+        min_scale = _get_minimum_scale(num_steps)
+        lo = torch.clamp(stats.min, max=0)
+        hi = torch.clamp(stats.max, min=0)
+        widen = min_scale * (((hi - lo) / num_steps) < min_scale)
+        pos, neg = math.floor(num_steps / 2), math.ceil(num_steps / 2)
+        if is_symmetric:
+            hi = hi + pos * widen
+            lo = lo - neg * widen
+            # a 2-bit grid would waste its only positive step on symmetric data: calibrate as if it had two
+            extra = 1 if num_steps == 3 else 0
+            delta = torch.maximum(hi / (pos + extra), -lo / neg)
+            lo = -1 * neg * delta
+            hi = pos * delta
+        else:
+            hi = hi + num_steps * widen
+        hi = torch.clamp(hi, max=torch.finfo(stats.min.dtype).max).to(stats.min.dtype)
+        lo = torch.clamp(lo, min=torch.finfo(stats.max.dtype).min).to(stats.max.dtype)
+        return lo, hi
+
+
+class _HistogramAnalyzer(EncodingAnalyzer):
+    observer: _HistogramObserver
+
+    @torch.no_grad()
+    def update_stats(self, input_tensor: torch.Tensor):
+        new_stats = self.observer.collect_stats(input_tensor)
+        self.observer.merge_stats(new_stats, input_tensor)
+        return new_stats
+
+    @staticmethod
+    def _batched(stats) -> _HistogramList:
+        if not isinstance(stats, _HistogramList) and stats[0].histogram is None:
+            raise StatisticsNotFoundError("No statistics present to compute encodings.")
+        return _HistogramList.from_stats(stats)
+
+
+def _adjust_min_max(cmin, cmax, num_steps, is_symmetric):
+    """Batched adjust_min_max (:501-534): include zero, keep finite, keep a minimum width, fit a
+    symmetric grid."""
+    min_scale = _get_minimum_scale(num_steps)
+    cmin = torch.minimum(cmin, torch.zeros_like(cmin))
+    cmax = torch.maximum(cmax, torch.zeros_like(cmax))
+    cmin = cmin.clamp(min=torch.finfo(cmax.dtype).min, max=0)
+    cmax = cmax.clamp(min=0, max=torch.finfo(cmax.dtype).max)
+    narrow = ((cmax - cmin) / num_steps) < min_scale
+    pos, neg = math.floor(num_steps / 2), math.ceil(num_steps / 2)
+    if is_symmetric:
+        cmin = torch.where(narrow, cmin - min_scale * neg, cmin)
+        cmax = torch.where(narrow, cmax + min_scale * pos, cmax)
+        a, b = cmax / pos, -cmin / neg
+        delta = torch.where(b > a, b, a)
+        return -1 * neg * delta, pos * delta
+    return cmin, torch.where(narrow, cmax + min_scale * num_steps, cmax)
+
+
+class PercentileEncodingAnalyzer(_HistogramAnalyzer):
+    """Range that clips the (100 - percentile)% smallest and largest observed values (:537-650)."""
+
+    def __init__(self, shape, num_bins: int = 2048, percentile: float = 100, block_size=None):
+        if num_bins <= 0:
+            raise ValueError("Number of bins cannot be less than or equal to 0.")
+        super().__init__(_HistogramObserver(shape=shape, num_bins=num_bins, block_size=block_size))
+        self.set_percentile(percentile)
+
+    def set_percentile(self, percentile):
+        if percentile < 50 or percentile > 100:
+            raise ValueError("Percentile value must be within 50-100 range")
+        self.percentile = percentile
+
+    @torch.no_grad()
+    def compute_encodings_from_stats(self, stats, num_steps: int, is_symmetric: bool):
+        _check_num_steps(num_steps)
+        st = self._batched(stats)
+        # prefix sums of integer counts: exact in float64, then rounded once like the reference's
+        # double-accumulating cumsum
+        cum = torch.cumsum(st.histogram.double(), dim=1).to(st.histogram.dtype)
+        total = cum[:, -1:]
+        hi_idx = torch.searchsorted(cum, total * self.percentile / 100)
+        lo_idx = torch.searchsorted(cum, total * (1 - self.percentile / 100))
+        if self.percentile == 100:
+            lo_idx = torch.zeros_like(lo_idx)
+            hi_idx = torch.full_like(hi_idx, st.bin_edges.shape[1] - 1)
+        cmin = torch.gather(st.bin_edges, 1, lo_idx)[:, 0]
+        cmax = torch.gather(st.bin_edges, 1, hi_idx)[:, 0]
+        emin, emax = _adjust_min_max(cmin, cmax, num_steps, is_symmetric)
+        shape = self.observer.shape
+        return emin.to(st.min.dtype).reshape(shape), emax.to(st.max.dtype).reshape(shape)
+
+
+class _LpNormEncodingAnalyzer(_HistogramAnalyzer):
+    """Searches (delta, offset) candidates for the lowest expected clipping + rounding noise,
+    estimated from the histogram (:653-899)."""
+
+    def __init__(self, shape, num_bins: int, *, p: float, asymmetric_delta_candidates: int,
+                 symmetric_delta_candidates: int, offset_candidates: int, max_parallelism: int, gamma: float,
+                 histogram_growth_limit: Optional[float] = None, block_size=None):
+        if num_bins <= 0:
+            raise ValueError("Number of bins cannot be less than or equal to 0.")
+        if p != 2.0:
+            raise NotImplementedError("the sweep kernel evaluates the squared error (p = 2) only")
+        super().__init__(_HistogramObserver(shape=shape, num_bins=num_bins, growth_limit=histogram_growth_limit,
+                                            block_size=block_size))
+        self.p = p
+        self.asym_delta_candidates = asymmetric_delta_candidates
+        self.sym_delta_candidates = symmetric_delta_candidates
+        self.num_offset_candidates = offset_candidates
+        self.gamma = gamma
+        self.max_parallelism = max_parallelism  # kept for interface parity; all histograms run in one launch
+
+    @torch.no_grad()
+    def compute_encodings_from_stats(self, stats, num_steps: int, is_symmetric: bool):
+        st = self._batched(stats)
+        _check_num_steps(num_steps)
+        deltas, offsets = self._pick_test_candidates(st, num_steps, is_symmetric)
+        best_delta, best_offset = self._select_best_candidates(deltas, offsets, st, num_steps)
+        emin = best_offset * best_delta
+        emax = emin + num_steps * best_delta
+        shape = self.observer.shape
+        return emin.to(st.min.dtype).view(shape), emax.to(st.max.dtype).view(shape)
+
+    # candidate grids -----------------------------------------------------------------------
+    def _pick_test_candidates(self, st: _HistogramList, num_steps, symmetric):
+        min_scale = _get_minimum_scale(num_steps)
+        mn = torch.min(st.min, torch.zeros_like(st.min))
+        mx = torch.max(st.max, torch.zeros_like(st.max))
+        mx = torch.max(mx, mn + min_scale * num_steps)
+        if symmetric:
+            return self._pick_test_candidates_symmetric(mn, mx, num_steps)
+        return self._pick_test_candidates_asymmetric(mn, mx, num_steps)
+
+    @staticmethod
+    def _host_arange(device, **kw):
+        # built on the host so that every device sees the CPU kernel's values
+        return torch.arange(dtype=torch.float32, **kw).to(device)
+
+    def _pick_test_candidates_asymmetric(self, mn, mx, num_steps):
+        """K deltas = max_delta * k / (K - 1), k = 1..K, times O offsets spread over [-steps, 0] plus the
+        observed one; every pair is then clipped to the observed range (:740-776, 797-820)."""
+        dev = mn.device
+        max_delta = (mx - mn).to(torch.float32) / num_steps
+        obs_offset = torch.round(mn / max_delta)
+        obs_min = max_delta * obs_offset
+        obs_max = obs_min + max_delta * num_steps
+        k = self.asym_delta_candidates
+        deltas = max_delta[:, None] * self._host_arange(dev, start=1, end=1 + k, step=1)[None, :] / (k - 1)
+        n_off = min(num_steps + 2, self.num_offset_candidates)
+        step = num_steps / (n_off - 2)
+        offsets = torch.round(self._host_arange(dev, start=-num_steps, end=step, step=step))
+        offsets = torch.concat((offsets[None, :].expand(mn.shape[0], -1), obs_offset[:, None]), dim=1)
+        return self._clamp_delta_offset_values(obs_min, obs_max, num_steps, deltas, offsets)
+
+    def _pick_test_candidates_symmetric(self, mn, mx, num_steps):
+        """K deltas up to 2 * max|x| / steps with the single offset -steps // 2 (:778-795)."""
+        dev = mn.device
+        min_scale = _get_minimum_scale(num_steps)
+        max_delta = 2 * torch.max(mx, -mn).to(torch.float32) / num_steps
+        offsets = torch.full((1,), (-num_steps) // 2, dtype=torch.float32, device=dev)
+        k = self.sym_delta_candidates
+        deltas = max_delta[:, None] * self._host_arange(dev, start=1, end=1 + k, step=1)[None, :] / (k - 1)
+        deltas = torch.max(deltas, torch.tensor([min_scale], dtype=torch.float32, device=dev))
+        return deltas[:, :, None], offsets[:, None, None]
+
+    @staticmethod
+    def _clamp_delta_offset_values(min_vals, max_vals, num_steps, deltas, offsets):
+        min_scale = _get_minimum_scale(num_steps)
+        tmin = deltas[:, :, None] * offsets[:, None, :]
+        tmax = tmin + deltas[:, :, None] * num_steps
+        tmin = torch.max(min_vals[:, None, None], tmin)
+        tmax = torch.min(max_vals[:, None, None], tmax)
+        deltas = (tmax - tmin) / num_steps
+        deltas = torch.max(deltas, torch.tensor([min_scale], device=deltas.device, dtype=deltas.dtype))
+        return deltas, torch.round(tmin / deltas)
+
+    # sweep -----------------------------------------------------------------------------------
+    def _select_best_candidates(self, deltas, offsets, st: _HistogramList, num_steps):
+        noise, best = self._estimate_clip_and_quant_noise(st, deltas, offsets, num_steps, self.p, self.gamma,
+                                                          return_best=True)
+        idx = best.long()[:, None]
+        best_delta = torch.gather(deltas.flatten(start_dim=1), 1, idx)
+        if offsets.numel() == 1:
+            return best_delta, offsets
+        return best_delta, torch.gather(offsets.flatten(start_dim=1), 1, idx)
+
+    @staticmethod
+    def _estimate_clip_and_quant_noise(stats, test_deltas, test_offsets, num_steps, p, gamma=1.0, return_best=False):
+        """Noise of every candidate, shape (hists, deltas, offsets): one kernel over the histogram."""
+        if p != 2.0:
+            raise NotImplementedError("the sweep kernel evaluates the squared error (p = 2) only")
+        st = _HistogramList.from_stats(stats)
+        hist = st.histogram.to(torch.float32).contiguous()
+        h, bins = hist.shape
+        dev = hist.device
+        edge0 = st.bin_edges[:, 0].to(torch.float32).contiguous()
+        width = (st.bin_edges[:, 1] - st.bin_edges[:, 0]).to(torch.float32).contiguous()
+        out_shape = torch.broadcast_shapes(test_deltas.shape, test_offsets.shape)
+        deltas = test_deltas.to(torch.float32).expand(out_shape).reshape(h, -1).contiguous()
+        per_hist = test_offsets.numel() != 1
+        offs = (test_offsets.to(torch.float32).expand(out_shape).reshape(h, -1) if per_hist
+                else test_offsets.to(torch.float32).reshape(1).expand(deltas.shape[1])).contiguous()
+        ncand = deltas.shape[1]
+        noise = torch.empty((h, ncand), dtype=torch.float32, device=dev)
+        best = torch.empty(h, dtype=torch.int32, device=dev)
+        with torch.cuda.device(dev):
+            rc = lib.aimet_b200_sqnr_sweep(hist.data_ptr(), edge0.data_ptr(), width.data_ptr(), deltas.data_ptr(),
+                                           offs.data_ptr(), int(per_hist), h, bins, ncand, float(num_steps),
+                                           float(gamma), noise.data_ptr(), best.data_ptr(), _lib.stream_ptr(dev))
+        _lib.check(rc)
+        noise = noise.view(out_shape)
+        return (noise, best) if return_best else noise
+
+
+class SqnrEncodingAnalyzer(_LpNormEncodingAnalyzer):
+    """Range with the lowest expected squared error; clipping noise weighted by ``gamma`` (:902-953)."""
+
+    def __init__(self, shape, num_bins: int = 2048, *, asymmetric_delta_candidates=17, symmetric_delta_candidates=101,
+                 offset_candidates=21, max_parallelism=64, gamma=3.0, histogram_growth_limit: Optional[float] = None,
+                 block_size=None):
+        super().__init__(shape=shape, num_bins=num_bins, p=2.0,
+                         asymmetric_delta_candidates=asymmetric_delta_candidates,
+                         symmetric_delta_candidates=symmetric_delta_candidates, offset_candidates=offset_candidates,
+                         max_parallelism=max_parallelism, gamma=gamma, histogram_growth_limit=histogram_growth_limit,
+                         block_size=block_size)
+
+
+class TfEnhancedEncodingAnalyzer(SqnrEncodingAnalyzer):
+    """SQNR analyzer with the legacy tf-enhanced constants: 512 bins, 17 x 21 asymmetric and 101
+    symmetric candidates, gamma 3, histogram range limited to 3x the first batch's (:956-1002)."""
+
+    _V1_HISTOGRAM_NUM_BINS = 512
+    _V1_ASYMMETRIC_DELTA_CANDIDATES = 17
+    _V1_SYMMETRIC_DELTA_CANDIDATES = 101
+    _V1_OFFSET_CANDIDATES = 21
+    _V1_GAMMA = 3.0
+    _V1_HISTOGRAM_MAX_GROWTH_RATE = 3.0
+
+    def __init__(self, shape, block_size=None):
+        super().__init__(shape=shape, num_bins=self._V1_HISTOGRAM_NUM_BINS,
+                         asymmetric_delta_candidates=self._V1_ASYMMETRIC_DELTA_CANDIDATES,
+                         symmetric_delta_candidates=self._V1_SYMMETRIC_DELTA_CANDIDATES,
+                         offset_candidates=self._V1_OFFSET_CANDIDATES, gamma=self._V1_GAMMA,
+                         histogram_growth_limit=self._V1_HISTOGRAM_MAX_GROWTH_RATE, block_size=block_size)
+
+    @classmethod
+    def set_growth_limit(cls, growth_limit: float):
+        if growth_limit < 1.0:
+            raise RuntimeError(f"Growth limit must be at least 1.0. Got {growth_limit}")
+        cls._V1_HISTOGRAM_MAX_GROWTH_RATE = growth_limit

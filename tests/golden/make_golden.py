@@ -133,9 +133,114 @@ def gen_affine():
     _save("affine_cases.pt", out)
 
 
+# --------------------------------------------------------------------------------------------
+# encoding analyzers: statistics after every update and the encodings computed from them
+# --------------------------------------------------------------------------------------------
+def _student_t(g, shape, df=3.0):
+    """Student-t samples from normals only (torch.distributions ignores generators)."""
+    z = torch.randn(shape, generator=g)
+    chi = torch.randn((*shape, int(df)), generator=g).pow(2).sum(-1)
+    return z / torch.sqrt(chi / df)
+
+
+def _analyzer_batches(kind, dtype, seed):
+    g = _gen(seed)
+    if kind == "activation":  # heavy tails + a few hot channels, later batches widen the range
+        xs = []
+        for b in range(3):
+            x = _student_t(g, (6, 64, 32))
+            x[..., [3, 17]] *= 50.0
+            xs.append((x * (1.0 + 0.7 * b)).to(dtype))
+        return xs
+    if kind == "weight":
+        w = torch.randn((12, 96), generator=g) * 0.02
+        w = w * (1 + 19 * (torch.rand((12, 96), generator=g) < 0.01))
+        return [w.to(dtype), (w * 0.5).to(dtype)]
+    if kind == "inf":
+        x = torch.randn((4, 500), generator=g)
+        x[0, 0], x[1, 1], x[2, 2] = float("inf"), -float("inf"), float("inf")
+        return [x.to(dtype), (2 * torch.randn((4, 500), generator=g)).to(dtype)]
+    if kind == "constant":
+        return [torch.full((3, 40), 1.25).to(dtype), torch.full((3, 40), 1.25).to(dtype),
+                torch.randn((3, 40), generator=g).to(dtype)]
+    if kind == "shrinking":  # later batches inside the first range: the histogram is carried over
+        x = torch.randn((8, 256), generator=g)
+        return [x.to(dtype), (0.5 * x).to(dtype), (0.25 * torch.randn((8, 256), generator=g)).to(dtype)]
+    raise ValueError(kind)
+
+
+ANALYZER_CASES = [
+    # name, analyzer, kwargs, shape, block_size, data kind, dtype
+    ("minmax_per_tensor_fp32", "minmax", {}, (), None, "activation", torch.float32),
+    ("minmax_per_tensor_bf16", "minmax", {}, (), None, "activation", torch.bfloat16),
+    ("minmax_per_channel_bf16", "minmax", {}, (12, 1), None, "weight", torch.bfloat16),
+    ("minmax_last_dim_fp32", "minmax", {}, (32,), None, "activation", torch.float32),
+    ("minmax_blockwise_fp32", "minmax", {}, (12, 3), (1, 32), "weight", torch.float32),
+    ("minmax_constant", "minmax", {}, (), None, "constant", torch.float32),
+    ("sqnr_per_tensor_fp32", "sqnr", dict(num_bins=2048), (), None, "activation", torch.float32),
+    ("sqnr_per_tensor_bf16", "sqnr", dict(num_bins=2048), (), None, "activation", torch.bfloat16),
+    ("sqnr_per_tensor_fp16", "sqnr", dict(num_bins=512), (), None, "shrinking", torch.float16),
+    ("sqnr_per_channel_fp32", "sqnr", dict(num_bins=256), (12, 1), None, "weight", torch.float32),
+    ("sqnr_blockwise_bf16", "sqnr", dict(num_bins=64), (12, 3), (1, 32), "weight", torch.bfloat16),
+    ("sqnr_inf_fp32", "sqnr", dict(num_bins=128), (), None, "inf", torch.float32),
+    ("sqnr_constant_bf16", "sqnr", dict(num_bins=32), (), None, "constant", torch.bfloat16),
+    ("sqnr_100_sym_candidates", "sqnr", dict(num_bins=2048, symmetric_delta_candidates=100), (), None, "activation", torch.bfloat16),
+    ("tfe_per_tensor_fp32", "tfe", {}, (), None, "activation", torch.float32),
+    ("tfe_per_tensor_bf16", "tfe", {}, (), None, "activation", torch.bfloat16),
+    ("tfe_last_dim_fp32", "tfe", {}, (32,), None, "activation", torch.float32),
+    ("percentile_99_fp32", "percentile", dict(num_bins=2048, percentile=99), (), None, "activation", torch.float32),
+    ("percentile_999_bf16", "percentile", dict(num_bins=2048, percentile=99.9), (), None, "activation", torch.bfloat16),
+    ("percentile_100_fp32", "percentile", dict(num_bins=100, percentile=100), (12, 1), None, "weight", torch.float32),
+    ("percentile_shrinking", "percentile", dict(num_bins=50, percentile=90), (), None, "shrinking", torch.float32),
+]
+
+ENCODING_GRIDS = [(255, False), (255, True), (15, True), (15, False), (3, True), (254, True), (65535, False)]
+
+
+def _make_ref_analyzer(kind, kwargs, shape, block):
+    if kind == "minmax":
+        return ref_ea.MinMaxEncodingAnalyzer(shape, block_size=block)
+    if kind == "sqnr":
+        return ref_ea.SqnrEncodingAnalyzer(shape, block_size=block, **kwargs)
+    if kind == "tfe":
+        return ref_ea.TfEnhancedEncodingAnalyzer(shape, block_size=block)
+    if kind == "percentile":
+        return ref_ea.PercentileEncodingAnalyzer(shape, block_size=block, **kwargs)
+    raise ValueError(kind)
+
+
+def _stats_to_plain(stats):
+    if isinstance(stats, list):
+        return [dict(histogram=h.histogram.clone(), bin_edges=h.bin_edges.clone(), min=h.min.clone(), max=h.max.clone())
+                for h in stats]
+    return dict(min=stats.min.clone(), max=stats.max.clone())
+
+
+def gen_analyzers():
+    import warnings
+
+    out = {}
+    for idx, (name, kind, kwargs, shape, block, data, dtype) in enumerate(ANALYZER_CASES):
+        batches = _analyzer_batches(data, dtype, 500 + idx)
+        an = _make_ref_analyzer(kind, kwargs, shape, block)
+        rec = dict(kind=kind, kwargs=kwargs, shape=shape, block_size=block, batches=batches, updates=[])
+        for x in batches:
+            ret = an.update_stats(x)
+            rec["updates"].append(dict(returned=_stats_to_plain(ret), merged=_stats_to_plain(an.observer.get_stats())))
+        rec["encodings"] = {}
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            for num_steps, sym in ENCODING_GRIDS:
+                mn, mx = an.compute_encodings(num_steps, sym)
+                rec["encodings"][(num_steps, sym)] = (mn.clone(), mx.clone())
+        out[name] = rec
+    _save("analyzer_cases.pt", out)
+
+
 GENERATORS = {
     "backend_vectors": gen_backend_vectors,
     "affine": gen_affine,
+    "analyzers": gen_analyzers,
 }
 
 

@@ -1,0 +1,146 @@
+"""CUDA encoding analyzers against the golden fixtures (reference outputs) and the CPU oracle."""
+
+import warnings
+
+import pytest
+import torch
+
+from conftest import assert_same, load_golden
+from oracle import encoding_analyzer as OA
+
+pytestmark = pytest.mark.gpu
+
+CASES = load_golden("analyzer_cases.pt")
+
+
+def make_analyzer(case):
+    from aimet_b200 import encoding_analyzer as EA
+
+    kind, kw, shape, block = case["kind"], case["kwargs"], case["shape"], case["block_size"]
+    if kind == "minmax":
+        return EA.MinMaxEncodingAnalyzer(shape, block_size=block)
+    if kind == "sqnr":
+        return EA.SqnrEncodingAnalyzer(shape, block_size=block, **kw)
+    if kind == "tfe":
+        return EA.TfEnhancedEncodingAnalyzer(shape, block_size=block)
+    return EA.PercentileEncodingAnalyzer(shape, block_size=block, **kw)
+
+
+def assert_stats_same(got, want, what):
+    if isinstance(want, list):
+        assert len(got) == len(want)
+        for i, w in enumerate(want):
+            g = got[i]
+            assert_same(g.histogram, w["histogram"], f"{what}[{i}].histogram")  # counts: bit-exact
+            assert_same(g.bin_edges, w["bin_edges"], f"{what}[{i}].bin_edges")
+            assert_same(g.min, w["min"], f"{what}[{i}].min")
+            assert_same(g.max, w["max"], f"{what}[{i}].max")
+    else:
+        assert_same(got.min, want["min"], f"{what}.min")  # min/max: bit-exact
+        assert_same(got.max, want["max"], f"{what}.max")
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_statistics_golden(name):
+    case = CASES[name]
+    an = make_analyzer(case)
+    for i, (x, want) in enumerate(zip(case["batches"], case["updates"])):
+        ret = an.update_stats(x.cuda())
+        assert_stats_same(ret, want["returned"], f"update {i} returned")
+        assert_stats_same(an.observer.get_stats(), want["merged"], f"update {i} merged")
+
+
+def _close_encoding(got, want, what):
+    """Encodings of the SQNR search depend on sums over 2048 bins: the arg-min can legitimately move
+    between candidates whose noise differs in the last float32 bits.  Everything else is exact."""
+    assert got.shape == want.shape and got.dtype == want.dtype, what
+    g, w = got.double().cpu(), want.double()
+    assert torch.allclose(g, w, rtol=1e-5, atol=0), f"{what}: {g.flatten()[:4]} vs {w.flatten()[:4]}"
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_encodings_golden(name):
+    case = CASES[name]
+    an = make_analyzer(case)
+    for x in case["batches"]:
+        an.update_stats(x.cuda())
+    exact = case["kind"] in ("minmax", "percentile")
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        for (num_steps, sym), (want_min, want_max) in case["encodings"].items():
+            got_min, got_max = an.compute_encodings(num_steps, sym)
+            if exact:
+                assert_same(got_min, want_min, f"min @ {num_steps},{sym}")
+                assert_same(got_max, want_max, f"max @ {num_steps},{sym}")
+            else:
+                _close_encoding(got_min, want_min, f"min @ {num_steps},{sym}")
+                _close_encoding(got_max, want_max, f"max @ {num_steps},{sym}")
+
+
+@pytest.mark.parametrize("name", sorted(n for n, c in CASES.items() if c["kind"] in ("sqnr", "tfe")))
+@pytest.mark.parametrize("grid", [(255, False), (255, True), (15, True)])
+def test_sqnr_noise_vs_oracle(name, grid):
+    """Per-candidate noise within 1e-5 relative of the oracle's float32 evaluation, and the same
+    arg-min wherever the two best candidates are further apart than that."""
+    case = CASES[name]
+    num_steps, sym = grid
+    an = make_analyzer(case)
+    for x in case["batches"]:
+        an.update_stats(x.cuda())
+    st = an.observer.get_stats()
+    deltas, offsets = an._pick_test_candidates(st, num_steps, sym)
+    noise, best = an._estimate_clip_and_quant_noise(st, deltas, offsets, num_steps, 2.0, an.gamma, return_best=True)
+
+    ostats = case["updates"][-1]["merged"]
+    kw = case["kwargs"]
+    od, oo = OA.sqnr_candidates(ostats, num_steps, sym, sym_deltas=kw.get("symmetric_delta_candidates", 101))
+    assert_same(deltas, od, "candidate deltas")      # candidate grids are elementwise float32: bit-exact
+    assert_same(offsets, oo, "candidate offsets")
+    onoise = OA.sqnr_noise(ostats, od, oo, num_steps, gamma=3.0)
+    assert torch.allclose(noise.cpu().double(), onoise.double(), rtol=1e-5, atol=0)
+    flat = onoise.flatten(start_dim=1).double()
+    top2 = flat.topk(2, dim=1, largest=False).values
+    decisive = (top2[:, 1] - top2[:, 0]) > 1e-5 * top2[:, 1].abs()
+    obest = flat.argmin(dim=1)
+    assert torch.equal(best.cpu().long()[decisive], obest[decisive])
+
+
+def test_large_counts_and_histc_rule():
+    """Counts beyond float32's exact range are accumulated as integers; the binning rule is
+    torch.histc's on this device as well as in the oracle."""
+    from aimet_b200 import encoding_analyzer as EA
+
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(1 << 22, generator=g) * 3).cuda()
+    obs = EA._HistogramObserver((), num_bins=2048)
+    st = obs.collect_stats(x)
+    ref = torch.histc(x, bins=2048, min=float(st.bin_edges[0, 0]), max=float(st.bin_edges[0, -1]))
+    assert torch.equal(st.histogram[0], ref)
+    cpu = torch.histc(x.cpu(), bins=2048, min=float(st.bin_edges[0, 0]), max=float(st.bin_edges[0, -1]))
+    assert torch.equal(st.histogram[0].cpu(), cpu)
+    assert float(st.histogram.sum()) == x.numel()
+    # all mass in one bin, > 2^24 elements: integer accumulation keeps the exact count
+    big = torch.zeros(1 << 25, dtype=torch.bfloat16, device="cuda")
+    big[0], big[1] = -1.0, 1.0
+    st = obs.collect_stats(big)
+    assert int(st.histogram[0].double().sum()) == big.numel()
+
+
+def test_errors():
+    from aimet_b200 import encoding_analyzer as EA
+
+    an = EA.MinMaxEncodingAnalyzer(())
+    with pytest.raises(EA.StatisticsNotFoundError):
+        an.compute_encodings(255, False)
+    an.update_stats(torch.randn(10).cuda())
+    with pytest.raises(ValueError):
+        an.compute_encodings(0, False)
+    with pytest.raises(RuntimeError):
+        an.update_stats(torch.randn(10))  # CPU tensor
+    with pytest.raises(RuntimeError):
+        EA.MinMaxEncodingAnalyzer((3,)).update_stats(torch.randn(10, 4).cuda())
+    sq = EA.SqnrEncodingAnalyzer(())
+    with pytest.raises(EA.StatisticsNotFoundError):
+        sq.compute_encodings(255, False)
+    with pytest.raises(ValueError):
+        EA.PercentileEncodingAnalyzer((), percentile=20)
