@@ -1,0 +1,30 @@
+"""aimet_b200 -- the quantization-simulation hot path of aimet_torch on B200 (sm_100a) kernels.
+
+* :mod:`aimet_b200.backend` -- ``quantize`` / ``dequantize`` / ``quantize_dequantize`` functionals
+  (aimet_torch's backend protocol); :func:`register_backend` plugs them into an installed aimet_torch.
+* :mod:`aimet_b200.quantizer` -- ``Quantize``, ``QuantizeDequantize``, ``Dequantize``,
+  ``GroupedBlockQuantizeDequantize`` modules with learnable ranges.
+* :mod:`aimet_b200.encoding_analyzer` -- MinMax / Percentile / SQNR / TF-enhanced analyzers.
+* :mod:`aimet_b200.seq_mse` -- SeqMSE candidate search for Linear layers.
+* :mod:`aimet_b200.distributed` -- sharded calibration and output-channel sharding helpers.
+
+Everything runs through ``libaimet_b200.so`` (``include/aimet_b200.h``); importing the package
+fails if that library has not been built (``python -m aimet_b200.build``).
+"""
+
+from . import _lib  # noqa: F401  (raises ImportError when the kernel library is missing)
+from . import backend
+from .backend import dequantize, quantize, quantize_dequantize
+
+__all__ = ["backend", "quantize", "dequantize", "quantize_dequantize", "register_backend"]
+
+
+def register_backend(name: str = "b200", select: bool = False):
+    """Register this backend with an installed ``aimet_torch`` under ``name``
+    (quantization/affine/backends/utils.py:110-114) and optionally make it the active one."""
+    from aimet_torch.quantization.affine.backends import utils as _ref_backends  # pylint: disable=import-error
+
+    _ref_backends.add_backend(name, backend)
+    if select:
+        return _ref_backends.set_backend(name)
+    return None

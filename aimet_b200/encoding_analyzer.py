@@ -43,6 +43,15 @@ def _get_minimum_scale(num_steps) -> float:
     return min(float(np.finfo(np.float32).eps), 0.01 / num_steps)
 
 
+def _div(a: torch.Tensor, b) -> torch.Tensor:
+    """``a / b`` for a Python number ``b`` with IEEE division.  PyTorch's CUDA kernels turn a division
+    by a Python scalar into a multiplication by its reciprocal, which differs from the CPU result in
+    the last bit whenever ``b`` is not a power of two; dividing by a 0-d tensor does not."""
+    if a.dtype in (torch.float16, torch.bfloat16):
+        return (a.float() / torch.tensor(float(b), dtype=torch.float32, device=a.device)).to(a.dtype)
+    return a / torch.tensor(float(b), dtype=a.dtype, device=a.device)
+
+
 @dataclass
 class _MinMaxRange:
     min: Optional[torch.Tensor] = None
@@ -268,7 +277,7 @@ class _HistogramObserver(_Observer):
         same = min_val == max_val
         lo = torch.where(same, min_val - 0.5, min_val).float()
         hi = torch.where(same, max_val + 0.5, max_val).float()
-        step = (hi - lo) / self.num_bins
+        step = _div(hi - lo, self.num_bins)
         ticks = torch.arange(0, self.num_bins + 1, device=min_val.device)
         return ticks[None, :] * step[:, None] + lo[:, None]
 
@@ -296,7 +305,7 @@ class _HistogramObserver(_Observer):
             e0, e1 = new.bin_edges[:, 0], new.bin_edges[:, -1]
             span = e1 - e0
             self._histogram_range_limit = torch.stack(
-                (e0 - span * self.growth_limit / 2, e1 + span * self.growth_limit / 2), dim=1
+                (e0 - _div(span * self.growth_limit, 2), e1 + _div(span * self.growth_limit, 2)), dim=1
             )
             return
         cur = self._state
@@ -307,7 +316,7 @@ class _HistogramObserver(_Observer):
 
         # move the accumulated counts into the bins of the new range; a source bin that straddles a
         # destination edge is split proportionally and rounded (:274-310)
-        dw = (umax - umin) / n
+        dw = _div(umax - umin, n)
         sw = cur.bin_edges[:, 1] - cur.bin_edges[:, 0]
         src = cur.bin_edges[:, :-1]
         d1 = self._bin_index(dw, umin, src)
@@ -391,14 +400,14 @@ class MinMaxEncodingAnalyzer(EncodingAnalyzer):
         min_scale = _get_minimum_scale(num_steps)
         lo = torch.clamp(stats.min, max=0)
         hi = torch.clamp(stats.max, min=0)
-        widen = min_scale * (((hi - lo) / num_steps) < min_scale)
+        widen = min_scale * (_div(hi - lo, num_steps) < min_scale)
         pos, neg = math.floor(num_steps / 2), math.ceil(num_steps / 2)
         if is_symmetric:
             hi = hi + pos * widen
             lo = lo - neg * widen
             # a 2-bit grid would waste its only positive step on symmetric data: calibrate as if it had two
             extra = 1 if num_steps == 3 else 0
-            delta = torch.maximum(hi / (pos + extra), -lo / neg)
+            delta = torch.maximum(_div(hi, pos + extra), _div(-lo, neg))
             lo = -1 * neg * delta
             hi = pos * delta
         else:
@@ -432,12 +441,12 @@ def _adjust_min_max(cmin, cmax, num_steps, is_symmetric):
     cmax = torch.maximum(cmax, torch.zeros_like(cmax))
     cmin = cmin.clamp(min=torch.finfo(cmax.dtype).min, max=0)
     cmax = cmax.clamp(min=0, max=torch.finfo(cmax.dtype).max)
-    narrow = ((cmax - cmin) / num_steps) < min_scale
+    narrow = _div(cmax - cmin, num_steps) < min_scale
     pos, neg = math.floor(num_steps / 2), math.ceil(num_steps / 2)
     if is_symmetric:
         cmin = torch.where(narrow, cmin - min_scale * neg, cmin)
         cmax = torch.where(narrow, cmax + min_scale * pos, cmax)
-        a, b = cmax / pos, -cmin / neg
+        a, b = _div(cmax, pos), _div(-cmin, neg)
         delta = torch.where(b > a, b, a)
         return -1 * neg * delta, pos * delta
     return cmin, torch.where(narrow, cmax + min_scale * num_steps, cmax)
@@ -465,7 +474,7 @@ class PercentileEncodingAnalyzer(_HistogramAnalyzer):
         # double-accumulating cumsum
         cum = torch.cumsum(st.histogram.double(), dim=1).to(st.histogram.dtype)
         total = cum[:, -1:]
-        hi_idx = torch.searchsorted(cum, total * self.percentile / 100)
+        hi_idx = torch.searchsorted(cum, _div(total * self.percentile, 100))
         lo_idx = torch.searchsorted(cum, total * (1 - self.percentile / 100))
         if self.percentile == 100:
             lo_idx = torch.zeros_like(lo_idx)
@@ -527,12 +536,12 @@ class _LpNormEncodingAnalyzer(_HistogramAnalyzer):
         """K deltas = max_delta * k / (K - 1), k = 1..K, times O offsets spread over [-steps, 0] plus the
         observed one; every pair is then clipped to the observed range (:740-776, 797-820)."""
         dev = mn.device
-        max_delta = (mx - mn).to(torch.float32) / num_steps
+        max_delta = _div((mx - mn).to(torch.float32), num_steps)
         obs_offset = torch.round(mn / max_delta)
         obs_min = max_delta * obs_offset
         obs_max = obs_min + max_delta * num_steps
         k = self.asym_delta_candidates
-        deltas = max_delta[:, None] * self._host_arange(dev, start=1, end=1 + k, step=1)[None, :] / (k - 1)
+        deltas = _div(max_delta[:, None] * self._host_arange(dev, start=1, end=1 + k, step=1)[None, :], k - 1)
         n_off = min(num_steps + 2, self.num_offset_candidates)
         step = num_steps / (n_off - 2)
         offsets = torch.round(self._host_arange(dev, start=-num_steps, end=step, step=step))
@@ -543,10 +552,10 @@ class _LpNormEncodingAnalyzer(_HistogramAnalyzer):
         """K deltas up to 2 * max|x| / steps with the single offset -steps // 2 (:778-795)."""
         dev = mn.device
         min_scale = _get_minimum_scale(num_steps)
-        max_delta = 2 * torch.max(mx, -mn).to(torch.float32) / num_steps
+        max_delta = _div(2 * torch.max(mx, -mn).to(torch.float32), num_steps)
         offsets = torch.full((1,), (-num_steps) // 2, dtype=torch.float32, device=dev)
         k = self.sym_delta_candidates
-        deltas = max_delta[:, None] * self._host_arange(dev, start=1, end=1 + k, step=1)[None, :] / (k - 1)
+        deltas = _div(max_delta[:, None] * self._host_arange(dev, start=1, end=1 + k, step=1)[None, :], k - 1)
         deltas = torch.max(deltas, torch.tensor([min_scale], dtype=torch.float32, device=dev))
         return deltas[:, :, None], offsets[:, None, None]
 
@@ -557,7 +566,7 @@ class _LpNormEncodingAnalyzer(_HistogramAnalyzer):
         tmax = tmin + deltas[:, :, None] * num_steps
         tmin = torch.max(min_vals[:, None, None], tmin)
         tmax = torch.min(max_vals[:, None, None], tmax)
-        deltas = (tmax - tmin) / num_steps
+        deltas = _div(tmax - tmin, num_steps)
         deltas = torch.max(deltas, torch.tensor([min_scale], device=deltas.device, dtype=deltas.dtype))
         return deltas, torch.round(tmin / deltas)
 

@@ -1,0 +1,601 @@
+"""Affine quantizer modules with learnable ranges, on the ``b200`` backend.
+
+Host-side mirror of aimet_torch's ``quantization/affine/quantizer.py``: ``Quantize``,
+``QuantizeDequantize``, ``Dequantize`` and ``GroupedBlockQuantizeDequantize`` with the same
+constructor overloads, ``min``/``max`` parameters, ``compute_encodings()`` calibration context and
+range accessors (``AffineQuantizerBase`` :71-838, ``Quantize`` :903-1069, ``QuantizeDequantize``
+:1072-1224, ``Dequantize`` :1227-1267, ``GroupedBlockQuantizeDequantize`` :1270-1440).  The
+parameter arithmetic (min/max -> scale/offset) stays ordinary differentiable PyTorch, so gradients
+reach ``min`` and ``max`` through autograd; the elementwise passes over the input run in the CUDA
+kernels of :mod:`aimet_b200.backend`.
+"""
+
+from __future__ import annotations
+
+import contextlib
+import math
+import warnings
+import weakref
+from collections import OrderedDict
+from itertools import chain, repeat
+from typing import Optional, Tuple
+
+import torch
+from torch import nn
+
+from . import backend
+from .encoding_analyzer import (
+    EncodingAnalyzer,
+    MinMaxEncodingAnalyzer,
+    StatisticsNotFoundError,
+    _get_minimum_scale,
+)
+
+__all__ = [
+    "AffineEncoding",
+    "AffineQuantizerBase",
+    "Quantize",
+    "QuantizeDequantize",
+    "Dequantize",
+    "GroupedBlockQuantizeDequantize",
+]
+
+
+class _SteRound(torch.autograd.Function):
+    """Round half to even with a straight-through gradient (aimet_torch/utils.py:1250-1254)."""
+
+    @staticmethod
+    def forward(ctx, x):  # pylint: disable=arguments-differ
+        return torch.round(x)
+
+    @staticmethod
+    def backward(ctx, grad):  # pylint: disable=arguments-differ
+        return grad
+
+
+def ste_round(x: torch.Tensor) -> torch.Tensor:
+    return _SteRound.apply(x)
+
+
+def _derive_qmin_qmax(*, bitwidth: int = None, num_steps: int = None, signed: bool):
+    """(backends/__init__.py:433-445)"""
+    if bitwidth is not None:
+        num_steps = 2**bitwidth - 1
+    if signed:
+        return -math.ceil(num_steps / 2), math.floor(num_steps / 2)
+    return 0, num_steps
+
+
+def _is_expandable(src, dst) -> bool:
+    if len(src) > len(dst):
+        return False
+    return all(s in (1, d) for s, d in zip(reversed(src), reversed(dst)))
+
+
+def _concretize_block_size(in_shape, p_shape, block_size):
+    in_shape = tuple(in_shape)[len(in_shape) - len(p_shape):]
+    k = len(p_shape) - len(block_size)
+    block_size = [*(1 if d > 1 else -1 for d in p_shape[:k]), *block_size]
+    return tuple(b if b != -1 else in_shape[i] // p_shape[i] for i, b in enumerate(block_size))
+
+
+def _interleave(a, b):
+    if isinstance(b, int):
+        b = [b] * len(a)
+    return tuple(chain.from_iterable(zip(a, b)))
+
+
+class AffineEncoding:
+    """Value object describing an affine grid: ``x_q = clamp(round(x / scale) - offset, qmin, qmax)``
+    (subset of quantization/affine/encoding.py:25-331 that the quantizers use)."""
+
+    def __init__(self, scale, offset, qmin, qmax, symmetry=False, block_size=None, zero_point_shift=None,
+                 producer=None):
+        self.scale, self.offset = scale, offset
+        self.qmin, self.qmax = qmin, qmax
+        self.symmetry = symmetry
+        self.block_size = block_size
+        self.zero_point_shift = zero_point_shift or 0.0
+        self.producer = producer
+
+    @property
+    def num_steps(self) -> int:
+        return self.qmax - self.qmin
+
+    @property
+    def min(self) -> torch.Tensor:
+        return (self.offset + self.qmin + self.zero_point_shift) * self.scale
+
+    @property
+    def max(self) -> torch.Tensor:
+        return (self.offset + self.qmax + self.zero_point_shift) * self.scale
+
+    @property
+    def bitwidth(self) -> int:
+        return int(math.log2(self.qmax - self.qmin + 1))
+
+    @property
+    def signed(self) -> bool:
+        return self.qmin < 0
+
+    @property
+    def mapping(self) -> str:
+        return "affine"
+
+    def to(self, *args, **kwargs):
+        return type(self)(self.scale.to(*args, **kwargs), self.offset.to(*args, **kwargs), self.qmin, self.qmax,
+                          self.symmetry, self.block_size, self.zero_point_shift, self.producer)
+
+    def quantize(self, input: torch.Tensor) -> torch.Tensor:  # pylint: disable=redefined-builtin
+        return backend.quantize(input, self.scale.to(input.dtype), self.offset.to(input.dtype), self.qmin, self.qmax,
+                                self.block_size)
+
+    def dequantize(self, input: torch.Tensor) -> torch.Tensor:  # pylint: disable=redefined-builtin
+        return backend.dequantize(input, self.scale.to(input.dtype), self.offset.to(input.dtype), self.block_size)
+
+    def quantize_dequantize(self, input: torch.Tensor) -> torch.Tensor:  # pylint: disable=redefined-builtin
+        return backend.quantize_dequantize(input, self.scale.to(input.dtype), self.offset.to(input.dtype), self.qmin,
+                                           self.qmax, self.block_size, self.zero_point_shift)
+
+
+class GroupedBlockEncoding(AffineEncoding):
+    """Blockwise grid whose block scales are integer multiples of a per-channel scale (LPBQ)."""
+
+    def __init__(self, scale, offset, bitwidth, signed, symmetry, block_size, block_grouping, decompressed_bw,
+                 per_channel_scale, zero_point_shift=None, producer=None):
+        qmin, qmax = _derive_qmin_qmax(bitwidth=bitwidth, signed=signed)
+        super().__init__(scale, offset, qmin, qmax, symmetry, block_size, zero_point_shift, producer)
+        self.block_grouping = block_grouping
+        self.decompressed_bw = decompressed_bw
+        self.per_channel_scale = per_channel_scale
+
+
+def _get_symmetric_offset(qmin, qmax, shape, dtype, device):
+    return torch.full(shape, fill_value=-round((qmin + qmax) / 2), requires_grad=False, dtype=dtype, device=device)
+
+
+def _get_scale_offset(min, max, qmin, qmax, symmetric):  # pylint: disable=redefined-builtin
+    """float32 (scale, offset) of a range (quantizer.py:869-900)."""
+    num_steps = qmax - qmin
+    if not isinstance(min, torch.Tensor):
+        min = torch.tensor(min, dtype=torch.float32)
+    if not isinstance(max, torch.Tensor):
+        max = torch.tensor(max, dtype=torch.float32)
+    out_dtype = min.dtype
+    min, max = min.to(torch.float32), max.to(torch.float32)
+    scale = (max - min) / torch.tensor(float(num_steps), device=min.device)
+    if symmetric:
+        offset = torch.full_like(min, fill_value=-round((qmin + qmax) / 2), requires_grad=False)
+    else:
+        offset = ste_round(min / scale) - qmin
+    return scale.to(out_dtype), offset.to(out_dtype)
+
+
+def _flag_extreme_min_max(curr_min, curr_max):
+    """(encoding_analyzer.py:484-498)"""
+    extreme = torch.full_like(curr_min, torch.finfo(curr_min.dtype).max)
+    if not (torch.all(torch.isfinite(curr_min)) and torch.all(torch.isfinite(curr_max))):
+        warnings.warn("Infinite or NaN values detected within input! This may skew the associated encodings")
+    if torch.any(torch.isclose(torch.abs(curr_min), extreme, rtol=0.05)) or torch.any(
+        torch.isclose(torch.abs(curr_max), extreme, rtol=0.05)
+    ):
+        warnings.warn("Extreme values detected within input! This may skew the associated encodings")
+
+
+class QuantizerBase(nn.Module):
+    """Bookkeeping shared by all quantizers: which parameters have been initialised since
+    construction and which may be overwritten by calibration (quantization/base/quantizer.py:30-306)."""
+
+    encoding_analyzer: EncodingAnalyzer
+
+    def __init__(self):
+        super().__init__()
+        self._initial_parameters = OrderedDict()
+        self._is_overwrite_allowed = OrderedDict()
+
+    def register_quantization_parameter(self, name: str, param: Optional[nn.Parameter]):
+        self.register_parameter(name, param)
+        if param is not None:
+            self._initial_parameters[name] = (weakref.ref(param), param._version)  # pylint: disable=protected-access
+
+    def is_initialized(self, name: Optional[str] = None) -> bool:
+        params = [(n, p) for n, p in self.named_parameters() if name is None or n == name]
+        return all(self._is_initialized(n, p) for n, p in params)
+
+    def _is_initialized(self, name, current) -> bool:
+        ref, version = self._initial_parameters.get(name, (None, None))
+        if ref is None:
+            return True
+        initial = ref()
+        if initial is None or current is not initial:
+            return True
+        return current._version != version  # pylint: disable=protected-access
+
+    def allow_overwrite(self, *args, **kwargs):
+        mode = kwargs.get("mode", args[0] if args else None)
+        flags = {n: mode for n in self._is_overwrite_allowed} if mode is not None else dict(kwargs)
+        unexpected = sorted(flags.keys() - self._is_overwrite_allowed.keys())
+        if unexpected:
+            raise RuntimeError(
+                f"'allow_overwrite' expected param names {sorted(self._is_overwrite_allowed)};"
+                f" got unexpected parameter names {unexpected}"
+            )
+        self._is_overwrite_allowed.update(flags)
+
+    def is_overwrite_allowed(self, name: Optional[str] = None) -> bool:
+        if name is None:
+            return any(self._is_overwrite_allowed.values())
+        return self._is_overwrite_allowed[name]
+
+    def get_extra_state(self):
+        return {
+            "is_initialized": {n: torch.tensor(self.is_initialized(n)) for n, _ in self.named_parameters()},
+        }
+
+    def set_extra_state(self, state):
+        for name, flag in state.get("is_initialized", {}).items():
+            if bool(flag) and name in self._initial_parameters:
+                self._initial_parameters.pop(name)
+
+
+class AffineQuantizerBase(QuantizerBase):
+    """Base of the affine quantizers.
+
+    ``AffineQuantizerBase(shape, bitwidth, symmetric, encoding_analyzer=None, block_size=None,
+    zero_point_shift=None)`` or ``AffineQuantizerBase(shape, qmin, qmax, symmetric, ...)``.
+    """
+
+    def __init__(self, shape, *args, **kwargs):
+        super().__init__()
+        if isinstance(shape, int):
+            shape = (shape,)
+        self.shape = tuple(shape)
+        full_args = (shape, *args)
+        args = tuple(chain(args, repeat(None, 6 - len(args))))
+        arg0 = kwargs.pop("qmin", kwargs.pop("bitwidth", args[0]))
+        arg1 = kwargs.pop("qmax", args[1])
+        if arg1 is not None and not isinstance(arg1, bool):
+            qmin, qmax = arg0, arg1
+            symmetric = kwargs.pop("symmetric", args[2])
+            if qmin is None or qmax is None or symmetric is None:
+                raise self._arg_parsing_error(full_args, kwargs)
+            encoding_analyzer = kwargs.pop("encoding_analyzer", args[3])
+            block_size = kwargs.pop("block_size", args[4])
+            zero_point_shift = kwargs.pop("zero_point_shift", args[5])
+        else:
+            bitwidth = arg0
+            symmetric = kwargs.pop("symmetric", args[1])
+            if bitwidth is None or symmetric is None:
+                raise self._arg_parsing_error(full_args, kwargs)
+            qmin, qmax = _derive_qmin_qmax(bitwidth=bitwidth, signed=symmetric)
+            encoding_analyzer = kwargs.pop("encoding_analyzer", args[2])
+            block_size = kwargs.pop("block_size", args[3])
+            zero_point_shift = kwargs.pop("zero_point_shift", args[4])
+        if kwargs:
+            raise TypeError(
+                f"{type(self).__qualname__}.__init__ got unexpected keyword argument: {', '.join(kwargs)}"
+            )
+        if qmin >= qmax:
+            raise ValueError(f"qmax should be strictly larger than qmin. Got qmax={qmax}, qmin={qmin}")
+        self.qmin, self.qmax = qmin, qmax
+        self._symmetric = symmetric
+        self.block_size = tuple(block_size) if block_size is not None else None
+        self.zero_point_shift = zero_point_shift or 0.0
+        if self.zero_point_shift not in (0.0, 0.5):
+            raise ValueError(f"zero_point_shift should be 0.0 or 0.5. Got {self.zero_point_shift}")
+        self.encoding_analyzer = encoding_analyzer or MinMaxEncodingAnalyzer(shape=self.shape, block_size=self.block_size)
+        if not _is_expandable(self.encoding_analyzer.observer.shape, self.shape):
+            raise RuntimeError(
+                f"Encoding analyzer of shape {self.encoding_analyzer.observer.shape} "
+                f"is incompatible with quantizer of shape {self.shape}."
+            )
+        self.register_quantization_parameter("min", nn.Parameter(-torch.ones(self.shape)))
+        self.register_quantization_parameter("max", nn.Parameter(torch.ones(self.shape)))
+        self._is_overwrite_allowed.update({"min": True, "max": True})
+        self._observer_hook = None  # set while compute_encodings() is active
+        self._pinned_encoding = None
+
+    def _arg_parsing_error(self, args, kwargs):
+        cls = type(self).__qualname__
+        given = ", ".join([*(type(a).__name__ for a in args), *(f"{k}={type(v).__name__}" for k, v in kwargs.items())])
+        return TypeError(
+            f"{cls}.__init__() takes (shape, bitwidth, symmetric, ...) or (shape, qmin, qmax, symmetric, ...); got ({given})"
+        )
+
+    # ---- grid properties -----------------------------------------------------------------
+    @property
+    def symmetric(self) -> bool:
+        return self._symmetric
+
+    @symmetric.setter
+    def symmetric(self, symmetric: bool):
+        self._symmetric = symmetric
+
+    @property
+    def bitwidth(self) -> int:
+        return int(math.log2(self.qmax - self.qmin + 1))
+
+    @bitwidth.setter
+    def bitwidth(self, bitwidth: int):
+        self.qmin, self.qmax = _derive_qmin_qmax(bitwidth=bitwidth, signed=self.signed)
+
+    @property
+    def signed(self) -> bool:
+        return self.qmin < 0
+
+    @signed.setter
+    def signed(self, signed: bool):
+        self.qmin, self.qmax = _derive_qmin_qmax(bitwidth=self.bitwidth, signed=signed)
+
+    # ---- range accessors (quantizer.py:287-376) ------------------------------------------
+    def get_scale(self, dtype=None) -> Optional[torch.Tensor]:
+        """``|max - min| / (qmax - qmin)``, never below the minimum scale; ``None`` before initialisation."""
+        if self._pinned_encoding is not None:
+            return self._pinned_encoding.scale.to(dtype or torch.float32)
+        if not self.is_initialized():
+            return None
+        dtype = dtype or torch.float32
+        num_steps = self.qmax - self.qmin
+        scale = (self.max.to(dtype) - self.min.to(dtype)) / torch.tensor(float(num_steps), dtype=dtype, device=self.min.device)
+        return scale.abs().clamp_min(_get_minimum_scale(num_steps)).to(dtype)
+
+    def get_offset(self, dtype=None) -> Optional[torch.Tensor]:
+        return self._get_offset(dtype=dtype)
+
+    def _get_offset(self, scale=None, dtype=None) -> Optional[torch.Tensor]:
+        if self._pinned_encoding is not None:
+            return self._pinned_encoding.offset.to(dtype or torch.float32)
+        if not self.is_initialized():
+            return None
+        dtype = dtype or torch.float32
+        if self.symmetric:
+            return _get_symmetric_offset(self.qmin, self.qmax, self.shape, dtype, self.min.device)
+        scale = scale if scale is not None else self.get_scale(dtype)
+        offset = torch.clamp(ste_round(self.min / scale) - self.qmin, -self.qmax, -self.qmin)
+        return offset.to(dtype)
+
+    def get_min(self, dtype=None) -> Optional[torch.Tensor]:
+        if self.get_scale(dtype) is None:
+            return None
+        return self.get_scale(dtype) * (self.get_offset(dtype) + self.qmin + self.zero_point_shift)
+
+    def get_max(self, dtype=None) -> Optional[torch.Tensor]:
+        if self.get_scale(dtype) is None:
+            return None
+        return self.get_scale(dtype) * (self.get_offset(dtype) + self.qmax + self.zero_point_shift)
+
+    @torch.no_grad()
+    def set_range(self, min, max):  # pylint: disable=redefined-builtin
+        """Overwrite ``min`` / ``max`` (either may be ``None`` to keep it)."""
+        if min is not None:
+            self.min.copy_(min if isinstance(min, torch.Tensor) else torch.tensor(min))
+        if max is not None:
+            self.max.copy_(max if isinstance(max, torch.Tensor) else torch.tensor(max))
+
+    def get_encodings(self) -> Optional[AffineEncoding]:
+        if self._pinned_encoding is not None:
+            return self._pinned_encoding
+        scale = self.get_scale(dtype=torch.float32)
+        if scale is None:
+            return None
+        offset = self._get_offset(scale=scale, dtype=torch.float32)
+        return AffineEncoding(scale, offset, self.qmin, self.qmax, self._symmetric, self.block_size,
+                              self.zero_point_shift, producer=self)
+
+    def _get_dummy_encoding(self) -> AffineEncoding:
+        device = self.min.device
+        return AffineEncoding(torch.ones((), device=device), torch.zeros((), device=device), self.qmin, self.qmax,
+                              self._symmetric, None, self.zero_point_shift, producer=self)
+
+    @contextlib.contextmanager
+    def _set_encodings(self, enc: Optional[AffineEncoding]):
+        prev, self._pinned_encoding = self._pinned_encoding, enc
+        try:
+            yield
+        finally:
+            self._pinned_encoding = prev
+
+    # ---- calibration (quantizer.py:591-698) ----------------------------------------------
+    @contextlib.contextmanager
+    def compute_encodings(self):
+        """Observe every input passed through the quantizer, quantizing each batch with the encodings
+        of its own statistics; on exit set ``min`` / ``max`` from the accumulated statistics."""
+        with self._compute_encodings(passthrough=False):
+            yield
+
+    @contextlib.contextmanager
+    def _compute_encodings(self, passthrough: bool = False):
+        if not any(self._is_overwrite_allowed.values()):
+            yield
+            return
+        shape = self.shape
+        dtype, device = self.min.dtype, self.min.device
+
+        def observe(input: torch.Tensor) -> torch.Tensor:  # pylint: disable=redefined-builtin
+            run = torch.Tensor.clone if passthrough else self._forward
+            if input.numel() == 0:
+                return run(input)
+            batch_stats = self.encoding_analyzer.update_stats(input)
+            dyn_min, dyn_max = self.encoding_analyzer.compute_encodings_from_stats(
+                batch_stats, self._calibration_steps(), self.symmetric
+            )
+            if self.block_size is not None:
+                dyn_min, dyn_max = dyn_min.view(shape), dyn_max.view(shape)
+            dyn_min = dyn_min.to(dtype=dtype, device=device).expand(shape)
+            dyn_max = dyn_max.to(dtype=dtype, device=device).expand(shape)
+            scale, offset = _get_scale_offset(dyn_min.to(torch.float32), dyn_max.to(torch.float32), qmin=self.qmin,
+                                              qmax=self.qmax, symmetric=self.symmetric)
+            enc = AffineEncoding(scale, offset, self.qmin, self.qmax, self.symmetric, self.block_size,
+                                 self.zero_point_shift, producer=self)
+            with self._set_encodings(enc):
+                ret = run(input)
+            if not hasattr(ret, "encoding"):
+                ret.encoding = enc
+            return ret
+
+        self.encoding_analyzer.reset_stats()
+        prev_hook, self._observer_hook = self._observer_hook, observe
+        try:
+            yield
+        finally:
+            self._observer_hook = prev_hook
+        try:
+            enc_min, enc_max = self.encoding_analyzer.compute_encodings(self._calibration_steps(), self.symmetric)
+        except StatisticsNotFoundError:
+            return
+        if self.block_size is not None:
+            enc_min, enc_max = enc_min.view(shape), enc_max.view(shape)
+        _flag_extreme_min_max(enc_min, enc_max)
+        self.set_range(enc_min if self._is_overwrite_allowed["min"] else None,
+                       enc_max if self._is_overwrite_allowed["max"] else None)
+
+    def _calibration_steps(self) -> int:
+        steps = self.qmax - self.qmin
+        return steps - 1 if self.zero_point_shift == 0.5 else steps
+
+    # ---- forward -------------------------------------------------------------------------
+    def forward(self, input: torch.Tensor) -> torch.Tensor:  # pylint: disable=redefined-builtin
+        if self._observer_hook is not None:
+            return self._observer_hook(input.as_subclass(torch.Tensor) if type(input) is not torch.Tensor else input)
+        return self._forward(input)
+
+    def _forward(self, input: torch.Tensor) -> torch.Tensor:  # pylint: disable=redefined-builtin
+        raise NotImplementedError
+
+    def _encoding_for(self, input: torch.Tensor, what: str) -> AffineEncoding:  # pylint: disable=redefined-builtin
+        enc = self.get_encodings()
+        if enc is None:
+            if input.numel() == 0:
+                return self._get_dummy_encoding()
+            raise RuntimeError(
+                f"Failed to run {what} since quantization parameters are not initialized."
+                " Please initialize the quantization parameters using `compute_encodings()`."
+            )
+        return enc
+
+    def extra_repr(self) -> str:
+        parts = [f"shape={self.shape}"]
+        if self.block_size:
+            parts.append(f"block_size={self.block_size}")
+        parts += [f"qmin={self.qmin}", f"qmax={self.qmax}", f"symmetric={self.symmetric}"]
+        if self.zero_point_shift:
+            parts.append(f"zero_point_shift={self.zero_point_shift}")
+        return ", ".join(parts)
+
+    def get_extra_state(self):
+        state = super().get_extra_state()
+        state.update(qmin=torch.tensor(self.qmin), qmax=torch.tensor(self.qmax), symmetric=torch.tensor(self.symmetric),
+                     block_size=torch.tensor(self.block_size or ()), zero_point_shift=torch.tensor(self.zero_point_shift))
+        return state
+
+    def set_extra_state(self, state):
+        super().set_extra_state(state)
+        if "qmin" in state:
+            self.qmin = int(state["qmin"])
+        if "qmax" in state:
+            self.qmax = int(state["qmax"])
+        if "symmetric" in state:
+            self.symmetric = bool(state["symmetric"])
+        if "block_size" in state:
+            self.block_size = tuple(int(b) for b in state["block_size"]) or None
+        if "zero_point_shift" in state:
+            self.zero_point_shift = float(state["zero_point_shift"])
+        self.shape = tuple(self.min.shape)
+
+
+class Quantize(AffineQuantizerBase):
+    """``out = clamp(round(input / scale) - offset, qmin, qmax)`` with scale / offset derived from the
+    learnable ``min`` / ``max``; the output carries its encoding as ``out.encoding``."""
+
+    def __init__(self, shape, *args, **kwargs):
+        super().__init__(shape, *args, **kwargs)
+        if self.zero_point_shift != 0.0:
+            raise RuntimeError("Nonzero quant shift not supported for Quantize")
+
+    def _forward(self, input: torch.Tensor) -> torch.Tensor:  # pylint: disable=redefined-builtin
+        enc = self._encoding_for(input, "Quantize")
+        out = backend.quantize(input, enc.scale, enc.offset, enc.qmin, enc.qmax, block_size=enc.block_size)
+        out.encoding = enc
+        return out
+
+
+class QuantizeDequantize(AffineQuantizerBase):
+    """Fake-quantization ``out = (clamp(round(input / scale) - offset, qmin, qmax) + offset) * scale``."""
+
+    def _forward(self, input: torch.Tensor) -> torch.Tensor:  # pylint: disable=redefined-builtin
+        enc = self._encoding_for(input, "QuantizeDequantize")
+        out = backend.quantize_dequantize(input, enc.scale, enc.offset, enc.qmin, enc.qmax, block_size=enc.block_size,
+                                          zero_point_shift=enc.zero_point_shift)
+        out.encoding = enc
+        return out
+
+
+class Dequantize(AffineQuantizerBase):
+    """``out = (input + offset) * scale``"""
+
+    def _forward(self, input: torch.Tensor) -> torch.Tensor:  # pylint: disable=redefined-builtin
+        if self.zero_point_shift != 0.0:
+            raise RuntimeError("Nonzero quant shift not supported for Dequantize")
+        enc = self._encoding_for(input, "Dequantize")
+        out = backend.dequantize(input, enc.scale, enc.offset, block_size=enc.block_size)
+        out.encoding = enc
+        return out
+
+
+class GroupedBlockQuantizeDequantize(QuantizeDequantize):
+    """Low-power blockwise quantization: every block scale is ``k * per_channel_scale`` with an integer
+    ``k`` in ``[1, 2^(decompressed_bw - bitwidth)]``, the per-channel scale being the largest block
+    scale of the group divided by that power of two (quantizer.py:1270-1440)."""
+
+    def __init__(self, shape, bitwidth: int, symmetric: bool, decompressed_bw: int,
+                 encoding_analyzer: EncodingAnalyzer = None, block_size: Optional[Tuple[int, ...]] = None,
+                 block_grouping: Optional[Tuple[int, ...]] = None):
+        super().__init__(shape, bitwidth, symmetric, encoding_analyzer, block_size)
+        self.decompressed_bw = decompressed_bw
+        self.block_grouping = tuple(block_grouping) if block_grouping is not None else tuple(1 for _ in self.shape)
+        if block_grouping is not None:
+            if len(block_grouping) != len(self.shape):
+                raise RuntimeError(f"Length of block grouping {block_grouping} must equal length of shape {shape}.")
+            for dim, group in zip(self.shape, block_grouping):
+                if group != -1 and dim % group != 0:
+                    raise RuntimeError(
+                        f"Quantizer shape dimensions must divide evenly with corresponding block "
+                        f"grouping values for shapes {shape} and block grouping {block_grouping}."
+                    )
+        if self.decompressed_bw < self.bitwidth:
+            raise RuntimeError(f"Decompressed bitwidth {decompressed_bw} cannot be smaller than self.bitwidth {bitwidth}")
+        if not symmetric:
+            raise RuntimeError("GroupedBlockQuantizeDequantize only supports symmetric quantization.")
+
+    def get_scale(self, dtype=None) -> Optional[torch.Tensor]:
+        return self._get_scale(dtype)[0]
+
+    def get_per_channel_scale(self, dtype=None) -> Optional[torch.Tensor]:
+        raw = super().get_scale(dtype)
+        return None if raw is None else self._get_per_channel_scale(raw)
+
+    def _get_scale(self, dtype=None):
+        raw = super().get_scale(dtype)
+        if raw is None:
+            return None, None
+        per_channel = self._get_per_channel_scale(raw)
+        lpbq = backend.quantize_dequantize(raw, per_channel, torch.zeros_like(per_channel), 1,
+                                           2 ** (self.decompressed_bw - self.bitwidth), self.block_grouping)
+        return lpbq, per_channel
+
+    def _get_per_channel_scale(self, raw: torch.Tensor) -> torch.Tensor:
+        pc_shape = [d // g if g != -1 else 1 for d, g in zip(raw.shape, self.block_grouping)]
+        grouping = _concretize_block_size(raw.shape, pc_shape, self.block_grouping)
+        grouped = raw.reshape(*raw.shape[: raw.dim() - len(pc_shape)], *_interleave(pc_shape, grouping))
+        group_max = torch.amax(grouped, dim=tuple(range(1, grouped.dim(), 2)))
+        return group_max / 2 ** (self.decompressed_bw - self.bitwidth)
+
+    def get_encodings(self) -> Optional[GroupedBlockEncoding]:
+        if self._pinned_encoding is not None:
+            return self._pinned_encoding
+        if not self.is_initialized():
+            return None
+        lpbq, per_channel = self._get_scale(dtype=torch.float32)
+        return GroupedBlockEncoding(lpbq, self.get_offset(dtype=torch.float32), self.bitwidth, self.signed,
+                                    self.symmetric, self.block_size, self.block_grouping, self.decompressed_bw,
+                                    per_channel, self.zero_point_shift, producer=self)

@@ -148,7 +148,7 @@ def _analyzer_batches(kind, dtype, seed):
     if kind == "activation":  # heavy tails + a few hot channels, later batches widen the range
         xs = []
         for b in range(3):
-            x = _student_t(g, (6, 64, 32))
+            x = _student_t(g, (4, 48, 32))
             x[..., [3, 17]] *= 50.0
             xs.append((x * (1.0 + 0.7 * b)).to(dtype))
         return xs
@@ -237,10 +237,57 @@ def gen_analyzers():
     _save("analyzer_cases.pt", out)
 
 
+# --------------------------------------------------------------------------------------------
+# quantizer modules: calibrate, forward, backward
+# --------------------------------------------------------------------------------------------
+QUANTIZER_CASES = [
+    # name, class, ctor kwargs, analyzer, dtype, input shape
+    ("qdq_per_tensor_asym8_fp32", "QuantizeDequantize", dict(shape=(), bitwidth=8, symmetric=False), None, torch.float32, (64, 256)),
+    ("qdq_per_channel_sym8_bf16", "QuantizeDequantize", dict(shape=(56, 1), bitwidth=8, symmetric=True), None, torch.bfloat16, (56, 128)),
+    ("qdq_blockwise_sym4_bf16", "QuantizeDequantize", dict(shape=(24, 4), bitwidth=4, symmetric=True, block_size=(1, 32)), None, torch.bfloat16, (24, 128)),
+    ("lpbq_sym4_bf16", "GroupedBlockQuantizeDequantize", dict(shape=(24, 4), bitwidth=4, symmetric=True, decompressed_bw=8, block_size=(1, 32), block_grouping=(1, -1)), None, torch.bfloat16, (24, 128)),
+    ("lpbq_sym4_fp32", "GroupedBlockQuantizeDequantize", dict(shape=(16, 8), bitwidth=4, symmetric=True, decompressed_bw=8, block_size=(1, 16), block_grouping=(1, 4)), None, torch.float32, (16, 128)),
+    ("q_per_tensor_asym8_fp32", "Quantize", dict(shape=(), bitwidth=8, symmetric=False), None, torch.float32, (32, 100)),
+    ("qdq_sqnr_asym8_fp32", "QuantizeDequantize", dict(shape=(), bitwidth=8, symmetric=False), "sqnr", torch.float32, (64, 256)),
+    ("qdq_zps_sym4_fp32", "QuantizeDequantize", dict(shape=(32, 1), bitwidth=4, symmetric=True, zero_point_shift=0.5), None, torch.float32, (32, 64)),
+    ("qdq_per_tensor_asym8_fp16", "QuantizeDequantize", dict(shape=(), bitwidth=8, symmetric=False), None, torch.float16, (32, 160)),
+    ("qdq_per_tensor_sym16_bf16", "QuantizeDequantize", dict(shape=(), bitwidth=16, symmetric=True), None, torch.bfloat16, (32, 160)),
+]
+
+
+def gen_quantizers():
+    from aimet_torch.quantization import affine as ref_affine
+
+    out = {}
+    for idx, (name, cls, kwargs, analyzer, dtype, shape) in enumerate(QUANTIZER_CASES):
+        g = _gen(900 + idx)
+        x = torch.randn(shape, generator=g) * 0.5
+        x = (x * (1 + 9 * (torch.rand(shape, generator=g) < 0.005))).to(dtype)
+        grad = torch.randn(shape, generator=g).to(dtype)
+        kw = dict(kwargs)
+        if analyzer == "sqnr":
+            kw["encoding_analyzer"] = ref_ea.SqnrEncodingAnalyzer(kw["shape"])
+        q = getattr(ref_affine, cls)(**kw)
+        with q.compute_encodings():
+            dyn = q(x)
+        rec = dict(cls=cls, kwargs=kwargs, analyzer=analyzer, x=x, grad=grad,
+                   dynamic_out=dyn.detach().as_subclass(torch.Tensor).clone(),
+                   min=q.min.detach().clone(), max=q.max.detach().clone())
+        xi = x.clone().requires_grad_(True)
+        y = q(xi)
+        y.backward(grad)
+        rec.update(out=y.detach().as_subclass(torch.Tensor).clone(), grad_x=xi.grad.clone(),
+                   grad_min=q.min.grad.clone(), grad_max=q.max.grad.clone(),
+                   scale=q.get_scale().detach().clone(), offset=q.get_offset().detach().clone())
+        out[name] = rec
+    _save("quantizer_cases.pt", out)
+
+
 GENERATORS = {
     "backend_vectors": gen_backend_vectors,
     "affine": gen_affine,
     "analyzers": gen_analyzers,
+    "quantizers": gen_quantizers,
 }
 
 
