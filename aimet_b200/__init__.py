@@ -12,11 +12,25 @@ Everything runs through ``libaimet_b200.so`` (``include/aimet_b200.h``); importi
 fails if that library has not been built (``python -m aimet_b200.build``).
 """
 
-from . import _lib  # noqa: F401  (raises ImportError when the kernel library is missing)
-from . import backend
-from .backend import dequantize, quantize, quantize_dequantize
+import importlib
 
-__all__ = ["backend", "quantize", "dequantize", "quantize_dequantize", "register_backend"]
+__all__ = [
+    "backend", "quantizer", "encoding_analyzer", "seq_mse", "distributed",
+    "quantize", "dequantize", "quantize_dequantize", "register_backend",
+]
+
+_SUBMODULES = ("_lib", "backend", "quantizer", "encoding_analyzer", "seq_mse", "distributed", "build")
+_FUNCTIONS = ("quantize", "dequantize", "quantize_dequantize")
+
+
+def __getattr__(name):
+    # Submodules load on first use so that ``python -m aimet_b200.build`` can run before the kernel
+    # library exists.  Anything else needs ``_lib`` and raises ImportError if the library is missing.
+    if name in _SUBMODULES:
+        return importlib.import_module(f"{__name__}.{name}")
+    if name in _FUNCTIONS:
+        return getattr(importlib.import_module(f"{__name__}.backend"), name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
 
 
 def register_backend(name: str = "b200", select: bool = False):
@@ -24,6 +38,7 @@ def register_backend(name: str = "b200", select: bool = False):
     (quantization/affine/backends/utils.py:110-114) and optionally make it the active one."""
     from aimet_torch.quantization.affine.backends import utils as _ref_backends  # pylint: disable=import-error
 
+    backend = importlib.import_module(f"{__name__}.backend")
     _ref_backends.add_backend(name, backend)
     if select:
         return _ref_backends.set_backend(name)

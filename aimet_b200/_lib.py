@@ -83,6 +83,8 @@ SIGNATURES = {
         _i32,
         [_vp, _vp, _vp, _vp, _lay, _i32, _i32, _i32, _i64, _i64, _f64, _vp],
     ),
+    "aimet_b200_fake_quantize": (_i32, [_vp, _vp, _vp, _vp, _lay, _i32, _i64, _i64, _vp]),
+    "aimet_b200_fake_quantize_backward": (_i32, [_vp, _vp, _vp, _vp, _lay, _i32, _i64, _i64, _vp, _vp]),
     "aimet_b200_backward_scratch_bytes": (_i64, [_lay, _i32]),
     "aimet_b200_quantize_dequantize_backward": (
         _i32,

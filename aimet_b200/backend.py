@@ -256,6 +256,9 @@ class _AffineFunction(torch.autograd.Function):
                 elif op == "dq":
                     rc = lib.aimet_b200_dequantize(x.data_ptr(), y.data_ptr(), s.data_ptr(), o.data_ptr(),
                                                    plan.layout, plan.io, plan.ct, _lib.DTYPE_CODE[plan.pt], st)
+                elif op == "fq":
+                    rc = lib.aimet_b200_fake_quantize(x.data_ptr(), y.data_ptr(), s.data_ptr(), o.data_ptr(),
+                                                      plan.layout, plan.io, qmin, qmax, st)
                 else:
                     rc = lib.aimet_b200_quantize_dequantize(x.data_ptr(), y.data_ptr(), s.data_ptr(),
                                                             o.data_ptr(), plan.layout, plan.io, plan.ct,
@@ -294,7 +297,11 @@ class _AffineFunction(torch.autograd.Function):
                           plan.ct, _lib.DTYPE_CODE[plan.pt])
                 tail = (_lib.ptr(gx), _lib.ptr(gs), _lib.ptr(go), _lib.ptr(scratch),
                         0 if scratch is None else scratch.numel(), st)
-                if ctx.op == "q":
+                if ctx.op == "fq":
+                    rc = lib.aimet_b200_fake_quantize_backward(x.data_ptr(), g.data_ptr(), s.data_ptr(), o.data_ptr(),
+                                                               plan.layout, plan.io, ctx.qmin, ctx.qmax,
+                                                               _lib.ptr(gx), st)
+                elif ctx.op == "q":
                     rc = lib.aimet_b200_quantize_backward(*common, ctx.qmin, ctx.qmax, *tail)
                 elif ctx.op == "dq":
                     rc = lib.aimet_b200_dequantize_backward(*common, *tail)
@@ -360,15 +367,46 @@ def quantize_dequantize(
     """Fake-quantization ``(clamp(round(input / scale - zps) - offset, qmin, qmax) + offset + zps) * scale``
     with straight-through gradients (torch_builtins.py:216-302).
 
-    Every mode -- with or without gradients -- evaluates the ``QuantDequantFunc`` arithmetic (true
-    division, round-half-to-even) in the reference's internal dtype.
+    Like the reference, two arithmetics exist.  When a gradient for ``scale`` or ``offset`` may be
+    needed (or for blockwise encodings, a non-zero ``zero_point_shift``, several channel axes) the
+    ``QuantDequantFunc`` chain runs: true division, round-half-to-even, every step in the internal
+    dtype.  Otherwise the reference calls ``torch.fake_quantize_per_tensor_affine`` /
+    ``..._per_channel_affine`` (torch_builtins.py:243-266): float32, multiplication by ``1 / scale``,
+    integer zero point -- and so does this backend, so results agree with the reference in both
+    modes.
     """
     if torch.onnx.is_in_onnx_export():
         return input
     block_size = _normalize_block_size(block_size)
     _validate(input, scale, offset, qmin, qmax, block_size)
     qmin, qmax = int(qmin), int(qmax)
+    zero_point_shift = zero_point_shift or 0.0
+    if _takes_fake_quantize_path(input, scale, offset, block_size, zero_point_shift):
+        return _AffineFunction.apply(input, scale.detach(), offset.detach(), "fq", qmin, qmax, 0.0, None, torch.float32)
     internal = _internal_dtype(input.dtype, qmin, qmax)
     if not _is_grid_representable(internal, qmin, qmax):
         raise RuntimeError(f"{internal} is unable to represent quantized output of range [{qmin}, {qmax}].")
-    return _AffineFunction.apply(input, scale, offset, "qdq", qmin, qmax, zero_point_shift or 0.0, block_size, internal)
+    return _AffineFunction.apply(input, scale, offset, "qdq", qmin, qmax, zero_point_shift, block_size, internal)
+
+
+def _takes_fake_quantize_path(tensor, scale, offset, block_size, zero_point_shift) -> bool:
+    """The reference's ``_fast_forward`` test plus the shape test of ``_torch_fake_quantize``
+    (torch_builtins.py:243-266, 352-431): no parameter gradient wanted, not blockwise, no shift, and
+    the parameters are per-tensor or vary along exactly one axis.  (Unlike the reference's
+    per-channel call, no host-side range check of the zero points is made -- that would force a
+    device synchronisation; symmetric and calibrated asymmetric encodings always pass it.)"""
+    if block_size is not None or zero_point_shift != 0.0 or torch.jit.is_tracing():
+        return False
+    if torch.is_grad_enabled() and (scale.requires_grad or offset.requires_grad):
+        return False
+    if tensor.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        return False
+    if scale.numel() == 1 and offset.numel() == 1:
+        return True
+    if scale.dim() > tensor.dim() or offset.dim() > tensor.dim():
+        return False
+    sshape = (1,) * (tensor.dim() - scale.dim()) + tuple(scale.shape)
+    oshape = (1,) * (tensor.dim() - offset.dim()) + tuple(offset.shape)
+    if sshape != oshape or any(d not in (1, t) for d, t in zip(sshape, tensor.shape)):
+        return False
+    return sum(1 for d in sshape if d != 1) == 1

@@ -11,7 +11,11 @@
 namespace ab {
 namespace {
 
-enum { OP_Q = 0, OP_DQ = 1, OP_QDQ = 2 };
+// OP_FQ: the arithmetic of torch.fake_quantize_per_{tensor,channel}_affine, which the reference
+// calls instead of QuantDequantFunc whenever no scale / offset gradient is needed
+// (torch_builtins.py:243-266, 335-431): out = (clamp(rint(x * (1/s)) + zp, qmin, qmax) - zp) * s
+// in float32 with the integer zero point zp = -(int)offset.
+enum { OP_Q = 0, OP_DQ = 1, OP_QDQ = 2, OP_FQ = 3 };
 
 constexpr int kFwdUnroll = 4;       // 16-byte vectors in flight per thread, forward
 
@@ -37,6 +41,7 @@ template <int CT> struct Enc {
     T r;     // correctly rounded 1 / s (float arithmetic only)
     T back;  // what is added back after clamping: o, or o + zero_point_shift
     T lo, hi;  // o + qmin, o + qmax in the internal dtype (backward clamp bounds)
+    T zp;      // -(int)o, the integer zero point of the fake-quantize arithmetic
     // float arithmetic: s is a normal number of moderate magnitude and the clamp
     // bounds are small integers, so x / s can be formed from r with an exact
     // remainder correction and rounding can use the 2^23 trick
@@ -62,6 +67,7 @@ __device__ __forceinline__ Enc<CT> load_enc(const ParamPtr &scale, const ParamPt
     e.lo = A::rnd(op_add(e.o, g.qmin));
     e.hi = A::rnd(op_add(e.o, g.qmax));
     e.r = (T)0;
+    e.zp = (T)0;
     e.fast = false;
     e.exact_int = false;
     if (CT != AB_F64) {
@@ -69,6 +75,7 @@ __device__ __forceinline__ Enc<CT> load_enc(const ParamPtr &scale, const ParamPt
         const float bound = fmaxf(fabsf((float)e.lo), fabsf((float)e.hi));
         e.fast = (as > 7.888609e-31f) && (as < 1.2676506e30f) && (bound < 4194304.0f);  // 2^-100, 2^100, 2^22
         e.r = (T)__frcp_rn((float)e.s);
+        e.zp = (T)(-(float)__float2int_rz((float)e.o));
         // all integers up to 2^(mantissa+1) are exact: 256 for bfloat16, 2048 for float16
         const float lim = CT == AB_BF16 ? 256.0f : 2048.0f;
         e.exact_int = g.exact_edges && bound <= lim && fabsf((float)e.o) <= lim && (float)e.o == rintf((float)e.o);
@@ -134,6 +141,14 @@ __device__ __forceinline__ typename Arith<CT>::T fwd_elem(typename Arith<CT>::T 
         T t = A::rnd(op_add(x, e.o));
         return A::rnd(op_mul(t, e.s));
     }
+    if (OP == OP_FQ) {
+        // the int64 cast of the reference kernel is the identity on integer-valued floats and its
+        // saturation coincides with the clamp; NaN converts to 0 on the device
+        T t = op_add(round_even<CT>(op_mul(x, e.r), e), e.zp);
+        t = (t != t) ? (T)0 : t;
+        t = t < g.qmin ? g.qmin : (t > g.qmax ? g.qmax : t);
+        return op_mul(op_sub(t, e.zp), e.s);
+    }
     T t = A::rnd(div_scale<CT>(x, e));
     if (OP == OP_QDQ && g.has_zps) t = A::rnd(op_sub(t, g.zps));
     t = round_even<CT>(t, e);
@@ -159,6 +174,12 @@ __device__ __forceinline__ typename Arith<CT>::T bwd_elem(typename Arith<CT>::T 
     using A = Arith<CT>;
     using T = typename A::T;
     dofs = (T)0;
+    if (OP == OP_FQ) {
+        T t = op_add(round_even<CT>(op_mul(x, e.r), e), e.zp);
+        t = (t != t) ? (T)0 : t;
+        ds = (T)0;
+        return ((g.qmin <= t) && (t <= g.qmax)) ? gy : (T)0;
+    }
     if (OP == OP_DQ) {
         T dx = A::rnd(op_mul(gy, e.s));
         ds = A::rnd(op_mul(gy, A::rnd(op_add(x, e.o))));
@@ -925,6 +946,14 @@ template <int IO, int CT> int dispatch_op(const Call &c, const Canon &canon, boo
         case OP_Q: return backward ? launch_backward<IO, CT, OP_Q>(c, canon) : launch_forward<IO, CT, OP_Q>(c, canon);
         case OP_DQ: return backward ? launch_backward<IO, CT, OP_DQ>(c, canon) : launch_forward<IO, CT, OP_DQ>(c, canon);
         case OP_QDQ: return backward ? launch_backward<IO, CT, OP_QDQ>(c, canon) : launch_forward<IO, CT, OP_QDQ>(c, canon);
+        case OP_FQ:
+            if constexpr (CT == AB_F32 && IO != AB_F64) {
+                if (backward && (c.gs || c.go))
+                    return fail(AB_ERR_INVALID, "fake_quantize has no scale / offset gradient");
+                return backward ? launch_backward<IO, CT, OP_FQ>(c, canon) : launch_forward<IO, CT, OP_FQ>(c, canon);
+            } else {
+                return fail(AB_ERR_UNSUPPORTED, "fake_quantize arithmetic is float32 on float32 / float16 / bfloat16 tensors");
+            }
     }
     return fail(AB_ERR_INVALID, "unknown op %d", c.op);
 }
@@ -1050,6 +1079,31 @@ extern "C" int aimet_b200_dequantize_backward(const void *x, const void *grad_y,
     c.io = io_dtype; c.ct = compute_dtype; c.pt = param_dtype;
     c.gx = grad_x; c.gs = grad_scale; c.go = grad_offset;
     c.scratch = scratch; c.scratch_bytes = scratch_bytes;
+    c.stream = static_cast<cudaStream_t>(stream);
+    return ab::dispatch(c, true);
+}
+
+extern "C" int aimet_b200_fake_quantize(const void *x, void *y, const void *scale, const void *offset,
+                                        const ab_layout *layout, int io_dtype, int64_t qmin, int64_t qmax,
+                                        void *stream) {
+    Call c{};
+    c.op = ab::OP_FQ;
+    c.x = x; c.y = y; c.scale = scale; c.offset = offset; c.layout = layout;
+    c.io = io_dtype; c.ct = AB_F32; c.pt = AB_F32;
+    c.qmin = qmin; c.qmax = qmax; c.zps = 0.0;
+    c.stream = static_cast<cudaStream_t>(stream);
+    return ab::dispatch(c, false);
+}
+
+extern "C" int aimet_b200_fake_quantize_backward(const void *x, const void *grad_y, const void *scale,
+                                                 const void *offset, const ab_layout *layout, int io_dtype,
+                                                 int64_t qmin, int64_t qmax, void *grad_x, void *stream) {
+    Call c{};
+    c.op = ab::OP_FQ;
+    c.x = x; c.gy = grad_y; c.scale = scale; c.offset = offset; c.layout = layout;
+    c.io = io_dtype; c.ct = AB_F32; c.pt = AB_F32;
+    c.qmin = qmin; c.qmax = qmax; c.zps = 0.0;
+    c.gx = grad_x;
     c.stream = static_cast<cudaStream_t>(stream);
     return ab::dispatch(c, true);
 }

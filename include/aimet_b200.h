@@ -85,6 +85,19 @@ int aimet_b200_quantize_dequantize(const void *x, void *y, const void *scale, co
                                    int param_dtype, int64_t qmin, int64_t qmax,
                                    double zero_point_shift, void *stream);
 
+/* out = (clamp(rint(x * (1 / scale)) + zp, qmin, qmax) - zp) * scale with zp = -(int)offset, all
+ * in float32: the arithmetic of torch.fake_quantize_per_tensor_affine /
+ * torch.fake_quantize_per_channel_affine, which backends.quantize_dequantize calls instead of
+ * QuantDequantFunc when neither scale nor offset needs a gradient (torch_builtins.py:243-266,
+ * _torch_fake_quantize :335-431).  scale / offset are float32; io_dtype is AB_F32, AB_F16 or
+ * AB_BF16.  The backward pass passes grad_y where rint(x / scale) + zp lies inside [qmin, qmax]. */
+int aimet_b200_fake_quantize(const void *x, void *y, const void *scale, const void *offset,
+                             const ab_layout *layout, int io_dtype, int64_t qmin, int64_t qmax,
+                             void *stream);
+int aimet_b200_fake_quantize_backward(const void *x, const void *grad_y, const void *scale,
+                                      const void *offset, const ab_layout *layout, int io_dtype,
+                                      int64_t qmin, int64_t qmax, void *grad_x, void *stream);
+
 /* Bytes of scratch the three backward entry points need for this layout. */
 int64_t aimet_b200_backward_scratch_bytes(const ab_layout *layout, int io_dtype);
 

@@ -168,3 +168,53 @@ def dequantize_backward(x, grad, scale, offset, block_size=None):
     gs = _sum_to(gs_full, s.shape).to(scale.dtype).view(scale.shape)
     go = _sum_to(gx_full, o.shape).to(offset.dtype).view(offset.shape)
     return gx, gs, go
+
+
+def takes_fake_quantize_path(x, scale, offset, block_size=None, zero_point_shift=0.0, param_grads=False) -> bool:
+    """The reference's fast-path test (torch_builtins.py:243-266 and the shape tests of
+    _torch_fake_quantize :352-431)."""
+    if block_size is not None or zero_point_shift != 0.0 or param_grads:
+        return False
+    if scale.numel() == 1 and offset.numel() == 1:
+        return True
+    if scale.dim() > x.dim():
+        return False
+    sshape = (1,) * (x.dim() - scale.dim()) + tuple(scale.shape)
+    oshape = (1,) * (x.dim() - offset.dim()) + tuple(offset.shape)
+    if sshape != oshape or any(d not in (1, t) for d, t in zip(sshape, x.shape)):
+        return False
+    return sum(1 for d in sshape if d != 1) == 1
+
+
+def fake_quantize(x, scale, offset, qmin, qmax):
+    """_torch_fake_quantize (torch_builtins.py:335-431): the reference hands the work to
+    torch.fake_quantize_per_tensor_affine / torch.fake_quantize_per_channel_affine with a float32
+    scale and the int32 zero point -offset.  Those ATen kernels evaluate, in float32,
+        out = (clamp(nearbyint(x * (1 / scale)) + zp, qmin, qmax) - zp) * scale
+    which is the formula the CUDA kernel implements; the oracle calls the same ATen function."""
+    s = scale.to(torch.float32)
+    zp = -offset.to(torch.int32)
+    if scale.numel() == 1:
+        return torch.fake_quantize_per_tensor_affine(x, s.reshape(()), zp.reshape(()), qmin, qmax)
+    sshape = (1,) * (x.dim() - scale.dim()) + tuple(scale.shape)
+    axis = [a for a, d in enumerate(sshape) if d != 1][0]
+    return torch.fake_quantize_per_channel_affine(x, s.flatten(), zp.flatten(), axis, qmin, qmax)
+
+
+def fake_quantize_formula(x, scale, offset, qmin, qmax):
+    """The same arithmetic written out (float32, parameters broadcast against x)."""
+    s = scale.to(torch.float32)
+    zp = (-offset.to(torch.int32)).to(torch.float32)
+    inv = 1.0 / s
+    q = torch.round(x.to(torch.float32) * inv) + zp
+    q = torch.where(q.isnan(), torch.zeros_like(q), q)
+    return ((q.clamp(qmin, qmax) - zp) * s).to(x.dtype)
+
+
+def fake_quantize_backward(x, grad, scale, offset, qmin, qmax):
+    """Backward of the ATen fake-quantize ops: grad where the integer code is inside the grid."""
+    s = scale.to(torch.float32)
+    zp = (-offset.to(torch.int32)).to(torch.float32)
+    q = torch.round(x.to(torch.float32) * (1.0 / s)) + zp
+    q = torch.where(q.isnan(), torch.zeros_like(q), q)
+    return torch.where((q >= qmin) & (q <= qmax), grad, torch.zeros_like(grad))

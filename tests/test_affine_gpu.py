@@ -157,8 +157,14 @@ def test_special_values_and_empty():
     B = _backend()
     x = torch.tensor([float("nan"), float("inf"), -float("inf"), 0.0, -0.0, 1e30, -1e-30, 0.25]).cuda()
     s, o = torch.tensor(0.5).cuda(), torch.tensor(-3.0).cuda()
-    assert_same(B.quantize_dequantize(x, s, o, 0, 15), O.quantize_dequantize(x.cpu(), s.cpu(), o.cpu(), 0, 15), "special")
+    # QuantDequantFunc arithmetic (a parameter wants a gradient): NaN propagates like torch.clamp
+    sg = s.clone().requires_grad_(True)
+    assert_same(B.quantize_dequantize(x, sg, o, 0, 15).detach(), O.quantize_dequantize(x.cpu(), s.cpu(), o.cpu(), 0, 15), "special")
     assert_same(B.quantize(x, s, o, 0, 15), O.quantize(x.cpu(), s.cpu(), o.cpu(), 0, 15), "special codes")
+    # fake-quantize arithmetic: what the float -> int64 cast does with NaN / inf is device-defined in
+    # ATen; the kernel follows the CUDA behaviour (saturate, NaN -> 0)
+    dev = torch.fake_quantize_per_tensor_affine(x, s, (-o).to(torch.int32), 0, 15)
+    assert_same(B.quantize_dequantize(x, s, o, 0, 15), dev.cpu(), "special, fake-quantize path")
     e = torch.empty(0, 4).cuda()
     assert B.quantize_dequantize(e, s, o, 0, 15).shape == (0, 4)
 
@@ -181,3 +187,41 @@ def test_error_contracts():
         B.quantize_dequantize(x, torch.ones(2, 2).cuda(), torch.zeros(2, 2).cuda(), 0, 15, block_size=(2, 2))
     with pytest.raises(RuntimeError):
         B.quantize(x.to(torch.bfloat16), s, o, 0, 2**16 - 1)           # grid not representable in bf16
+
+
+# ---- no parameter gradients: the reference switches to torch.fake_quantize_* arithmetic --------
+FQ_CASES = sorted(
+    n for n, c in CASES.items()
+    if c["dtype"] != torch.float64 and O.takes_fake_quantize_path(c["x"], c["scale"], c["offset"], c["block_size"], c["zero_point_shift"])
+)
+
+
+@pytest.mark.parametrize("name", FQ_CASES)
+def test_fake_quantize_path(name):
+    c = CASES[name]
+    B = _backend()
+    x = c["x"].cuda().requires_grad_(True)
+    y = B.quantize_dequantize(x, c["scale"].cuda(), c["offset"].cuda(), c["qmin"], c["qmax"])
+    want = O.fake_quantize(c["x"], c["scale"], c["offset"], c["qmin"], c["qmax"])
+    assert_same(y.detach(), want, "fake-quantize output")
+    y.backward(c["grad"].cuda())
+    assert_same(x.grad, O.fake_quantize_backward(c["x"], c["grad"], c["scale"], c["offset"], c["qmin"], c["qmax"]), "grad_x")
+    with torch.no_grad():  # parameters that require grad still take this path when grad mode is off
+        y2 = B.quantize_dequantize(c["x"].cuda(), c["scale"].cuda().requires_grad_(True), c["offset"].cuda(), c["qmin"], c["qmax"])
+    assert_same(y2, want, "no_grad output")
+    # the device's own ATen kernel agrees too
+    s32 = c["scale"].cuda().float()
+    zp = -c["offset"].cuda().to(torch.int32)
+    if s32.numel() == 1:
+        dev = torch.fake_quantize_per_tensor_affine(c["x"].cuda(), s32.reshape(()), zp.reshape(()), c["qmin"], c["qmax"])
+        assert_same(y.detach(), dev.cpu(), "device ATen kernel")
+
+
+def test_fake_quantize_large_per_channel():
+    B = _backend()
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(64, 96, 28, 28, generator=g).to(torch.bfloat16)
+    scale = torch.rand(96, 1, 1, generator=g) * 0.02 + 0.005
+    offset = torch.zeros(96, 1, 1)
+    y = B.quantize_dequantize(x.cuda(), scale.cuda(), offset.cuda(), -128, 127)
+    assert_same(y, O.fake_quantize(x, scale, offset, -128, 127), "per-channel fake-quantize")

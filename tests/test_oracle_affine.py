@@ -56,3 +56,14 @@ def test_known_answer_vectors(name, dtype):
     assert torch.equal(O.quantize_dequantize(x, scale, offset, v["qmin"], v["qmax"]), v["tensor_qdq"].to(dtype))
     gx, _, _ = O.quantize_dequantize_backward(x, torch.ones_like(x), scale, offset, v["qmin"], v["qmax"])
     assert torch.equal(gx, (~v["mask"]).to(dtype))
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_fake_quantize_formula_is_what_aten_computes(name):
+    """The float32 formula the CUDA kernel implements equals the ATen fake-quantize ops the
+    reference calls when no parameter gradient is needed."""
+    c = CASES[name]
+    if c["dtype"] == torch.float64 or not O.takes_fake_quantize_path(c["x"], c["scale"], c["offset"], c["block_size"], c["zero_point_shift"]):
+        pytest.skip("reference does not take the fake-quantize path here")
+    a = O.fake_quantize(c["x"], c["scale"], c["offset"], c["qmin"], c["qmax"])
+    assert_same(O.fake_quantize_formula(c["x"], c["scale"], c["offset"], c["qmin"], c["qmax"]), a, "formula")
