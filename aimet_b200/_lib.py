@@ -77,6 +77,7 @@ _lay = ctypes.POINTER(Layout)
 SIGNATURES = {
     "aimet_b200_version": (_i32, []),
     "aimet_b200_last_error": (ctypes.c_char_p, []),
+    "aimet_b200_launch_count": (_i64, []),
     "aimet_b200_quantize": (_i32, [_vp, _vp, _vp, _vp, _lay, _i32, _i32, _i32, _i64, _i64, _vp]),
     "aimet_b200_dequantize": (_i32, [_vp, _vp, _vp, _vp, _lay, _i32, _i32, _i32, _vp]),
     "aimet_b200_quantize_dequantize": (

@@ -2,6 +2,7 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -9,6 +10,9 @@
 namespace ab {
 
 static thread_local char g_error[512] = "";
+static std::atomic<long long> g_launches{0};
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int fail(int code, const char *fmt, ...) {
     va_list ap;
@@ -190,3 +194,4 @@ ReducePlan plan_reduce(const Canon &c, int io_dtype, bool ptr_aligned) {
 
 extern "C" int aimet_b200_version(void) { return 1; }
 extern "C" const char *aimet_b200_last_error(void) { return ab::g_error; }
+extern "C" int64_t aimet_b200_launch_count(void) { return ab::g_launches.load(std::memory_order_relaxed); }

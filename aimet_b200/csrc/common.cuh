@@ -16,6 +16,7 @@ namespace ab {
 // errors (thread-local message, C-ABI functions return the code)
 // ---------------------------------------------------------------------------
 int fail(int code, const char *fmt, ...);
+void count_launch();  // bumps the process-wide kernel-launch counter
 
 #define AB_CUDA_OK(expr)                                                                        \
     do {                                                                                        \
@@ -27,6 +28,7 @@ int fail(int code, const char *fmt, ...);
 
 #define AB_LAUNCH_OK()                                                                          \
     do {                                                                                        \
+        ::ab::count_launch();                                                                   \
         cudaError_t _e = cudaPeekAtLastError();                                                 \
         if (_e != cudaSuccess)                                                                  \
             return ::ab::fail(AB_ERR_CUDA, "kernel launch failed: %s (%s:%d)",                  \

@@ -52,6 +52,8 @@ typedef struct ab_layout {
 
 int aimet_b200_version(void);
 const char *aimet_b200_last_error(void);
+/* Number of CUDA kernels this library has launched in this process (diagnostics). */
+int64_t aimet_b200_launch_count(void);
 
 /* ------------------------------------------------------------------------- *
  * Affine functionals.

@@ -283,11 +283,71 @@ def gen_quantizers():
     _save("quantizer_cases.pt", out)
 
 
+# --------------------------------------------------------------------------------------------
+# SeqMSE: optimize_module on a Linear layer
+# --------------------------------------------------------------------------------------------
+SEQMSE_CASES = [
+    # name, dtype, (out, in), quantizer shape, block_size, bitwidth, loss_fn, num_candidates, x shape (batches first)
+    ("per_channel_int4_mse_fp32", torch.float32, (48, 64), (48, 1), None, 4, "mse", 20, (2, 24, 64)),
+    ("per_channel_int4_l1_fp32", torch.float32, (48, 64), (48, 1), None, 4, "l1", 20, (2, 24, 64)),
+    ("per_channel_int4_sqnr_fp32", torch.float32, (48, 64), (48, 1), None, 4, "sqnr", 20, (2, 24, 64)),
+    ("per_tensor_int4_mse_fp32", torch.float32, (48, 64), (), None, 4, "mse", 10, (2, 24, 64)),
+    ("blockwise_int4_mse_fp32", torch.float32, (48, 64), (48, 4), (-1, -1), 4, "mse", 20, (2, 24, 64)),
+    ("per_channel_int4_mse_bf16", torch.bfloat16, (64, 128), (64, 1), None, 4, "mse", 20, (1, 256, 128)),
+    ("per_channel_int4_mse_bf16_values_fp32", torch.float32, (64, 128), (64, 1), None, 4, "mse", 20, (1, 256, 128)),
+]
+
+
+def gen_seqmse():
+    from aimet_torch.nn import QuantizationMixin
+    from aimet_torch.quantization.affine import QuantizeDequantize
+    from aimet_torch.seq_mse import SequentialMse, SeqMseParams
+
+    out = {}
+    for idx, (name, dtype, (co, ci), qshape, block, bw, loss_fn, ncand, xshape) in enumerate(SEQMSE_CASES):
+        g = _gen(1300 + (idx if "values_fp32" not in name else idx - 1))
+        w = torch.randn(co, ci, generator=g) * 0.02
+        x = torch.randn(xshape, generator=g)
+        x[..., :2] *= 30.0
+        if dtype == torch.bfloat16 or "values_fp32" in name:
+            w, x = w.to(torch.bfloat16), x.to(torch.bfloat16)  # bf16-representable values
+        w, x = w.to(dtype), x.to(dtype)
+        linear = torch.nn.Linear(ci, co, bias=False).to(dtype)
+        with torch.no_grad():
+            linear.weight.copy_(w)
+        qlin = QuantizationMixin.from_module(linear)
+        qtz = QuantizeDequantize(shape=qshape, bitwidth=bw, symmetric=True, block_size=block)
+        qlin.param_quantizers["weight"] = qtz
+        with qtz.compute_encodings():
+            qtz(qlin.weight.data)
+        min_t, max_t = qtz.get_min().detach().clone(), qtz.get_max().detach().clone()
+        captured = []
+        orig = SequentialMse._compute_loss.__func__
+
+        def spy(cls, *a, **k):
+            r = orig(cls, *a, **k)
+            captured.append(r.detach().clone())
+            return r
+
+        SequentialMse._compute_loss = classmethod(spy)
+        try:
+            SequentialMse.optimize_module(qlin, x, x, SeqMseParams(num_batches=None, num_candidates=ncand, loss_fn=loss_fn))
+        finally:
+            SequentialMse._compute_loss = classmethod(orig)
+        nb = xshape[0]
+        losses = torch.stack([sum(captured[c * nb:(c + 1) * nb]) for c in range(ncand)])
+        out[name] = dict(dtype=dtype, w=w, x=x, qshape=qshape, block_size=block, bitwidth=bw, loss_fn=loss_fn,
+                         num_candidates=ncand, min_before=min_t, max_before=max_t, losses=losses,
+                         best=losses.min(0)[1], min_after=qtz.min.detach().clone(), max_after=qtz.max.detach().clone())
+    _save("seqmse_cases.pt", out)
+
+
 GENERATORS = {
     "backend_vectors": gen_backend_vectors,
     "affine": gen_affine,
     "analyzers": gen_analyzers,
     "quantizers": gen_quantizers,
+    "seqmse": gen_seqmse,
 }
 
 
