@@ -23,6 +23,7 @@ from torch import nn
 
 from . import _lib
 from ._lib import lib
+from .encoding_analyzer import _div
 from .quantizer import AffineQuantizerBase, QuantizeDequantize
 
 __all__ = ["SeqMseParams", "SequentialMse", "QuantizedLinear", "optimize_module"]
@@ -136,8 +137,8 @@ def linear_loss_all_candidates(x, xq, w, wq_all, loss_fn: str = "mse", lowp: boo
     if code != 0:
         raise RuntimeError(f"aimet_b200: the SeqMSE kernel gave up waiting (device status {code})")
     if kind == 2:
-        noise = out[..., 0] / m + 1e-10
-        signal = out[..., 1] / m
+        noise = _div(out[..., 0], m) + 1e-10
+        signal = _div(out[..., 1], m)
         return -(10 * torch.log10(signal / noise))
     return out[..., 0]
 
@@ -193,8 +194,8 @@ class SequentialMse:
     def _get_candidate(cls, candidate_idx, num_candidates: int, min_tensor, max_tensor):
         """Candidate i keeps (i + 1) / num_candidates of the range; the division comes first
         (seq_mse.py:360-372), which matters in the last bit."""
-        cand_max = max_tensor / num_candidates * (candidate_idx + 1)
-        cand_min = min_tensor / num_candidates * (candidate_idx + 1)
+        cand_max = _div(max_tensor, num_candidates) * (candidate_idx + 1)
+        cand_min = _div(min_tensor, num_candidates) * (candidate_idx + 1)
         return cand_min, cand_max
 
     @classmethod
