@@ -1,0 +1,237 @@
+"""Multi-GPU partitioning of the hot path: one process per GPU, ``torch.distributed`` for the plumbing.
+
+The reference is single-process; these helpers add the two partitionings the work allows, with
+results defined against the single-process computation:
+
+* **Calibration statistics** -- batches are dealt out to the ranks, every rank observes only its
+  own batches, and the statistics are combined with all-reduces: MIN / MAX for the running range,
+  SUM of integer bin counts for histograms.  For histograms the exchange has two phases (agree on
+  the range first, then bin over the common range), so the combined histogram is exactly the one a
+  single ``collect_stats`` call on the concatenation of all batches yields
+  (quantization/encoding_analyzer.py:194-211) -- not the order-dependent result of merging batch
+  after batch.  Payloads are tiny (2 values, or ``num_bins`` counters, per statistic).
+* **Per-output-channel work** (weight quantize-dequantize, SeqMSE) -- rows of the weight are split
+  across ranks, no reduction crosses rows, and an all-gather of the per-channel results (best
+  candidate index, encoding min / max) reassembles the answer.
+
+No activation ever crosses a link.  Every collective is preceded by nothing that can fault a GPU;
+a missing peer surfaces as ``PeerFailure`` (from the process group's time-out) on the host.
+"""
+
+from __future__ import annotations
+
+import datetime
+from typing import Callable, Iterable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+__all__ = [
+    "PeerFailure",
+    "shard_range",
+    "my_batches",
+    "allreduce_minmax",
+    "allreduce_counts",
+    "calibrate_minmax",
+    "calibrate_histogram",
+    "gather_rows",
+    "optimize_module_sharded",
+]
+
+
+class PeerFailure(RuntimeError):
+    """A collective did not complete because another rank failed, left or timed out."""
+
+
+def _world(group) -> Tuple[int, int]:
+    if not dist.is_available() or not dist.is_initialized():
+        return 0, 1
+    return dist.get_rank(group), dist.get_world_size(group)
+
+
+def shard_range(n: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous [lo, hi) slice of ``n`` items for ``rank``; sizes differ by at most one."""
+    base, extra = divmod(n, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def my_batches(num_batches: int, rank: int, world: int) -> List[int]:
+    """Round-robin assignment of calibration batches: batch b goes to rank b mod world."""
+    return list(range(rank, num_batches, world))
+
+
+def _collective(fn: Callable, *args, **kwargs):
+    try:
+        return fn(*args, **kwargs)
+    except (RuntimeError, dist.DistBackendError) as e:  # time-out, connection reset, peer exit
+        raise PeerFailure(f"collective failed: {e}") from e
+
+
+def check_peers(group=None, timeout_s: float = 30.0):
+    """Host-side liveness check before entering collectives (gloo: monitored barrier that names the
+    missing rank; other backends: a plain barrier under the group's own time-out)."""
+    rank, world = _world(group)
+    if world == 1:
+        return
+    if dist.get_backend(group) == "gloo":
+        _collective(dist.monitored_barrier, group=group, timeout=datetime.timedelta(seconds=timeout_s))
+    else:
+        _collective(dist.barrier, group=group)
+
+
+def allreduce_minmax(mn: torch.Tensor, mx: torch.Tensor, group=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Element-wise MIN / MAX over ranks.  16-bit statistics travel as float32 (exact) because not
+    every backend reduces them natively."""
+    rank, world = _world(group)
+    if world == 1:
+        return mn, mx
+    dt = mn.dtype
+    lo, hi = mn.to(torch.float32).contiguous(), mx.to(torch.float32).contiguous()
+    _collective(dist.all_reduce, lo, op=dist.ReduceOp.MIN, group=group)
+    _collective(dist.all_reduce, hi, op=dist.ReduceOp.MAX, group=group)
+    return lo.to(dt), hi.to(dt)
+
+
+def allreduce_counts(counts: torch.Tensor, group=None) -> torch.Tensor:
+    """Integer SUM of histogram counts over ranks (int64: exact and order-independent)."""
+    rank, world = _world(group)
+    if counts.dtype != torch.int64:
+        raise TypeError("histogram counts are exchanged as int64")
+    if world == 1:
+        return counts
+    counts = counts.contiguous()
+    _collective(dist.all_reduce, counts, op=dist.ReduceOp.SUM, group=group)
+    return counts
+
+
+# --------------------------------------------------------------------------------------------
+# calibration
+# --------------------------------------------------------------------------------------------
+def _default_minmax(x, shape, block_size, finite_only):
+    from .encoding_analyzer import _check_input, _minmax, _StatLayout
+
+    return _minmax(_StatLayout(_check_input(x), tuple(shape), block_size), finite_only)
+
+
+def _default_counts(x, shape, block_size, num_bins, lo, hi):
+    from .encoding_analyzer import _check_input, _histogram_counts, _StatLayout
+
+    return _histogram_counts(_StatLayout(_check_input(x), tuple(shape), block_size), num_bins, lo, hi)
+
+
+def calibrate_minmax(analyzer, batches: Iterable[torch.Tensor], group=None):
+    """Observe this rank's batches with a min-max analyzer and combine the ranges over all ranks.
+    Afterwards ``analyzer.compute_encodings`` gives the same result on every rank, equal to
+    observing all batches in one process."""
+    from .encoding_analyzer import _MinMaxRange
+
+    for x in batches:
+        analyzer.update_stats(x)
+    st = analyzer.observer.get_stats()
+    rank, world = _world(group)
+    if world > 1:
+        if st.min is None:
+            raise PeerFailure(f"rank {rank} observed no batch; give every rank at least one")
+        mn, mx = allreduce_minmax(st.min, st.max, group)
+        analyzer.observer.stats = _MinMaxRange(mn, mx)
+    return analyzer.observer.get_stats()
+
+
+def calibrate_histogram(analyzer, batches: Sequence[torch.Tensor], group=None, *,
+                        minmax_fn: Callable = _default_minmax, counts_fn: Callable = _default_counts):
+    """Two-phase histogram calibration of this rank's batches for a histogram-based analyzer
+    (percentile / SQNR / TF-enhanced).
+
+    Phase 1: finite min / max of every local batch, combined locally and then over ranks.
+    Phase 2: every batch is binned over the common range (integer counts, values outside the range
+    or infinite go to the edge bins); counts are summed locally and then over ranks.
+    The analyzer's observer is left holding the combined statistics.  ``minmax_fn`` / ``counts_fn``
+    compute the per-batch statistics (default: the CUDA kernels); they exist so that the exchange
+    logic can be exercised with CPU tensors.
+    """
+    from .encoding_analyzer import _HistogramList
+
+    obs = analyzer.observer
+    shape, block, nbins = obs.shape, obs.block_size, obs.num_bins
+    batches = list(batches)
+    rank, world = _world(group)
+    if not batches:
+        raise PeerFailure(f"rank {rank} has no calibration batch; give every rank at least one")
+    mn = mx = None
+    for x in batches:
+        bmn, bmx = minmax_fn(x, shape, block, True)
+        mn = bmn if mn is None else torch.minimum(mn, bmn)
+        mx = bmx if mx is None else torch.maximum(mx, bmx)
+    mn, mx = allreduce_minmax(mn, mx, group)
+    edges = obs._create_bin_edges(mn, mx)  # pylint: disable=protected-access
+    counts = None
+    for x in batches:
+        c = counts_fn(x, shape, block, nbins, edges[:, 0], edges[:, -1])
+        counts = c if counts is None else counts + c
+    counts = allreduce_counts(counts, group)
+    obs._state = _HistogramList(counts.to(torch.float32), edges, mn, mx)  # pylint: disable=protected-access
+    e0, e1 = edges[:, 0], edges[:, -1]
+    span = e1 - e0
+    obs._histogram_range_limit = torch.stack(  # pylint: disable=protected-access
+        (e0 - span * obs.growth_limit / 2, e1 + span * obs.growth_limit / 2), dim=1)
+    return obs.get_stats()
+
+
+# --------------------------------------------------------------------------------------------
+# per-output-channel work
+# --------------------------------------------------------------------------------------------
+def gather_rows(local: torch.Tensor, total_rows: int, group=None) -> torch.Tensor:
+    """Reassemble a tensor whose dim 0 was split with :func:`shard_range` (shards may differ by one
+    row, so they are padded to the longest for the all-gather)."""
+    rank, world = _world(group)
+    if world == 1:
+        return local
+    longest = -(-total_rows // world)
+    pad = longest - local.shape[0]
+    buf = torch.cat([local, local.new_zeros((pad, *local.shape[1:]))]) if pad else local.contiguous()
+    parts = [torch.empty_like(buf) for _ in range(world)]
+    _collective(dist.all_gather, parts, buf, group=group)
+    out = []
+    for r, p in enumerate(parts):
+        lo, hi = shard_range(total_rows, r, world)
+        out.append(p[: hi - lo])
+    return torch.cat(out)
+
+
+def optimize_module_sharded(quant_module, x, xq, params, group=None):
+    """SeqMSE with the output channels of the weight split across ranks.
+
+    Every rank holds the whole layer and the whole calibration input (replicated once into its own
+    memory), searches the candidates for its slice of output channels only, and the per-channel
+    winners are all-gathered so that every rank ends with the full, identical encodings.  Needs a
+    per-channel or blockwise weight quantizer (a per-tensor range couples all channels)."""
+    from .seq_mse import QuantizedLinear, SequentialMse
+
+    rank, world = _world(group)
+    qtz = quant_module.param_quantizers["weight"]
+    if world == 1:
+        return SequentialMse.optimize_module(quant_module, x, xq, params)
+    out_ch = quant_module.weight.shape[0]
+    if len(qtz.shape) == 0 or qtz.shape[0] != out_ch:
+        raise RuntimeError("output-channel sharding needs a per-channel or blockwise weight quantizer")
+    lo, hi = shard_range(out_ch, rank, world)
+    if hi == lo:
+        raise PeerFailure(f"rank {rank} received no output channel ({out_ch} channels over {world} ranks)")
+
+    # a view of the layer restricted to this rank's rows, with a quantizer of the matching shape
+    part = QuantizedLinear(quant_module.in_features, hi - lo, bias=False, device=quant_module.weight.device,
+                           dtype=quant_module.weight.dtype)
+    with torch.no_grad():
+        part.weight.copy_(quant_module.weight[lo:hi])
+    pq = type(qtz)((hi - lo, *qtz.shape[1:]), qtz.bitwidth, qtz.symmetric, block_size=qtz.block_size,
+                   zero_point_shift=qtz.zero_point_shift).to(quant_module.weight.device)
+    pq.set_range(qtz.min.detach()[lo:hi], qtz.max.detach()[lo:hi])
+    part.param_quantizers["weight"] = pq
+    best = SequentialMse.optimize_module(part, x, xq, params)
+
+    new_min = gather_rows(pq.min.detach(), out_ch, group)
+    new_max = gather_rows(pq.max.detach(), out_ch, group)
+    qtz.set_range(new_min, new_max)
+    SequentialMse._freeze_quantizer_encoding(qtz)  # pylint: disable=protected-access
+    return gather_rows(best.reshape(hi - lo, -1), out_ch, group)

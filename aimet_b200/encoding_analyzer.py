@@ -196,8 +196,8 @@ def _run_histogram(lay: _StatLayout, num_bins: int, lo, hi, below, above):
     return counts
 
 
-def _histogram(lay: _StatLayout, num_bins: int, lo: torch.Tensor, hi: torch.Tensor) -> torch.Tensor:
-    """float32 [count, num_bins] histogram of the observed tensor over [lo, hi] per statistic, values
+def _histogram_counts(lay: _StatLayout, num_bins: int, lo: torch.Tensor, hi: torch.Tensor) -> torch.Tensor:
+    """int64 [count, num_bins] histogram of the observed tensor over [lo, hi] per statistic, values
     below / above the range (including -inf / +inf) added to the first / last bin.  The outlier
     comparison happens in the observed tensor's dtype, like the reference's ``input < edge``."""
     if lay.x.dtype == torch.float64:
@@ -208,11 +208,15 @@ def _histogram(lay: _StatLayout, num_bins: int, lo: torch.Tensor, hi: torch.Tens
     below = lo.to(lay.x.dtype).to(torch.float32)
     above = hi.to(lay.x.dtype).to(torch.float32)
     try:
-        counts = _run_histogram(lay, num_bins, lo, hi, below, above)
+        return _run_histogram(lay, num_bins, lo, hi, below, above)
     except NotImplementedError:
         lay.densify()
-        counts = _run_histogram(lay, num_bins, lo, hi, below, above)
-    return counts.to(torch.float32)
+        return _run_histogram(lay, num_bins, lo, hi, below, above)
+
+
+def _histogram(lay: _StatLayout, num_bins: int, lo: torch.Tensor, hi: torch.Tensor) -> torch.Tensor:
+    """The same as float32, the dtype the reference keeps histograms in (exact below 2^24)."""
+    return _histogram_counts(lay, num_bins, lo, hi).to(torch.float32)
 
 
 # --------------------------------------------------------------------------------------------

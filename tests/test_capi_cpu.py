@@ -1,0 +1,103 @@
+"""CPU-only checks: the C-ABI library loads, exports what the header declares, and the host-side
+logic (argument validation, dtype rules, layout planning) behaves like the reference's."""
+
+import os
+import re
+
+import pytest
+import torch
+
+from conftest import ROOT
+from oracle import affine as O
+
+
+def _header_symbols():
+    text = open(os.path.join(ROOT, "include", "aimet_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(aimet_b200_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from aimet_b200 import _lib
+
+    names = _header_symbols()
+    assert len(names) >= 20
+    for name in names:
+        assert hasattr(_lib.lib, name), f"{name} is declared in the header but not exported"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+    assert sorted(_lib.SIGNATURES) == names
+    assert _lib.lib.aimet_b200_version() >= 1
+
+
+def test_layout_errors_and_scratch_queries_without_a_gpu():
+    from aimet_b200 import _lib
+
+    lib = _lib.lib
+    bad = _lib.make_layout([6, 8], [4, 8])  # 4 does not divide 6
+    assert lib.aimet_b200_backward_scratch_bytes(bad, _lib.AB_F32) == _lib.AB_ERR_INVALID
+    assert "does not divide" in _lib.last_error()
+    # the query is an upper bound over the 16-byte-vector and the scalar kernel: rows of 4096 are
+    # reduced in-kernel by the vector kernel but cut into four 1024-element chunks by the scalar one
+    assert lib.aimet_b200_backward_scratch_bytes(_lib.make_layout([14336, 4096], [1, 4096]), _lib.AB_BF16) == 14336 * 4 * 16
+    assert lib.aimet_b200_backward_scratch_bytes(_lib.make_layout([14336, 4096], [1, 64]), _lib.AB_BF16) == 0
+    # per-tensor: one partial (two doubles) per 1024-vector chunk
+    n = lib.aimet_b200_backward_scratch_bytes(_lib.make_layout([4096, 4096], [4096, 4096]), _lib.AB_F32)
+    assert n == (4096 * 4096 // 1024) * 16  # the scalar path (1024-element chunks) is the upper bound
+    assert lib.aimet_b200_backward_scratch_bytes(_lib.make_layout([0, 4], [1, 4]), _lib.AB_F32) == 0
+    assert lib.aimet_b200_seqmse_scratch_bytes(8192, 4096, 4096, 20) == 32 * 20 * 4096 * 2 * 4
+    with pytest.raises(RuntimeError):
+        _lib.make_layout([1] * 9, [1] * 9)
+
+
+def test_cpu_tensors_are_refused():
+    from aimet_b200 import backend as B
+    from aimet_b200 import encoding_analyzer as EA
+
+    x, s, o = torch.randn(4, 4), torch.tensor(0.1), torch.tensor(0.0)
+    for fn, args in ((B.quantize, (0, 15)), (B.quantize_dequantize, (0, 15)), (B.dequantize, ())):
+        with pytest.raises(RuntimeError, match="no CPU fallback"):
+            fn(x, s, o, *args)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        EA.MinMaxEncodingAnalyzer(()).update_stats(x)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("grid", [(0, 15), (-8, 7), (0, 255), (-128, 127), (0, 65535), (-(2**31), 2**31 - 1), (0, 31), (0, 63)])
+def test_internal_dtype_rule_matches_oracle(dtype, grid):
+    from aimet_b200 import backend as B
+
+    assert B._internal_dtype(dtype, *grid) == O.internal_dtype(dtype, *grid)
+    assert B._is_grid_representable(dtype, *grid) == O.grid_representable(dtype, *grid)
+
+
+def test_param_blocks_and_fast_path_selection():
+    from aimet_b200 import backend as B
+
+    assert B._param_blocks((4, 6, 5, 7), (6, 1, 1), None) == (4, 1, 5, 7)
+    assert B._param_blocks((8, 12), (4, 3), (2, 4)) == (2, 4)
+    assert B._param_blocks((6, 2, 8, 10), (2, 2, 5), (1, -1, 2)) == (6, 1, 4, 2)
+    assert B._param_blocks((3, 5), (), None) == (3, 5)
+    x = torch.zeros(4, 6, 5)
+    s1, s2 = torch.ones(6, 1), torch.ones(4, 1, 5)
+    for scale, block, zps in ((torch.ones(()), None, 0.0), (s1, None, 0.0), (s2, None, 0.0), (s1, (1, 1), 0.0), (s1, None, 0.5)):
+        assert B._takes_fake_quantize_path(x, scale, torch.zeros_like(scale), block, zps) == O.takes_fake_quantize_path(
+            x, scale, torch.zeros_like(scale), block, zps)
+    assert not B._takes_fake_quantize_path(x, s1.requires_grad_(True), torch.zeros(6, 1), None, 0.0)
+
+
+def test_quantizer_constructor_contracts():
+    from aimet_b200 import quantizer as Q
+
+    q = Q.QuantizeDequantize((3, 1), 8, True)
+    assert (q.qmin, q.qmax, q.bitwidth, q.signed, q.symmetric) == (-128, 127, 8, True, True)
+    q = Q.QuantizeDequantize((), qmin=0, qmax=15, symmetric=False)
+    assert q.bitwidth == 4 and not q.signed and not q.is_initialized()
+    assert q.get_scale() is None and q.get_encodings() is None
+    with pytest.raises(TypeError):
+        Q.QuantizeDequantize((), 8, False, bogus=1)
+    with pytest.raises(TypeError):
+        Q.QuantizeDequantize(())
+    with pytest.raises(RuntimeError):
+        Q.QuantizeDequantize((3,), 8, False, encoding_analyzer=__import__("aimet_b200.encoding_analyzer", fromlist=["x"]).MinMaxEncodingAnalyzer((4,)))
+    with pytest.raises(RuntimeError):
+        q.allow_overwrite(scale=False)
