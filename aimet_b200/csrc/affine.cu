@@ -6,6 +6,8 @@
 // reference (quantization/affine/backends/torch_builtins.py:588-831) step by
 // step, including the re-rounding to the internal dtype after every step when
 // that dtype is float16 / bfloat16.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace ab {
@@ -1104,6 +1106,81 @@ extern "C" int aimet_b200_fake_quantize_backward(const void *x, const void *grad
     c.io = io_dtype; c.ct = AB_F32; c.pt = AB_F32;
     c.qmin = qmin; c.qmax = qmax; c.zps = 0.0;
     c.gx = grad_x;
+    c.stream = static_cast<cudaStream_t>(stream);
+    return ab::dispatch(c, true);
+}
+
+// ---------------------------------------------------------------------------
+// Quantize-dequantize backward for hosts that may not allocate device memory.
+//
+// The partial sums of the scale / offset gradients normally live in a scratch
+// buffer the caller allocates.  A caller that runs inside someone else's memory
+// budget -- an operator plugged into a serving runtime whose execute hook must
+// not touch the allocator, a worker that has handed all of its memory to a
+// pool it does not own -- cannot provide one.  For them the partial sums go to
+// the fixed array below, which every GPU that loads this library holds until
+// the process exits.
+//
+// The array is shared by all calls on a device and keeps whatever the last call
+// left in it.  Nothing in it has to start at zero: every slot the finishing
+// kernel reads was written by the pass before it in the same call.  Two calls
+// whose kernels overlap on the GPU (different streams) would write the same
+// slots and race; issue them on one stream or order them yourself.
+// ---------------------------------------------------------------------------
+namespace ab {
+namespace {
+
+constexpr int64_t kFixedScratchBytes = 1 << 20;  // 65536 partial (scale, offset) pairs
+static __device__ __align__(256) unsigned char g_fixed_scratch[kFixedScratchBytes];
+
+// Device address of g_fixed_scratch for the current device.  In host code the array's name is
+// only a handle; the address a kernel can use comes from cudaGetSymbolAddress, looked up once per
+// device with that device current.
+int fixed_scratch_ptr(void **out) {
+    static void *ptrs[64] = {};
+    static std::mutex lock;
+    int dev = 0;
+    AB_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(AB_ERR_UNSUPPORTED, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> guard(lock);
+    if (!ptrs[dev]) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_fixed_scratch);
+        if (e != cudaSuccess || !p)
+            return fail(AB_ERR_CUDA, "cudaGetSymbolAddress(fixed scratch) failed on device %d: %s", dev,
+                        cudaGetErrorString(e));
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return AB_OK;
+}
+
+}  // namespace
+}  // namespace ab
+
+extern "C" int64_t aimet_b200_fixed_scratch_capacity(void) { return ab::kFixedScratchBytes; }
+
+extern "C" int aimet_b200_quantize_dequantize_backward_fixed_scratch(
+    const void *x, const void *grad_y, const void *scale, const void *offset, const ab_layout *layout,
+    int io_dtype, int compute_dtype, int param_dtype, int64_t qmin, int64_t qmax, double zero_point_shift,
+    void *grad_x, void *grad_scale, void *grad_offset, void *stream) {
+    const int64_t need = aimet_b200_backward_scratch_bytes(layout, io_dtype);
+    if (need < 0) return (int)need;
+    if (need > ab::kFixedScratchBytes)
+        return ab::fail(AB_ERR_SCRATCH,
+                        "this layout needs %lld bytes of reduction scratch but the built-in buffer holds %lld; "
+                        "use aimet_b200_quantize_dequantize_backward with a caller-provided buffer",
+                        (long long)need, (long long)ab::kFixedScratchBytes);
+    void *scratch = nullptr;
+    int rc = ab::fixed_scratch_ptr(&scratch);
+    if (rc != AB_OK) return rc;
+    Call c{};
+    c.op = ab::OP_QDQ;
+    c.x = x; c.gy = grad_y; c.scale = scale; c.offset = offset; c.layout = layout;
+    c.io = io_dtype; c.ct = compute_dtype; c.pt = param_dtype;
+    c.qmin = qmin; c.qmax = qmax; c.zps = zero_point_shift;
+    c.gx = grad_x; c.gs = grad_scale; c.go = grad_offset;
+    c.scratch = scratch; c.scratch_bytes = ab::kFixedScratchBytes;
     c.stream = static_cast<cudaStream_t>(stream);
     return ab::dispatch(c, true);
 }

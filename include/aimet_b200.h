@@ -127,6 +127,22 @@ int aimet_b200_dequantize_backward(const void *x, const void *grad_y, const void
                                    void *grad_scale, void *grad_offset, void *scratch,
                                    int64_t scratch_bytes, void *stream);
 
+/* No counterpart in the reference.  Same computation and results as
+ * aimet_b200_quantize_dequantize_backward, for callers that cannot hand over a scratch buffer
+ * because they are not allowed to allocate device memory where they run (an operator inside a
+ * serving runtime that owns the allocator, a worker whose memory is all committed to a pool).
+ * The reduction scratch is a fixed array inside the library instead:
+ * aimet_b200_fixed_scratch_capacity() bytes (1 MiB), resident on every GPU that loads the library.
+ * Layouts whose aimet_b200_backward_scratch_bytes() exceeds that are refused with AB_ERR_SCRATCH.
+ * The first call on a device looks up the array's device address (a host-side runtime query, no
+ * allocation); make that first call before starting any stream capture.  All calls on a device
+ * share the array: calls whose kernels overlap on the GPU race, so keep them on one stream. */
+int64_t aimet_b200_fixed_scratch_capacity(void);
+int aimet_b200_quantize_dequantize_backward_fixed_scratch(
+    const void *x, const void *grad_y, const void *scale, const void *offset, const ab_layout *layout,
+    int io_dtype, int compute_dtype, int param_dtype, int64_t qmin, int64_t qmax,
+    double zero_point_shift, void *grad_x, void *grad_scale, void *grad_offset, void *stream);
+
 /* ------------------------------------------------------------------------- *
  * Calibration statistics.  The layout must reduce to (outer, channel, inner):
  * one statistic per parameter element, taken over everything that shares it.

@@ -45,6 +45,7 @@ def test_layout_errors_and_scratch_queries_without_a_gpu():
     assert n == (4096 * 4096 // 1024) * 16  # the scalar path (1024-element chunks) is the upper bound
     assert lib.aimet_b200_backward_scratch_bytes(_lib.make_layout([0, 4], [1, 4]), _lib.AB_F32) == 0
     assert lib.aimet_b200_seqmse_scratch_bytes(8192, 4096, 4096, 20) == 32 * 20 * 4096 * 2 * 4
+    assert lib.aimet_b200_fixed_scratch_capacity() == 1 << 20
     with pytest.raises(RuntimeError):
         _lib.make_layout([1] * 9, [1] * 9)
 
