@@ -298,6 +298,82 @@ __device__ __forceinline__ void bwd_pair(typename Arith<CT>::T &xa, typename Ari
 }
 
 // ---------------------------------------------------------------------------
+// Straight-line fast paths for a whole 16-byte vector sharing one parameter pair.
+// Preconditions (checked once per vector by the caller): float arithmetic,
+// Enc::fast (moderate scale, clamp bounds below 2^22), no zero-point shift, an
+// integer offset, and for a 16-bit internal dtype Enc::exact_int.  Under these
+//   * x / s comes from the exact-remainder form (div_scale_f32, no branches);
+//   * t = v + 1.5*2^23 is the integer nearest to v (ties to even) plus the magic
+//     constant, and t - (1.5*2^23 + o) is round(v) - o in one exact subtraction
+//     (both operands are integers below 2^24); values of |v| >= 2^22 come out
+//     inexact but still far outside the clamp range, which is all that is
+//     observable of them;
+//   * integer sums need no re-rounding in the 16-bit internal dtypes.
+// ---------------------------------------------------------------------------
+constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+
+template <int CT> __device__ __forceinline__ bool vec_fast_ok(const Enc<CT> &e, const Grid<typename Arith<CT>::T> &g) {
+    if (CT == AB_F64) return false;
+    const bool int_offset = (float)e.o == rintf((float)e.o);
+    const bool lowp_ok = (CT == AB_F32) || e.exact_int;
+    return e.fast && !g.has_zps && int_offset && lowp_ok;
+}
+
+template <int CT, int OP, int NV>
+__device__ __forceinline__ void fwd_vec_fast(float (&f)[NV], const Enc<CT> &e, const Grid<float> &g) {
+    using A = Arith<CT>;
+    const float s = (float)e.s, r = (float)e.r, o = (float)e.o;
+    const float c_sub = __fadd_rn(kMagic, o);  // exact: |o| < 2^22
+#pragma unroll
+    for (int i = 0; i < NV; i += 2) {
+        float a = div_scale_f32(f[i], s, r, true), b = div_scale_f32(f[i + 1], s, r, true);
+        A::rnd2(a, b);
+        a = __fsub_rn(__fadd_rn(a, kMagic), c_sub);
+        b = __fsub_rn(__fadd_rn(b, kMagic), c_sub);
+        a = clamp_prop(a, g.qmin, g.qmax);
+        b = clamp_prop(b, g.qmin, g.qmax);
+        if (OP == OP_QDQ) {
+            a = __fmul_rn(__fadd_rn(a, o), s);
+            b = __fmul_rn(__fadd_rn(b, o), s);
+        }
+        f[i] = a;
+        f[i + 1] = b;
+    }
+}
+
+template <int CT, bool WANT_O, int NV>
+__device__ __forceinline__ void bwd_vec_fast(float (&x)[NV], const float (&gy)[NV], const Enc<CT> &e,
+                                             const Grid<float> &g, float &acc_s, float &acc_o) {
+    using A = Arith<CT>;
+    const float s = (float)e.s, r = (float)e.r, o = (float)e.o;
+    const float c_sub = __fadd_rn(kMagic, o);
+    const float lo = (float)e.lo, hi = (float)e.hi;
+#pragma unroll
+    for (int i = 0; i < NV; i += 2) {
+        float sa = div_scale_f32(x[i], s, r, true), sb = div_scale_f32(x[i + 1], s, r, true);
+        A::rnd2(sa, sb);
+        const float ta = __fadd_rn(sa, kMagic), tb = __fadd_rn(sb, kMagic);
+        const float ra = __fsub_rn(ta, kMagic), rb = __fsub_rn(tb, kMagic);  // round(x / s)
+        const float qa = __fsub_rn(ta, c_sub), qb = __fsub_rn(tb, c_sub);    // round(x / s) - o
+        const bool ina = (g.qmin <= qa) && (qa <= g.qmax);
+        const bool inb = (g.qmin <= qb) && (qb <= g.qmax);
+        float da = __fmul_rn(gy[i], ina ? __fsub_rn(ra, sa) : clamp_prop(ra, lo, hi));
+        float db = __fmul_rn(gy[i + 1], inb ? __fsub_rn(rb, sb) : clamp_prop(rb, lo, hi));
+        A::rnd2(da, db);
+        acc_s += da;
+        acc_s += db;
+        if (WANT_O) {
+            float oa = __fmul_rn(gy[i], s), ob = __fmul_rn(gy[i + 1], s);
+            A::rnd2(oa, ob);
+            acc_o += ina ? 0.0f : oa;
+            acc_o += inb ? 0.0f : ob;
+        }
+        x[i] = ina ? gy[i] : 0.0f;
+        x[i + 1] = inb ? gy[i + 1] : 0.0f;
+    }
+}
+
+// ---------------------------------------------------------------------------
 // forward kernels
 // ---------------------------------------------------------------------------
 struct FwdArgs {
@@ -341,8 +417,17 @@ __global__ void __launch_bounds__(kThreads) k_fwd_oci(FwdArgs a) {
                 constexpr int NV = 16 / (int)sizeof(E);
                 T f[NV];
                 VecCvt<T, E>::unpack(xv[u], f);
+                bool done = false;
+                if constexpr (CT != AB_F64 && NV >= 2 && (OP == OP_QDQ || OP == OP_Q)) {
+                    if (vec_fast_ok<CT>(e, g)) {
+                        fwd_vec_fast<CT, OP, NV>(f, e, g);
+                        done = true;
+                    }
+                }
+                if (!done) {
 #pragma unroll
-                for (int i = 0; i + 1 < NV; i += 2) fwd_pair<CT, OP>(f[i], f[i + 1], e, g);
+                    for (int i = 0; i + 1 < NV; i += 2) fwd_pair<CT, OP>(f[i], f[i + 1], e, g);
+                }
                 VecCvt<T, E>::pack(f, yv);
             } else {
 #pragma unroll
@@ -360,6 +445,86 @@ __global__ void __launch_bounds__(kThreads) k_fwd_oci(FwdArgs a) {
             if (v >= nvec) continue;
             Enc<CT> e = load_enc<CT>(a.scale, a.offset, a.cm.of(v), g);
             yp[v] = C::store(fwd_elem<CT, OP>(C::load(xp[v]), e, g));
+        }
+    }
+}
+
+// Forward over runs of elements that share a parameter: a group of threads per run, each thread
+// loading its parameter pair once and streaming several 16-byte vectors of the run.
+struct FwdSegArgs {
+    const void *x;
+    void *y;
+    ParamPtr scale, offset;
+    ChanMap cm;
+    int64_t seg_len, nseg, nchunk;
+    int group;
+    double qmin, qmax, zps;
+    int exact_edges;
+};
+
+template <int IO, int CT, int OP>
+__global__ void __launch_bounds__(kThreads, 5) k_fwd_seg(FwdSegArgs a) {
+    using E = typename Elem<IO>::type;
+    using A = Arith<CT>;
+    using T = typename A::T;
+    constexpr int NV = 16 / (int)sizeof(E);
+    constexpr int U = 4;
+    const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0, a.exact_edges};
+    const Vec16<E> *__restrict__ xp = static_cast<const Vec16<E> *>(a.x);
+    Vec16<E> *__restrict__ yp = static_cast<Vec16<E> *>(a.y);
+
+    const int G = a.group;
+    const int64_t s = (int64_t)blockIdx.x * (kThreads / G) + threadIdx.x / G;
+    const int lane = threadIdx.x % G;
+    if (s >= a.nseg) return;
+    int64_t ts = s, k = 0;
+    if (a.nchunk > 1) {
+        if (a.cm.narrow) {
+            ts = (uint32_t)s / (uint32_t)a.nchunk;
+            k = (uint32_t)s - (uint32_t)ts * (uint32_t)a.nchunk;
+        } else {
+            ts = s / a.nchunk;
+            k = s - ts * a.nchunk;
+        }
+    }
+    const int64_t start = ts * a.cm.I + k * a.seg_len;
+    int64_t len = a.cm.I - k * a.seg_len;
+    if (len > a.seg_len) len = a.seg_len;
+    int64_t param;
+    if (a.cm.C == 1)
+        param = 0;
+    else if (!a.cm.wrap)
+        param = ts;
+    else
+        param = a.cm.narrow ? (int64_t)((uint32_t)ts % (uint32_t)a.cm.C) : ts % a.cm.C;
+    const Enc<CT> e = load_enc<CT>(a.scale, a.offset, param, g);
+    const bool fast_ok = vec_fast_ok<CT>(e, g);
+    (void)fast_ok;
+    const int64_t nv = len / NV, v0 = start / NV;
+    for (int64_t v = lane; v < nv; v += (int64_t)U * G) {
+        Vec16<E> xv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (v + (int64_t)u * G < nv) xv[u] = xp[v0 + v + (int64_t)u * G];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (v + (int64_t)u * G >= nv) continue;
+            T f[NV];
+            VecCvt<T, E>::unpack(xv[u], f);
+            bool done = false;
+            if constexpr (CT != AB_F64 && NV >= 2 && (OP == OP_QDQ || OP == OP_Q)) {
+                if (fast_ok) {
+                    fwd_vec_fast<CT, OP, NV>(f, e, g);
+                    done = true;
+                }
+            }
+            if (!done) {
+#pragma unroll
+                for (int i = 0; i + 1 < NV; i += 2) fwd_pair<CT, OP>(f[i], f[i + 1], e, g);
+            }
+            Vec16<E> yv;
+            VecCvt<T, E>::pack(f, yv);
+            yp[v0 + v + (int64_t)u * G] = yv;
         }
     }
 }
@@ -422,7 +587,7 @@ template <int CT> __device__ __forceinline__ double finalize(double v) {
 // One group of `group` threads per pseudo-segment; a pseudo-segment is a
 // contiguous run of elements that share one parameter.
 template <int IO, int CT, int OP, bool VECT, bool WANT_O>
-__global__ void __launch_bounds__(kThreads) k_bwd_seg(BwdArgs a) {
+__global__ void __launch_bounds__(kThreads, 4) k_bwd_seg(BwdArgs a) {
     using E = typename Elem<IO>::type;
     using A = Arith<CT>;
     using T = typename A::T;
@@ -442,14 +607,29 @@ __global__ void __launch_bounds__(kThreads) k_bwd_seg(BwdArgs a) {
     T acc_s = 0, acc_o = 0;
     int64_t param = 0;
     if (valid) {
-        const int64_t ts = s / a.nchunk;
-        const int64_t k = s - ts * a.nchunk;
+        // pseudo-segment -> (true segment, chunk); 64-bit divisions are avoided where they can be
+        int64_t ts = s, k = 0;
+        if (a.nchunk > 1) {
+            if (a.cm.narrow) {
+                ts = (uint32_t)s / (uint32_t)a.nchunk;
+                k = (uint32_t)s - (uint32_t)ts * (uint32_t)a.nchunk;
+            } else {
+                ts = s / a.nchunk;
+                k = s - ts * a.nchunk;
+            }
+        }
         const int64_t start = ts * a.cm.I + k * a.seg_len;
         int64_t len = a.cm.I - k * a.seg_len;
         if (len > a.seg_len) len = a.seg_len;
-        param = a.cm.wrap ? ts % a.cm.C : ts;
-        if (a.cm.C == 1) param = 0;
+        if (a.cm.C == 1)
+            param = 0;
+        else if (!a.cm.wrap)
+            param = ts;
+        else
+            param = a.cm.narrow ? (int64_t)((uint32_t)ts % (uint32_t)a.cm.C) : ts % a.cm.C;
         const Enc<CT> e = load_enc<CT>(a.scale, a.offset, param, g);
+        const bool fast_ok = vec_fast_ok<CT>(e, g);
+        (void)fast_ok;
         const int64_t nv = len / VEC;
         const int64_t v0 = start / VEC;
         for (int64_t v = lane; v < nv; v += 2 * (int64_t)G) {
@@ -467,9 +647,18 @@ __global__ void __launch_bounds__(kThreads) k_bwd_seg(BwdArgs a) {
                 T fx[NV], fg[NV];
                 VecCvt<T, E>::unpack(xa, fx);
                 VecCvt<T, E>::unpack(ga, fg);
+                bool done = false;
+                if constexpr (CT != AB_F64 && NV >= 2 && OP == OP_QDQ) {
+                    if (fast_ok) {
+                        bwd_vec_fast<CT, WANT_O, NV>(fx, fg, e, g, acc_s, acc_o);
+                        done = true;
+                    }
+                }
+                if (!done) {
 #pragma unroll
-                for (int i = 0; i + 1 < NV; i += 2)
-                    bwd_pair<CT, OP, WANT_O>(fx[i], fx[i + 1], fg[i], fg[i + 1], e, g, acc_s, acc_o);
+                    for (int i = 0; i + 1 < NV; i += 2)
+                        bwd_pair<CT, OP, WANT_O>(fx[i], fx[i + 1], fg[i], fg[i + 1], e, g, acc_s, acc_o);
+                }
                 if (dxp) {
                     VecCvt<T, E>::pack(fx, xa);
                     reinterpret_cast<Vec16<E> *>(dxp)[va] = xa;
@@ -477,9 +666,18 @@ __global__ void __launch_bounds__(kThreads) k_bwd_seg(BwdArgs a) {
                 if (hb) {
                     VecCvt<T, E>::unpack(xb, fx);
                     VecCvt<T, E>::unpack(gb, fg);
+                    done = false;
+                    if constexpr (CT != AB_F64 && NV >= 2 && OP == OP_QDQ) {
+                        if (fast_ok) {
+                            bwd_vec_fast<CT, WANT_O, NV>(fx, fg, e, g, acc_s, acc_o);
+                            done = true;
+                        }
+                    }
+                    if (!done) {
 #pragma unroll
-                    for (int i = 0; i + 1 < NV; i += 2)
-                        bwd_pair<CT, OP, WANT_O>(fx[i], fx[i + 1], fg[i], fg[i + 1], e, g, acc_s, acc_o);
+                        for (int i = 0; i + 1 < NV; i += 2)
+                            bwd_pair<CT, OP, WANT_O>(fx[i], fx[i + 1], fg[i], fg[i + 1], e, g, acc_s, acc_o);
+                    }
                     if (dxp) {
                         VecCvt<T, E>::pack(fx, xb);
                         reinterpret_cast<Vec16<E> *>(dxp)[vb] = xb;
@@ -501,15 +699,16 @@ __global__ void __launch_bounds__(kThreads) k_bwd_seg(BwdArgs a) {
         }
     }
 
-    // fixed-order reduction over the group
-    double rs = (double)acc_s, ro = (double)acc_o;
+    // fixed-order reduction over the group, in the register type (the partials are summed in
+    // float64 by the finishing kernel)
+    T rs = acc_s, ro = acc_o;
     const int span = G < 32 ? G : 32;
     for (int o = span >> 1; o > 0; o >>= 1) {
         rs += __shfl_xor_sync(0xffffffffu, rs, o);
-        ro += __shfl_xor_sync(0xffffffffu, ro, o);
+        if (WANT_O) ro += __shfl_xor_sync(0xffffffffu, ro, o);
     }
     if (G > 32) {
-        __shared__ double sh[2][kThreads / 32];
+        __shared__ T sh[2][kThreads / 32];
         const int warp = threadIdx.x >> 5;
         if ((threadIdx.x & 31) == 0) {
             sh[0][warp] = rs;
@@ -528,11 +727,11 @@ __global__ void __launch_bounds__(kThreads) k_bwd_seg(BwdArgs a) {
     }
     if (valid && lane == 0) {
         if (a.direct) {
-            if (a.gs.p) a.gs.put(param, finalize<CT>(rs));
-            if (a.go.p) a.go.put(param, finalize<CT>(ro));
+            if (a.gs.p) a.gs.put(param, finalize<CT>((double)rs));
+            if (a.go.p) a.go.put(param, finalize<CT>((double)ro));
         } else {
-            a.partial[2 * s] = rs;
-            a.partial[2 * s + 1] = ro;
+            a.partial[2 * s] = (double)rs;
+            a.partial[2 * s + 1] = (double)ro;
         }
     }
 }
@@ -789,6 +988,29 @@ template <int IO, int CT, int OP> int launch_forward(const Call &c, const Canon 
         a.zps = c.zps;
         a.exact_edges = exact_edges(CT, c.qmin, c.qmax);
         const bool vect = aligned16(c.x) && aligned16(c.y) && (canon.numel % vecw == 0);
+        const ReducePlan sp = plan_reduce(canon, IO, vect);
+        if (vect && vecw >= 2 && sp.mode == ReducePlan::SEG && sp.vect) {
+            FwdSegArgs f;
+            f.x = c.x;
+            f.y = c.y;
+            f.scale = a.scale;
+            f.offset = a.offset;
+            f.cm = a.cm;
+            f.seg_len = sp.seg_len;
+            f.nseg = sp.nseg;
+            f.nchunk = sp.nchunk;
+            f.group = sp.group;
+            f.qmin = a.qmin;
+            f.qmax = a.qmax;
+            f.zps = a.zps;
+            f.exact_edges = a.exact_edges;
+            const int gpc = kThreads / sp.group;
+            const int64_t sgrid = (sp.nseg + gpc - 1) / gpc;
+            if (sgrid > 2147483647LL) return fail(AB_ERR_UNSUPPORTED, "tensor too large for one launch");
+            k_fwd_seg<IO, CT, OP><<<(unsigned)sgrid, kThreads, 0, c.stream>>>(f);
+            AB_LAUNCH_OK();
+            return AB_OK;
+        }
         const int64_t nvec = vect ? canon.numel / vecw : canon.numel;
         const int64_t per_cta = (int64_t)kThreads * kFwdUnroll;
         const int64_t grid = (nvec + per_cta - 1) / per_cta;

@@ -178,7 +178,12 @@ ReducePlan plan_reduce(const Canon &c, int io_dtype, bool ptr_aligned) {
     }
     p.nseg = c.O * c.C * p.nchunk;
     const int64_t vec_per_seg = (p.seg_len + v - 1) / v;
-    int grp = pow2_ceil((vec_per_seg + 1) / 2);
+    // aim at kSegVecPerThread vectors per thread (index arithmetic and the group reduction are paid per
+    // thread)
+    int grp = pow2_ceil((vec_per_seg + kSegVecPerThread - 1) / kSegVecPerThread);
+    // two neighbouring lanes read one 32-byte sector together
+    const int floor_grp = vec_per_seg >= 2 ? 2 : 1;
+    if (grp < floor_grp) grp = floor_grp;
     if (grp > kThreads) grp = kThreads;
     p.group = grp;
     p.direct = (c.O == 1 && p.nchunk == 1) ? 1 : 0;

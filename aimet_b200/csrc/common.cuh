@@ -282,7 +282,7 @@ GenMap make_gen_map(const Canon &c);
 // walked column-wise; GEN: no (O, C, I) form.
 // ---------------------------------------------------------------------------
 constexpr int kThreads = 256;
-constexpr int kSegVecPerThread = 4;  // 16-byte vectors per thread in one chunk
+constexpr int kSegVecPerThread = 8;  // 16-byte vectors per thread in one chunk
 
 struct ReducePlan {
     enum Mode { SEG, COL, GEN } mode;
