@@ -374,6 +374,105 @@ __device__ __forceinline__ void bwd_vec_fast(float (&x)[NV], const float (&gy)[N
 }
 
 // ---------------------------------------------------------------------------
+// Packed 16-bit fast paths: when the internal dtype IS the tensor dtype (bfloat16 for <= 5-bit
+// grids, float16 for <= 8-bit grids) every step after the division is a native two-wide
+// half-precision instruction.  A native add / sub / mul rounds the exact result once to the
+// 16-bit type; the reference computes the same operation in float and rounds to the 16-bit type,
+// which is the same value whenever the float result is exact -- true for every operation below
+// (products of two 8/11-bit significands, sums of small integers).  Rounding to an integer uses
+// the 16-bit magic constant 1.5 * 2^(p-1) (p significant bits): exact for |v| < 2^(p-2); beyond
+// that the result stays outside the grid as long as the clamp bounds are below 2^(p-3)
+// (vec_packed_ok), which is all that is observable.
+// ---------------------------------------------------------------------------
+template <int CT> struct Packed;
+template <> struct Packed<AB_BF16> {
+    using H2 = __nv_bfloat162;
+    static constexpr float kMagic16 = 192.0f;   // 1.5 * 2^7
+    static constexpr float kLimit = 32.0f;      // 2^5
+    static __device__ __forceinline__ H2 dup(float v) { return __float2bfloat162_rn(v); }
+    static __device__ __forceinline__ H2 pack(float a, float b) { return __floats2bfloat162_rn(a, b); }
+    static __device__ __forceinline__ float lo(H2 v) { return __uint_as_float(*reinterpret_cast<uint32_t *>(&v) << 16); }
+    static __device__ __forceinline__ float hi(H2 v) { return __uint_as_float(*reinterpret_cast<uint32_t *>(&v) & 0xffff0000u); }
+};
+template <> struct Packed<AB_F16> {
+    using H2 = __half2;
+    static constexpr float kMagic16 = 1536.0f;  // 1.5 * 2^10
+    static constexpr float kLimit = 256.0f;     // 2^8
+    static __device__ __forceinline__ H2 dup(float v) { return __float2half2_rn(v); }
+    static __device__ __forceinline__ H2 pack(float a, float b) { return __floats2half2_rn(a, b); }
+    static __device__ __forceinline__ float lo(H2 v) { return __low2float(v); }
+    static __device__ __forceinline__ float hi(H2 v) { return __high2float(v); }
+};
+
+template <int CT> __device__ __forceinline__ bool vec_packed_ok(const Enc<CT> &e, const Grid<typename Arith<CT>::T> &g) {
+    if (CT != AB_BF16 && CT != AB_F16) return false;
+    const float lim = CT == AB_BF16 ? 32.0f : 256.0f;
+    const float o = (float)e.o;
+    return e.fast && e.exact_int && !g.has_zps && o == rintf(o) && fabsf(o) <= lim &&
+           fabsf((float)e.lo) <= lim && fabsf((float)e.hi) <= lim;
+}
+
+template <typename H2> __device__ __forceinline__ H2 bit_select(H2 a, H2 b, unsigned mask) {  // mask ? a : b
+    const unsigned ua = *reinterpret_cast<unsigned *>(&a), ub = *reinterpret_cast<unsigned *>(&b);
+    const unsigned r = (ua & mask) | (ub & ~mask);
+    return *reinterpret_cast<const H2 *>(&r);
+}
+
+// E is the 16-bit tensor element type matching CT
+template <int CT, int OP, typename E>
+__device__ __forceinline__ void fwd_vec_packed(const Vec16<E> &in, Vec16<E> &out, const Enc<CT> &e, const Grid<float> &g) {
+    using P = Packed<CT>;
+    using H2 = typename P::H2;
+    const float s = (float)e.s, r = (float)e.r, o = (float)e.o;
+    const H2 magic = P::dup(P::kMagic16), csub = P::dup(P::kMagic16 + o);
+    const H2 qmin = P::dup(g.qmin), qmax = P::dup(g.qmax), o2 = P::dup(o), s2 = P::dup(s);
+    const H2 *ip = reinterpret_cast<const H2 *>(&in);
+    H2 *op = reinterpret_cast<H2 *>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float a = div_scale_f32(P::lo(ip[i]), s, r, true), b = div_scale_f32(P::hi(ip[i]), s, r, true);
+        H2 q = __hsub2(__hadd2(P::pack(a, b), magic), csub);
+        q = __hmin2_nan(__hmax2_nan(q, qmin), qmax);
+        op[i] = OP == OP_QDQ ? __hmul2(__hadd2(q, o2), s2) : q;
+    }
+}
+
+template <int CT, bool WANT_O, typename E>
+__device__ __forceinline__ void bwd_vec_packed(const Vec16<E> &x, const Vec16<E> &gy, Vec16<E> &dx, const Enc<CT> &e,
+                                               const Grid<float> &g, float &acc_s, float &acc_o) {
+    using P = Packed<CT>;
+    using H2 = typename P::H2;
+    const float s = (float)e.s, r = (float)e.r, o = (float)e.o;
+    const H2 magic = P::dup(P::kMagic16), csub = P::dup(P::kMagic16 + o);
+    const H2 qmin = P::dup(g.qmin), qmax = P::dup(g.qmax), lo2 = P::dup((float)e.lo), hi2 = P::dup((float)e.hi);
+    const H2 s2 = P::dup(s);
+    const H2 *xp = reinterpret_cast<const H2 *>(&x);
+    const H2 *gp = reinterpret_cast<const H2 *>(&gy);
+    unsigned *dp = reinterpret_cast<unsigned *>(&dx);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float a = div_scale_f32(P::lo(xp[i]), s, r, true), b = div_scale_f32(P::hi(xp[i]), s, r, true);
+        const H2 v = P::pack(a, b);                 // x / s in the internal dtype
+        const H2 t = __hadd2(v, magic);
+        const H2 rd = __hsub2(t, magic);            // round(x / s)
+        const H2 q = __hsub2(t, csub);              // round(x / s) - o
+        const unsigned m = __hge2_mask(q, qmin) & __hle2_mask(q, qmax);
+        const H2 sel = bit_select(__hsub2(rd, v), __hmin2_nan(__hmax2_nan(rd, lo2), hi2), m);
+        const H2 d = __hmul2(gp[i], sel);
+        acc_s += P::lo(d);
+        acc_s += P::hi(d);
+        if (WANT_O) {
+            H2 od = __hmul2(gp[i], s2);
+            const unsigned uo = *reinterpret_cast<unsigned *>(&od) & ~m;
+            od = *reinterpret_cast<const H2 *>(&uo);
+            acc_o += P::lo(od);
+            acc_o += P::hi(od);
+        }
+        dp[i] = *reinterpret_cast<const unsigned *>(&gp[i]) & m;
+    }
+}
+
+// ---------------------------------------------------------------------------
 // forward kernels
 // ---------------------------------------------------------------------------
 struct FwdArgs {
@@ -499,7 +598,9 @@ __global__ void __launch_bounds__(kThreads, 5) k_fwd_seg(FwdSegArgs a) {
         param = a.cm.narrow ? (int64_t)((uint32_t)ts % (uint32_t)a.cm.C) : ts % a.cm.C;
     const Enc<CT> e = load_enc<CT>(a.scale, a.offset, param, g);
     const bool fast_ok = vec_fast_ok<CT>(e, g);
+    const bool packed_ok = vec_packed_ok<CT>(e, g);
     (void)fast_ok;
+    (void)packed_ok;
     const int64_t nv = len / NV, v0 = start / NV;
     for (int64_t v = lane; v < nv; v += (int64_t)U * G) {
         Vec16<E> xv[U];
@@ -509,6 +610,14 @@ __global__ void __launch_bounds__(kThreads, 5) k_fwd_seg(FwdSegArgs a) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             if (v + (int64_t)u * G >= nv) continue;
+            if constexpr ((CT == AB_BF16 || CT == AB_F16) && CT == IO && (OP == OP_QDQ || OP == OP_Q)) {
+                if (packed_ok) {
+                    Vec16<E> yp16;
+                    fwd_vec_packed<CT, OP, E>(xv[u], yp16, e, g);
+                    yp[v0 + v + (int64_t)u * G] = yp16;
+                    continue;
+                }
+            }
             T f[NV];
             VecCvt<T, E>::unpack(xv[u], f);
             bool done = false;
@@ -629,7 +738,9 @@ __global__ void __launch_bounds__(kThreads, 4) k_bwd_seg(BwdArgs a) {
             param = a.cm.narrow ? (int64_t)((uint32_t)ts % (uint32_t)a.cm.C) : ts % a.cm.C;
         const Enc<CT> e = load_enc<CT>(a.scale, a.offset, param, g);
         const bool fast_ok = vec_fast_ok<CT>(e, g);
+        const bool packed_ok = vec_packed_ok<CT>(e, g);
         (void)fast_ok;
+        (void)packed_ok;
         const int64_t nv = len / VEC;
         const int64_t v0 = start / VEC;
         for (int64_t v = lane; v < nv; v += 2 * (int64_t)G) {
@@ -643,6 +754,18 @@ __global__ void __launch_bounds__(kThreads, 4) k_bwd_seg(BwdArgs a) {
                 if (hb) {
                     xb = reinterpret_cast<const Vec16<E> *>(xp)[vb];
                     gb = reinterpret_cast<const Vec16<E> *>(gp)[vb];
+                }
+                if constexpr ((CT == AB_BF16 || CT == AB_F16) && CT == IO && OP == OP_QDQ) {
+                    if (packed_ok) {
+                        Vec16<E> da;
+                        bwd_vec_packed<CT, WANT_O, E>(xa, ga, da, e, g, acc_s, acc_o);
+                        if (dxp) reinterpret_cast<Vec16<E> *>(dxp)[va] = da;
+                        if (hb) {
+                            bwd_vec_packed<CT, WANT_O, E>(xb, gb, da, e, g, acc_s, acc_o);
+                            if (dxp) reinterpret_cast<Vec16<E> *>(dxp)[vb] = da;
+                        }
+                        continue;
+                    }
                 }
                 T fx[NV], fg[NV];
                 VecCvt<T, E>::unpack(xa, fx);
