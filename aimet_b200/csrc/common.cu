@@ -137,7 +137,7 @@ static int pow2_ceil(int64_t v) {
     return r;
 }
 
-ReducePlan plan_reduce(const Canon &c, int io_dtype, bool ptr_aligned) {
+ReducePlan plan_reduce(const Canon &c, int io_dtype, bool ptr_aligned, int chunk_mult) {
     ReducePlan p{};
     if (!c.oci) {
         p.mode = ReducePlan::GEN;
@@ -168,7 +168,7 @@ ReducePlan plan_reduce(const Canon &c, int io_dtype, bool ptr_aligned) {
     p.mode = ReducePlan::SEG;
     p.vect = ptr_aligned && (c.I % vecw == 0);
     const int v = p.vect ? vecw : 1;
-    const int64_t chunk = (int64_t)kThreads * kSegVecPerThread * v;
+    const int64_t chunk = (int64_t)kThreads * kSegVecPerThread * v * chunk_mult;
     if (c.I > chunk) {
         p.seg_len = chunk;
         p.nchunk = (c.I + chunk - 1) / chunk;

@@ -297,7 +297,7 @@ struct ReducePlan {
 
 // Depends only on the layout and the element size (plus whether the pointers
 // allow 16-byte accesses), so a scratch-size query and the launch agree.
-ReducePlan plan_reduce(const Canon &c, int io_dtype, bool ptr_aligned);
+ReducePlan plan_reduce(const Canon &c, int io_dtype, bool ptr_aligned, int chunk_mult = 1);
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 

@@ -5,6 +5,8 @@
 // _LpNormEncodingAnalyzer._estimate_clip_and_quant_noise (:822-899).
 #include <math.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace ab {
@@ -13,6 +15,8 @@ namespace {
 // ---------------------------------------------------------------------------
 // min / max
 // ---------------------------------------------------------------------------
+constexpr int kStatChunkMult = 4;  // read-only passes take longer runs per thread group
+
 template <typename T> struct MinMax {
     T lo, hi;
 };
@@ -54,6 +58,47 @@ template <> __device__ __forceinline__ __nv_bfloat16 stat_store<__nv_bfloat16>(d
     return __float2bfloat16_rn((float)v);
 }
 
+// Packed running min / max over the two 16-bit halves of each word: two instructions per pair of
+// elements in the NaN-propagating mode, seven in the finite-only mode (non-finite halves are
+// replaced by +inf / -inf before the comparison).
+template <typename E> struct PackedMM { static constexpr bool ok = false; };
+template <> struct PackedMM<__nv_bfloat16> {
+    static constexpr bool ok = true;
+    using H2 = __nv_bfloat162;
+    static __device__ __forceinline__ H2 dup(float v) { return __float2bfloat162_rn(v); }
+    static __device__ __forceinline__ float lo(H2 v) { return __low2float(v); }
+    static __device__ __forceinline__ float hi(H2 v) { return __high2float(v); }
+};
+template <> struct PackedMM<__half> {
+    static constexpr bool ok = true;
+    using H2 = __half2;
+    static __device__ __forceinline__ H2 dup(float v) { return __float2half2_rn(v); }
+    static __device__ __forceinline__ float lo(H2 v) { return __low2float(v); }
+    static __device__ __forceinline__ float hi(H2 v) { return __high2float(v); }
+};
+
+template <typename H2> __device__ __forceinline__ H2 mm_bit_select(H2 a, H2 b, unsigned mask) {  // mask ? a : b
+    const unsigned ua = *reinterpret_cast<unsigned *>(&a), ub = *reinterpret_cast<unsigned *>(&b);
+    const unsigned r = (ua & mask) | (ub & ~mask);
+    return *reinterpret_cast<const H2 *>(&r);
+}
+
+template <typename E, typename H2>
+__device__ __forceinline__ void mm_update_packed(H2 &pmin, H2 &pmax, const Vec16<E> &v, bool finite_only, H2 pinf, H2 ninf) {
+    const H2 *w = reinterpret_cast<const H2 *>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (finite_only) {
+            const unsigned bad = __hgeu2_mask(__habs2(w[i]), pinf);  // inf or NaN
+            pmin = __hmin2(pmin, mm_bit_select(pinf, w[i], bad));
+            pmax = __hmax2(pmax, mm_bit_select(ninf, w[i], bad));
+        } else {
+            pmin = __hmin2_nan(pmin, w[i]);
+            pmax = __hmax2_nan(pmax, w[i]);
+        }
+    }
+}
+
 struct MinMaxArgs {
     const void *x;
     void *min_out, *max_out;  // io dtype, direct mode
@@ -77,16 +122,46 @@ template <int IO, bool VECT> __global__ void __launch_bounds__(kThreads) k_minma
     MinMax<T> m = mm_init<T>();
     int64_t param = 0;
     if (valid) {
-        const int64_t ts = s / a.nchunk;
-        const int64_t k = s - ts * a.nchunk;
+        int64_t ts = s, k = 0;
+        if (a.nchunk > 1) {
+            if (a.cm.narrow) {
+                ts = (uint32_t)s / (uint32_t)a.nchunk;
+                k = (uint32_t)s - (uint32_t)ts * (uint32_t)a.nchunk;
+            } else {
+                ts = s / a.nchunk;
+                k = s - ts * a.nchunk;
+            }
+        }
         const int64_t start = ts * a.cm.I + k * a.seg_len;
         int64_t len = a.cm.I - k * a.seg_len;
         if (len > a.seg_len) len = a.seg_len;
-        param = a.cm.C == 1 ? 0 : (a.cm.wrap ? ts % a.cm.C : ts);
+        if (a.cm.C == 1)
+            param = 0;
+        else if (!a.cm.wrap)
+            param = ts;
+        else
+            param = a.cm.narrow ? (int64_t)((uint32_t)ts % (uint32_t)a.cm.C) : ts % a.cm.C;
         const int64_t nv = len / VEC, v0 = start / VEC;
         for (int64_t v = lane; v < nv; v += 2 * (int64_t)G) {
             const bool hb = v + G < nv;
-            if (VECT) {
+            if constexpr (VECT && PackedMM<E>::ok) {
+                using PM = PackedMM<E>;
+                const typename PM::H2 pinf = PM::dup(INFINITY), ninf = PM::dup(-INFINITY);
+                typename PM::H2 pmin = pinf, pmax = ninf;
+                // this path walks the whole run itself, four vectors in flight per thread
+                for (int64_t w = v; w < nv; w += 4 * (int64_t)G) {
+                    Vec16<E> xs[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (w + (int64_t)u * G < nv) xs[u] = reinterpret_cast<const Vec16<E> *>(xp)[v0 + w + (int64_t)u * G];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (w + (int64_t)u * G < nv) mm_update_packed<E>(pmin, pmax, xs[u], a.finite_only != 0, pinf, ninf);
+                }
+                mm_merge(m, (T)PM::lo(pmin), (T)PM::lo(pmax));
+                mm_merge(m, (T)PM::hi(pmin), (T)PM::hi(pmax));
+                break;
+            } else if constexpr (VECT) {
                 Vec16<E> xa = reinterpret_cast<const Vec16<E> *>(xp)[v0 + v], xb;
                 if (hb) xb = reinterpret_cast<const Vec16<E> *>(xp)[v0 + v + G];
 #pragma unroll
@@ -176,14 +251,16 @@ struct MinMaxFinishArgs {
     int64_t nparam, na, sa, sc, nb;
 };
 
-template <int IO> __global__ void __launch_bounds__(kThreads) k_minmax_finish(MinMaxFinishArgs a) {
+template <int IO, bool PER_CTA> __global__ void __launch_bounds__(kThreads) k_minmax_finish(MinMaxFinishArgs a) {
+    // PER_CTA: one CTA per statistic (many partials each); else one warp per statistic
     using E = typename Elem<IO>::type;
-    const int64_t c = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+    const int64_t c = PER_CTA ? (int64_t)blockIdx.x : (((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5);
     const int lane = threadIdx.x & 31;
     if (c >= a.nparam) return;
     MinMax<double> m = mm_init<double>();
     const int64_t n = a.na * a.nb;
-    for (int64_t t = lane; t < n; t += 32) {
+    const int step = PER_CTA ? kThreads : 32;
+    for (int64_t t = PER_CTA ? threadIdx.x : lane; t < n; t += step) {
         const int64_t ia = t / a.nb, ib = t - ia * a.nb;
         const double *p = a.partial + 2 * (ia * a.sa + c * a.sc + ib);
         mm_merge(m, p[0], p[1]);
@@ -194,16 +271,35 @@ template <int IO> __global__ void __launch_bounds__(kThreads) k_minmax_finish(Mi
         double hi = __shfl_xor_sync(0xffffffffu, m.hi, o);
         mm_merge(m, lo, hi);
     }
+    if (PER_CTA) {
+        __shared__ double sh[2][kThreads / 32];
+        if (lane == 0) {
+            sh[0][threadIdx.x >> 5] = m.lo;
+            sh[1][threadIdx.x >> 5] = m.hi;
+        }
+        __syncthreads();
+        if (threadIdx.x != 0) return;
+        for (int w = 1; w < kThreads / 32; ++w) mm_merge(m, sh[0][w], sh[1][w]);
+    }
     if (lane == 0) {
         static_cast<E *>(a.min_out)[c] = stat_store<E>(m.lo);
         static_cast<E *>(a.max_out)[c] = stat_store<E>(m.hi);
     }
 }
 
+template <int IO> void launch_minmax_finish(const MinMaxFinishArgs &f, cudaStream_t stream) {
+    if (f.na * f.nb > 256) {
+        k_minmax_finish<IO, true><<<(unsigned)f.nparam, kThreads, 0, stream>>>(f);
+    } else {
+        const int64_t grid = (f.nparam * 32 + kThreads - 1) / kThreads;
+        k_minmax_finish<IO, false><<<(unsigned)grid, kThreads, 0, stream>>>(f);
+    }
+}
+
 template <int IO>
 int launch_minmax(const void *x, const Canon &canon, int finite_only, void *min_out, void *max_out,
                   void *scratch, int64_t scratch_bytes, cudaStream_t stream) {
-    const ReducePlan p = plan_reduce(canon, IO, aligned16(x));
+    const ReducePlan p = plan_reduce(canon, IO, aligned16(x), kStatChunkMult);
     if (p.mode == ReducePlan::GEN)
         return fail(AB_ERR_UNSUPPORTED, "statistics need a layout that reduces to (outer, channel, inner)");
     const int64_t need = p.npartial * 2 * (int64_t)sizeof(double);
@@ -245,8 +341,7 @@ int launch_minmax(const void *x, const Canon &canon, int finite_only, void *min_
     AB_LAUNCH_OK();
     if (p.npartial > 0) {
         MinMaxFinishArgs f{a.partial, min_out, max_out, canon.nparam, p.na, p.sa, p.sc, p.nb};
-        const int64_t grid = (canon.nparam * 32 + kThreads - 1) / kThreads;
-        k_minmax_finish<IO><<<(unsigned)grid, kThreads, 0, stream>>>(f);
+        launch_minmax_finish<IO>(f, stream);
         AB_LAUNCH_OK();
     }
     return AB_OK;
@@ -411,6 +506,149 @@ template <int IO, bool VECT> __global__ void __launch_bounds__(kThreads) k_histo
     }
 }
 
+// ---------------------------------------------------------------------------
+// 16-bit inputs: a bfloat16 / float16 tensor has only 65536 distinct values, so the histc bin (and
+// the outlier rule) of every bit pattern is tabulated once per call and the pass over the tensor
+// is a table look-up plus a shared-memory increment -- the exact float arithmetic runs 65536 times
+// instead of once per element.  Table entry: bits 3..15 bin (num_bins = a spare bin for values that
+// count nowhere), bit 1 "also counts in bin 0", bit 2 "also counts in the last bin" (only when a
+// value is inside the binning range and at the same time beyond an outlier threshold, which can
+// happen when the thresholds were rounded to the tensor dtype).
+// ---------------------------------------------------------------------------
+constexpr int kLutEntries = 65536;
+constexpr int kLutThreads = 1024;
+constexpr int64_t kLutMinElems = 1 << 20;  // per channel; below this the table does not pay off
+constexpr int kLutMaxChannels = 64;
+constexpr unsigned kLutExtra0 = 1u << 1, kLutExtraN = 1u << 2;  // bits 3..15: bin, or num_bins for "counts nowhere"
+
+template <int IO>
+__global__ void __launch_bounds__(256) k_hist_lut_build(const float *lo, const float *hi, const float *below,
+                                                        const float *above, int num_bins, uint16_t *lut) {
+    using E = typename Elem<IO>::type;
+    const int c = blockIdx.y;
+    const unsigned p = blockIdx.x * 256 + threadIdx.x;
+    const uint16_t raw = (uint16_t)p;
+    const float v = to_f32(*reinterpret_cast<const E *>(&raw));
+    const float l = lo[c], h = hi[c];
+    unsigned code = 0;
+    bool valid = (v >= l) && (v <= h);
+    int bin = 0;
+    if (valid) bin = histc_bin(v, l, __fsub_rn(h, l), (float)num_bins, num_bins);
+    bool ex0 = v < below[c], exn = v > above[c];
+    if (!valid && ex0) { valid = true; bin = 0; ex0 = false; }
+    if (!valid && exn) { valid = true; bin = num_bins - 1; exn = false; }
+    code = (unsigned)(valid ? bin : num_bins) << 3;
+    if (ex0) code |= kLutExtra0;
+    if (exn) code |= kLutExtraN;
+    lut[(int64_t)c * kLutEntries + p] = (uint16_t)code;
+}
+
+struct HistLutArgs {
+    const void *x;
+    const uint16_t *lut;         // [C][65536]
+    unsigned long long *counts;  // [C][num_bins]
+    int64_t O, C, I, chan_elems, tile_elems;
+    int num_bins;
+};
+
+// Shared memory: the 128 KB table plus `copies` interleaved replicas of the histogram (replica k of
+// bin b at word b * copies + k).  A lane increments replica (lane % copies), so lanes that hit the
+// same hot bin spread over `copies` different banks instead of serialising on one address.
+__device__ __forceinline__ int hist_lut_copies(int num_bins) {
+    return num_bins <= 2048 ? 8 : 4;  // the table path is used for at most 4096 bins
+}
+
+__device__ __noinline__ void hist_lut_rare(unsigned int *hist, unsigned code, int shift, int copy, int last) {
+    // a value inside the binning range that is also beyond an outlier threshold counts twice
+    if (code & kLutExtra0) atomicAdd(&hist[copy], 1u);
+    if (code & kLutExtraN) atomicAdd(&hist[((unsigned)last << shift) + copy], 1u);
+}
+
+__global__ void __launch_bounds__(kLutThreads, 1) k_hist_lut(HistLutArgs a) {
+    extern __shared__ __align__(16) unsigned char sh_raw[];
+    uint16_t *sh_lut = reinterpret_cast<uint16_t *>(sh_raw);
+    unsigned int *sh_hist = reinterpret_cast<unsigned int *>(sh_raw + kLutEntries * sizeof(uint16_t));
+    const int64_t c = blockIdx.y;
+    const int copies = hist_lut_copies(a.num_bins);
+    const int shift = copies == 8 ? 3 : 2;
+    {
+        const uint4 *src = reinterpret_cast<const uint4 *>(a.lut + c * kLutEntries);
+        uint4 *dst = reinterpret_cast<uint4 *>(sh_lut);
+        for (int i = threadIdx.x; i < kLutEntries * 2 / 16; i += kLutThreads) dst[i] = src[i];
+        for (int b = threadIdx.x; b < (a.num_bins + 1) * copies; b += kLutThreads) sh_hist[b] = 0;
+    }
+    __syncthreads();
+
+    const uint4 *xp = reinterpret_cast<const uint4 *>(a.x);
+    const int64_t e0 = (int64_t)blockIdx.x * a.tile_elems;
+    int64_t e1 = e0 + a.tile_elems;
+    if (e1 > a.chan_elems) e1 = a.chan_elems;
+    const int64_t nvec = (e1 - e0) / 8;
+    const bool flat = a.C == 1;
+    const int last = a.num_bins - 1;
+    const int copy = threadIdx.x & (copies - 1);
+    const unsigned lut_base = (unsigned)__cvta_generic_to_shared(sh_lut);
+    const unsigned hist_base = (unsigned)__cvta_generic_to_shared(sh_hist) + 4u * copy;
+    const int hshift = shift + 2;  // bin -> byte offset of its replica group
+
+    // two elements per 32-bit word: one increment of 2 when both fall in the same bin.  The table
+    // code is the bin pre-shifted by 3, so its replica group starts at byte (code & ~7) << (hshift-3)
+    const int cshift = hshift - 3;
+    auto feed_word = [&](unsigned w) {
+        unsigned short c0h, c1h;
+        asm("ld.shared.u16 %0, [%1];" : "=h"(c0h) : "r"(lut_base + ((w << 1) & 0x1fffeu)));
+        asm("ld.shared.u16 %0, [%1];" : "=h"(c1h) : "r"(lut_base + ((w >> 15) & 0x1fffeu)));
+        const unsigned c0 = c0h, c1 = c1h;
+        const bool same = (c0 >> 3) == (c1 >> 3);
+        asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(hist_base + ((c0 & 0xfff8u) << cshift)), "r"(same ? 2u : 1u) : "memory");
+        if (!same) asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(hist_base + ((c1 & 0xfff8u) << cshift)), "r"(1u) : "memory");
+        if (__builtin_expect(((c0 | c1) & (kLutExtra0 | kLutExtraN)) != 0, 0)) {
+            hist_lut_rare(sh_hist, c0, shift, copy, last);
+            hist_lut_rare(sh_hist, c1, shift, copy, last);
+        }
+    };
+    for (int64_t v0 = threadIdx.x; v0 < nvec; v0 += 2 * kLutThreads) {
+        const int64_t v1 = v0 + kLutThreads;
+        int64_t a0, a1;
+        if (flat) {
+            a0 = e0 / 8 + v0;
+            a1 = e0 / 8 + v1;
+        } else {
+            const int64_t ea = e0 + v0 * 8, eb = e0 + v1 * 8;
+            const int64_t oa = ea / a.I, ob = eb / a.I;
+            a0 = ((oa * a.C + c) * a.I + (ea - oa * a.I)) / 8;
+            a1 = ((ob * a.C + c) * a.I + (eb - ob * a.I)) / 8;
+        }
+        const uint4 wa = xp[a0];
+        uint4 wb = make_uint4(0, 0, 0, 0);
+        const bool hb = v1 < nvec;
+        if (hb) wb = xp[a1];
+        feed_word(wa.x);
+        feed_word(wa.y);
+        feed_word(wa.z);
+        feed_word(wa.w);
+        if (hb) {
+            feed_word(wb.x);
+            feed_word(wb.y);
+            feed_word(wb.z);
+            feed_word(wb.w);
+        }
+    }
+    __syncthreads();
+    unsigned long long *out = a.counts + c * (int64_t)a.num_bins;
+    for (int b = threadIdx.x; b < a.num_bins; b += kLutThreads) {
+        unsigned long long n = 0;
+        for (int k = 0; k < copies; ++k) n += sh_hist[(b << shift) + k];
+        if (n) atomicAdd(out + b, n);
+    }
+}
+
+inline int64_t hist_lut_bytes(const Canon &canon, int io_dtype) {
+    if (dtype_size(io_dtype) != 2 || !canon.oci || canon.C > kLutMaxChannels) return 0;
+    if (canon.O * canon.I < kLutMinElems) return 0;
+    return canon.C * (int64_t)kLutEntries * (int64_t)sizeof(uint16_t);
+}
+
 template <int IO>
 int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const float *lo, const float *hi,
                      const float *below, const float *above, int64_t *counts, void *fin_min, void *fin_max,
@@ -432,6 +670,44 @@ int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const 
     tiles = (chan_elems + tile_elems - 1) / tile_elems;
 
     const bool want_mm = fin_min && fin_max;
+    // table look-up path for 16-bit tensors with enough elements per histogram
+    if constexpr (IO == AB_BF16 || IO == AB_F16) {
+        const int64_t lut_bytes = hist_lut_bytes(canon, IO);
+        if (lut_bytes > 0 && num_bins <= 4096 && !want_mm && vect && scratch && scratch_bytes >= lut_bytes && aligned16(scratch)) {
+            static std::once_flag once;
+            static cudaError_t attr_err = cudaSuccess;
+            const size_t smem = kLutEntries * sizeof(uint16_t) + sizeof(unsigned int) * (16384 + 8);  // table + replicas (+ spare bin)
+            std::call_once(once, [smem]() {
+                attr_err = cudaFuncSetAttribute(k_hist_lut, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            });
+            if (attr_err == cudaSuccess) {
+                AB_CUDA_OK(cudaMemsetAsync(counts, 0, sizeof(int64_t) * canon.C * (int64_t)num_bins, stream));
+                uint16_t *lut = static_cast<uint16_t *>(scratch);
+                dim3 bgrid(kLutEntries / 256, (unsigned)canon.C);
+                k_hist_lut_build<IO><<<bgrid, 256, 0, stream>>>(lo, hi, below, above, num_bins, lut);
+                AB_LAUNCH_OK();
+                int64_t ltiles = sm_count() / canon.C;
+                if (ltiles < 1) ltiles = 1;
+                int64_t lt_elems = (chan_elems + ltiles - 1) / ltiles;
+                lt_elems = ((lt_elems + 15) / 16) * 16;
+                ltiles = (chan_elems + lt_elems - 1) / lt_elems;
+                HistLutArgs h;
+                h.x = x;
+                h.lut = lut;
+                h.counts = reinterpret_cast<unsigned long long *>(counts);
+                h.O = canon.O;
+                h.C = canon.C;
+                h.I = canon.I;
+                h.chan_elems = chan_elems;
+                h.tile_elems = lt_elems;
+                h.num_bins = num_bins;
+                dim3 grid((unsigned)ltiles, (unsigned)canon.C);
+                k_hist_lut<<<grid, kLutThreads, smem, stream>>>(h);
+                AB_LAUNCH_OK();
+                return AB_OK;
+            }
+        }
+    }
     const int64_t need = want_mm ? canon.C * tiles * 2 * (int64_t)sizeof(double) : 0;
     if (need > 0 && (!scratch || scratch_bytes < need))
         return fail(AB_ERR_SCRATCH, "histogram needs %lld bytes of scratch, got %lld", (long long)need,
@@ -462,8 +738,7 @@ int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const 
     AB_LAUNCH_OK();
     if (want_mm) {
         MinMaxFinishArgs f{a.mm_partial, fin_min, fin_max, canon.C, 1, 0, tiles, tiles};
-        const int64_t g = (canon.C * 32 + kThreads - 1) / kThreads;
-        k_minmax_finish<IO><<<(unsigned)g, kThreads, 0, stream>>>(f);
+        launch_minmax_finish<IO>(f, stream);
         AB_LAUNCH_OK();
     }
     return AB_OK;
@@ -553,13 +828,16 @@ extern "C" int64_t aimet_b200_stats_scratch_bytes(const ab_layout *layout, int i
     if (rc != AB_OK) return rc;
     if (ab::dtype_size(io_dtype) == 0) return ab::fail(AB_ERR_INVALID, "unknown io_dtype %d", io_dtype);
     if (canon.numel == 0 || !canon.oci) return 0;
-    const ab::ReducePlan pa = ab::plan_reduce(canon, io_dtype, true);
-    const ab::ReducePlan pb = ab::plan_reduce(canon, io_dtype, false);
+    const ab::ReducePlan pa = ab::plan_reduce(canon, io_dtype, true, ab::kStatChunkMult);
+    const ab::ReducePlan pb = ab::plan_reduce(canon, io_dtype, false, ab::kStatChunkMult);
     int64_t n = pa.npartial > pb.npartial ? pa.npartial : pb.npartial;
     // histogram min/max partials: at most 8 * SMs tiles in total, plus one per channel
     const int64_t hist = (int64_t)ab::sm_count() * 8 + 2 * canon.C;
     if (hist > n) n = hist;
-    return n * 2 * (int64_t)sizeof(double);
+    int64_t bytes = n * 2 * (int64_t)sizeof(double);
+    const int64_t lut = ab::hist_lut_bytes(canon, io_dtype);
+    if (lut > bytes) bytes = lut;
+    return bytes;
 }
 
 extern "C" int aimet_b200_minmax(const void *x, const ab_layout *layout, int io_dtype, int finite_only,

@@ -189,8 +189,12 @@ def _run_histogram(lay: _StatLayout, num_bins: int, lo, hi, below, above):
     x = lay.x
     counts = torch.empty((lay.count, num_bins), dtype=torch.int64, device=x.device)
     with torch.cuda.device(x.device):
+        nbytes = lib.aimet_b200_stats_scratch_bytes(lay.layout, lay.io)
+        _lib.check(nbytes)
+        scratch = _lib.scratch.get(x.device, nbytes)
         rc = lib.aimet_b200_histogram(x.data_ptr(), lay.layout, lay.io, num_bins, lo.data_ptr(), hi.data_ptr(),
-                                      below.data_ptr(), above.data_ptr(), counts.data_ptr(), None, None, None, 0,
+                                      below.data_ptr(), above.data_ptr(), counts.data_ptr(), None, None,
+                                      _lib.ptr(scratch), 0 if scratch is None else scratch.numel(),
                                       _lib.stream_ptr(x.device))
     _lib.check(rc)
     return counts
