@@ -276,6 +276,109 @@ def cpu_baseline(sample_rows=1024, repeats=3):
             "sample": f"{sample_rows} of {ROWS} rows of the weight, all three encodings, median of {repeats} runs"}
 
 
+# --------------------------------------------------------------------------------------------
+# secondary figures: calibration (config 3) and SeqMSE (config 5)
+# --------------------------------------------------------------------------------------------
+def student_t_batch(gen, hot, dev, tokens=16 * 2048, channels=4096, df=3):
+    z = torch.randn((tokens, channels), device=dev, generator=gen)
+    chi = torch.randn((tokens, channels, df), device=dev, generator=gen).pow_(2).sum(-1)
+    x = z / torch.sqrt(chi / df)
+    x[:, hot] *= 50
+    return x.to(torch.bfloat16).view(16, 2048, channels)
+
+
+def calibration_figure(dev, rank, world, num_batches=64):
+    """SQNR calibration of config 3: ``num_batches`` activation batches [16,2048,4096] bf16 (Student-t,
+    df 3, 32 channels x50) dealt round-robin to the ranks; two-phase exact histogram (min/max
+    all-reduce, 2048-bin int64 count all-reduce), then the 17x21 asymmetric candidate sweep."""
+    import torch.distributed as dist
+
+    from aimet_b200 import distributed as D
+    from aimet_b200 import encoding_analyzer as EA
+
+    gen = torch.Generator(device=dev).manual_seed(3000)
+    hot = torch.randperm(4096, device=dev, generator=gen)[:32]
+    mine = D.my_batches(num_batches, rank, world)
+    batches = []
+    for b in range(num_batches):  # every rank draws the same stream and keeps its own share
+        x = student_t_batch(gen, hot, dev)
+        if b in mine:
+            batches.append(x)
+    group = dist.group.WORLD if world > 1 else None
+
+    def run():
+        an = EA.SqnrEncodingAnalyzer((), num_bins=2048)
+        D.calibrate_histogram(an, batches, group)
+        return an.compute_encodings(255, False)
+
+    run()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 3
+    e0.record()
+    for _ in range(reps):
+        enc = run()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    tokens = num_batches * 16 * 2048
+    peaks, kind = measured_peaks()
+    bytes_moved = num_batches * 16 * 2048 * 4096 * 2 * 2  # two passes over every batch
+    return {"metric": "calibration_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "ms": ms,
+            "batches": num_batches, "batch_shape": [16, 2048, 4096], "analyzer": "SQNR, 2048 bins, 17x21 asymmetric candidates",
+            "algorithmic_bytes": bytes_moved, "achieved_GBps_per_gpu": bytes_moved / world / (ms * 1e-3) / 1e9,
+            "frac_of_" + kind + "_hbm": bytes_moved / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "encoding_min_max": [float(enc[0]), float(enc[1])]}
+
+
+def seqmse_figure(dev, rank, world, m=8192, n=4096, k=4096, cands=20):
+    """Config 5: reconstruction loss of 20 candidates for a [4096,4096] bf16 weight on 8192 tokens;
+    output channels split across ranks."""
+    import torch.distributed as dist
+
+    from aimet_b200 import distributed as D
+    from aimet_b200.seq_mse import linear_loss_all_candidates
+
+    gen = torch.Generator(device=dev).manual_seed(5000)
+    x = torch.randn((m, k), device=dev, generator=gen)
+    x[:, torch.randperm(k, device=dev, generator=gen)[:20]] *= 30
+    x = x.to(torch.bfloat16)
+    lo, hi = D.shard_range(n, rank, world)
+    w = (torch.randn((n, k), device=dev, generator=gen) * 0.02).to(torch.bfloat16)[lo:hi].contiguous()
+    fr = torch.linspace(0.5, 1.0, cands, device=dev)  # BASELINE's candidate grid: [0.5 max, max]
+    smax = w.float().abs().amax(1, keepdim=True) / 7
+    wq = torch.stack([(torch.clamp(torch.round(w.float() / (smax * f)), -8, 7) * (smax * f)).to(torch.bfloat16) for f in fr])
+    for _ in range(2):
+        linear_loss_all_candidates(x, x, w, wq, "mse")
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    e0.record()
+    for _ in range(reps):
+        loss = linear_loss_all_candidates(x, x, w, wq, "mse")
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    flops = 2.0 * m * n * k * cands
+    peaks, kind = measured_peaks()
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"metric": "seqmse_candidate_TFLOPs", "value": tf, "unit": "TFLOP/s (whole job)", "ms": ms,
+            "shape": {"tokens": m, "out": n, "in": k, "candidates": cands}, "per_gpu_TFLOPs": tf / world,
+            "frac_of_" + kind + "_bf16_burst": tf / world / peaks["bf16_tflops"],
+            "frac_of_sustained": tf / world / peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]),
+            "best_index_histogram": torch.bincount(loss.argmin(0), minlength=cands).tolist()}
+
+
 def base_config(n_gpus):
     return {"workload": "configs[1]: Llama-3-8B MLP weight [14336,4096] bf16 QDQ fwd+bwd: per-channel int8 + "
                         "blockwise int4 (block 64) + LPBQ (int4, 8-bit per-channel scale), scale grads on",
@@ -401,6 +504,15 @@ def run_ours(args):
         }
         if world == 1 and not args.no_cpu:
             out["cpu_baseline"] = cpu_baseline()
+    extras = {}
+    if not args.no_extras:
+        del resident, host
+        torch.cuda.empty_cache()
+        extras["calibration"] = calibration_figure(dev, rank, world)
+        torch.cuda.empty_cache()
+        extras["seqmse"] = seqmse_figure(dev, rank, world)
+    if rank == 0:
+        out.update(extras)
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
@@ -413,6 +525,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-oracle baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the calibration and SeqMSE figures")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
