@@ -210,10 +210,15 @@ def _prepare(tensor, scale, offset, block_size, internal_dtype):
     return x, plan
 
 
+def _param(t, plan: _Plan):
+    t = t.detach()
+    if t.dtype == plan.pt and tuple(t.shape) == plan.pshape and t.is_contiguous():
+        return t  # the common case: float32 parameters of the parameter shape
+    return t.expand(plan.pshape).to(plan.pt).contiguous()
+
+
 def _params(scale, offset, plan: _Plan):
-    s = scale.detach().expand(plan.pshape).to(plan.pt).contiguous()
-    o = offset.detach().expand(plan.pshape).to(plan.pt).contiguous()
-    return s, o
+    return _param(scale, plan), _param(offset, plan)
 
 
 def _restore(y_dense: torch.Tensor, plan: _Plan, like: torch.Tensor) -> torch.Tensor:
@@ -233,6 +238,38 @@ _OPS_FWD = {
 }
 
 
+def _run_forward(tensor, scale, offset, op, qmin, qmax, zps, block_size, internal_dtype):
+    """Launch one forward kernel.  Returns (output, dense input view, scale, offset, plan)."""
+    x, plan = _prepare(tensor, scale, offset, block_size, internal_dtype)
+    s, o = _params(scale, offset, plan)
+    y = torch.empty_like(x, memory_format=torch.contiguous_format)
+    if x.numel() > 0:
+        pt = _lib.DTYPE_CODE[plan.pt]
+        with torch.cuda.device(x.device):
+            st = _lib.stream_ptr(x.device)
+            if op == "q":
+                rc = lib.aimet_b200_quantize(x.data_ptr(), y.data_ptr(), s.data_ptr(), o.data_ptr(), plan.layout,
+                                             plan.io, plan.ct, pt, qmin, qmax, st)
+            elif op == "dq":
+                rc = lib.aimet_b200_dequantize(x.data_ptr(), y.data_ptr(), s.data_ptr(), o.data_ptr(), plan.layout,
+                                               plan.io, plan.ct, pt, st)
+            elif op == "fq":
+                rc = lib.aimet_b200_fake_quantize(x.data_ptr(), y.data_ptr(), s.data_ptr(), o.data_ptr(), plan.layout,
+                                                  plan.io, qmin, qmax, st)
+            else:
+                rc = lib.aimet_b200_quantize_dequantize(x.data_ptr(), y.data_ptr(), s.data_ptr(), o.data_ptr(),
+                                                        plan.layout, plan.io, plan.ct, pt, qmin, qmax, float(zps), st)
+        _lib.check(rc)
+    return _restore(y, plan, tensor), x, s, o, plan
+
+
+def _apply(tensor, scale, offset, op, qmin, qmax, zps, block_size, internal_dtype):
+    """Through autograd only when a gradient can flow; otherwise straight to the kernel."""
+    if torch.is_grad_enabled() and (tensor.requires_grad or scale.requires_grad or offset.requires_grad):
+        return _AffineFunction.apply(tensor, scale, offset, op, qmin, qmax, zps, block_size, internal_dtype)
+    return _run_forward(tensor, scale, offset, op, qmin, qmax, zps, block_size, internal_dtype)[0]
+
+
 class _AffineFunction(torch.autograd.Function):
     """Forward and backward of the three affine functionals through the C ABI.
 
@@ -243,27 +280,7 @@ class _AffineFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, tensor, scale, offset, op, qmin, qmax, zps, block_size, internal_dtype):
-        x, plan = _prepare(tensor, scale, offset, block_size, internal_dtype)
-        s, o = _params(scale, offset, plan)
-        y = torch.empty_like(x, memory_format=torch.contiguous_format)
-        if x.numel() > 0:
-            with torch.cuda.device(x.device):
-                st = _lib.stream_ptr(x.device)
-                if op == "q":
-                    rc = lib.aimet_b200_quantize(x.data_ptr(), y.data_ptr(), s.data_ptr(), o.data_ptr(),
-                                                 plan.layout, plan.io, plan.ct, _lib.DTYPE_CODE[plan.pt],
-                                                 qmin, qmax, st)
-                elif op == "dq":
-                    rc = lib.aimet_b200_dequantize(x.data_ptr(), y.data_ptr(), s.data_ptr(), o.data_ptr(),
-                                                   plan.layout, plan.io, plan.ct, _lib.DTYPE_CODE[plan.pt], st)
-                elif op == "fq":
-                    rc = lib.aimet_b200_fake_quantize(x.data_ptr(), y.data_ptr(), s.data_ptr(), o.data_ptr(),
-                                                      plan.layout, plan.io, qmin, qmax, st)
-                else:
-                    rc = lib.aimet_b200_quantize_dequantize(x.data_ptr(), y.data_ptr(), s.data_ptr(),
-                                                            o.data_ptr(), plan.layout, plan.io, plan.ct,
-                                                            _lib.DTYPE_CODE[plan.pt], qmin, qmax, float(zps), st)
-            _lib.check(rc)
+        y, x, s, o, plan = _run_forward(tensor, scale, offset, op, qmin, qmax, zps, block_size, internal_dtype)
         ctx.plan = plan
         ctx.op, ctx.qmin, ctx.qmax, ctx.zps = op, qmin, qmax, float(zps)
         ctx.in_dtype = tensor.dtype
@@ -271,7 +288,7 @@ class _AffineFunction(torch.autograd.Function):
         ctx.offset_meta = (offset.shape, offset.dtype)
         if any(ctx.needs_input_grad[:3]):
             ctx.save_for_backward(x, s, o)
-        return _restore(y, plan, tensor)
+        return y
 
     @staticmethod
     def backward(ctx, grad):
@@ -340,7 +357,7 @@ def quantize(
     if not _is_grid_representable(input.dtype, qmin, qmax):
         raise RuntimeError(f"{input.dtype} is unable to represent quantized output of range [{qmin}, {qmax}].")
     internal = _internal_dtype(input.dtype, qmin, qmax)
-    return _AffineFunction.apply(input, scale, offset, "q", qmin, qmax, 0.0, block_size, internal)
+    return _apply(input, scale, offset, "q", qmin, qmax, 0.0, block_size, internal)
 
 
 def dequantize(
@@ -352,7 +369,7 @@ def dequantize(
     """``(input + offset) * scale`` evaluated in ``input.dtype`` (torch_builtins.py:537-571)."""
     block_size = _normalize_block_size(block_size)
     _validate(input, scale, offset, block_size=block_size)
-    return _AffineFunction.apply(input, scale, offset, "dq", 0, 0, 0.0, block_size, input.dtype)
+    return _apply(input, scale, offset, "dq", 0, 0, 0.0, block_size, input.dtype)
 
 
 def quantize_dequantize(
@@ -382,11 +399,11 @@ def quantize_dequantize(
     qmin, qmax = int(qmin), int(qmax)
     zero_point_shift = zero_point_shift or 0.0
     if _takes_fake_quantize_path(input, scale, offset, block_size, zero_point_shift):
-        return _AffineFunction.apply(input, scale.detach(), offset.detach(), "fq", qmin, qmax, 0.0, None, torch.float32)
+        return _apply(input, scale.detach(), offset.detach(), "fq", qmin, qmax, 0.0, None, torch.float32)
     internal = _internal_dtype(input.dtype, qmin, qmax)
     if not _is_grid_representable(internal, qmin, qmax):
         raise RuntimeError(f"{internal} is unable to represent quantized output of range [{qmin}, {qmax}].")
-    return _AffineFunction.apply(input, scale, offset, "qdq", qmin, qmax, zero_point_shift, block_size, internal)
+    return _apply(input, scale, offset, "qdq", qmin, qmax, zero_point_shift, block_size, internal)
 
 
 def _takes_fake_quantize_path(tensor, scale, offset, block_size, zero_point_shift) -> bool:

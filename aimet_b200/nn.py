@@ -1,0 +1,97 @@
+"""Quantized Conv2d / Linear wrappers and a model-level calibration context.
+
+A small mirror of the part of aimet_torch's quantized-module layer that BASELINE config 4
+exercises (nn/base.py:258-325 ``_patch_quantized_parameters``, nn/true_quant.py:600-616
+``_forward_no_dispatch``, nn/__init__.py:22-84 ``compute_encodings``): a wrapped layer quantizes its
+weight with ``param_quantizers["weight"]`` on every forward, its input with ``input_quantizers[0]``
+and its output with ``output_quantizers[0]``.  It is a caller of the hot path, not a QuantSim
+replacement: no config files, no graph analysis, no supergroups.
+"""
+
+from __future__ import annotations
+
+import contextlib
+from typing import Callable, Iterable, Optional
+
+import torch
+from torch import nn
+
+from .encoding_analyzer import MinMaxEncodingAnalyzer
+from .quantizer import QuantizeDequantize
+
+__all__ = ["QuantizedLayer", "quantize_model", "compute_encodings", "quantized_layers"]
+
+
+class QuantizedLayer(nn.Module):
+    """``out = Q_out(layer(Q_in(x)))`` with the layer's weight replaced by ``Q_w(weight)``."""
+
+    def __init__(self, layer: nn.Module, input_quantizer=None, output_quantizer=None, weight_quantizer=None):
+        super().__init__()
+        if not isinstance(layer, (nn.Conv2d, nn.Linear)):
+            raise NotImplementedError(f"QuantizedLayer wraps Conv2d and Linear, got {type(layer).__name__}")
+        self.layer = layer
+        self.input_quantizers = nn.ModuleList([input_quantizer])
+        self.output_quantizers = nn.ModuleList([output_quantizer])
+        self.param_quantizers = nn.ModuleDict({"weight": weight_quantizer, "bias": None})
+
+    @property
+    def weight(self):
+        return self.layer.weight
+
+    def forward(self, x):
+        qi, qo, qw = self.input_quantizers[0], self.output_quantizers[0], self.param_quantizers["weight"]
+        if qi is not None:
+            x = qi(x)
+        w = self.layer.weight if qw is None else qw(self.layer.weight)
+        if isinstance(self.layer, nn.Conv2d):
+            out = self.layer._conv_forward(x, w, self.layer.bias)  # pylint: disable=protected-access
+        else:
+            out = nn.functional.linear(x, w, self.layer.bias)
+        return out if qo is None else qo(out)
+
+
+def _per_channel_shape(weight: torch.Tensor):
+    return (weight.shape[0],) + (1,) * (weight.dim() - 1)
+
+
+def quantize_model(model: nn.Module, *, param_bw: int = 8, act_bw: int = 8,
+                   analyzer_factory: Optional[Callable] = None) -> nn.Module:
+    """Replace every Conv2d / Linear of ``model`` in place by a :class:`QuantizedLayer` with a
+    per-channel symmetric weight quantizer and per-tensor asymmetric input and output quantizers
+    (the layout BASELINE config 4 asks for).  ``analyzer_factory(shape)`` builds the activation
+    analyzers (default: min-max)."""
+    factory = analyzer_factory or (lambda shape: MinMaxEncodingAnalyzer(shape))
+    for name, child in list(model.named_children()):
+        if isinstance(child, (nn.Conv2d, nn.Linear)):
+            dev = child.weight.device
+            wrapped = QuantizedLayer(
+                child,
+                QuantizeDequantize((), act_bw, False, encoding_analyzer=factory(())),
+                QuantizeDequantize((), act_bw, False, encoding_analyzer=factory(())),
+                QuantizeDequantize(_per_channel_shape(child.weight), param_bw, True),
+            ).to(dev)
+            setattr(model, name, wrapped)
+        else:
+            quantize_model(child, param_bw=param_bw, act_bw=act_bw, analyzer_factory=analyzer_factory)
+    return model
+
+
+def quantized_layers(model: nn.Module) -> Iterable[QuantizedLayer]:
+    return (m for m in model.modules() if isinstance(m, QuantizedLayer))
+
+
+@contextlib.contextmanager
+def compute_encodings(model: nn.Module):
+    """Calibrate every quantizer of the model from the forward passes run inside the context:
+    weights are calibrated on entry, activation quantizers observe (pass-through) and get their
+    ranges on exit."""
+    with contextlib.ExitStack() as stack:
+        for layer in quantized_layers(model):
+            qw = layer.param_quantizers["weight"]
+            if qw is not None:
+                with qw.compute_encodings():
+                    qw(layer.layer.weight.detach())
+            for q in (*layer.input_quantizers, *layer.output_quantizers):
+                if q is not None:
+                    stack.enter_context(q._compute_encodings(passthrough=True))  # pylint: disable=protected-access
+        yield

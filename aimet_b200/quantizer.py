@@ -372,15 +372,32 @@ class AffineQuantizerBase(QuantizerBase):
         if max is not None:
             self.max.copy_(max if isinstance(max, torch.Tensor) else torch.tensor(max))
 
+    def _encoding_cache_key(self):
+        # parameters are versioned tensors: an in-place update or a re-assignment changes the key
+        return (id(self.min), self.min._version, id(self.max), self.max._version, self.min.device, self.min.dtype, self.qmin,  # pylint: disable=protected-access
+                self.qmax, self._symmetric, self.block_size, self.zero_point_shift)
+
     def get_encodings(self) -> Optional[AffineEncoding]:
         if self._pinned_encoding is not None:
             return self._pinned_encoding
+        # inference: scale / offset only change when the parameters do, so they are derived once
+        # (the reference offers the same through its _precompute_encodings context)
+        cacheable = not torch.is_grad_enabled() and type(self).get_scale is AffineQuantizerBase.get_scale
+        if cacheable:
+            key = self._encoding_cache_key()
+            cached = getattr(self, "_encoding_cache", None)
+            if cached is not None and cached[0] == key:
+                return cached[1]
         scale = self.get_scale(dtype=torch.float32)
         if scale is None:
             return None
         offset = self._get_offset(scale=scale, dtype=torch.float32)
-        return AffineEncoding(scale, offset, self.qmin, self.qmax, self._symmetric, self.block_size,
-                              self.zero_point_shift, producer=self)
+        enc = AffineEncoding(scale, offset, self.qmin, self.qmax, self._symmetric, self.block_size,
+                             self.zero_point_shift, producer=self)
+        if cacheable:
+            enc.scale, enc.offset = scale.detach().contiguous(), offset.detach().contiguous()
+            object.__setattr__(self, "_encoding_cache", (key, enc))
+        return enc
 
     def _get_dummy_encoding(self) -> AffineEncoding:
         device = self.min.device

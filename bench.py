@@ -221,20 +221,23 @@ class HostStep:
         for q in self.mods:
             with q.compute_encodings():
                 q(wd)
-        self.h2d = 3 * (self.w_host.numel() + self.dy_host.numel()) * 2
+        self.h2d = (self.w_host.numel() + self.dy_host.numel()) * 2
         self.d2h = 0
 
     def run(self):
-        d2h = 0
+        # one step: the weight and the upstream gradient come from pinned host memory once, then the
+        # three encodings run on them; parameter gradients and a checksum go back to the host
+        w = self.w_host.to(self.dev, non_blocking=True)
+        dy = self.dy_host.to(self.dev, non_blocking=True)
+        outs = []
         for q in self.mods:
-            w = self.w_host.to(self.dev, non_blocking=True).requires_grad_(True)
-            dy = self.dy_host.to(self.dev, non_blocking=True)
+            wi = w.detach().requires_grad_(True)
             q.min.grad = q.max.grad = None
-            y = q(w)
+            y = q(wi)
             y.backward(dy)
-            res = torch.cat([q.min.grad.flatten(), q.max.grad.flatten(), w.grad.float().sum().reshape(1)]).cpu()
-            d2h += res.numel() * 4
-        self.d2h = d2h
+            outs += [q.min.grad.flatten(), q.max.grad.flatten(), wi.grad.float().sum().reshape(1)]
+        res = torch.cat(outs).cpu()
+        self.d2h = res.numel() * 4
         return res
 
 
@@ -379,6 +382,64 @@ def seqmse_figure(dev, rank, world, m=8192, n=4096, k=4096, cands=20):
             "best_index_histogram": torch.bincount(loss.argmin(0), minlength=cands).tolist()}
 
 
+def resnet50_figure(dev, batch=256):
+    """Config 4: forward of a random-init ResNet-50 at batch 256 (224x224 fp32, N(0,1)) with per-channel
+    int8 weight QDQ and per-tensor int8 QDQ on the input and output of all 54 conv / linear layers
+    (the reference's QuantSim model builder is replaced by ``aimet_b200.nn.quantize_model``).
+    QDQ share = 1 - plain forward time / quantized forward time."""
+    try:
+        import torchvision
+    except ImportError:
+        return {"unavailable": "torchvision is not installed"}
+    from aimet_b200 import nn as qnn
+
+    torch.manual_seed(4000)
+    model = torchvision.models.resnet50(weights=None).eval().to(dev)
+    x = torch.randn(batch, 3, 224, 224, device=dev)
+
+    def timed(m, reps=5):
+        with torch.no_grad():
+            for _ in range(2):
+                m(x)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                m(x)
+            e1.record()
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    plain_ms = timed(model)
+    qmodel = qnn.quantize_model(model)
+    with torch.no_grad(), qnn.compute_encodings(qmodel):
+        qmodel(x[:32])
+    quant_ms = timed(qmodel)
+    layers = list(qnn.quantized_layers(qmodel))
+    act_elems, w_elems = 0, 0
+    hooks = []
+
+    def count(_m, inp, out):
+        nonlocal act_elems
+        act_elems += inp[0].numel() + out.numel()
+
+    for layer in layers:
+        hooks.append(layer.register_forward_hook(count))
+        w_elems += layer.weight.numel()
+    with torch.no_grad():
+        qmodel(x)
+    for h in hooks:
+        h.remove()
+    qdq_bytes = (act_elems + w_elems) * 8
+    peaks, kind = measured_peaks()
+    qdq_ms = quant_ms - plain_ms
+    return {"metric": "quantsim_resnet50_images_per_s", "value": batch / (quant_ms * 1e-3), "unit": "images/s",
+            "batch": batch, "quantized_layers": len(layers), "forward_ms": quant_ms, "plain_forward_ms": plain_ms,
+            "qdq_ms": qdq_ms, "qdq_share": qdq_ms / quant_ms, "qdq_algorithmic_bytes": qdq_bytes,
+            "qdq_achieved_GBps": qdq_bytes / (qdq_ms * 1e-3) / 1e9,
+            "qdq_frac_of_" + kind + "_hbm": qdq_bytes / (qdq_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+
+
 def base_config(n_gpus):
     return {"workload": "configs[1]: Llama-3-8B MLP weight [14336,4096] bf16 QDQ fwd+bwd: per-channel int8 + "
                         "blockwise int4 (block 64) + LPBQ (int4, 8-bit per-channel scale), scale grads on",
@@ -511,6 +572,9 @@ def run_ours(args):
         extras["calibration"] = calibration_figure(dev, rank, world)
         torch.cuda.empty_cache()
         extras["seqmse"] = seqmse_figure(dev, rank, world)
+        if world == 1:  # a model forward does not shard: replicas only
+            torch.cuda.empty_cache()
+            extras["quantsim_resnet50"] = resnet50_figure(dev)
     if rank == 0:
         out.update(extras)
         print(json.dumps(out))
