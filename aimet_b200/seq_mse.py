@@ -168,6 +168,24 @@ class SequentialMse:
         quantizer.set_range(probe.min, probe.max)
 
     @classmethod
+    def _candidate_encodings(cls, quantizer: AffineQuantizerBase, x_min: torch.Tensor, x_max: torch.Tensor):
+        """The (min, max) that :meth:`compute_param_encodings` would set, computed with a handful of
+        tensor ops instead of a throw-away quantizer: the min-max statistics of the stacked pair
+        (x_min, x_max) reduced to the quantizer's shape, then the min-max analyzer's range rule."""
+        from .encoding_analyzer import MinMaxEncodingAnalyzer, _MinMaxRange
+
+        shape = tuple(quantizer.shape)
+        lo, hi = torch.minimum(x_min, x_max), torch.maximum(x_min, x_max)
+        lo, hi = torch.broadcast_tensors(lo, hi)
+        pad = (1,) * (lo.dim() - len(shape)) + shape
+        dims = tuple(d for d, (have, want) in enumerate(zip(lo.shape, pad)) if have != want)
+        if dims:
+            lo, hi = lo.amin(dims, keepdim=True), hi.amax(dims, keepdim=True)
+        lo, hi = lo.reshape(shape), hi.reshape(shape)
+        steps = quantizer.qmax - quantizer.qmin - (1 if quantizer.zero_point_shift == 0.5 else 0)
+        return MinMaxEncodingAnalyzer(shape).compute_encodings_from_stats(_MinMaxRange(lo, hi), steps, quantizer.symmetric)
+
+    @classmethod
     def _freeze_quantizer_encoding(cls, quantizer):
         quantizer.requires_grad_(False)
         quantizer.allow_overwrite(False)
@@ -232,7 +250,7 @@ class SequentialMse:
         wq_all = torch.empty((c, out_ch, in_ch), dtype=w.dtype, device=w.device)
         for i in range(c):
             cmin, cmax = cls._get_candidate(i, c, min_t, max_t)
-            cls.compute_param_encodings(qtz, cmin, cmax)
+            qtz.set_range(*cls._candidate_encodings(qtz, cmin, cmax))
             wq_all[i].copy_(cls._get_quantized_weight(quant_module).detach())
 
         lowp = not params.precise_loss and w.dtype != torch.float32
@@ -260,7 +278,7 @@ class SequentialMse:
         while best.dim() < max_t.dim():
             best = best[..., None]
         bmin, bmax = cls._get_candidate(best, c, min_t, max_t)
-        cls.compute_param_encodings(qtz, bmin, bmax)
+        qtz.set_range(*cls._candidate_encodings(qtz, bmin, bmax))
         cls._freeze_quantizer_encoding(qtz)
         return best
 
