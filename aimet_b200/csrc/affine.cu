@@ -319,58 +319,115 @@ template <int CT> __device__ __forceinline__ bool vec_fast_ok(const Enc<CT> &e, 
     return e.fast && !g.has_zps && int_offset && lowp_ok;
 }
 
-template <int CT, int OP, int NV>
-__device__ __forceinline__ void fwd_vec_fast(float (&f)[NV], const Enc<CT> &e, const Grid<float> &g) {
+// x / s by reciprocal and exact remainder.  GUARD keeps q0 when it is infinite or absurdly large
+// (the remainder would be NaN); without it the caller has bounded |x| beforehand (clamp_abs16).
+template <bool GUARD> __device__ __forceinline__ float div_fast(float x, float s, float r) {
+    const float q0 = __fmul_rn(x, r);
+    float rem = __fmaf_rn(-q0, s, x);
+    if (GUARD) rem = fabsf(q0) < 1.2676506e30f ? rem : 0.0f;
+    return __fmaf_rn(rem, r, q0);
+}
+
+// The same for two values at once with the two-wide float instructions (one issue slot for both).
+template <bool GUARD> __device__ __forceinline__ float2 div_fast2(float2 x, float s, float r) {
+    const float2 q0 = __fmul2_rn(x, make_float2(r, r));
+    float2 rem = __ffma2_rn(q0, make_float2(-s, -s), x);  // x - q0 * s, exact
+    if (GUARD) {
+        rem.x = fabsf(q0.x) < 1.2676506e30f ? rem.x : 0.0f;
+        rem.y = fabsf(q0.y) < 1.2676506e30f ? rem.y : 0.0f;
+    }
+    return __ffma2_rn(rem, make_float2(r, r), q0);
+}
+
+// The clamp is applied to round(v) + magic against (o + qmin) + magic and (o + qmax) + magic,
+// which is clamp(round(v) - o, qmin, qmax) + o on exact integers; quantize subtracts magic + o
+// afterwards, quantize-dequantize subtracts magic and multiplies by the scale.
+template <int CT, int OP, int NV, bool GUARD>
+__device__ __forceinline__ void fwd_vec_fast(float (&f)[NV], const Enc<CT> &e) {
     using A = Arith<CT>;
-    const float s = (float)e.s, r = (float)e.r, o = (float)e.o;
-    const float c_sub = __fadd_rn(kMagic, o);  // exact: |o| < 2^22
+    const float s = (float)e.s, r = (float)e.r;
+    const float c_lo = __fadd_rn(kMagic, (float)e.lo), c_hi = __fadd_rn(kMagic, (float)e.hi);  // exact: |lo|, |hi| < 2^22
+    const float c_back = OP == OP_QDQ ? kMagic : __fadd_rn(kMagic, (float)e.o);
 #pragma unroll
     for (int i = 0; i < NV; i += 2) {
-        float a = div_scale_f32(f[i], s, r, true), b = div_scale_f32(f[i + 1], s, r, true);
-        A::rnd2(a, b);
-        a = __fsub_rn(__fadd_rn(a, kMagic), c_sub);
-        b = __fsub_rn(__fadd_rn(b, kMagic), c_sub);
-        a = clamp_prop(a, g.qmin, g.qmax);
-        b = clamp_prop(b, g.qmin, g.qmax);
-        if (OP == OP_QDQ) {
-            a = __fmul_rn(__fadd_rn(a, o), s);
-            b = __fmul_rn(__fadd_rn(b, o), s);
+        if constexpr (CT == AB_F32) {
+            float2 t = __fadd2_rn(div_fast2<GUARD>(make_float2(f[i], f[i + 1]), s, r), make_float2(kMagic, kMagic));
+            t.x = clamp_prop(t.x, c_lo, c_hi);
+            t.y = clamp_prop(t.y, c_lo, c_hi);
+            t = __fadd2_rn(t, make_float2(-c_back, -c_back));
+            if (OP == OP_QDQ) t = __fmul2_rn(t, make_float2(s, s));
+            f[i] = t.x;
+            f[i + 1] = t.y;
+        } else {
+            float a = div_fast<GUARD>(f[i], s, r), b = div_fast<GUARD>(f[i + 1], s, r);
+            A::rnd2(a, b);
+            a = __fsub_rn(clamp_prop(__fadd_rn(a, kMagic), c_lo, c_hi), c_back);
+            b = __fsub_rn(clamp_prop(__fadd_rn(b, kMagic), c_lo, c_hi), c_back);
+            if (OP == OP_QDQ) {
+                a = __fmul_rn(a, s);
+                b = __fmul_rn(b, s);
+            }
+            f[i] = a;
+            f[i + 1] = b;
         }
-        f[i] = a;
-        f[i + 1] = b;
     }
 }
 
-template <int CT, bool WANT_O, int NV>
-__device__ __forceinline__ void bwd_vec_fast(float (&x)[NV], const float (&gy)[NV], const Enc<CT> &e,
-                                             const Grid<float> &g, float &acc_s, float &acc_o) {
+// Backward of quantize-dequantize: x[] becomes the input gradient, the scale-gradient terms are
+// added to acc_s.  An element is inside the grid exactly when clamping round(x / s) to
+// [o + qmin, o + qmax] leaves it unchanged (NaN compares unequal, as in the reference's mask).
+// The offset-gradient terms are added by the caller, which finds the (rare) masked elements by
+// comparing the input gradient with the upstream gradient.
+template <int CT, int NV, bool GUARD>
+__device__ __forceinline__ void bwd_vec_fast(float (&x)[NV], const float (&gy)[NV], const Enc<CT> &e, float &acc_s,
+                                             float &acc_s2) {
     using A = Arith<CT>;
-    const float s = (float)e.s, r = (float)e.r, o = (float)e.o;
-    const float c_sub = __fadd_rn(kMagic, o);
+    const float s = (float)e.s, r = (float)e.r;
     const float lo = (float)e.lo, hi = (float)e.hi;
 #pragma unroll
     for (int i = 0; i < NV; i += 2) {
-        float sa = div_scale_f32(x[i], s, r, true), sb = div_scale_f32(x[i + 1], s, r, true);
-        A::rnd2(sa, sb);
-        const float ta = __fadd_rn(sa, kMagic), tb = __fadd_rn(sb, kMagic);
-        const float ra = __fsub_rn(ta, kMagic), rb = __fsub_rn(tb, kMagic);  // round(x / s)
-        const float qa = __fsub_rn(ta, c_sub), qb = __fsub_rn(tb, c_sub);    // round(x / s) - o
-        const bool ina = (g.qmin <= qa) && (qa <= g.qmax);
-        const bool inb = (g.qmin <= qb) && (qb <= g.qmax);
-        float da = __fmul_rn(gy[i], ina ? __fsub_rn(ra, sa) : clamp_prop(ra, lo, hi));
-        float db = __fmul_rn(gy[i + 1], inb ? __fsub_rn(rb, sb) : clamp_prop(rb, lo, hi));
-        A::rnd2(da, db);
-        acc_s += da;
-        acc_s += db;
-        if (WANT_O) {
-            float oa = __fmul_rn(gy[i], s), ob = __fmul_rn(gy[i + 1], s);
-            A::rnd2(oa, ob);
-            acc_o += ina ? 0.0f : oa;
-            acc_o += inb ? 0.0f : ob;
+        if constexpr (CT == AB_F32) {
+            // float32 arithmetic: two elements per instruction, and the product gy * term goes into
+            // the running sums (one per element parity) through an fma, i.e. without the
+            // intermediate rounding of the product -- the sums differ from any summation order of
+            // the rounded products by less than that rounding
+            const float2 sa = div_fast2<GUARD>(make_float2(x[i], x[i + 1]), s, r);
+            const float2 ra = __fadd2_rn(__fadd2_rn(sa, make_float2(kMagic, kMagic)), make_float2(-kMagic, -kMagic));
+            const float2 err = __ffma2_rn(sa, make_float2(-1.0f, -1.0f), ra);  // round(x / s) - x / s
+            const float ca = clamp_prop(ra.x, lo, hi), cb = clamp_prop(ra.y, lo, hi);
+            const bool ina = ca == ra.x, inb = cb == ra.y;
+            const float2 acc = __ffma2_rn(make_float2(gy[i], gy[i + 1]), make_float2(ina ? err.x : ca, inb ? err.y : cb),
+                                          make_float2(acc_s, acc_s2));
+            acc_s = acc.x;
+            acc_s2 = acc.y;
+            x[i] = ina ? gy[i] : 0.0f;
+            x[i + 1] = inb ? gy[i + 1] : 0.0f;
+        } else {
+            float sa = div_fast<GUARD>(x[i], s, r), sb = div_fast<GUARD>(x[i + 1], s, r);
+            A::rnd2(sa, sb);
+            const float ra = __fsub_rn(__fadd_rn(sa, kMagic), kMagic), rb = __fsub_rn(__fadd_rn(sb, kMagic), kMagic);
+            const float ca = clamp_prop(ra, lo, hi), cb = clamp_prop(rb, lo, hi);
+            const bool ina = ca == ra, inb = cb == rb;
+            float da = __fmul_rn(gy[i], ina ? __fsub_rn(ra, sa) : ca);
+            float db = __fmul_rn(gy[i + 1], inb ? __fsub_rn(rb, sb) : cb);
+            A::rnd2(da, db);
+            acc_s += da;
+            acc_s2 += db;
+            x[i] = ina ? gy[i] : 0.0f;
+            x[i + 1] = inb ? gy[i + 1] : 0.0f;
         }
-        x[i] = ina ? gy[i] : 0.0f;
-        x[i + 1] = inb ? gy[i + 1] : 0.0f;
     }
+}
+
+// Offset-gradient terms of one vector, given the upstream gradient and the input gradient just
+// computed from it: an element was masked exactly when the two differ bitwise (a masked zero
+// contributes nothing either way).  Only called for vectors that contain such an element.
+template <int CT, int NV>
+__device__ __forceinline__ void bwd_offset_terms(const float (&dx)[NV], const float (&gy)[NV], float s, float &acc_o) {
+    using A = Arith<CT>;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+        if (__float_as_uint(dx[i]) != __float_as_uint(gy[i])) acc_o += A::rnd(__fmul_rn(gy[i], s));
 }
 
 // ---------------------------------------------------------------------------
@@ -418,58 +475,92 @@ template <typename H2> __device__ __forceinline__ H2 bit_select(H2 a, H2 b, unsi
     return *reinterpret_cast<const H2 *>(&r);
 }
 
+// Bound on |x| for 16-bit tensors, applied to the packed input before the division so that
+// x * (1/s) cannot overflow: (largest clamp bound + 4) * |s| with some slack, as a pair of the
+// tensor's own 16-bit type.  Returns false when that bound is not finite in the type.
+template <int IO, int CT> __device__ __forceinline__ bool abs_bound16(const Enc<CT> &e, uint32_t &big2) {
+    using P = Packed<IO>;
+    const float bound = fmaxf(fabsf((float)e.lo), fabsf((float)e.hi));
+    const float big = (bound + 4.0f) * fabsf((float)e.s) * 1.0625f;
+    const typename P::H2 h = P::dup(big);
+    big2 = *reinterpret_cast<const uint32_t *>(&h);
+    return e.fast && P::lo(h) < 3.0e38f && P::lo(h) >= big * 0.99f;
+}
+template <int IO, typename E> __device__ __forceinline__ void clamp_abs16(Vec16<E> &v, uint32_t big2) {
+    using H2 = typename Packed<IO>::H2;
+    const uint32_t nb = big2 ^ 0x80008000u;
+    const H2 pos = *reinterpret_cast<const H2 *>(&big2), neg = *reinterpret_cast<const H2 *>(&nb);
+    H2 *w = reinterpret_cast<H2 *>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = __hmin2_nan(__hmax2_nan(w[i], neg), pos);
+}
+
 // E is the 16-bit tensor element type matching CT
-template <int CT, int OP, typename E>
-__device__ __forceinline__ void fwd_vec_packed(const Vec16<E> &in, Vec16<E> &out, const Enc<CT> &e, const Grid<float> &g) {
+template <int CT, int OP, typename E, bool GUARD>
+__device__ __forceinline__ void fwd_vec_packed(const Vec16<E> &in, Vec16<E> &out, const Enc<CT> &e) {
     using P = Packed<CT>;
     using H2 = typename P::H2;
-    const float s = (float)e.s, r = (float)e.r, o = (float)e.o;
-    const H2 magic = P::dup(P::kMagic16), csub = P::dup(P::kMagic16 + o);
-    const H2 qmin = P::dup(g.qmin), qmax = P::dup(g.qmax), o2 = P::dup(o), s2 = P::dup(s);
+    const float s = (float)e.s, r = (float)e.r;
+    const H2 magic = P::dup(P::kMagic16), s2 = P::dup(s);
+    const H2 c_lo = P::dup(P::kMagic16 + (float)e.lo), c_hi = P::dup(P::kMagic16 + (float)e.hi);
+    const H2 c_back = OP == OP_QDQ ? magic : P::dup(P::kMagic16 + (float)e.o);
     const H2 *ip = reinterpret_cast<const H2 *>(&in);
     H2 *op = reinterpret_cast<H2 *>(&out);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float a = div_scale_f32(P::lo(ip[i]), s, r, true), b = div_scale_f32(P::hi(ip[i]), s, r, true);
-        H2 q = __hsub2(__hadd2(P::pack(a, b), magic), csub);
-        q = __hmin2_nan(__hmax2_nan(q, qmin), qmax);
-        op[i] = OP == OP_QDQ ? __hmul2(__hadd2(q, o2), s2) : q;
+        const float2 ab = div_fast2<GUARD>(make_float2(P::lo(ip[i]), P::hi(ip[i])), s, r);
+        H2 q = __hadd2(P::pack(ab.x, ab.y), magic);
+        q = __hsub2(__hmin2_nan(__hmax2_nan(q, c_lo), c_hi), c_back);
+        op[i] = OP == OP_QDQ ? __hmul2(q, s2) : q;
     }
 }
 
-template <int CT, bool WANT_O, typename E>
+template <int CT, typename E, bool GUARD>
 __device__ __forceinline__ void bwd_vec_packed(const Vec16<E> &x, const Vec16<E> &gy, Vec16<E> &dx, const Enc<CT> &e,
-                                               const Grid<float> &g, float &acc_s, float &acc_o) {
+                                               float &acc_s, float &acc_s2) {
     using P = Packed<CT>;
     using H2 = typename P::H2;
-    const float s = (float)e.s, r = (float)e.r, o = (float)e.o;
-    const H2 magic = P::dup(P::kMagic16), csub = P::dup(P::kMagic16 + o);
-    const H2 qmin = P::dup(g.qmin), qmax = P::dup(g.qmax), lo2 = P::dup((float)e.lo), hi2 = P::dup((float)e.hi);
-    const H2 s2 = P::dup(s);
+    const float s = (float)e.s, r = (float)e.r;
+    const H2 magic = P::dup(P::kMagic16);
+    const H2 lo2 = P::dup((float)e.lo), hi2 = P::dup((float)e.hi);
     const H2 *xp = reinterpret_cast<const H2 *>(&x);
     const H2 *gp = reinterpret_cast<const H2 *>(&gy);
     unsigned *dp = reinterpret_cast<unsigned *>(&dx);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float a = div_scale_f32(P::lo(xp[i]), s, r, true), b = div_scale_f32(P::hi(xp[i]), s, r, true);
-        const H2 v = P::pack(a, b);                 // x / s in the internal dtype
-        const H2 t = __hadd2(v, magic);
-        const H2 rd = __hsub2(t, magic);            // round(x / s)
-        const H2 q = __hsub2(t, csub);              // round(x / s) - o
-        const unsigned m = __hge2_mask(q, qmin) & __hle2_mask(q, qmax);
-        const H2 sel = bit_select(__hsub2(rd, v), __hmin2_nan(__hmax2_nan(rd, lo2), hi2), m);
-        const H2 d = __hmul2(gp[i], sel);
+        const float2 ab = div_fast2<GUARD>(make_float2(P::lo(xp[i]), P::hi(xp[i])), s, r);
+        const H2 v = P::pack(ab.x, ab.y);                    // x / s in the internal dtype
+        const H2 rd = __hsub2(__hadd2(v, magic), magic);     // round(x / s)
+        const H2 cl = __hmin2_nan(__hmax2_nan(rd, lo2), hi2);
+        const unsigned m = __heq2_mask(cl, rd);              // inside the grid (false for NaN)
+        const H2 d = __hmul2(gp[i], bit_select(__hsub2(rd, v), cl, m));
         acc_s += P::lo(d);
-        acc_s += P::hi(d);
-        if (WANT_O) {
-            H2 od = __hmul2(gp[i], s2);
-            const unsigned uo = *reinterpret_cast<unsigned *>(&od) & ~m;
-            od = *reinterpret_cast<const H2 *>(&uo);
-            acc_o += P::lo(od);
-            acc_o += P::hi(od);
-        }
+        acc_s2 += P::hi(d);
         dp[i] = *reinterpret_cast<const unsigned *>(&gp[i]) & m;
     }
+}
+
+// Offset-gradient terms of one packed vector (see bwd_offset_terms).
+template <int CT, typename E>
+__device__ __forceinline__ void bwd_offset_terms_packed(const Vec16<E> &dx, const Vec16<E> &gy, float s, float &acc_o) {
+    using P = Packed<CT>;
+    using H2 = typename P::H2;
+    const H2 s2 = P::dup(s);
+    const H2 *gp = reinterpret_cast<const H2 *>(&gy);
+    const unsigned *dw = reinterpret_cast<const unsigned *>(&dx);
+    const unsigned *gw = reinterpret_cast<const unsigned *>(&gy);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const unsigned diff = dw[i] ^ gw[i];
+        const H2 od = __hmul2(gp[i], s2);
+        if (diff & 0xffffu) acc_o += P::lo(od);
+        if (diff >> 16) acc_o += P::hi(od);
+    }
+}
+
+template <typename E> __device__ __forceinline__ bool same_bits(const Vec16<E> &a, const Vec16<E> &b) {
+    const uint4 u = *reinterpret_cast<const uint4 *>(&a), w = *reinterpret_cast<const uint4 *>(&b);
+    return u.x == w.x && u.y == w.y && u.z == w.z && u.w == w.w;
 }
 
 // ---------------------------------------------------------------------------
@@ -519,7 +610,7 @@ __global__ void __launch_bounds__(kThreads) k_fwd_oci(FwdArgs a) {
                 bool done = false;
                 if constexpr (CT != AB_F64 && NV >= 2 && (OP == OP_QDQ || OP == OP_Q)) {
                     if (vec_fast_ok<CT>(e, g)) {
-                        fwd_vec_fast<CT, OP, NV>(f, e, g);
+                        fwd_vec_fast<CT, OP, NV, true>(f, e);
                         done = true;
                     }
                 }
@@ -548,8 +639,64 @@ __global__ void __launch_bounds__(kThreads) k_fwd_oci(FwdArgs a) {
     }
 }
 
-// Forward over runs of elements that share a parameter: a group of threads per run, each thread
-// loading its parameter pair once and streaming several 16-byte vectors of the run.
+// ---------------------------------------------------------------------------
+// Segment kernels: a group of threads (a power of two) per contiguous run of elements that share
+// a parameter ("pseudo-segment"; long runs are cut into several).  A thread sets up its parameter
+// pair once, picks one of the loop bodies below and streams 16-byte vectors of its run.
+// ---------------------------------------------------------------------------
+struct SegPos {
+    int64_t s;      // pseudo-segment index
+    int64_t v0;     // first 16-byte vector of the run
+    int64_t param;  // parameter index
+    int nv;         // vectors in the run
+    int lane;       // position in the group
+    bool valid;
+};
+
+template <int VEC>
+__device__ __forceinline__ SegPos seg_pos(const ChanMap &cm, int64_t seg_len, int64_t nseg, int64_t nchunk, int group) {
+    SegPos p;
+    const int glog = 31 - __clz(group);
+    const unsigned gi = threadIdx.x >> glog;
+    p.lane = (int)(threadIdx.x & (unsigned)(group - 1));
+    const unsigned gpc = (unsigned)kThreads >> glog;
+    if (cm.narrow) {  // everything fits 32 bits
+        const uint32_t s = blockIdx.x * gpc + gi;
+        p.s = s;
+        p.valid = s < (uint32_t)nseg;
+        uint32_t ts = s, k = 0;
+        if (nchunk > 1) {
+            ts = s / (uint32_t)nchunk;
+            k = s - ts * (uint32_t)nchunk;
+        }
+        const uint32_t I = (uint32_t)cm.I, sl = (uint32_t)seg_len;
+        const uint32_t start = ts * I + k * sl;
+        uint32_t len = I - k * sl;
+        if (len > sl) len = sl;
+        p.param = cm.C == 1 ? 0 : (!cm.wrap ? ts : ts % (uint32_t)cm.C);
+        p.v0 = start / VEC;
+        p.nv = (int)(len / VEC);
+    } else {
+        const int64_t s = (int64_t)blockIdx.x * gpc + gi;
+        p.s = s;
+        p.valid = s < nseg;
+        int64_t ts = s, k = 0;
+        if (nchunk > 1) {
+            ts = s / nchunk;
+            k = s - ts * nchunk;
+        }
+        const int64_t start = ts * cm.I + k * seg_len;
+        int64_t len = cm.I - k * seg_len;
+        if (len > seg_len) len = seg_len;
+        p.param = cm.C == 1 ? 0 : (!cm.wrap ? ts : ts % cm.C);
+        p.v0 = start / VEC;
+        p.nv = (int)(len / VEC);
+    }
+    return p;
+}
+
+enum { PATH_GENERIC = 0, PATH_FAST = 1, PATH_PACKED = 2 };
+
 struct FwdSegArgs {
     const void *x;
     void *y;
@@ -561,81 +708,88 @@ struct FwdSegArgs {
     int exact_edges;
 };
 
+template <int IO, int CT, int OP, int PATH, bool PRE>
+__device__ __forceinline__ void fwd_vec(Vec16<typename Elem<IO>::type> xv, Vec16<typename Elem<IO>::type> &yv,
+                                        const Enc<CT> &e, const Grid<typename Arith<CT>::T> &g, uint32_t big2) {
+    using E = typename Elem<IO>::type;
+    using T = typename Arith<CT>::T;
+    constexpr int NV = 16 / (int)sizeof(E);
+    if constexpr (PRE) clamp_abs16<IO, E>(xv, big2);
+    if constexpr (PATH == PATH_PACKED) {
+        fwd_vec_packed<CT, OP, E, !PRE>(xv, yv, e);
+    } else {
+        T f[NV];
+        VecCvt<T, E>::unpack(xv, f);
+        if constexpr (PATH == PATH_FAST) {
+            fwd_vec_fast<CT, OP, NV, !PRE>(f, e);
+        } else {
+#pragma unroll
+            for (int i = 0; i + 1 < NV; i += 2) fwd_pair<CT, OP>(f[i], f[i + 1], e, g);
+        }
+        VecCvt<T, E>::pack(f, yv);
+    }
+}
+
+template <int IO, int CT, int OP, int PATH, bool PRE>
+__device__ __forceinline__ void fwd_seg_loop(const Vec16<typename Elem<IO>::type> *__restrict__ px,
+                                             Vec16<typename Elem<IO>::type> *__restrict__ py, int lane, int nv, int G,
+                                             const Enc<CT> &e, const Grid<typename Arith<CT>::T> &g, uint32_t big2) {
+    using E = typename Elem<IO>::type;
+    constexpr int U = 4;
+    int v = lane;
+    const int step = U * G;
+    for (; v + (U - 1) * G < nv; v += step, px += step, py += step) {
+        Vec16<E> xv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) xv[u] = px[u * G];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            Vec16<E> yv;
+            fwd_vec<IO, CT, OP, PATH, PRE>(xv[u], yv, e, g, big2);
+            py[u * G] = yv;
+        }
+    }
+    for (; v < nv; v += G, px += G, py += G) {
+        Vec16<E> yv;
+        fwd_vec<IO, CT, OP, PATH, PRE>(*px, yv, e, g, big2);
+        *py = yv;
+    }
+}
+
 template <int IO, int CT, int OP>
 __global__ void __launch_bounds__(kThreads, 5) k_fwd_seg(FwdSegArgs a) {
     using E = typename Elem<IO>::type;
-    using A = Arith<CT>;
-    using T = typename A::T;
+    using T = typename Arith<CT>::T;
     constexpr int NV = 16 / (int)sizeof(E);
-    constexpr int U = 4;
+    constexpr bool kIo16 = IO == AB_BF16 || IO == AB_F16;
+    constexpr bool kQuant = OP == OP_QDQ || OP == OP_Q;
     const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0, a.exact_edges};
-    const Vec16<E> *__restrict__ xp = static_cast<const Vec16<E> *>(a.x);
-    Vec16<E> *__restrict__ yp = static_cast<Vec16<E> *>(a.y);
-
-    const int G = a.group;
-    const int64_t s = (int64_t)blockIdx.x * (kThreads / G) + threadIdx.x / G;
-    const int lane = threadIdx.x % G;
-    if (s >= a.nseg) return;
-    int64_t ts = s, k = 0;
-    if (a.nchunk > 1) {
-        if (a.cm.narrow) {
-            ts = (uint32_t)s / (uint32_t)a.nchunk;
-            k = (uint32_t)s - (uint32_t)ts * (uint32_t)a.nchunk;
-        } else {
-            ts = s / a.nchunk;
-            k = s - ts * a.nchunk;
-        }
-    }
-    const int64_t start = ts * a.cm.I + k * a.seg_len;
-    int64_t len = a.cm.I - k * a.seg_len;
-    if (len > a.seg_len) len = a.seg_len;
-    int64_t param;
-    if (a.cm.C == 1)
-        param = 0;
-    else if (!a.cm.wrap)
-        param = ts;
-    else
-        param = a.cm.narrow ? (int64_t)((uint32_t)ts % (uint32_t)a.cm.C) : ts % a.cm.C;
-    const Enc<CT> e = load_enc<CT>(a.scale, a.offset, param, g);
-    const bool fast_ok = vec_fast_ok<CT>(e, g);
-    const bool packed_ok = vec_packed_ok<CT>(e, g);
-    (void)fast_ok;
-    (void)packed_ok;
-    const int64_t nv = len / NV, v0 = start / NV;
-    for (int64_t v = lane; v < nv; v += (int64_t)U * G) {
-        Vec16<E> xv[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-            if (v + (int64_t)u * G < nv) xv[u] = xp[v0 + v + (int64_t)u * G];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            if (v + (int64_t)u * G >= nv) continue;
-            if constexpr ((CT == AB_BF16 || CT == AB_F16) && CT == IO && (OP == OP_QDQ || OP == OP_Q)) {
-                if (packed_ok) {
-                    Vec16<E> yp16;
-                    fwd_vec_packed<CT, OP, E>(xv[u], yp16, e, g);
-                    yp[v0 + v + (int64_t)u * G] = yp16;
-                    continue;
+    const SegPos p = seg_pos<NV>(a.cm, a.seg_len, a.nseg, a.nchunk, a.group);
+    if (!p.valid) return;
+    const Vec16<E> *px = static_cast<const Vec16<E> *>(a.x) + p.v0 + p.lane;
+    Vec16<E> *py = static_cast<Vec16<E> *>(a.y) + p.v0 + p.lane;
+    const Enc<CT> e = load_enc<CT>(a.scale, a.offset, p.param, g);
+    if constexpr (kQuant && kIo16) {
+        uint32_t big2;
+        if (abs_bound16<IO, CT>(e, big2)) {
+            if constexpr (CT == IO) {
+                if (vec_packed_ok<CT>(e, g)) {
+                    fwd_seg_loop<IO, CT, OP, PATH_PACKED, true>(px, py, p.lane, p.nv, a.group, e, g, big2);
+                    return;
                 }
             }
-            T f[NV];
-            VecCvt<T, E>::unpack(xv[u], f);
-            bool done = false;
-            if constexpr (CT != AB_F64 && NV >= 2 && (OP == OP_QDQ || OP == OP_Q)) {
-                if (fast_ok) {
-                    fwd_vec_fast<CT, OP, NV>(f, e, g);
-                    done = true;
-                }
+            if (vec_fast_ok<CT>(e, g)) {
+                fwd_seg_loop<IO, CT, OP, PATH_FAST, true>(px, py, p.lane, p.nv, a.group, e, g, big2);
+                return;
             }
-            if (!done) {
-#pragma unroll
-                for (int i = 0; i + 1 < NV; i += 2) fwd_pair<CT, OP>(f[i], f[i + 1], e, g);
-            }
-            Vec16<E> yv;
-            VecCvt<T, E>::pack(f, yv);
-            yp[v0 + v + (int64_t)u * G] = yv;
+        }
+    } else if constexpr (kQuant && CT != AB_F64) {
+        if (vec_fast_ok<CT>(e, g)) {
+            fwd_seg_loop<IO, CT, OP, PATH_FAST, false>(px, py, p.lane, p.nv, a.group, e, g, 0u);
+            return;
         }
     }
+    fwd_seg_loop<IO, CT, OP, PATH_GENERIC, false>(px, py, p.lane, p.nv, a.group, e, g, 0u);
 }
 
 struct FwdGenArgs {
@@ -693,6 +847,72 @@ template <int CT> __device__ __forceinline__ double finalize(double v) {
     return (double)A::rnd((T)v);
 }
 
+template <int IO, int CT, int OP, bool WANT_O, int PATH, bool PRE>
+__device__ __forceinline__ void bwd_vec(Vec16<typename Elem<IO>::type> xv, const Vec16<typename Elem<IO>::type> &gv,
+                                        Vec16<typename Elem<IO>::type> &dv, const Enc<CT> &e,
+                                        const Grid<typename Arith<CT>::T> &g, uint32_t big2,
+                                        typename Arith<CT>::T &acc_s, typename Arith<CT>::T &acc_s2,
+                                        typename Arith<CT>::T &acc_o) {
+    using E = typename Elem<IO>::type;
+    using T = typename Arith<CT>::T;
+    constexpr int NV = 16 / (int)sizeof(E);
+    if constexpr (PRE) clamp_abs16<IO, E>(xv, big2);
+    if constexpr (PATH == PATH_PACKED) {
+        bwd_vec_packed<CT, E, !PRE>(xv, gv, dv, e, acc_s, acc_s2);
+        if (WANT_O) {
+            if (!same_bits(dv, gv)) bwd_offset_terms_packed<CT, E>(dv, gv, (float)e.s, acc_o);
+        }
+    } else {
+        T fx[NV], fg[NV];
+        VecCvt<T, E>::unpack(xv, fx);
+        VecCvt<T, E>::unpack(gv, fg);
+        if constexpr (PATH == PATH_FAST) {
+            bwd_vec_fast<CT, NV, !PRE>(fx, fg, e, acc_s, acc_s2);
+            VecCvt<T, E>::pack(fx, dv);
+            if (WANT_O) {
+                if (!same_bits(dv, gv)) bwd_offset_terms<CT, NV>(fx, fg, (float)e.s, acc_o);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i + 1 < NV; i += 2)
+                bwd_pair<CT, OP, WANT_O>(fx[i], fx[i + 1], fg[i], fg[i + 1], e, g, acc_s, acc_o);
+            VecCvt<T, E>::pack(fx, dv);
+        }
+    }
+}
+
+template <int IO, int CT, int OP, bool WANT_O, int PATH, bool PRE>
+__device__ __forceinline__ void bwd_seg_loop(const Vec16<typename Elem<IO>::type> *__restrict__ px,
+                                             const Vec16<typename Elem<IO>::type> *__restrict__ pg,
+                                             Vec16<typename Elem<IO>::type> *__restrict__ pd, int lane, int nv, int G,
+                                             const Enc<CT> &e, const Grid<typename Arith<CT>::T> &g, uint32_t big2,
+                                             typename Arith<CT>::T &acc_s, typename Arith<CT>::T &acc_o) {
+    using E = typename Elem<IO>::type;
+    using T = typename Arith<CT>::T;
+    // the generic body also serves callers that want no input gradient; the others always store
+    constexpr bool kMayskip = PATH == PATH_GENERIC;
+    T acc_s2 = 0;
+    int v = lane;
+    const int step = 2 * G;
+    for (; v + G < nv; v += step, px += step, pg += step) {
+        const Vec16<E> xa = px[0], ga = pg[0], xb = px[G], gb = pg[G];
+        Vec16<E> da, db;
+        bwd_vec<IO, CT, OP, WANT_O, PATH, PRE>(xa, ga, da, e, g, big2, acc_s, acc_s2, acc_o);
+        if (!kMayskip || pd) pd[0] = da;
+        bwd_vec<IO, CT, OP, WANT_O, PATH, PRE>(xb, gb, db, e, g, big2, acc_s, acc_s2, acc_o);
+        if (!kMayskip || pd) {
+            pd[G] = db;
+            pd += step;
+        }
+    }
+    if (v < nv) {
+        Vec16<E> da;
+        bwd_vec<IO, CT, OP, WANT_O, PATH, PRE>(*px, *pg, da, e, g, big2, acc_s, acc_s2, acc_o);
+        if (!kMayskip || pd) *pd = da;
+    }
+    acc_s += acc_s2;
+}
+
 // One group of `group` threads per pseudo-segment; a pseudo-segment is a
 // contiguous run of elements that share one parameter.
 template <int IO, int CT, int OP, bool VECT, bool WANT_O>
@@ -702,122 +922,56 @@ __global__ void __launch_bounds__(kThreads, 4) k_bwd_seg(BwdArgs a) {
     using T = typename A::T;
     using C = Cvt<T, E>;
     constexpr int VEC = VECT ? 16 / (int)sizeof(E) : 1;
+    constexpr bool kIo16 = IO == AB_BF16 || IO == AB_F16;
     const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0, a.exact_edges};
-    const E *__restrict__ xp = static_cast<const E *>(a.x);
-    const E *__restrict__ gp = static_cast<const E *>(a.gy);
-    E *__restrict__ dxp = static_cast<E *>(a.gx);
 
     const int G = a.group;
-    const int groups_per_cta = kThreads / G;
-    const int64_t s = (int64_t)blockIdx.x * groups_per_cta + threadIdx.x / G;
-    const int lane = threadIdx.x % G;
-    const bool valid = s < a.nseg;
+    const SegPos p = seg_pos<VEC>(a.cm, a.seg_len, a.nseg, a.nchunk, G);
+    const int lane = p.lane;
+    const bool valid = p.valid;
+    const int64_t s = p.s, param = p.param;
 
     T acc_s = 0, acc_o = 0;
-    int64_t param = 0;
     if (valid) {
-        // pseudo-segment -> (true segment, chunk); 64-bit divisions are avoided where they can be
-        int64_t ts = s, k = 0;
-        if (a.nchunk > 1) {
-            if (a.cm.narrow) {
-                ts = (uint32_t)s / (uint32_t)a.nchunk;
-                k = (uint32_t)s - (uint32_t)ts * (uint32_t)a.nchunk;
-            } else {
-                ts = s / a.nchunk;
-                k = s - ts * a.nchunk;
-            }
-        }
-        const int64_t start = ts * a.cm.I + k * a.seg_len;
-        int64_t len = a.cm.I - k * a.seg_len;
-        if (len > a.seg_len) len = a.seg_len;
-        if (a.cm.C == 1)
-            param = 0;
-        else if (!a.cm.wrap)
-            param = ts;
-        else
-            param = a.cm.narrow ? (int64_t)((uint32_t)ts % (uint32_t)a.cm.C) : ts % a.cm.C;
         const Enc<CT> e = load_enc<CT>(a.scale, a.offset, param, g);
-        const bool fast_ok = vec_fast_ok<CT>(e, g);
-        const bool packed_ok = vec_packed_ok<CT>(e, g);
-        (void)fast_ok;
-        (void)packed_ok;
-        const int64_t nv = len / VEC;
-        const int64_t v0 = start / VEC;
-        for (int64_t v = lane; v < nv; v += 2 * (int64_t)G) {
-            const int64_t va = v0 + v, vb = va + G;
-            const bool hb = v + G < nv;
-            if constexpr (VECT) {
-                constexpr int NV = 16 / (int)sizeof(E);
-                Vec16<E> xa, ga, xb, gb;
-                xa = reinterpret_cast<const Vec16<E> *>(xp)[va];
-                ga = reinterpret_cast<const Vec16<E> *>(gp)[va];
-                if (hb) {
-                    xb = reinterpret_cast<const Vec16<E> *>(xp)[vb];
-                    gb = reinterpret_cast<const Vec16<E> *>(gp)[vb];
-                }
-                if constexpr ((CT == AB_BF16 || CT == AB_F16) && CT == IO && OP == OP_QDQ) {
-                    if (packed_ok) {
-                        Vec16<E> da;
-                        bwd_vec_packed<CT, WANT_O, E>(xa, ga, da, e, g, acc_s, acc_o);
-                        if (dxp) reinterpret_cast<Vec16<E> *>(dxp)[va] = da;
-                        if (hb) {
-                            bwd_vec_packed<CT, WANT_O, E>(xb, gb, da, e, g, acc_s, acc_o);
-                            if (dxp) reinterpret_cast<Vec16<E> *>(dxp)[vb] = da;
-                        }
-                        continue;
-                    }
-                }
-                T fx[NV], fg[NV];
-                VecCvt<T, E>::unpack(xa, fx);
-                VecCvt<T, E>::unpack(ga, fg);
-                bool done = false;
-                if constexpr (CT != AB_F64 && NV >= 2 && OP == OP_QDQ) {
-                    if (fast_ok) {
-                        bwd_vec_fast<CT, WANT_O, NV>(fx, fg, e, g, acc_s, acc_o);
-                        done = true;
-                    }
-                }
-                if (!done) {
-#pragma unroll
-                    for (int i = 0; i + 1 < NV; i += 2)
-                        bwd_pair<CT, OP, WANT_O>(fx[i], fx[i + 1], fg[i], fg[i + 1], e, g, acc_s, acc_o);
-                }
-                if (dxp) {
-                    VecCvt<T, E>::pack(fx, xa);
-                    reinterpret_cast<Vec16<E> *>(dxp)[va] = xa;
-                }
-                if (hb) {
-                    VecCvt<T, E>::unpack(xb, fx);
-                    VecCvt<T, E>::unpack(gb, fg);
-                    done = false;
-                    if constexpr (CT != AB_F64 && NV >= 2 && OP == OP_QDQ) {
-                        if (fast_ok) {
-                            bwd_vec_fast<CT, WANT_O, NV>(fx, fg, e, g, acc_s, acc_o);
+        if constexpr (VECT) {
+            const Vec16<E> *px = static_cast<const Vec16<E> *>(a.x) + p.v0 + lane;
+            const Vec16<E> *pg = static_cast<const Vec16<E> *>(a.gy) + p.v0 + lane;
+            Vec16<E> *pd = a.gx ? static_cast<Vec16<E> *>(a.gx) + p.v0 + lane : nullptr;
+            // the specialised bodies always write the input gradient; a caller that wants none
+            // takes the generic one
+            bool done = false;
+            if constexpr (OP == OP_QDQ && kIo16) {
+                uint32_t big2;
+                if (pd && abs_bound16<IO, CT>(e, big2)) {
+                    if constexpr (CT == IO) {
+                        if (vec_packed_ok<CT>(e, g)) {
+                            bwd_seg_loop<IO, CT, OP, WANT_O, PATH_PACKED, true>(px, pg, pd, lane, p.nv, G, e, g, big2, acc_s, acc_o);
                             done = true;
                         }
                     }
-                    if (!done) {
-#pragma unroll
-                        for (int i = 0; i + 1 < NV; i += 2)
-                            bwd_pair<CT, OP, WANT_O>(fx[i], fx[i + 1], fg[i], fg[i + 1], e, g, acc_s, acc_o);
-                    }
-                    if (dxp) {
-                        VecCvt<T, E>::pack(fx, xb);
-                        reinterpret_cast<Vec16<E> *>(dxp)[vb] = xb;
+                    if (!done && vec_fast_ok<CT>(e, g)) {
+                        bwd_seg_loop<IO, CT, OP, WANT_O, PATH_FAST, true>(px, pg, pd, lane, p.nv, G, e, g, big2, acc_s, acc_o);
+                        done = true;
                     }
                 }
-            } else {
+            } else if constexpr (OP == OP_QDQ && CT != AB_F64) {
+                if (pd && vec_fast_ok<CT>(e, g)) {
+                    bwd_seg_loop<IO, CT, OP, WANT_O, PATH_FAST, false>(px, pg, pd, lane, p.nv, G, e, g, 0u, acc_s, acc_o);
+                    done = true;
+                }
+            }
+            if (!done) bwd_seg_loop<IO, CT, OP, WANT_O, PATH_GENERIC, false>(px, pg, pd, lane, p.nv, G, e, g, 0u, acc_s, acc_o);
+        } else {
+            const E *__restrict__ xp = static_cast<const E *>(a.x) + p.v0;
+            const E *__restrict__ gp = static_cast<const E *>(a.gy) + p.v0;
+            E *__restrict__ dxp = a.gx ? static_cast<E *>(a.gx) + p.v0 : nullptr;
+            for (int v = lane; v < p.nv; v += G) {
                 T ds, dofs;
-                T dx = bwd_elem<CT, OP, WANT_O>(C::load(xp[va]), C::load(gp[va]), e, g, ds, dofs);
+                const T dx = bwd_elem<CT, OP, WANT_O>(C::load(xp[v]), C::load(gp[v]), e, g, ds, dofs);
                 acc_s += ds;
                 acc_o += dofs;
-                if (dxp) dxp[va] = C::store(dx);
-                if (hb) {
-                    dx = bwd_elem<CT, OP, WANT_O>(C::load(xp[vb]), C::load(gp[vb]), e, g, ds, dofs);
-                    acc_s += ds;
-                    acc_o += dofs;
-                    if (dxp) dxp[vb] = C::store(dx);
-                }
+                if (dxp) dxp[v] = C::store(dx);
             }
         }
     }
