@@ -172,6 +172,19 @@ ReducePlan plan_reduce(const Canon &c, int io_dtype, bool ptr_aligned, int chunk
     if (c.I > chunk) {
         p.seg_len = chunk;
         p.nchunk = (c.I + chunk - 1) / chunk;
+        // one long run (per-tensor): cut it into a whole number of waves of CTAs so that the
+        // last wave is not nearly empty
+        const int64_t slots = (int64_t)sms * 4;
+        if (c.O * c.C == 1 && p.nchunk > slots) {
+            int64_t waves = (p.nchunk + slots / 2) / slots;
+            if (waves < 1) waves = 1;
+            const int64_t want = waves * slots;
+            const int64_t unit = 2 * (int64_t)v;  // two vectors: one loop iteration of a thread
+            int64_t len = (c.I + want - 1) / want;
+            len = (len + unit - 1) / unit * unit;
+            p.seg_len = len;
+            p.nchunk = (c.I + len - 1) / len;
+        }
     } else {
         p.seg_len = c.I;
         p.nchunk = 1;

@@ -8,6 +8,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/aimet_b200.h"
 
 namespace ab {
@@ -68,6 +70,44 @@ inline int dtype_size(int dt) {
 }
 
 int sm_count();
+
+// Programmatic dependent launch: a kernel launched through launch_pdl may become resident while
+// its predecessor in the stream is still draining; it must execute pdl_prologue() before it
+// touches global memory (the wait returns once the predecessor has completed and its writes are
+// visible).  The launch latency of back-to-back kernels disappears behind the predecessor's tail.
+__device__ __forceinline__ void pdl_prologue() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// Opt a kernel in to `bytes` of dynamic shared memory (needed above 48 KB), once per device.
+template <auto kernel> int opt_in_smem(size_t bytes) {
+    static std::mutex mu;
+    static uint64_t done = 0;
+    int dev = 0;
+    AB_CUDA_OK(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 64 && ((done >> dev) & 1)) return AB_OK;
+    AB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    if (dev < 64) done |= 1ull << dev;
+    return AB_OK;
+}
 
 // ---------------------------------------------------------------------------
 // element types at the boundary

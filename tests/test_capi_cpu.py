@@ -36,13 +36,15 @@ def test_layout_errors_and_scratch_queries_without_a_gpu():
     bad = _lib.make_layout([6, 8], [4, 8])  # 4 does not divide 6
     assert lib.aimet_b200_backward_scratch_bytes(bad, _lib.AB_F32) == _lib.AB_ERR_INVALID
     assert "does not divide" in _lib.last_error()
-    # the query is an upper bound over the 16-byte-vector and the scalar kernel: rows of 4096 are
-    # reduced in-kernel by the vector kernel but cut into two 2048-element chunks by the scalar one
-    assert lib.aimet_b200_backward_scratch_bytes(_lib.make_layout([14336, 4096], [1, 4096]), _lib.AB_BF16) == 14336 * 2 * 16
+    # rows of 4096 and blocks of 64 are reduced inside the kernel: no partial sums
+    assert lib.aimet_b200_backward_scratch_bytes(_lib.make_layout([14336, 4096], [1, 4096]), _lib.AB_BF16) == 0
     assert lib.aimet_b200_backward_scratch_bytes(_lib.make_layout([14336, 4096], [1, 64]), _lib.AB_BF16) == 0
-    # per-tensor: one partial (two doubles) per chunk of 2048 vectors
+    # longer rows are cut into chunks of at most 8192 elements (scalar kernel): one partial pair each
+    assert lib.aimet_b200_backward_scratch_bytes(_lib.make_layout([16, 65536], [1, 65536]), _lib.AB_BF16) == 16 * 8 * 16
+    # per-tensor: one partial pair (two doubles) per chunk; the chunk count is rounded to whole
+    # waves of CTAs, so only its range is fixed
     n = lib.aimet_b200_backward_scratch_bytes(_lib.make_layout([4096, 4096], [4096, 4096]), _lib.AB_F32)
-    assert n == (4096 * 4096 // 2048) * 16  # the scalar path (2048-element chunks) is the upper bound
+    assert n % 16 == 0 and 4096 * 4096 // 32768 * 16 <= n <= (4096 * 4096 // 2048) * 16
     assert lib.aimet_b200_backward_scratch_bytes(_lib.make_layout([0, 4], [1, 4]), _lib.AB_F32) == 0
     assert lib.aimet_b200_seqmse_scratch_bytes(8192, 4096, 4096, 20) == 32 * 20 * 4096 * 2 * 4
     assert lib.aimet_b200_fixed_scratch_capacity() == 1 << 20
