@@ -43,13 +43,28 @@ def _get_minimum_scale(num_steps) -> float:
     return min(float(np.finfo(np.float32).eps), 0.01 / num_steps)
 
 
+_SCALARS = {}
+
+
+def _scalar(value, dtype, device) -> torch.Tensor:
+    """A cached 0-d tensor holding ``value``.  Built with a fill kernel: ``torch.tensor(value,
+    device=cuda)`` copies from pageable host memory, which makes the host wait for everything
+    queued on the stream -- in the middle of a forward pass."""
+    key = (float(value), dtype, str(device))
+    t = _SCALARS.get(key)
+    if t is None:
+        t = torch.full((), float(value), dtype=dtype, device=device)
+        _SCALARS[key] = t
+    return t
+
+
 def _div(a: torch.Tensor, b) -> torch.Tensor:
     """``a / b`` for a Python number ``b`` with IEEE division.  PyTorch's CUDA kernels turn a division
     by a Python scalar into a multiplication by its reciprocal, which differs from the CPU result in
     the last bit whenever ``b`` is not a power of two; dividing by a 0-d tensor does not."""
     if a.dtype in (torch.float16, torch.bfloat16):
-        return (a.float() / torch.tensor(float(b), dtype=torch.float32, device=a.device)).to(a.dtype)
-    return a / torch.tensor(float(b), dtype=a.dtype, device=a.device)
+        return (a.float() / _scalar(b, torch.float32, a.device)).to(a.dtype)
+    return a / _scalar(b, a.dtype, a.device)
 
 
 @dataclass
@@ -564,7 +579,7 @@ class _LpNormEncodingAnalyzer(_HistogramAnalyzer):
         offsets = torch.full((1,), (-num_steps) // 2, dtype=torch.float32, device=dev)
         k = self.sym_delta_candidates
         deltas = _div(max_delta[:, None] * self._host_arange(dev, start=1, end=1 + k, step=1)[None, :], k - 1)
-        deltas = torch.max(deltas, torch.tensor([min_scale], dtype=torch.float32, device=dev))
+        deltas = torch.max(deltas, _scalar(min_scale, torch.float32, dev))
         return deltas[:, :, None], offsets[:, None, None]
 
     @staticmethod
@@ -575,7 +590,7 @@ class _LpNormEncodingAnalyzer(_HistogramAnalyzer):
         tmin = torch.max(min_vals[:, None, None], tmin)
         tmax = torch.min(max_vals[:, None, None], tmax)
         deltas = _div(tmax - tmin, num_steps)
-        deltas = torch.max(deltas, torch.tensor([min_scale], device=deltas.device, dtype=deltas.dtype))
+        deltas = torch.max(deltas, _scalar(min_scale, deltas.dtype, deltas.device))
         return deltas, torch.round(tmin / deltas)
 
     # sweep -----------------------------------------------------------------------------------

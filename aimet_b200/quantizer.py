@@ -29,6 +29,7 @@ from .encoding_analyzer import (
     MinMaxEncodingAnalyzer,
     StatisticsNotFoundError,
     _get_minimum_scale,
+    _scalar,
 )
 
 __all__ = [
@@ -163,7 +164,7 @@ def _get_scale_offset(min, max, qmin, qmax, symmetric):  # pylint: disable=redef
         max = torch.tensor(max, dtype=torch.float32)
     out_dtype = min.dtype
     min, max = min.to(torch.float32), max.to(torch.float32)
-    scale = (max - min) / torch.tensor(float(num_steps), device=min.device)
+    scale = (max - min) / _scalar(num_steps, torch.float32, min.device)
     if symmetric:
         offset = torch.full_like(min, fill_value=-round((qmin + qmax) / 2), requires_grad=False)
     else:
@@ -336,7 +337,7 @@ class AffineQuantizerBase(QuantizerBase):
             return None
         dtype = dtype or torch.float32
         num_steps = self.qmax - self.qmin
-        scale = (self.max.to(dtype) - self.min.to(dtype)) / torch.tensor(float(num_steps), dtype=dtype, device=self.min.device)
+        scale = (self.max.to(dtype) - self.min.to(dtype)) / _scalar(num_steps, dtype, self.min.device)
         return scale.abs().clamp_min(_get_minimum_scale(num_steps)).to(dtype)
 
     def get_offset(self, dtype=None) -> Optional[torch.Tensor]:

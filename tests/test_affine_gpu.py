@@ -113,6 +113,10 @@ ORACLE_CASES = [
     (torch.float32, (1000, 77), (77,), None, -8, 7, 0.5),              # scalar column mode + zps
     (torch.float32, (48, 64), (6, 8), (8, 8), 0, 15, 0.0),             # 2-d blocks: general path
     (torch.bfloat16, (6, 40, 50), (3, 1, 5), (2, -1, 10), -8, 7, 0.0),
+    (torch.float32, (5000, 4096), (), None, 0, 255, 0.0),              # per-tensor cut into whole waves of chunks
+    (torch.bfloat16, (32, 4104), (32, 1), None, -128, 127, 0.0),       # 513 vectors per row: ragged loop ends
+    (torch.bfloat16, (16, 65536), (16, 1), None, -128, 127, 0.0),      # 32 vectors per thread: the copy ring wraps
+    (torch.float16, (16, 65536), (16, 1), None, -8, 7, 0.0),           # float16 internal, packed arithmetic
 ]
 
 
@@ -167,6 +171,53 @@ def test_special_values_and_empty():
     assert_same(B.quantize_dequantize(x, s, o, 0, 15), dev.cpu(), "special, fake-quantize path")
     e = torch.empty(0, 4).cuda()
     assert B.quantize_dequantize(e, s, o, 0, 15).shape == (0, 4)
+
+
+@pytest.mark.parametrize("dtype,qmin,qmax", [(torch.bfloat16, -128, 127), (torch.bfloat16, -8, 7), (torch.float16, -128, 127),
+                                             (torch.float32, 0, 255)])
+def test_non_finite_and_huge_inputs_in_the_vector_kernels(dtype, qmin, qmax):
+    """Infinities, NaN and magnitudes far outside the grid scattered through large rows: the fast
+    bodies (bounded input instead of a per-element overflow guard) must agree with the oracle bit
+    for bit, forward and backward."""
+    B = _backend()
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(24, 8192, generator=g)
+    idx = torch.randperm(x.numel(), generator=g)
+    flat = x.view(-1)
+    big = 6.0e4 if dtype == torch.float16 else 3.0e38
+    for k, v in enumerate([float("inf"), -float("inf"), float("nan"), big, -big, 1e-30, -0.0]):
+        flat[idx[k * 50:(k + 1) * 50]] = v
+    x = x.to(dtype)
+    grad = torch.randn(24, 8192, generator=g).to(dtype)
+    scale = (3.0 / (qmax - qmin)) * (0.5 + torch.rand(24, 1, generator=g))
+    offset = torch.zeros(24, 1) if qmin < 0 else torch.full((24, 1), -128.0)
+    idt = O.internal_dtype(dtype, qmin, qmax)
+    y, gx, gs, go = _run(B.quantize_dequantize, x, grad, scale, offset, qmin, qmax, None, 0.0)
+    assert_same(y, O.quantize_dequantize(x, scale, offset, qmin, qmax, None, 0.0), "qdq")
+    ogx, ogs, ogo = O.quantize_dequantize_backward(x, grad, scale, offset, qmin, qmax, None, 0.0)
+    assert_same(gx, ogx, "grad_x")
+    # rows that hold a NaN have NaN sums in both; the others follow the usual tolerance
+    ok = ~(ogs.isnan() | ogo.isnan()).flatten()
+    assert torch.equal(gs.cpu().isnan().flatten(), ~ok | ogs.isnan().flatten())
+    _check_param_grad(gs.cpu().flatten()[ok], ogs.flatten()[ok], idt, "grad_scale")
+    _check_param_grad(go.cpu().flatten()[ok], ogo.flatten()[ok], idt, "grad_offset")
+
+
+def test_float16_scale_too_large_for_the_input_bound():
+    """float16 tensors with a scale so large that (qmax + 4) * scale overflows float16: the packed
+    bound on |x| does not exist and the kernels fall back to the guarded arithmetic."""
+    B = _backend()
+    g = torch.Generator().manual_seed(11)
+    x = (torch.randn(8, 4096, generator=g) * 2.0e4).to(torch.float16)
+    x[0, :4] = torch.tensor([float("inf"), -float("inf"), 65504.0, -65504.0], dtype=torch.float16)
+    grad = torch.randn(8, 4096, generator=g).to(torch.float16)
+    scale = torch.full((8, 1), 600.0)
+    offset = torch.zeros(8, 1)
+    y, gx, gs, go = _run(B.quantize_dequantize, x, grad, scale, offset, -128, 127, None, 0.0)
+    assert_same(y, O.quantize_dequantize(x, scale, offset, -128, 127, None, 0.0), "qdq")
+    ogx, ogs, ogo = O.quantize_dequantize_backward(x, grad, scale, offset, -128, 127, None, 0.0)
+    assert_same(gx, ogx, "grad_x")
+    _check_param_grad(gs, ogs, torch.float16, "grad_scale")
 
 
 def test_error_contracts():
