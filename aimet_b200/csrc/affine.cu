@@ -200,10 +200,19 @@ __device__ __forceinline__ void fwd_seg_loop(const Vec16<typename Elem<IO>::type
             py[u * G] = yv;
         }
     }
-    for (; v < nv; v += G, px += G, py += G) {
-        Vec16<E> yv;
-        fwd_vec<IO, CT, OP, PATH, PRE>(*px, yv, e, g, big2);
-        *py = yv;
+    if (v < nv) {  // the last, partial iteration: all its loads first, like the full ones
+        Vec16<E> xv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (v + u * G < nv) xv[u] = px[u * G];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (v + u * G < nv) {
+                Vec16<E> yv;
+                fwd_vec<IO, CT, OP, PATH, PRE>(xv[u], yv, e, g, big2);
+                py[u * G] = yv;
+            }
+        }
     }
 }
 

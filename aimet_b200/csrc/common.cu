@@ -193,7 +193,12 @@ ReducePlan plan_reduce(const Canon &c, int io_dtype, bool ptr_aligned, int chunk
     const int64_t vec_per_seg = (p.seg_len + v - 1) / v;
     // aim at kSegVecPerThread vectors per thread (index arithmetic and the group reduction are paid per
     // thread)
-    int grp = pow2_ceil((vec_per_seg + kSegVecPerThread - 1) / kSegVecPerThread);
+    // small tensors: fewer vectors per thread, so that there are enough threads to fill the GPU
+    // and a thread's chain of dependent memory latencies stays short
+    const int64_t total_vec = vec_per_seg * p.nseg;
+    int per_thread = kSegVecPerThread;
+    while (per_thread > 2 && total_vec / per_thread < (int64_t)sms * 1024) per_thread >>= 1;
+    int grp = pow2_ceil((vec_per_seg + per_thread - 1) / per_thread);
     // two neighbouring lanes read one 32-byte sector together
     const int floor_grp = vec_per_seg >= 2 ? 2 : 1;
     if (grp < floor_grp) grp = floor_grp;

@@ -636,6 +636,19 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_kernels_only(steps):
+    """A few eager resident steps and nothing else: the small, fixed launch sequence that the ncu
+    captures under ``profiles/`` are taken from (8 launches per step, see ResidentStep.run)."""
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    w, dy = make_weight(ROWS, COLS, seed=2000)
+    resident = ResidentStep(w, dy, dev)
+    for _ in range(steps):
+        resident.run()
+    torch.cuda.synchronize()
+    print(json.dumps({"kernels_only_steps": steps}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -644,8 +657,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-oracle baseline leg")
     ap.add_argument("--no-extras", action="store_true", help="skip the calibration and SeqMSE figures")
+    ap.add_argument("--kernels-only", type=int, default=0, metavar="STEPS",
+                    help="run STEPS eager resident steps and exit (for profiler captures)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.kernels_only:
+        run_kernels_only(args.kernels_only)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
