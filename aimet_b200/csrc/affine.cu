@@ -683,7 +683,7 @@ __global__ void __launch_bounds__(kThreads) k_bwd_gen(BwdGenArgs a) {
 // ---------------------------------------------------------------------------
 using BwdPlan = ReducePlan;
 // long runs are cut into chunks of 32 vectors per thread
-inline BwdPlan plan_backward(const Canon &c, int io_dtype, bool ptr_aligned) { return plan_reduce(c, io_dtype, ptr_aligned, 4); }
+inline BwdPlan plan_backward(const Canon &c, int io_dtype, bool ptr_aligned) { return plan_reduce(c, io_dtype, ptr_aligned, 4, 4); }
 
 // qmin-1 and qmax+1 are exactly representable in the 16-bit internal dtype
 bool fits_significand(int64_t v, int bits) {

@@ -137,7 +137,7 @@ static int pow2_ceil(int64_t v) {
     return r;
 }
 
-ReducePlan plan_reduce(const Canon &c, int io_dtype, bool ptr_aligned, int chunk_mult) {
+ReducePlan plan_reduce(const Canon &c, int io_dtype, bool ptr_aligned, int chunk_mult, int ctas_per_sm) {
     ReducePlan p{};
     if (!c.oci) {
         p.mode = ReducePlan::GEN;
@@ -174,8 +174,8 @@ ReducePlan plan_reduce(const Canon &c, int io_dtype, bool ptr_aligned, int chunk
         p.nchunk = (c.I + chunk - 1) / chunk;
         // one long run (per-tensor): cut it into a whole number of waves of CTAs so that the
         // last wave is not nearly empty
-        const int64_t slots = (int64_t)sms * 4;
-        if (c.O * c.C == 1 && p.nchunk > slots) {
+        const int64_t slots = (int64_t)sms * ctas_per_sm;
+        if (ctas_per_sm > 0 && c.O * c.C == 1 && p.nchunk > slots) {
             int64_t waves = (p.nchunk + slots / 2) / slots;
             if (waves < 1) waves = 1;
             const int64_t want = waves * slots;

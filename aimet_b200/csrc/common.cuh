@@ -337,7 +337,8 @@ struct ReducePlan {
 
 // Depends only on the layout and the element size (plus whether the pointers
 // allow 16-byte accesses), so a scratch-size query and the launch agree.
-ReducePlan plan_reduce(const Canon &c, int io_dtype, bool ptr_aligned, int chunk_mult = 1);
+// ctas_per_sm > 0: a single long run is cut into a whole number of waves of that many CTAs per SM
+ReducePlan plan_reduce(const Canon &c, int io_dtype, bool ptr_aligned, int chunk_mult = 1, int ctas_per_sm = 0);
 
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 

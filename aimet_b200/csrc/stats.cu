@@ -7,6 +7,8 @@
 
 #include <mutex>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace ab {
@@ -507,146 +509,169 @@ template <int IO, bool VECT> __global__ void __launch_bounds__(kThreads) k_histo
 }
 
 // ---------------------------------------------------------------------------
-// 16-bit inputs: a bfloat16 / float16 tensor has only 65536 distinct values, so the histc bin (and
-// the outlier rule) of every bit pattern is tabulated once per call and the pass over the tensor
-// is a table look-up plus a shared-memory increment -- the exact float arithmetic runs 65536 times
-// instead of once per element.  Table entry: bits 3..15 bin (num_bins = a spare bin for values that
-// count nowhere), bit 1 "also counts in bin 0", bit 2 "also counts in the last bin" (only when a
-// value is inside the binning range and at the same time beyond an outlier threshold, which can
-// happen when the thresholds were rounded to the tensor dtype).
+// Large histograms.  The pass over the tensor is instruction-bound (2-4 bytes per element), so
+// the common case is kept to a handful of instructions per element:
+//  * the bin is computed arithmetically with the exact torch.histc formula,
+//    (v - lo) * bins / (hi - lo), the division by reciprocal and exact remainder (see div_fast in
+//    the affine kernels), the truncation by an add of 2^23 rounded toward zero, two elements per
+//    instruction (FADD2 / FMUL2 / FFMA2);
+//  * a 16-byte vector is checked as a whole (packed min / max, NaN-propagating): when all its
+//    values lie inside the binning range and inside the outlier thresholds they are counted
+//    without any per-element predicate; otherwise the vector takes the element-wise general body;
+//  * 16 replicas of the histogram, counter (bin, lane mod 16) at (bin * 16 + lane mod 16) * 4:
+//    calibration batches pile up in a handful of bins, and with replicas a warp's increments of
+//    one bin collide at most two-fold (measured: peaked and flat data take the same time, and
+//    counting the most frequent bins in registers instead did not pay for its instructions);
+//  * the next iteration's loads are issued before this one's arithmetic: the warps of the one
+//    1024-thread CTA per SM run in step and would otherwise all wait on memory together.
 // ---------------------------------------------------------------------------
-constexpr int kLutEntries = 65536;
-constexpr int kLutThreads = 1024;
-constexpr int64_t kLutMinElems = 1 << 20;  // per channel; below this the table does not pay off
-constexpr int kLutMaxChannels = 64;
-constexpr unsigned kLutExtra0 = 1u << 1, kLutExtraN = 1u << 2;  // bits 3..15: bin, or num_bins for "counts nowhere"
+constexpr int kPrivThreads = 1024;
+constexpr int kPrivCopies = 16;
+constexpr int kPrivMaxBins = 3072;                    // (bins + 1) * 64 B of counters: 192 KB
+constexpr int64_t kPrivMinElems = 1 << 20;            // per histogram; below this the plain kernel
 
-template <int IO>
-__global__ void __launch_bounds__(256) k_hist_lut_build(const float *lo, const float *hi, const float *below,
-                                                        const float *above, int num_bins, uint16_t *lut) {
-    using E = typename Elem<IO>::type;
-    const int c = blockIdx.y;
-    const unsigned p = blockIdx.x * 256 + threadIdx.x;
-    const uint16_t raw = (uint16_t)p;
-    const float v = to_f32(*reinterpret_cast<const E *>(&raw));
-    const float l = lo[c], h = hi[c];
-    unsigned code = 0;
-    bool valid = (v >= l) && (v <= h);
-    int bin = 0;
-    if (valid) bin = histc_bin(v, l, __fsub_rn(h, l), (float)num_bins, num_bins);
-    bool ex0 = v < below[c], exn = v > above[c];
-    if (!valid && ex0) { valid = true; bin = 0; ex0 = false; }
-    if (!valid && exn) { valid = true; bin = num_bins - 1; exn = false; }
-    code = (unsigned)(valid ? bin : num_bins) << 3;
-    if (ex0) code |= kLutExtra0;
-    if (exn) code |= kLutExtraN;
-    lut[(int64_t)c * kLutEntries + p] = (uint16_t)code;
-}
-
-struct HistLutArgs {
+struct HistPrivArgs {
     const void *x;
-    const uint16_t *lut;         // [C][65536]
-    unsigned long long *counts;  // [C][num_bins]
-    int64_t O, C, I, chan_elems, tile_elems;
+    const float *lo, *hi, *below, *above;
+    unsigned long long *counts;
+    int64_t O, C, I;
+    int64_t chan_elems, tile_elems;
     int num_bins;
 };
 
-// Shared memory: the 128 KB table plus `copies` interleaved replicas of the histogram (replica k of
-// bin b at word b * copies + k).  A lane increments replica (lane % copies), so lanes that hit the
-// same hot bin spread over `copies` different banks instead of serialising on one address.
-__device__ __forceinline__ int hist_lut_copies(int num_bins) {
-    return num_bins <= 2048 ? 8 : 4;  // the table path is used for at most 4096 bins
+// all values of the vector inside [plo, phi] (false if any is NaN)
+__device__ __forceinline__ bool vec_inside(const Vec16<float> &v, float plo, float phi) {
+    float mn, mx;
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(mn) : "f"(v.v[0]), "f"(v.v[1]));
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(mx) : "f"(v.v[0]), "f"(v.v[1]));
+    float mn2, mx2;
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(mn2) : "f"(v.v[2]), "f"(v.v[3]));
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(mx2) : "f"(v.v[2]), "f"(v.v[3]));
+    asm("min.NaN.f32 %0, %1, %2;" : "=f"(mn) : "f"(mn), "f"(mn2));
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(mx) : "f"(mx), "f"(mx2));
+    return mn >= plo && mx <= phi;
+}
+template <typename E> __device__ __forceinline__ bool vec_inside(const Vec16<E> &v, float plo, float phi) {
+    using H2 = typename std::conditional<std::is_same<E, __half>::value, __half2, __nv_bfloat162>::type;
+    const H2 *w = reinterpret_cast<const H2 *>(&v);
+    const H2 mn = __hmin2_nan(__hmin2_nan(w[0], w[1]), __hmin2_nan(w[2], w[3]));
+    const H2 mx = __hmax2_nan(__hmax2_nan(w[0], w[1]), __hmax2_nan(w[2], w[3]));
+    const float2 fmn = std::is_same<E, __half>::value ? __half22float2(*reinterpret_cast<const __half2 *>(&mn))
+                                                       : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&mn));
+    const float2 fmx = std::is_same<E, __half>::value ? __half22float2(*reinterpret_cast<const __half2 *>(&mx))
+                                                       : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&mx));
+    return fmn.x >= plo && fmn.y >= plo && fmx.x <= phi && fmx.y <= phi;
 }
 
-__device__ __noinline__ void hist_lut_rare(unsigned int *hist, unsigned code, int shift, int copy, int last) {
-    // a value inside the binning range that is also beyond an outlier threshold counts twice
-    if (code & kLutExtra0) atomicAdd(&hist[copy], 1u);
-    if (code & kLutExtraN) atomicAdd(&hist[((unsigned)last << shift) + copy], 1u);
-}
-
-__global__ void __launch_bounds__(kLutThreads, 1) k_hist_lut(HistLutArgs a) {
-    extern __shared__ __align__(16) unsigned char sh_raw[];
-    uint16_t *sh_lut = reinterpret_cast<uint16_t *>(sh_raw);
-    unsigned int *sh_hist = reinterpret_cast<unsigned int *>(sh_raw + kLutEntries * sizeof(uint16_t));
+template <int IO> __global__ void __launch_bounds__(kPrivThreads, 1) k_hist_private(HistPrivArgs a) {
+    using E = typename Elem<IO>::type;
+    constexpr int NV = 16 / (int)sizeof(E);
+    extern __shared__ __align__(16) unsigned int sh_cnt[];  // [num_bins + 1][16]; row num_bins: v == hi
+    __shared__ unsigned long long sh_edge[2];
     const int64_t c = blockIdx.y;
-    const int copies = hist_lut_copies(a.num_bins);
-    const int shift = copies == 8 ? 3 : 2;
-    {
-        const uint4 *src = reinterpret_cast<const uint4 *>(a.lut + c * kLutEntries);
-        uint4 *dst = reinterpret_cast<uint4 *>(sh_lut);
-        for (int i = threadIdx.x; i < kLutEntries * 2 / 16; i += kLutThreads) dst[i] = src[i];
-        for (int b = threadIdx.x; b < (a.num_bins + 1) * copies; b += kLutThreads) sh_hist[b] = 0;
-    }
+    for (int i = threadIdx.x; i < (a.num_bins + 1) * kPrivCopies; i += kPrivThreads) sh_cnt[i] = 0;
+    if (threadIdx.x < 2) sh_edge[threadIdx.x] = 0;
     __syncthreads();
 
-    const uint4 *xp = reinterpret_cast<const uint4 *>(a.x);
+    const float lo = a.lo[c], hi = a.hi[c], below = a.below[c], above = a.above[c];
+    const float range = __fsub_rn(hi, lo), nbf = (float)a.num_bins;
+    const float r = __frcp_rn(range);
+    // the quick body needs a moderate range (exact reciprocal division)
+    const bool quick = range > 7.888609e-31f && range < 1.2676506e30f && fabsf(lo) < 1.2676506e30f &&
+                       fabsf(hi) < 1.2676506e30f;
+    // "plain" values lie inside the binning range and inside the outlier thresholds: they count in
+    // their bin and nowhere else
+    const float plo = fmaxf(lo, below), phi = fminf(hi, above);
+    const int lane = threadIdx.x & 31;
+    const unsigned base = (unsigned)__cvta_generic_to_shared(sh_cnt) + 4u * (lane & (kPrivCopies - 1));
+    unsigned int n_below = 0, n_above = 0;
+
+    auto count = [&](int b) {  // b in [0, num_bins]
+        asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(base + ((unsigned)b << 6)), "r"(1u) : "memory");
+    };
+    auto quick_vec = [&](const float (&f)[NV]) {
+#pragma unroll
+        for (int i = 0; i < NV; i += 2) {
+            const float2 t = __fmul2_rn(__fadd2_rn(make_float2(f[i], f[i + 1]), make_float2(-lo, -lo)), make_float2(nbf, nbf));
+            const float2 q0 = __fmul2_rn(t, make_float2(r, r));
+            const float2 rem = __ffma2_rn(q0, make_float2(-range, -range), t);
+            const float2 q = __ffma2_rn(rem, make_float2(r, r), q0);
+            const float2 tb = __ffma2_rz(q, make_float2(1.0f, 1.0f), make_float2(8388608.0f, 8388608.0f));
+            count(__float_as_int(tb.x) & 0x7fffff);
+            count(__float_as_int(tb.y) & 0x7fffff);
+        }
+    };
+    auto general_vec = [&](const Vec16<E> &w) {  // rare: its own copy of the vector, indexed in a loop
+        const Vec16<E> tmp = w;
+#pragma unroll 1
+        for (int i = 0; i < NV; ++i) {
+            const float v = to_f32(tmp.v[i]);
+            if (v >= lo && v <= hi) count(histc_bin(v, lo, range, nbf, a.num_bins));
+            n_below += v < below;
+            n_above += v > above;
+        }
+    };
+    auto feed = [&](const Vec16<E> &w) {
+        if (quick && vec_inside(w, plo, phi)) {
+            float f[NV];
+            VecCvt<float, E>::unpack(w, f);
+            quick_vec(f);
+        } else {
+            general_vec(w);
+        }
+    };
+
+    const Vec16<E> *xp = static_cast<const Vec16<E> *>(a.x);
     const int64_t e0 = (int64_t)blockIdx.x * a.tile_elems;
     int64_t e1 = e0 + a.tile_elems;
     if (e1 > a.chan_elems) e1 = a.chan_elems;
-    const int64_t nvec = (e1 - e0) / 8;
+    const int64_t nvec = (e1 - e0) / NV;
     const bool flat = a.C == 1;
-    const int last = a.num_bins - 1;
-    const int copy = threadIdx.x & (copies - 1);
-    const unsigned lut_base = (unsigned)__cvta_generic_to_shared(sh_lut);
-    const unsigned hist_base = (unsigned)__cvta_generic_to_shared(sh_hist) + 4u * copy;
-    const int hshift = shift + 2;  // bin -> byte offset of its replica group
-
-    // two elements per 32-bit word: one increment of 2 when both fall in the same bin.  The table
-    // code is the bin pre-shifted by 3, so its replica group starts at byte (code & ~7) << (hshift-3)
-    const int cshift = hshift - 3;
-    auto feed_word = [&](unsigned w) {
-        unsigned short c0h, c1h;
-        asm("ld.shared.u16 %0, [%1];" : "=h"(c0h) : "r"(lut_base + ((w << 1) & 0x1fffeu)));
-        asm("ld.shared.u16 %0, [%1];" : "=h"(c1h) : "r"(lut_base + ((w >> 15) & 0x1fffeu)));
-        const unsigned c0 = c0h, c1 = c1h;
-        const bool same = (c0 >> 3) == (c1 >> 3);
-        asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(hist_base + ((c0 & 0xfff8u) << cshift)), "r"(same ? 2u : 1u) : "memory");
-        if (!same) asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(hist_base + ((c1 & 0xfff8u) << cshift)), "r"(1u) : "memory");
-        if (__builtin_expect(((c0 | c1) & (kLutExtra0 | kLutExtraN)) != 0, 0)) {
-            hist_lut_rare(sh_hist, c0, shift, copy, last);
-            hist_lut_rare(sh_hist, c1, shift, copy, last);
-        }
+    auto addr_of = [&](int64_t v) -> int64_t {
+        if (flat) return e0 / NV + v;
+        const int64_t e = e0 + v * NV;
+        const int64_t o = e / a.I;
+        return ((o * a.C + c) * a.I + (e - o * a.I)) / NV;
     };
-    for (int64_t v0 = threadIdx.x; v0 < nvec; v0 += 2 * kLutThreads) {
-        const int64_t v1 = v0 + kLutThreads;
-        int64_t a0, a1;
-        if (flat) {
-            a0 = e0 / 8 + v0;
-            a1 = e0 / 8 + v1;
-        } else {
-            const int64_t ea = e0 + v0 * 8, eb = e0 + v1 * 8;
-            const int64_t oa = ea / a.I, ob = eb / a.I;
-            a0 = ((oa * a.C + c) * a.I + (ea - oa * a.I)) / 8;
-            a1 = ((ob * a.C + c) * a.I + (eb - ob * a.I)) / 8;
-        }
-        const uint4 wa = xp[a0];
-        uint4 wb = make_uint4(0, 0, 0, 0);
-        const bool hb = v1 < nvec;
-        if (hb) wb = xp[a1];
-        feed_word(wa.x);
-        feed_word(wa.y);
-        feed_word(wa.z);
-        feed_word(wa.w);
-        if (hb) {
-            feed_word(wb.x);
-            feed_word(wb.y);
-            feed_word(wb.z);
-            feed_word(wb.w);
-        }
+    // two vectors per iteration; the next iteration's loads are issued before this one's arithmetic
+    // (the warps of the CTA run in step, so without this all of them would wait on memory together)
+    Vec16<E> wa, wb, na, nb;
+    int64_t v0 = threadIdx.x;
+    if (v0 < nvec) wa = xp[addr_of(v0)];
+    if (v0 + kPrivThreads < nvec) wb = xp[addr_of(v0 + kPrivThreads)];
+    for (; v0 < nvec; v0 += 2 * kPrivThreads) {
+        const bool hb = v0 + kPrivThreads < nvec;
+        const int64_t n0 = v0 + 2 * kPrivThreads, n1 = n0 + kPrivThreads;
+        if (n0 < nvec) na = xp[addr_of(n0)];
+        if (n1 < nvec) nb = xp[addr_of(n1)];
+        feed(wa);
+        if (hb) feed(wb);
+        wa = na;
+        wb = nb;
+    }
+    n_below = __reduce_add_sync(0xffffffffu, n_below);
+    n_above = __reduce_add_sync(0xffffffffu, n_above);
+    if (lane == 0) {
+        if (n_below) atomicAdd(&sh_edge[0], (unsigned long long)n_below);
+        if (n_above) atomicAdd(&sh_edge[1], (unsigned long long)n_above);
     }
     __syncthreads();
+    // merge the replicas: half a warp per bin
     unsigned long long *out = a.counts + c * (int64_t)a.num_bins;
-    for (int b = threadIdx.x; b < a.num_bins; b += kLutThreads) {
-        unsigned long long n = 0;
-        for (int k = 0; k < copies; ++k) n += sh_hist[(b << shift) + k];
-        if (n) atomicAdd(out + b, n);
+    const int last = a.num_bins - 1;
+    for (int b0 = (threadIdx.x >> 5) * 2; b0 <= a.num_bins; b0 += kPrivThreads / 16) {
+        const int b = b0 + (lane >> 4);
+        unsigned int v = b <= a.num_bins ? sh_cnt[b * kPrivCopies + (lane & 15)] : 0u;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if ((lane & 15) == 0 && b <= a.num_bins) {
+            unsigned long long n = v;
+            const int dst = b > last ? last : b;  // row num_bins (v == hi) belongs to the last bin
+            if (b == 0) n += sh_edge[0];
+            if (b == last) n += sh_edge[1];
+            if (n) atomicAdd(out + dst, n);
+        }
     }
-}
-
-inline int64_t hist_lut_bytes(const Canon &canon, int io_dtype) {
-    if (dtype_size(io_dtype) != 2 || !canon.oci || canon.C > kLutMaxChannels) return 0;
-    if (canon.O * canon.I < kLutMinElems) return 0;
-    return canon.C * (int64_t)kLutEntries * (int64_t)sizeof(uint16_t);
 }
 
 template <int IO>
@@ -670,42 +695,35 @@ int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const 
     tiles = (chan_elems + tile_elems - 1) / tile_elems;
 
     const bool want_mm = fin_min && fin_max;
-    // table look-up path for 16-bit tensors with enough elements per histogram
-    if constexpr (IO == AB_BF16 || IO == AB_F16) {
-        const int64_t lut_bytes = hist_lut_bytes(canon, IO);
-        if (lut_bytes > 0 && num_bins <= 4096 && !want_mm && vect && scratch && scratch_bytes >= lut_bytes && aligned16(scratch)) {
-            static std::once_flag once;
-            static cudaError_t attr_err = cudaSuccess;
-            const size_t smem = kLutEntries * sizeof(uint16_t) + sizeof(unsigned int) * (16384 + 8);  // table + replicas (+ spare bin)
-            std::call_once(once, [smem]() {
-                attr_err = cudaFuncSetAttribute(k_hist_lut, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            });
-            if (attr_err == cudaSuccess) {
-                AB_CUDA_OK(cudaMemsetAsync(counts, 0, sizeof(int64_t) * canon.C * (int64_t)num_bins, stream));
-                uint16_t *lut = static_cast<uint16_t *>(scratch);
-                dim3 bgrid(kLutEntries / 256, (unsigned)canon.C);
-                k_hist_lut_build<IO><<<bgrid, 256, 0, stream>>>(lo, hi, below, above, num_bins, lut);
-                AB_LAUNCH_OK();
-                int64_t ltiles = sm_count() / canon.C;
-                if (ltiles < 1) ltiles = 1;
-                int64_t lt_elems = (chan_elems + ltiles - 1) / ltiles;
-                lt_elems = ((lt_elems + 15) / 16) * 16;
-                ltiles = (chan_elems + lt_elems - 1) / lt_elems;
-                HistLutArgs h;
-                h.x = x;
-                h.lut = lut;
-                h.counts = reinterpret_cast<unsigned long long *>(counts);
-                h.O = canon.O;
-                h.C = canon.C;
-                h.I = canon.I;
-                h.chan_elems = chan_elems;
-                h.tile_elems = lt_elems;
-                h.num_bins = num_bins;
-                dim3 grid((unsigned)ltiles, (unsigned)canon.C);
-                k_hist_lut<<<grid, kLutThreads, smem, stream>>>(h);
-                AB_LAUNCH_OK();
-                return AB_OK;
-            }
+    // lane-private counters for large histograms
+    if constexpr (IO == AB_BF16 || IO == AB_F16 || IO == AB_F32) {
+        if (vect && !want_mm && num_bins <= kPrivMaxBins && chan_elems >= kPrivMinElems && canon.C <= 1024) {
+            const size_t smem = (size_t)(num_bins + 1) * kPrivCopies * sizeof(unsigned int);
+            int rc = opt_in_smem<k_hist_private<IO>>((size_t)(kPrivMaxBins + 1) * kPrivCopies * sizeof(unsigned int));
+            if (rc != AB_OK) return rc;
+            AB_CUDA_OK(cudaMemsetAsync(counts, 0, sizeof(int64_t) * canon.C * (int64_t)num_bins, stream));
+            int64_t ptiles = (sm_count() + canon.C - 1) / canon.C;
+            if (ptiles < 1) ptiles = 1;
+            int64_t pt_elems = (chan_elems + ptiles - 1) / ptiles;
+            pt_elems = ((pt_elems + 15) / 16) * 16;
+            ptiles = (chan_elems + pt_elems - 1) / pt_elems;
+            HistPrivArgs h;
+            h.x = x;
+            h.lo = lo;
+            h.hi = hi;
+            h.below = below;
+            h.above = above;
+            h.counts = reinterpret_cast<unsigned long long *>(counts);
+            h.O = canon.O;
+            h.C = canon.C;
+            h.I = canon.I;
+            h.chan_elems = chan_elems;
+            h.tile_elems = pt_elems;
+            h.num_bins = num_bins;
+            dim3 grid((unsigned)ptiles, (unsigned)canon.C);
+            k_hist_private<IO><<<grid, kPrivThreads, smem, stream>>>(h);
+            AB_LAUNCH_OK();
+            return AB_OK;
         }
     }
     const int64_t need = want_mm ? canon.C * tiles * 2 * (int64_t)sizeof(double) : 0;
@@ -835,8 +853,6 @@ extern "C" int64_t aimet_b200_stats_scratch_bytes(const ab_layout *layout, int i
     const int64_t hist = (int64_t)ab::sm_count() * 8 + 2 * canon.C;
     if (hist > n) n = hist;
     int64_t bytes = n * 2 * (int64_t)sizeof(double);
-    const int64_t lut = ab::hist_lut_bytes(canon, io_dtype);
-    if (lut > bytes) bytes = lut;
     return bytes;
 }
 

@@ -144,3 +144,32 @@ def test_errors():
         sq.compute_encodings(255, False)
     with pytest.raises(ValueError):
         EA.PercentileEncodingAnalyzer((), percentile=20)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("channels", [1, 3])
+def test_large_histograms_with_outliers_and_non_finite_values(dtype, channels):
+    """The large-histogram kernel (lane-private counters, arithmetic binning) against torch.histc
+    plus the outlier rule, with a binning range narrower than the data, thresholds rounded to the
+    tensor dtype, infinities and NaN."""
+    from aimet_b200 import encoding_analyzer as EA
+
+    g = torch.Generator().manual_seed(5 + channels)
+    n = (1 << 20) + 4096
+    x = torch.randn(4, channels, n // 4, generator=g) * torch.tensor([1.0, 7.0, 0.01][:channels]).view(1, -1, 1)
+    x[0, 0, :6] = torch.tensor([float("inf"), -float("inf"), float("nan"), 1e30, -1e30, 0.0])
+    x = x.to(dtype).cuda()
+    shape = (1, channels, 1) if channels > 1 else ()
+    lay = EA._StatLayout(x, shape, None)
+    lo = torch.tensor([-2.3017, -20.0, -0.02][:channels], device="cuda")
+    hi = torch.tensor([2.7011, 13.0, 0.03][:channels], device="cuda")
+    got = EA._histogram_counts(lay, 2048, lo, hi).cpu()
+    xf = x.float().cpu()
+    for c in range(channels):
+        v = xf[:, c].flatten() if channels > 1 else xf.flatten()
+        below = lo[c].to(dtype).float().cpu()
+        above = hi[c].to(dtype).float().cpu()
+        want = torch.histc(v[(v >= lo[c].cpu()) & (v <= hi[c].cpu())], bins=2048, min=float(lo[c]), max=float(hi[c])).long()
+        want[0] += int((v < below).sum())
+        want[-1] += int((v > above).sum())
+        assert torch.equal(got[c], want), f"channel {c}: {(got[c] != want).sum()} bins differ"
