@@ -636,11 +636,26 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def run_kernels_only(steps):
+def run_kernels_only(steps, case):
     """A few eager resident steps and nothing else: the small, fixed launch sequence that the ncu
-    captures under ``profiles/`` are taken from (8 launches per step, see ResidentStep.run)."""
+    captures under ``profiles/`` are taken from (``qdq``: 8 launches per step, see
+    ResidentStep.run; ``calibration``: a two-phase SQNR calibration over 4 config-3 batches)."""
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
+    if case == "calibration":
+        from aimet_b200 import distributed as D
+        from aimet_b200 import encoding_analyzer as EA
+
+        gen = torch.Generator(device=dev).manual_seed(3000)
+        hot = torch.randperm(4096, device=dev, generator=gen)[:32]
+        batches = [student_t_batch(gen, hot, dev) for _ in range(4)]
+        for _ in range(steps):
+            an = EA.SqnrEncodingAnalyzer((), num_bins=2048)
+            D.calibrate_histogram(an, batches, None)
+            an.compute_encodings(255, False)
+        torch.cuda.synchronize()
+        print(json.dumps({"kernels_only_steps": steps, "case": case}))
+        return
     w, dy = make_weight(ROWS, COLS, seed=2000)
     resident = ResidentStep(w, dy, dev)
     for _ in range(steps):
@@ -659,9 +674,10 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the calibration and SeqMSE figures")
     ap.add_argument("--kernels-only", type=int, default=0, metavar="STEPS",
                     help="run STEPS eager resident steps and exit (for profiler captures)")
+    ap.add_argument("--kernels-case", default="qdq", choices=["qdq", "calibration"])
     args = ap.parse_args()
     if args.kernels_only:
-        run_kernels_only(args.kernels_only)
+        run_kernels_only(args.kernels_only, args.kernels_case)
     elif args.impl == "reference":
         run_reference(args)
     else:
