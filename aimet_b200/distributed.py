@@ -158,17 +158,16 @@ def calibrate_histogram(analyzer, batches: Sequence[torch.Tensor], group=None, *
     rank, world = _world(group)
     if not batches:
         raise PeerFailure(f"rank {rank} has no calibration batch; give every rank at least one")
-    mn = mx = None
-    for x in batches:
-        bmn, bmx = minmax_fn(x, shape, block, True)
-        mn = bmn if mn is None else torch.minimum(mn, bmn)
-        mx = bmx if mx is None else torch.maximum(mx, bmx)
+    # per-batch statistics are kept and combined once (one stack + reduce instead of a small
+    # kernel per batch)
+    mins, maxs = zip(*(minmax_fn(x, shape, block, True) for x in batches))
+    mn = torch.stack(mins).amin(dim=0) if len(mins) > 1 else mins[0]
+    mx = torch.stack(maxs).amax(dim=0) if len(maxs) > 1 else maxs[0]
     mn, mx = allreduce_minmax(mn, mx, group)
     edges = obs._create_bin_edges(mn, mx)  # pylint: disable=protected-access
-    counts = None
-    for x in batches:
-        c = counts_fn(x, shape, block, nbins, edges[:, 0], edges[:, -1])
-        counts = c if counts is None else counts + c
+    lo, hi = edges[:, 0].contiguous(), edges[:, -1].contiguous()
+    per_batch = [counts_fn(x, shape, block, nbins, lo, hi) for x in batches]
+    counts = torch.stack(per_batch).sum(dim=0) if len(per_batch) > 1 else per_batch[0]
     counts = allreduce_counts(counts, group)
     obs._state = _HistogramList(counts.to(torch.float32), edges, mn, mx)  # pylint: disable=protected-access
     e0, e1 = edges[:, 0], edges[:, -1]
