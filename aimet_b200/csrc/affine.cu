@@ -181,14 +181,52 @@ template <typename E> __device__ __forceinline__ Vec16<E> ring_read(uint32_t add
 }
 constexpr uint32_t kSlotStride = kThreads * 16;
 
+constexpr int kFwdU = 4;  // 16-byte vectors per forward iteration
+
+// The vectors of a thread's first forward iteration, requested into its ring slots (one commit
+// group) before the thread loads its parameters, so that the two memory latencies overlap.
+template <typename E>
+__device__ __forceinline__ void fwd_first_issue(uint32_t ring, const Vec16<E> *px, int lane, int nv, int G) {
+#pragma unroll
+    for (int u = 0; u < kFwdU; ++u)
+        if (lane + u * G < nv) cp_async16(ring + u * kSlotStride, px + u * G);
+    cp_async_commit();
+}
+
 template <int IO, int CT, int OP, int PATH, bool PRE>
-__device__ __forceinline__ void fwd_seg_loop(const Vec16<typename Elem<IO>::type> *__restrict__ px,
+__device__ __forceinline__ void fwd_seg_loop(uint32_t ring, const Vec16<typename Elem<IO>::type> *__restrict__ px,
                                              Vec16<typename Elem<IO>::type> *__restrict__ py, int lane, int nv, int G,
                                              const Enc<CT> &e, const Grid<typename Arith<CT>::T> &g, uint32_t big2) {
     using E = typename Elem<IO>::type;
-    constexpr int U = 4;
+    constexpr int U = kFwdU;
     int v = lane;
     const int step = U * G;
+    // first iteration: from the ring (see fwd_first_issue)
+    cp_async_wait<0>();
+    if (v + (U - 1) * G < nv) {
+        Vec16<E> xv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) xv[u] = ring_read<E>(ring + u * kSlotStride);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            Vec16<E> yv;
+            fwd_vec<IO, CT, OP, PATH, PRE>(xv[u], yv, e, g, big2);
+            py[u * G] = yv;
+        }
+    } else {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (v + u * G < nv) {
+                Vec16<E> yv;
+                fwd_vec<IO, CT, OP, PATH, PRE>(ring_read<E>(ring + u * kSlotStride), yv, e, g, big2);
+                py[u * G] = yv;
+            }
+        }
+        return;
+    }
+    v += step;
+    px += step;
+    py += step;
     for (; v + (U - 1) * G < nv; v += step, px += step, py += step) {
         Vec16<E> xv[U];
 #pragma unroll
@@ -229,28 +267,31 @@ __global__ void __launch_bounds__(kThreads, 5) k_fwd_seg(FwdSegArgs a) {
     if (!p.valid) return;
     const Vec16<E> *px = static_cast<const Vec16<E> *>(a.x) + p.v0 + p.lane;
     Vec16<E> *py = static_cast<Vec16<E> *>(a.y) + p.v0 + p.lane;
+    __shared__ __align__(16) unsigned char ring_mem[kFwdU * kSlotStride];
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(ring_mem) + threadIdx.x * 16u;
+    fwd_first_issue<E>(ring, px, p.lane, p.nv, a.group);
     const Enc<CT> e = load_enc<CT>(a.scale, a.offset, p.param, g);
     if constexpr (kQuant && kIo16) {
         uint32_t big2;
         if (abs_bound16<IO, CT>(e, big2)) {
             if constexpr (CT == IO) {
                 if (vec_packed_ok<CT>(e, g)) {
-                    fwd_seg_loop<IO, CT, OP, PATH_PACKED, true>(px, py, p.lane, p.nv, a.group, e, g, big2);
+                    fwd_seg_loop<IO, CT, OP, PATH_PACKED, true>(ring, px, py, p.lane, p.nv, a.group, e, g, big2);
                     return;
                 }
             }
             if (vec_fast_ok<CT>(e, g)) {
-                fwd_seg_loop<IO, CT, OP, PATH_FAST, true>(px, py, p.lane, p.nv, a.group, e, g, big2);
+                fwd_seg_loop<IO, CT, OP, PATH_FAST, true>(ring, px, py, p.lane, p.nv, a.group, e, g, big2);
                 return;
             }
         }
     } else if constexpr (kQuant && CT != AB_F64) {
         if (vec_fast_ok<CT>(e, g)) {
-            fwd_seg_loop<IO, CT, OP, PATH_FAST, false>(px, py, p.lane, p.nv, a.group, e, g, 0u);
+            fwd_seg_loop<IO, CT, OP, PATH_FAST, false>(ring, px, py, p.lane, p.nv, a.group, e, g, 0u);
             return;
         }
     }
-    fwd_seg_loop<IO, CT, OP, PATH_GENERIC, false>(px, py, p.lane, p.nv, a.group, e, g, 0u);
+    fwd_seg_loop<IO, CT, OP, PATH_GENERIC, false>(ring, px, py, p.lane, p.nv, a.group, e, g, 0u);
 }
 
 struct FwdGenArgs {
