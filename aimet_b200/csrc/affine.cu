@@ -256,14 +256,16 @@ __device__ __forceinline__ void fwd_seg_loop(uint32_t ring, const Vec16<typename
 
 template <int IO, int CT, int OP>
 __global__ void __launch_bounds__(kThreads, 5) k_fwd_seg(FwdSegArgs a) {
-    pdl_prologue();
+    pdl_launch_dependents();
     using E = typename Elem<IO>::type;
     using T = typename Arith<CT>::T;
     constexpr int NV = 16 / (int)sizeof(E);
     constexpr bool kIo16 = IO == AB_BF16 || IO == AB_F16;
     constexpr bool kQuant = OP == OP_QDQ || OP == OP_Q;
+    // index arithmetic needs no memory: it runs while the preceding kernel drains
     const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0, a.exact_edges};
     const SegPos p = seg_pos<NV>(a.cm, a.seg_len, a.nseg, a.nchunk, a.group);
+    pdl_wait();
     if (!p.valid) return;
     const Vec16<E> *px = static_cast<const Vec16<E> *>(a.x) + p.v0 + p.lane;
     Vec16<E> *py = static_cast<Vec16<E> *>(a.y) + p.v0 + p.lane;
@@ -416,7 +418,7 @@ __device__ __forceinline__ void bwd_seg_loop(uint32_t ring, const Vec16<typename
 // contiguous run of elements that share one parameter.
 template <int IO, int CT, int OP, bool VECT, bool WANT_O>
 __global__ void __launch_bounds__(kThreads, 4) k_bwd_seg(BwdArgs a) {
-    pdl_prologue();
+    pdl_launch_dependents();
     using E = typename Elem<IO>::type;
     using A = Arith<CT>;
     using T = typename A::T;
@@ -426,7 +428,9 @@ __global__ void __launch_bounds__(kThreads, 4) k_bwd_seg(BwdArgs a) {
     const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0, a.exact_edges};
 
     const int G = a.group;
+    // index arithmetic needs no memory: it runs while the preceding kernel drains
     const SegPos p = seg_pos<VEC>(a.cm, a.seg_len, a.nseg, a.nchunk, G);
+    pdl_wait();
     const int lane = p.lane;
     const bool valid = p.valid;
     const int64_t s = p.s, param = p.param;

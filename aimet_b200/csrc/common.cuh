@@ -75,9 +75,11 @@ int sm_count();
 // its predecessor in the stream is still draining; it must execute pdl_prologue() before it
 // touches global memory (the wait returns once the predecessor has completed and its writes are
 // visible).  The launch latency of back-to-back kernels disappears behind the predecessor's tail.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_prologue() {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    pdl_launch_dependents();
+    pdl_wait();
 }
 
 template <typename... KArgs, typename... Args>
