@@ -113,6 +113,7 @@ struct MinMaxArgs {
 };
 
 template <int IO, bool VECT> __global__ void __launch_bounds__(kThreads) k_minmax_seg(MinMaxArgs a) {
+    pdl_prologue();
     using E = typename Elem<IO>::type;
     using T = typename StatT<IO>::T;
     constexpr int VEC = VECT ? 16 / (int)sizeof(E) : 1;
@@ -209,6 +210,7 @@ template <int IO, bool VECT> __global__ void __launch_bounds__(kThreads) k_minma
 }
 
 template <int IO, bool VECT> __global__ void __launch_bounds__(kThreads) k_minmax_col(MinMaxArgs a) {
+    pdl_prologue();
     using E = typename Elem<IO>::type;
     using T = typename StatT<IO>::T;
     constexpr int VEC = VECT ? 16 / (int)sizeof(E) : 1;
@@ -254,6 +256,7 @@ struct MinMaxFinishArgs {
 };
 
 template <int IO, bool PER_CTA> __global__ void __launch_bounds__(kThreads) k_minmax_finish(MinMaxFinishArgs a) {
+    pdl_prologue();
     // PER_CTA: one CTA per statistic (many partials each); else one warp per statistic
     using E = typename Elem<IO>::type;
     const int64_t c = PER_CTA ? (int64_t)blockIdx.x : (((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5);
@@ -291,10 +294,10 @@ template <int IO, bool PER_CTA> __global__ void __launch_bounds__(kThreads) k_mi
 
 template <int IO> void launch_minmax_finish(const MinMaxFinishArgs &f, cudaStream_t stream) {
     if (f.na * f.nb > 256) {
-        k_minmax_finish<IO, true><<<(unsigned)f.nparam, kThreads, 0, stream>>>(f);
+        launch_pdl(k_minmax_finish<IO, true>, (unsigned)f.nparam, kThreads, 0, stream, f);
     } else {
         const int64_t grid = (f.nparam * 32 + kThreads - 1) / kThreads;
-        k_minmax_finish<IO, false><<<(unsigned)grid, kThreads, 0, stream>>>(f);
+        launch_pdl(k_minmax_finish<IO, false>, (unsigned)grid, kThreads, 0, stream, f);
     }
 }
 
@@ -328,17 +331,17 @@ int launch_minmax(const void *x, const Canon &canon, int finite_only, void *min_
         const int64_t grid = (p.nseg + gpc - 1) / gpc;
         if (grid > 2147483647LL) return fail(AB_ERR_UNSUPPORTED, "tensor too large for one launch");
         if (p.vect)
-            k_minmax_seg<IO, true><<<(unsigned)grid, kThreads, 0, stream>>>(a);
+            launch_pdl(k_minmax_seg<IO, true>, (unsigned)grid, kThreads, 0, stream, a);
         else
-            k_minmax_seg<IO, false><<<(unsigned)grid, kThreads, 0, stream>>>(a);
+            launch_pdl(k_minmax_seg<IO, false>, (unsigned)grid, kThreads, 0, stream, a);
     } else {
         const int v = p.vect ? 16 / dtype_size(IO) : 1;
         const int64_t gx = (a.row_len / v + kThreads - 1) / kThreads;
         dim3 grid((unsigned)gx, (unsigned)p.row_tiles);
         if (p.vect)
-            k_minmax_col<IO, true><<<grid, kThreads, 0, stream>>>(a);
+            launch_pdl(k_minmax_col<IO, true>, grid, kThreads, 0, stream, a);
         else
-            k_minmax_col<IO, false><<<grid, kThreads, 0, stream>>>(a);
+            launch_pdl(k_minmax_col<IO, false>, grid, kThreads, 0, stream, a);
     }
     AB_LAUNCH_OK();
     if (p.npartial > 0) {
@@ -377,6 +380,7 @@ __device__ __forceinline__ int histc_bin(float v, float lo, float range, float n
 // of a calibration batch pile up in a handful of bins, so a warp whose lanes all
 // hit the same bin issues a single shared-memory atomic.
 template <int IO, bool VECT> __global__ void __launch_bounds__(kThreads) k_histogram(HistArgs a) {
+    pdl_prologue();
     using E = typename Elem<IO>::type;
     constexpr int VEC = VECT ? 16 / (int)sizeof(E) : 1;
     extern __shared__ unsigned int sh_hist[];
@@ -564,6 +568,7 @@ template <typename E> __device__ __forceinline__ bool vec_inside(const Vec16<E> 
 }
 
 template <int IO> __global__ void __launch_bounds__(kPrivThreads, 1) k_hist_private(HistPrivArgs a) {
+    pdl_prologue();
     using E = typename Elem<IO>::type;
     constexpr int NV = 16 / (int)sizeof(E);
     extern __shared__ __align__(16) unsigned int sh_cnt[];  // [num_bins + 1][16]; row num_bins: v == hi
@@ -674,6 +679,20 @@ template <int IO> __global__ void __launch_bounds__(kPrivThreads, 1) k_hist_priv
     }
 }
 
+// Zeroes the count array.  A kernel rather than a memset node, so that the chain of launches stays
+// kernel -> kernel and the programmatic dependency of the histogram kernel has a grid to wait for.
+__global__ void __launch_bounds__(kThreads) k_zero_counts(unsigned long long *p, int64_t n) {
+    pdl_prologue();
+    const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (i < n) p[i] = 0ull;
+}
+inline int zero_counts(int64_t *counts, int64_t n, cudaStream_t stream) {
+    launch_pdl(k_zero_counts, (unsigned)((n + kThreads - 1) / kThreads), kThreads, 0, stream,
+               reinterpret_cast<unsigned long long *>(counts), n);
+    AB_LAUNCH_OK();
+    return AB_OK;
+}
+
 template <int IO>
 int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const float *lo, const float *hi,
                      const float *below, const float *above, int64_t *counts, void *fin_min, void *fin_max,
@@ -701,7 +720,8 @@ int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const 
             const size_t smem = (size_t)(num_bins + 1) * kPrivCopies * sizeof(unsigned int);
             int rc = opt_in_smem<k_hist_private<IO>>((size_t)(kPrivMaxBins + 1) * kPrivCopies * sizeof(unsigned int));
             if (rc != AB_OK) return rc;
-            AB_CUDA_OK(cudaMemsetAsync(counts, 0, sizeof(int64_t) * canon.C * (int64_t)num_bins, stream));
+            rc = zero_counts(counts, canon.C * (int64_t)num_bins, stream);
+            if (rc != AB_OK) return rc;
             int64_t ptiles = (sm_count() + canon.C - 1) / canon.C;
             if (ptiles < 1) ptiles = 1;
             int64_t pt_elems = (chan_elems + ptiles - 1) / ptiles;
@@ -721,7 +741,7 @@ int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const 
             h.tile_elems = pt_elems;
             h.num_bins = num_bins;
             dim3 grid((unsigned)ptiles, (unsigned)canon.C);
-            k_hist_private<IO><<<grid, kPrivThreads, smem, stream>>>(h);
+            launch_pdl(k_hist_private<IO>, grid, kPrivThreads, smem, stream, h);
             AB_LAUNCH_OK();
             return AB_OK;
         }
@@ -731,7 +751,10 @@ int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const 
         return fail(AB_ERR_SCRATCH, "histogram needs %lld bytes of scratch, got %lld", (long long)need,
                     (long long)scratch_bytes);
 
-    AB_CUDA_OK(cudaMemsetAsync(counts, 0, sizeof(int64_t) * canon.C * (int64_t)num_bins, stream));
+    {
+        const int zrc = zero_counts(counts, canon.C * (int64_t)num_bins, stream);
+        if (zrc != AB_OK) return zrc;
+    }
     HistArgs a;
     a.x = x;
     a.lo = lo;
@@ -750,9 +773,9 @@ int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const 
     dim3 grid((unsigned)tiles, (unsigned)canon.C);
     const size_t smem = sizeof(unsigned int) * (size_t)num_bins;
     if (vect)
-        k_histogram<IO, true><<<grid, kThreads, smem, stream>>>(a);
+        launch_pdl(k_histogram<IO, true>, grid, kThreads, smem, stream, a);
     else
-        k_histogram<IO, false><<<grid, kThreads, smem, stream>>>(a);
+        launch_pdl(k_histogram<IO, false>, grid, kThreads, smem, stream, a);
     AB_LAUNCH_OK();
     if (want_mm) {
         MinMaxFinishArgs f{a.mm_partial, fin_min, fin_max, canon.C, 1, 0, tiles, tiles};
@@ -777,6 +800,7 @@ struct SweepArgs {
 constexpr int kSweepThreads = 128;
 
 __global__ void __launch_bounds__(kSweepThreads) k_sqnr_sweep(SweepArgs a) {
+    pdl_prologue();
     const int cand = blockIdx.x, h = blockIdx.y;
     const float delta = a.deltas[(int64_t)h * a.num_cand + cand];
     const float offset = a.offsets[(a.offsets_per_hist ? (int64_t)h * a.num_cand : 0) + cand];
@@ -807,6 +831,7 @@ __global__ void __launch_bounds__(kSweepThreads) k_sqnr_sweep(SweepArgs a) {
 }
 
 __global__ void __launch_bounds__(kSweepThreads) k_argmin(const float *noise, int num_cand, int *best) {
+    pdl_prologue();
     const int h = blockIdx.x;
     const float *n = noise + (int64_t)h * num_cand;
     float bv = INFINITY;
@@ -922,9 +947,9 @@ extern "C" int aimet_b200_sqnr_sweep(const float *hist, const float *edge0, cons
     a.use_gamma = gamma != 1.0;
     a.noise = noise_out;
     dim3 grid((unsigned)num_cand, (unsigned)num_hist);
-    ab::k_sqnr_sweep<<<grid, ab::kSweepThreads, 0, st>>>(a);
+    ab::launch_pdl(ab::k_sqnr_sweep, grid, ab::kSweepThreads, 0, st, a);
     AB_LAUNCH_OK();
-    ab::k_argmin<<<(unsigned)num_hist, ab::kSweepThreads, 0, st>>>(noise_out, num_cand, best_out);
+    ab::launch_pdl(ab::k_argmin, (unsigned)num_hist, ab::kSweepThreads, 0, st, noise_out, num_cand, best_out);
     AB_LAUNCH_OK();
     return AB_OK;
 }
