@@ -490,7 +490,6 @@ def base_config(n_gpus):
                         "blockwise int4 (block 64) + LPBQ (int4, 8-bit per-channel scale), scale grads on",
             "elements_per_step": 3 * ROWS * COLS, "algorithmic_bytes_per_element": BYTES_PER_ELEM,
             "l2": "inputs larger than L2: 470 MB touched per encoding vs 126 MB L2",
-            "launch": "the step's kernel launches (C-ABI calls) are captured once and replayed as one CUDA graph",
             "parallelism": f"replicated layers x{n_gpus}"}
 
 
@@ -602,6 +601,7 @@ def run_ours(args):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": base_config(world),
+            "launch": "the step's kernel launches (C-ABI calls) are captured once and replayed as one CUDA graph",
             "roofline": {"bound": "hbm", "kernel": "k_bwd_seg (quantize-dequantize backward, bf16, [14336,4096])",
                          "achieved": achieved, "peak": peaks["hbm_gbs"], "peak_source": f"{peak_kind} copy bandwidth",
                          "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
