@@ -186,6 +186,38 @@ class SequentialMse:
         return MinMaxEncodingAnalyzer(shape).compute_encodings_from_stats(_MinMaxRange(lo, hi), steps, quantizer.symmetric)
 
     @classmethod
+    def _all_candidate_weights(cls, quantizer: AffineQuantizerBase, w: torch.Tensor, min_t, max_t, num_candidates: int):
+        """The weight quantize-dequantized under every candidate range, [C, out, in], with one kernel
+        launch: the candidates' ranges are formed with the same element-wise operations as
+        :meth:`_get_candidate` / :meth:`_candidate_encodings` (a leading candidate dimension added),
+        and a quantizer of shape (C, *shape) applies them to the weight repeated along that
+        dimension -- the same arithmetic per element as C separate calls."""
+        from .encoding_analyzer import MinMaxEncodingAnalyzer, _MinMaxRange
+
+        c = num_candidates
+        shape = tuple(quantizer.shape)
+        idx = torch.arange(1, c + 1, device=w.device, dtype=min_t.dtype).reshape((c,) + (1,) * min_t.dim())
+        cmax = _div(max_t, c).unsqueeze(0) * idx
+        cmin = _div(min_t, c).unsqueeze(0) * idx
+        lo, hi = torch.minimum(cmin, cmax), torch.maximum(cmin, cmax)
+        pad = (1,) * (lo.dim() - 1 - len(shape)) + shape
+        dims = tuple(d + 1 for d, (have, want) in enumerate(zip(lo.shape[1:], pad)) if have != want)
+        if dims:
+            lo, hi = lo.amin(dims, keepdim=True), hi.amax(dims, keepdim=True)
+        wide = (c,) + (1,) * (w.dim() - len(shape)) + shape
+        lo, hi = lo.reshape(wide), hi.reshape(wide)
+        steps = quantizer.qmax - quantizer.qmin - (1 if quantizer.zero_point_shift == 0.5 else 0)
+        lo, hi = MinMaxEncodingAnalyzer(wide).compute_encodings_from_stats(_MinMaxRange(lo, hi), steps, quantizer.symmetric)
+        block = None
+        if quantizer.block_size:
+            block = (1,) * (len(wide) - len(quantizer.block_size)) + tuple(quantizer.block_size)
+        probe = QuantizeDequantize(wide, quantizer.bitwidth, quantizer.symmetric, block_size=block,
+                                   zero_point_shift=quantizer.zero_point_shift).to(w.device)
+        probe.signed = quantizer.signed
+        probe.set_range(lo, hi)
+        return probe(w.unsqueeze(0).expand((c,) + tuple(w.shape))).detach()
+
+    @classmethod
     def _freeze_quantizer_encoding(cls, quantizer):
         quantizer.requires_grad_(False)
         quantizer.allow_overwrite(False)
@@ -247,11 +279,14 @@ class SequentialMse:
         nb = in_ch // block
         c = params.num_candidates
 
-        wq_all = torch.empty((c, out_ch, in_ch), dtype=w.dtype, device=w.device)
-        for i in range(c):
-            cmin, cmax = cls._get_candidate(i, c, min_t, max_t)
-            qtz.set_range(*cls._candidate_encodings(qtz, cmin, cmax))
-            wq_all[i].copy_(cls._get_quantized_weight(quant_module).detach())
+        if type(qtz) is QuantizeDequantize:  # pylint: disable=unidiomatic-typecheck
+            wq_all = cls._all_candidate_weights(qtz, w, min_t, max_t, c)
+        else:  # quantizers that derive their scale in their own way (LPBQ): one candidate at a time
+            wq_all = torch.empty((c, out_ch, in_ch), dtype=w.dtype, device=w.device)
+            for i in range(c):
+                cmin, cmax = cls._get_candidate(i, c, min_t, max_t)
+                qtz.set_range(*cls._candidate_encodings(qtz, cmin, cmax))
+                wq_all[i].copy_(cls._get_quantized_weight(quant_module).detach())
 
         lowp = not params.precise_loss and w.dtype != torch.float32
         total = None
