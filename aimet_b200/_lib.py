@@ -110,6 +110,7 @@ SIGNATURES = {
         _i32,
         [_vp, _lay, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp],
     ),
+    "aimet_b200_histogram_merge": (_i32, [_vp] * 7 + [_i32, _i32] + [_vp] * 5),
     "aimet_b200_sqnr_sweep": (
         _i32,
         [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f64, _f64, _vp, _vp, _vp],

@@ -786,6 +786,77 @@ int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const 
 }
 
 // ---------------------------------------------------------------------------
+// Merging an accumulated histogram into a (possibly wider) range, one CTA per histogram: the
+// body of _HistogramObserver.merge_stats (encoding_analyzer.py:231-323 of the reference) as one
+// launch instead of some sixty small tensor operations.  Every float operation is the one the
+// tensor expression performs, in the same order and without contraction: the updated range is
+// the batch's range clamped between the growth limit and the current edges; a source bin that
+// straddles a destination edge is split proportionally, the first part rounded half to even;
+// the new edges are ticks * step + lo.
+// ---------------------------------------------------------------------------
+struct MergeArgs {
+    const float *new_min, *new_max, *cur_min, *cur_max;
+    const float *cur_edges;  // [H][n + 1]
+    const float *cur_hist;   // [H][n]
+    const float *limit;      // [H][2]
+    float *out_min, *out_max;
+    float *out_carry;        // [H][n]
+    float *out_edges;        // [H][n + 1]
+    int num_bins;
+};
+
+__device__ __forceinline__ float min_prop(float a, float b) {  // torch.minimum: NaN propagates
+    return (a != a) ? a : ((b != b) ? b : (a < b ? a : b));
+}
+
+__global__ void __launch_bounds__(kThreads) k_hist_merge(MergeArgs a) {
+    pdl_prologue();
+    extern __shared__ float sh_carry[];
+    const int n = a.num_bins;
+    const int64_t h = blockIdx.x;
+    const float *edges = a.cur_edges + h * (int64_t)(n + 1);
+    const float *hist = a.cur_hist + h * (int64_t)n;
+    const float e0 = edges[0], e_last = edges[n];
+    const float umin = clamp_nan(a.new_min[h], a.limit[2 * h], e0);
+    const float umax = clamp_nan(a.new_max[h], e_last, a.limit[2 * h + 1]);
+    const bool keep = (umin == a.cur_min[h]) && (umax == a.cur_max[h]);
+    const float nf = (float)n;
+    const float dw = __fdiv_rn(__fsub_rn(umax, umin), nf);
+    const float sw = __fsub_rn(edges[1], edges[0]);
+    for (int j = threadIdx.x; j < n; j += kThreads) sh_carry[j] = 0.0f;
+    __syncthreads();
+    if (!keep) {
+        for (int j = threadIdx.x; j < n; j += kThreads) {
+            const float src = edges[j], cnt = hist[j];
+            int d1 = __float2int_rz(__fdiv_rn(__fsub_rn(src, umin), dw));
+            d1 = d1 > n - 1 ? n - 1 : d1;
+            const float d1_end = __fadd_rn(umin, __fmul_rn(dw, (float)(d1 + 1)));
+            const float part = __fmul_rn(__fdiv_rn(__fsub_rn(d1_end, src), sw), cnt);
+            const float first = min_prop(rintf(part), cnt);
+            int d2 = __float2int_rz(__fdiv_rn(__fsub_rn(__fadd_rn(src, dw), umin), dw));
+            d2 = d2 > n - 1 ? n - 1 : d2;
+            const float rest = __fsub_rn(cnt, first);
+            const int i1 = d1 < 0 ? 0 : d1, i2 = d2 < 0 ? 0 : d2;
+            atomicAdd(&sh_carry[i1], first);
+            if (first < cnt) atomicAdd(&sh_carry[i2], rest);
+        }
+    }
+    __syncthreads();
+    float *carry = a.out_carry + h * (int64_t)n;
+    for (int j = threadIdx.x; j < n; j += kThreads) carry[j] = keep ? hist[j] : sh_carry[j];
+    // edges of the merged range; a degenerate range is widened by 0.5 on each side
+    const bool same = umin == umax;
+    const float lo = same ? __fsub_rn(umin, 0.5f) : umin, hi = same ? __fadd_rn(umax, 0.5f) : umax;
+    const float step = __fdiv_rn(__fsub_rn(hi, lo), nf);
+    float *oe = a.out_edges + h * (int64_t)(n + 1);
+    for (int j = threadIdx.x; j <= n; j += kThreads) oe[j] = __fadd_rn(__fmul_rn((float)j, step), lo);
+    if (threadIdx.x == 0) {
+        a.out_min[h] = umin;
+        a.out_max[h] = umax;
+    }
+}
+
+// ---------------------------------------------------------------------------
 // SQNR sweep: noise of every (delta, offset) candidate against a histogram
 // ---------------------------------------------------------------------------
 struct SweepArgs {
@@ -950,6 +1021,23 @@ extern "C" int aimet_b200_sqnr_sweep(const float *hist, const float *edge0, cons
     ab::launch_pdl(ab::k_sqnr_sweep, grid, ab::kSweepThreads, 0, st, a);
     AB_LAUNCH_OK();
     ab::launch_pdl(ab::k_argmin, (unsigned)num_hist, ab::kSweepThreads, 0, st, noise_out, num_cand, best_out);
+    AB_LAUNCH_OK();
+    return AB_OK;
+}
+
+extern "C" int aimet_b200_histogram_merge(const float *new_min, const float *new_max, const float *cur_min,
+                                          const float *cur_max, const float *cur_edges, const float *cur_hist,
+                                          const float *range_limit, int32_t num_hist, int32_t num_bins, float *out_min,
+                                          float *out_max, float *out_carry, float *out_edges, void *stream) {
+    if (num_hist <= 0 || num_bins <= 0) return ab::fail(AB_ERR_INVALID, "num_hist and num_bins must be positive");
+    if (num_bins > 8192) return ab::fail(AB_ERR_UNSUPPORTED, "at most 8192 bins, got %d", (int)num_bins);
+    if (!new_min || !new_max || !cur_min || !cur_max || !cur_edges || !cur_hist || !range_limit || !out_min || !out_max ||
+        !out_carry || !out_edges)
+        return ab::fail(AB_ERR_INVALID, "NULL pointer argument");
+    ab::MergeArgs a{new_min, new_max, cur_min, cur_max, cur_edges, cur_hist, range_limit,
+                    out_min, out_max, out_carry, out_edges, num_bins};
+    ab::launch_pdl(ab::k_hist_merge, (unsigned)num_hist, ab::kThreads, sizeof(float) * (size_t)num_bins,
+                   static_cast<cudaStream_t>(stream), a);
     AB_LAUNCH_OK();
     return AB_OK;
 }

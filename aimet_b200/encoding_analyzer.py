@@ -238,6 +238,23 @@ def _histogram(lay: _StatLayout, num_bins: int, lo: torch.Tensor, hi: torch.Tens
     return _histogram_counts(lay, num_bins, lo, hi).to(torch.float32)
 
 
+def _merge_histograms(new: "_HistogramList", cur: "_HistogramList", limit: torch.Tensor, num_bins: int):
+    """(updated min, updated max, carried counts, updated edges) of ``cur`` widened to cover ``new``."""
+    dev = cur.histogram.device
+    f32 = lambda t: t.detach().to(torch.float32).contiguous()  # noqa: E731  (exact for 16-bit statistics)
+    h = cur.histogram.shape[0]
+    out_min = torch.empty(h, dtype=torch.float32, device=dev)
+    out_max = torch.empty(h, dtype=torch.float32, device=dev)
+    carry = torch.empty((h, num_bins), dtype=torch.float32, device=dev)
+    edges = torch.empty((h, num_bins + 1), dtype=torch.float32, device=dev)
+    args = [f32(new.min), f32(new.max), f32(cur.min), f32(cur.max), f32(cur.bin_edges), f32(cur.histogram), f32(limit)]
+    with torch.cuda.device(dev):
+        rc = lib.aimet_b200_histogram_merge(*[t.data_ptr() for t in args], h, num_bins, out_min.data_ptr(),
+                                            out_max.data_ptr(), carry.data_ptr(), edges.data_ptr(), _lib.stream_ptr(dev))
+    _lib.check(rc)
+    return out_min, out_max, carry, edges
+
+
 # --------------------------------------------------------------------------------------------
 # observers
 # --------------------------------------------------------------------------------------------
@@ -332,34 +349,15 @@ class _HistogramObserver(_Observer):
             )
             return
         cur = self._state
-        lim = self._histogram_range_limit
-        umin = new.min.clamp(lim[:, 0], cur.bin_edges[:, 0])
-        umax = new.max.clamp(cur.bin_edges[:, -1], lim[:, 1])
-        keep = (umin == cur.min) & (umax == cur.max)  # the current range already covers the batch
-
-        # move the accumulated counts into the bins of the new range; a source bin that straddles a
-        # destination edge is split proportionally and rounded (:274-310)
-        dw = _div(umax - umin, n)
-        sw = cur.bin_edges[:, 1] - cur.bin_edges[:, 0]
-        src = cur.bin_edges[:, :-1]
-        d1 = self._bin_index(dw, umin, src)
-        d1_end = umin[:, None] + dw[:, None] * (d1 + 1)
-        first = torch.minimum(torch.round(((d1_end - src) / sw[:, None]) * cur.histogram), cur.histogram)
-        d2 = self._bin_index(dw, umin, src + dw[:, None])
-        rest = cur.histogram - first
-        split = first < cur.histogram
-        live = ~keep[:, None]
-        rows = torch.arange(len(cur), device=umin.device)[:, None] * n
-        carry = torch.zeros(len(cur) * n, dtype=cur.histogram.dtype, device=umin.device)
-        carry.index_add_(0, (rows + d1.clamp(0, n - 1)).flatten(), torch.where(live, first, 0.0).flatten())
-        carry.index_add_(0, (rows + d2.clamp(0, n - 1)).flatten(), torch.where(live & split, rest, 0.0).flatten())
-        carry = torch.where(keep[:, None], cur.histogram, carry.view(len(cur), n))
-
         x = _check_input(input_tensor)
+        # the accumulated counts moved into the bins of the updated range, the updated range and its
+        # edges: one kernel (a source bin that straddles a destination edge is split proportionally
+        # and rounded, :274-310)
+        umin, umax, carry, edges = _merge_histograms(new, cur, self._histogram_range_limit, n)
         lay = _StatLayout(x, self.shape, self.block_size)
         hist = _histogram(lay, n, umin, umax)
         hist += carry
-        self._state = _HistogramList(hist, self._create_bin_edges(umin, umax), umin, umax)
+        self._state = _HistogramList(hist, edges, umin, umax)
 
     def reset_stats(self):
         self._state = None

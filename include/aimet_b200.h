@@ -173,6 +173,25 @@ int aimet_b200_histogram(const void *x, const ab_layout *layout, int io_dtype, i
                          int64_t *counts, void *fin_min, void *fin_max, void *scratch,
                          int64_t scratch_bytes, void *stream);
 
+/* Moves accumulated histograms into the range that also covers a new batch, one launch for
+ * what _HistogramObserver.merge_stats (encoding_analyzer.py:231-323) does with tensor
+ * expressions: updated range = batch range clamped between the growth limit and the current
+ * edges; counts of a source bin that straddles a destination edge are split proportionally
+ * (first part rounded half to even); new edges = ticks * step + lo.  All float32.
+ *   new_min/new_max   [H]   finite range of the new batch
+ *   cur_min/cur_max   [H]   range of the accumulated histograms
+ *   cur_edges         [H][num_bins + 1], cur_hist [H][num_bins]
+ *   range_limit       [H][2] growth limit (lower, upper)
+ *   out_min/out_max   [H]   updated range
+ *   out_carry         [H][num_bins] the accumulated counts in the bins of the updated range
+ *                     (a copy of cur_hist where the range did not change)
+ *   out_edges         [H][num_bins + 1] edges of the updated range */
+int aimet_b200_histogram_merge(const float *new_min, const float *new_max, const float *cur_min,
+                               const float *cur_max, const float *cur_edges, const float *cur_hist,
+                               const float *range_limit, int32_t num_hist, int32_t num_bins,
+                               float *out_min, float *out_max, float *out_carry, float *out_edges,
+                               void *stream);
+
 /* Expected clipping + rounding noise of every (delta, offset) candidate against
  * a histogram, and the arg-min per histogram.
  *   hist        float32 [H][num_bins]
