@@ -111,6 +111,30 @@ class _HistogramList(_SequenceABC):
         )
 
 
+class _LazyHistogramList(_HistogramList):
+    """Statistics of one batch whose histogram is computed when it is first read.  Merging into an
+    accumulated histogram only needs the batch's range (the counts are taken again over the merged
+    range), so a caller that does not look at the per-batch histogram saves a pass over the tensor.
+    The observed tensor must not be modified before the histogram is read."""
+
+    def __init__(self, compute, bin_edges, min, max):  # pylint: disable=redefined-builtin,super-init-not-called
+        self._compute, self._hist = compute, None
+        self.bin_edges, self.min, self.max = bin_edges, min, max
+
+    @property
+    def histogram(self):
+        if self._hist is None:
+            self._hist, self._compute = self._compute(), None
+        return self._hist
+
+    @histogram.setter
+    def histogram(self, value):
+        self._hist, self._compute = value, None
+
+    def __len__(self):
+        return self.bin_edges.shape[0]
+
+
 # --------------------------------------------------------------------------------------------
 # kernel plumbing
 # --------------------------------------------------------------------------------------------
@@ -329,6 +353,8 @@ class _HistogramObserver(_Observer):
         lay = _StatLayout(x, self.shape, self.block_size)
         mn, mx = _minmax(lay, finite_only=True)
         edges = self._create_bin_edges(mn, mx)
+        if self._state is not None:  # statistics exist already: this batch's own histogram may never be read
+            return _LazyHistogramList(lambda: _histogram(lay, self.num_bins, edges[:, 0], edges[:, -1]), edges, mn, mx)
         hist = _histogram(lay, self.num_bins, edges[:, 0], edges[:, -1])
         return _HistogramList(hist, edges, mn, mx)
 

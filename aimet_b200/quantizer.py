@@ -434,6 +434,8 @@ class AffineQuantizerBase(QuantizerBase):
             if input.numel() == 0:
                 return run(input)
             batch_stats = self.encoding_analyzer.update_stats(input)
+            if passthrough:  # nothing is quantized while observing: no per-batch encoding needed
+                return run(input)
             dyn_min, dyn_max = self.encoding_analyzer.compute_encodings_from_stats(
                 batch_stats, self._calibration_steps(), self.symmetric
             )

@@ -377,7 +377,20 @@ def calibration_figure(dev, rank, world, num_batches=64):
     tokens = num_batches * 16 * 2048
     peaks, kind = measured_peaks()
     bytes_moved = num_batches * 16 * 2048 * 4096 * 2 * 2  # two passes over every batch
-    return {"metric": "calibration_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "ms": ms,
+    # the reference's own calling pattern: update_stats batch after batch (range growth + merge)
+    seq = EA.SqnrEncodingAnalyzer((), num_bins=2048)
+    seq.update_stats(batches[0])
+    torch.cuda.synchronize()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for x in batches:
+        seq.update_stats(x)
+    s1.record()
+    torch.cuda.synchronize()
+    seq_ms = s0.elapsed_time(s1)
+    sequential = {"tokens_per_s_per_gpu": len(batches) * 16 * 2048 / (seq_ms * 1e-3), "ms_per_batch": seq_ms / len(batches),
+                  "what": "analyzer.update_stats on this rank's batches one after the other (no exchange)"}
+    return {"sequential_update_stats": sequential, "metric": "calibration_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "ms": ms,
             "batches": num_batches, "batch_shape": [16, 2048, 4096], "analyzer": "SQNR, 2048 bins, 17x21 asymmetric candidates",
             "algorithmic_bytes": bytes_moved, "achieved_GBps_per_gpu": bytes_moved / world / (ms * 1e-3) / 1e9,
             "frac_of_" + kind + "_hbm": bytes_moved / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
