@@ -1,6 +1,6 @@
-// Device-side arithmetic of the affine quantizers, shared by the kernels in affine.cu and
-// affine_rows.cu: the per-parameter set-up (Enc), the element functions that follow the
-// reference op by op, and the straight-line fast paths over one 16-byte vector.
+// Device-side arithmetic of the affine quantizers, used by the kernels in affine.cu: the
+// per-parameter set-up (Enc), the element functions that follow the reference op by op, and the
+// straight-line fast paths over one 16-byte vector.
 //
 // Arithmetic follows QuantizeFunc / DequantizeFunc / QuantDequantFunc of the reference
 // (quantization/affine/backends/torch_builtins.py:588-831) step by step, including the
