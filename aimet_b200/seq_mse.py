@@ -94,12 +94,21 @@ def _expand_fp32_rhs(w: torch.Tensor) -> torch.Tensor:
     return torch.cat([w1, w2, w1, w3, w2, w1], dim=-1).contiguous()
 
 
-def linear_loss_all_candidates(x, xq, w, wq_all, loss_fn: str = "mse", lowp: bool = False) -> torch.Tensor:
+def _raise_on_status(status: torch.Tensor):
+    code = int(status.max().item())
+    if code != 0:
+        raise RuntimeError(f"aimet_b200: the SeqMSE kernel gave up waiting (device status {code})")
+
+
+def linear_loss_all_candidates(x, xq, w, wq_all, loss_fn: str = "mse", lowp: bool = False,
+                               status_sink: Optional[list] = None) -> torch.Tensor:
     """Loss of every candidate and output channel for one batch of tokens.
 
     x, xq: [tokens, K]; w: [N, K]; wq_all: [C, N, K].  Returns float32 [C, N]:
     ``mse``: sum_m (x.w - xq.wq_c)^2, ``l1``: sum_m |x.w - xq.wq_c|, ``sqnr``: the reference's negative
     SQNR in dB with ``xq.wq_c`` as the signal (seq_mse.py:440-454 passes (xw, xqwq) in that order).
+    ``status_sink``: a list that receives the launch's device status word instead of it being read
+    back (and the host waiting) here; the caller then checks all its launches with one read.
     """
     if not x.is_cuda:
         raise RuntimeError("aimet_b200 SeqMSE runs on CUDA tensors only; there is no CPU fallback.")
@@ -133,9 +142,10 @@ def linear_loss_all_candidates(x, xq, w, wq_all, loss_fn: str = "mse", lowp: boo
                                                status.data_ptr(), scratch.data_ptr(), scratch.numel(),
                                                _lib.stream_ptr(dev))
     _lib.check(rc)
-    code = int(status.item())
-    if code != 0:
-        raise RuntimeError(f"aimet_b200: the SeqMSE kernel gave up waiting (device status {code})")
+    if status_sink is None:
+        _raise_on_status(status)  # reads the kernel's status word: synchronises with the device
+    else:
+        status_sink.append(status)  # the caller checks all its launches at once
     if kind == 2:
         noise = _div(out[..., 0], m) + 1e-10
         signal = _div(out[..., 1], m)
@@ -290,6 +300,8 @@ class SequentialMse:
 
         lowp = not params.precise_loss and w.dtype != torch.float32
         total = None
+        pending = []  # status words of the launches below, read back once
+        w_blocks = wq_blocks = None
         with torch.no_grad():
             for b, (bx, bxq) in enumerate(zip(x, xq)):
                 if params.num_batches and b >= params.num_batches:
@@ -297,17 +309,27 @@ class SequentialMse:
                 bx2, bxq2 = bx.reshape(-1, in_ch), bxq.reshape(-1, in_ch)
                 same = bxq is bx or (bxq.data_ptr() == bx.data_ptr() and bxq.shape == bx.shape)
                 cols = []
-                for k in range(nb):
-                    sl = slice(k * block, (k + 1) * block)
-                    xs = bx2[:, sl].contiguous() if nb > 1 else bx2.contiguous()
-                    xqs = xs if same else (bxq2[:, sl].contiguous() if nb > 1 else bxq2.contiguous())
-                    ws = w[:, sl].contiguous() if nb > 1 else w
-                    wqs = wq_all[:, :, sl].contiguous() if nb > 1 else wq_all
-                    cols.append(linear_loss_all_candidates(xs, xqs, ws, wqs, params.loss_fn, lowp))
+                if nb > 1:
+                    # block-major copies once per batch: [nb, rows, block], contiguous per block
+                    xb = bx2.reshape(-1, nb, block).permute(1, 0, 2).contiguous()
+                    xqb = xb if same else bxq2.reshape(-1, nb, block).permute(1, 0, 2).contiguous()
+                    if w_blocks is None:
+                        w_blocks = w.reshape(out_ch, nb, block).permute(1, 0, 2).contiguous()
+                        wq_blocks = wq_all.reshape(c, out_ch, nb, block).permute(2, 0, 1, 3).contiguous()
+                    for k in range(nb):
+                        xk = xb[k]
+                        cols.append(linear_loss_all_candidates(xk, xk if same else xqb[k], w_blocks[k], wq_blocks[k],
+                                                               params.loss_fn, lowp, pending))
+                else:
+                    xs = bx2.contiguous()
+                    cols.append(linear_loss_all_candidates(xs, xs if same else bxq2.contiguous(), w, wq_all,
+                                                           params.loss_fn, lowp, pending))
                 loss = torch.stack(cols, dim=-1)  # [C, out, nb] float32
                 if lowp:
                     loss = loss.to(w.dtype)
                 total = loss if total is None else total + loss
+        if pending:
+            _raise_on_status(torch.cat(pending))
         cls.last_losses = total  # kept for inspection by tests and tools
         best = total.min(0)[1]
         while best.dim() < max_t.dim():
