@@ -38,11 +38,27 @@ class QuantizedLayer(nn.Module):
     def weight(self):
         return self.layer.weight
 
+    def _quantized_weight(self, qw):
+        """The quantize-dequantized weight.  The reference re-quantizes every weight on every forward
+        (nn/base.py:296-325); without autograd the result only changes when the weight or the
+        quantizer's range does, so it is kept until either is modified (both are versioned tensors)."""
+        weight = self.layer.weight
+        calibrating = getattr(qw, "_observer_hook", None) is not None
+        if torch.is_grad_enabled() or calibrating or not qw.is_initialized():
+            return qw(weight)
+        key = (id(weight), weight._version, id(qw._pinned_encoding), qw._encoding_cache_key())  # pylint: disable=protected-access
+        cached = self.__dict__.get("_wq_cache")
+        if cached is not None and cached[0] == key:
+            return cached[1]
+        out = qw(weight)
+        self.__dict__["_wq_cache"] = (key, out)
+        return out
+
     def forward(self, x):
         qi, qo, qw = self.input_quantizers[0], self.output_quantizers[0], self.param_quantizers["weight"]
         if qi is not None:
             x = qi(x)
-        w = self.layer.weight if qw is None else qw(self.layer.weight)
+        w = self.layer.weight if qw is None else self._quantized_weight(qw)
         if isinstance(self.layer, nn.Conv2d):
             out = self.layer._conv_forward(x, w, self.layer.bias)  # pylint: disable=protected-access
         else:

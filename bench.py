@@ -483,6 +483,13 @@ def resnet50_figure(dev, batch=256):
     qmodel = qnn.quantize_model(model)
     with torch.no_grad(), qnn.compute_encodings(qmodel):
         qmodel(x[:32])
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    with torch.no_grad(), qnn.compute_encodings(qmodel):  # model-level calibration, timed on its second run
+        qmodel(x[:64])
+        qmodel(x[64:128])
+    torch.cuda.synchronize()
+    calib_ms = (time.perf_counter() - t0) * 1e3
     quant_ms = timed(qmodel)
     layers = list(qnn.quantized_layers(qmodel))
     act_elems, w_elems = 0, 0
@@ -499,12 +506,14 @@ def resnet50_figure(dev, batch=256):
         qmodel(x)
     for h in hooks:
         h.remove()
-    qdq_bytes = (act_elems + w_elems) * 8
+    qdq_bytes = act_elems * 8  # the quantized weights are kept across forwards (25.5 M elements, once)
     peaks, kind = measured_peaks()
     qdq_ms = quant_ms - plain_ms
     return {"metric": "quantsim_resnet50_images_per_s", "value": batch / (quant_ms * 1e-3), "unit": "images/s",
             "batch": batch, "quantized_layers": len(layers), "forward_ms": quant_ms, "plain_forward_ms": plain_ms,
             "qdq_ms": qdq_ms, "qdq_share": qdq_ms / quant_ms, "qdq_algorithmic_bytes": qdq_bytes,
+            "weight_elements": w_elems, "weight_qdq": "kept across forwards while weight and range are unchanged",
+            "calibration_ms_128_images": calib_ms,
             "qdq_achieved_GBps": qdq_bytes / (qdq_ms * 1e-3) / 1e9,
             "qdq_frac_of_" + kind + "_hbm": qdq_bytes / (qdq_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
 

@@ -44,10 +44,16 @@ def test_quantized_cnn_matches_oracle_layer_by_layer():
     hooks = [spy(q) for layer in layers
              for q in (layer.input_quantizers[0], layer.output_quantizers[0], layer.param_quantizers["weight"])]
     with torch.no_grad():
+        for layer in layers:
+            layer.layer.weight.add_(0)  # an in-place update: the kept quantized weight must be refreshed
         y = model(x)
+        assert y.shape == (5, 10) and len(seen) == 9
+        # a second forward reuses the quantized weights (6 activation quantizer calls only), same result
+        y2 = model(x)
+        assert len(seen) == 15 and torch.equal(y, y2)
+        del seen[9:]
     for h in hooks:
         h.remove()
-    assert y.shape == (5, 10) and len(seen) == 9
     for q, inp, out in seen:
         assert q.is_initialized()
         scale, offset = q.get_scale().detach().cpu(), q.get_offset().detach().cpu()
