@@ -196,14 +196,17 @@ __device__ __forceinline__ void fwd_first_issue(uint32_t ring, const Vec16<E> *p
 template <int IO, int CT, int OP, int PATH, bool PRE>
 __device__ __forceinline__ void fwd_seg_loop(uint32_t ring, const Vec16<typename Elem<IO>::type> *__restrict__ px,
                                              Vec16<typename Elem<IO>::type> *__restrict__ py, int lane, int nv, int G,
-                                             const Enc<CT> &e, const Grid<typename Arith<CT>::T> &g, uint32_t big2) {
+                                             const Enc<CT> &e, const Grid<typename Arith<CT>::T> &g, uint32_t big2,
+                                             bool ringed) {
     using E = typename Elem<IO>::type;
     constexpr int U = kFwdU;
     int v = lane;
     const int step = U * G;
-    // first iteration: from the ring (see fwd_first_issue)
-    cp_async_wait<0>();
-    if (v + (U - 1) * G < nv) {
+    // first iteration: from the ring (see fwd_first_issue) when the caller requested it there
+    if (ringed) cp_async_wait<0>();
+    if (!ringed) {
+        // nothing requested: the loops below start at the thread's first vector
+    } else if (v + (U - 1) * G < nv) {
         Vec16<E> xv[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) xv[u] = ring_read<E>(ring + u * kSlotStride);
@@ -224,9 +227,11 @@ __device__ __forceinline__ void fwd_seg_loop(uint32_t ring, const Vec16<typename
         }
         return;
     }
-    v += step;
-    px += step;
-    py += step;
+    if (ringed) {
+        v += step;
+        px += step;
+        py += step;
+    }
     for (; v + (U - 1) * G < nv; v += step, px += step, py += step) {
         Vec16<E> xv[U];
 #pragma unroll
@@ -271,29 +276,32 @@ __global__ void __launch_bounds__(kThreads, 5) k_fwd_seg(FwdSegArgs a) {
     Vec16<E> *py = static_cast<Vec16<E> *>(a.y) + p.v0 + p.lane;
     __shared__ __align__(16) unsigned char ring_mem[kFwdU * kSlotStride];
     const uint32_t ring = (uint32_t)__cvta_generic_to_shared(ring_mem) + threadIdx.x * 16u;
-    fwd_first_issue<E>(ring, px, p.lane, p.nv, a.group);
+    // worth it when the thread has further iterations; a single-iteration thread (short runs) is
+    // better off with plain loads
+    const bool ringed = p.nv > kFwdU * a.group;
+    if (ringed) fwd_first_issue<E>(ring, px, p.lane, p.nv, a.group);
     const Enc<CT> e = load_enc<CT>(a.scale, a.offset, p.param, g);
     if constexpr (kQuant && kIo16) {
         uint32_t big2;
         if (abs_bound16<IO, CT>(e, big2)) {
             if constexpr (CT == IO) {
                 if (vec_packed_ok<CT>(e, g)) {
-                    fwd_seg_loop<IO, CT, OP, PATH_PACKED, true>(ring, px, py, p.lane, p.nv, a.group, e, g, big2);
+                    fwd_seg_loop<IO, CT, OP, PATH_PACKED, true>(ring, px, py, p.lane, p.nv, a.group, e, g, big2, ringed);
                     return;
                 }
             }
             if (vec_fast_ok<CT>(e, g)) {
-                fwd_seg_loop<IO, CT, OP, PATH_FAST, true>(ring, px, py, p.lane, p.nv, a.group, e, g, big2);
+                fwd_seg_loop<IO, CT, OP, PATH_FAST, true>(ring, px, py, p.lane, p.nv, a.group, e, g, big2, ringed);
                 return;
             }
         }
     } else if constexpr (kQuant && CT != AB_F64) {
         if (vec_fast_ok<CT>(e, g)) {
-            fwd_seg_loop<IO, CT, OP, PATH_FAST, false>(ring, px, py, p.lane, p.nv, a.group, e, g, 0u);
+            fwd_seg_loop<IO, CT, OP, PATH_FAST, false>(ring, px, py, p.lane, p.nv, a.group, e, g, 0u, ringed);
             return;
         }
     }
-    fwd_seg_loop<IO, CT, OP, PATH_GENERIC, false>(ring, px, py, p.lane, p.nv, a.group, e, g, 0u);
+    fwd_seg_loop<IO, CT, OP, PATH_GENERIC, false>(ring, px, py, p.lane, p.nv, a.group, e, g, 0u, ringed);
 }
 
 struct FwdGenArgs {
