@@ -115,6 +115,12 @@ SIGNATURES = {
         _i32,
         [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f64, _f64, _vp, _vp, _vp],
     ),
+    "aimet_b200_seqmse_blocks_scratch_bytes": (_i64, [_i64, _i64, _i64, _i32, _i32]),
+    "aimet_b200_seqmse_linear_loss_blocks": (
+        _i32,
+        [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i64, _vp],
+    ),
+    "aimet_b200_seqmse_wait_selftest": (_i32, [_vp, _i64, _vp]),
     "aimet_b200_seqmse_scratch_bytes": (_i64, [_i64, _i64, _i64, _i32]),
     "aimet_b200_seqmse_linear_loss": (
         _i32,

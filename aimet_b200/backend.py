@@ -263,8 +263,14 @@ def _run_forward(tensor, scale, offset, op, qmin, qmax, zps, block_size, interna
     return _restore(y, plan, tensor), x, s, o, plan
 
 
+@torch.compiler.disable
 def _apply(tensor, scale, offset, op, qmin, qmax, zps, block_size, internal_dtype):
-    """Through autograd only when a gradient can flow; otherwise straight to the kernel."""
+    """Through autograd only when a gradient can flow; otherwise straight to the kernel.
+
+    Opaque to ``torch.compile``: the kernels are reached through ctypes, which a tracing compiler
+    cannot follow, so a compiled region breaks its graph here and runs this call eagerly (the
+    reference registers ``torch.library`` operators with meta kernels for its Triton backend,
+    triton.py:685-881; an opaque eager call gives the same results without a second code path)."""
     if torch.is_grad_enabled() and (tensor.requires_grad or scale.requires_grad or offset.requires_grad):
         return _AffineFunction.apply(tensor, scale, offset, op, qmin, qmax, zps, block_size, internal_dtype)
     return _run_forward(tensor, scale, offset, op, qmin, qmax, zps, block_size, internal_dtype)[0]
@@ -398,7 +404,7 @@ def quantize_dequantize(
     _validate(input, scale, offset, qmin, qmax, block_size)
     qmin, qmax = int(qmin), int(qmax)
     zero_point_shift = zero_point_shift or 0.0
-    if _takes_fake_quantize_path(input, scale, offset, block_size, zero_point_shift):
+    if _takes_fake_quantize_path(input, scale, offset, block_size, zero_point_shift, qmin, qmax):
         return _apply(input, scale.detach(), offset.detach(), "fq", qmin, qmax, 0.0, None, torch.float32)
     internal = _internal_dtype(input.dtype, qmin, qmax)
     if not _is_grid_representable(internal, qmin, qmax):
@@ -406,13 +412,27 @@ def quantize_dequantize(
     return _apply(input, scale, offset, "qdq", qmin, qmax, zero_point_shift, block_size, internal)
 
 
-def _takes_fake_quantize_path(tensor, scale, offset, block_size, zero_point_shift) -> bool:
-    """The reference's ``_fast_forward`` test plus the shape test of ``_torch_fake_quantize``
-    (torch_builtins.py:243-266, 352-431): no parameter gradient wanted, not blockwise, no shift, and
-    the parameters are per-tensor or vary along exactly one axis.  (Unlike the reference's
-    per-channel call, no host-side range check of the zero points is made -- that would force a
-    device synchronisation; symmetric and calibrated asymmetric encodings always pass it.)"""
+def _zero_points_in_grid(offset: torch.Tensor, qmin: int, qmax: int) -> bool:
+    """Whether every zero point (-offset) lies in [qmin, qmax].  torch.fake_quantize_per_channel_affine
+    refuses anything else, and the reference then falls back to the QuantDequantFunc arithmetic
+    (torch_builtins.py:418-425).  Offsets that a quantizer module built from a constant carry that
+    constant, so the usual case (symmetric per-channel weights) is decided on the host; otherwise
+    the device is asked, as ATen's own check does."""
+    const = getattr(offset, "_b200_constant", None)
+    if const is not None:
+        return qmin <= -const <= qmax
+    lo, hi = torch.aminmax(offset.detach())
+    return bool((-hi >= qmin) & (-lo <= qmax))
+
+
+def _takes_fake_quantize_path(tensor, scale, offset, block_size, zero_point_shift, qmin=None, qmax=None) -> bool:
+    """The reference's ``_fast_forward`` test plus the tests of ``_torch_fake_quantize``
+    (torch_builtins.py:243-266, 352-431): no parameter gradient wanted, not blockwise, no shift, not
+    being traced by ``torch.compile``, and the parameters are per-tensor or vary along exactly one
+    axis with every zero point inside the grid."""
     if block_size is not None or zero_point_shift != 0.0 or torch.jit.is_tracing():
+        return False
+    if torch.compiler.is_compiling():
         return False
     if torch.is_grad_enabled() and (scale.requires_grad or offset.requires_grad):
         return False
@@ -426,4 +446,6 @@ def _takes_fake_quantize_path(tensor, scale, offset, block_size, zero_point_shif
     oshape = (1,) * (tensor.dim() - offset.dim()) + tuple(offset.shape)
     if sshape != oshape or any(d not in (1, t) for d, t in zip(sshape, tensor.shape)):
         return False
-    return sum(1 for d in sshape if d != 1) == 1
+    if sum(1 for d in sshape if d != 1) != 1:
+        return False
+    return qmin is None or _zero_points_in_grid(offset, qmin, qmax)

@@ -17,6 +17,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 SRC_DIR = os.path.join(PKG_DIR, "csrc")
 OBJ_DIR = os.path.join(PKG_DIR, "build")
 LIB_PATH = os.path.join(PKG_DIR, "libaimet_b200.so")
+STAMP_PATH = LIB_PATH + ".stamp"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -37,15 +38,27 @@ def _sources() -> list[str]:
     return sorted(os.path.join(SRC_DIR, f) for f in os.listdir(SRC_DIR) if f.endswith(".cu"))
 
 
-def _deps_mtime() -> float:
-    paths = [os.path.join(SRC_DIR, f) for f in os.listdir(SRC_DIR)]
+def _source_digest() -> str:
+    """Hash of everything the library is made from: the sources, the public header, the flags."""
+    import hashlib
+
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    paths = sorted(os.path.join(SRC_DIR, f) for f in os.listdir(SRC_DIR))
     paths.append(os.path.join(PKG_DIR, os.pardir, "include", "aimet_b200.h"))
-    paths.append(os.path.abspath(__file__))
-    return max(os.path.getmtime(p) for p in paths)
+    for p in paths:
+        h.update(os.path.basename(p).encode())
+        with open(p, "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
 
 
 def is_up_to_date() -> bool:
-    return os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= _deps_mtime()
+    """True when the library on disk was built from exactly the present sources (by content, not by
+    file times: a checkout or a copy to another machine changes times but not contents)."""
+    if not (os.path.exists(LIB_PATH) and os.path.exists(STAMP_PATH)):
+        return False
+    with open(STAMP_PATH) as f:
+        return f.read().strip() == _source_digest()
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
@@ -75,6 +88,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
     os.replace(tmp, LIB_PATH)
+    with open(STAMP_PATH, "w") as f:
+        f.write(_source_digest() + "\n")
     return LIB_PATH
 
 

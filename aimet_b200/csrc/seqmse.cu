@@ -1,21 +1,33 @@
-// SeqMSE reconstruction loss of a Linear layer for all candidates in one launch.
+// SeqMSE reconstruction loss of a Linear layer for all candidates (and all input-channel blocks)
+// in one launch.
 //
-//   out[c][n] = sum_m f( x[m,:] . w[n,:] ,  xq[m,:] . wq[c][n,:] )
+//   out[c][n][b] = sum_m f( x[m,Kb] . w[n,Kb] ,  xq[m,Kb] . wq[c][n,Kb] )     Kb = columns of block b
 //
-// (SequentialMse._compute_linear_loss, seq_mse.py:403-454 of the reference, which runs two
+// (SequentialMse._compute_linear_loss, seq_mse.py:403-454 of the reference, which runs two batched
 // matmuls and three elementwise passes per candidate.)  Here the contraction runs on the 5th
 // generation tensor cores: operands are staged in shared memory by TMA (128-byte swizzle),
-// tcgen05.mma accumulates in tensor memory, and the epilogue reads both accumulators back with
+// tcgen05.mma accumulates in tensor memory, and the epilogue reads the accumulators back with
 // tcgen05.ld, forms f() and sums over the tokens without the products ever touching HBM.
 //
 // Orientation: the weights are the M operand (128 output channels per tile = 128 TMEM lanes), the
 // tokens the N operand (256 per tile = 256 TMEM columns), so one epilogue thread owns one output
-// channel and its sum over tokens is thread-local.  TMEM holds x.w^T of the tile in columns
-// [0,256) for the whole unit and the product of the current candidate in columns [256,512).
+// channel and its sum over tokens is thread-local.
 //
-// Warp roles (192 threads): warp 0 TMA producer, warp 1 TMEM allocation + MMA issue, warps 2-5
-// epilogue (one per TMEM lane quadrant).  Every wait is bounded: on a time-out the kernel raises
-// the status word, all roles leave their loops, TMEM is freed and the kernel returns.
+// Tensor memory holds two full accumulators, columns [0,256) and [256,512), used in turn by
+// consecutive passes.  The product x.w^T of a tile ("reference pass") is moved into registers by the
+// epilogue warps (128 values per thread) as soon as it is complete and stays there for all the
+// candidates of the tile, so both accumulators are free for candidates: the MMAs of candidate g+1
+// run while the epilogue reads candidate g.
+//
+// Work items are (channel tile, token tile, block, candidate); every CTA takes a contiguous range
+// of them and recomputes the reference pass of a tile it enters in the middle, so that the load
+// balances at the granularity of one candidate pass (a 512-row shard of the weight still fills
+// all SMs).
+//
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 TMEM allocation + MMA issue, warps 2-9
+// epilogue (two per TMEM lane quadrant, one per half of the columns).  Every wait is bounded: on a
+// time-out the kernel raises the status word, all roles leave their loops, TMEM is freed and the
+// kernel returns.
 #include <cuda.h>
 
 #include <mutex>
@@ -30,11 +42,13 @@ constexpr int BN = 256;      // tokens per tile (MMA N, TMEM columns per accumul
 constexpr int BK = 64;       // K elements per pipeline stage: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;   // K elements per tcgen05.mma (16-bit operands)
 constexpr int STAGES = 4;
-constexpr int kSeqThreads = 192;
+constexpr int kEpiWarps = 8;                 // two per TMEM lane quadrant
+constexpr int kSeqThreads = 64 + 32 * kEpiWarps;
+constexpr int kHalfCols = BN / 2;            // columns of one epilogue thread
 constexpr uint32_t A_BYTES = BM * BK * 2;
 constexpr uint32_t B_BYTES = BN * BK * 2;
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t TMEM_COLS = 512;          // two accumulators of BN columns
 constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // 2 s per wait
 
@@ -72,7 +86,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
 // Bounded wait.  Returns false if the abort flag was raised or the time-out expired (in which case
 // it raises the flag and records `code`).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status,
-                                          int code) {
+                                          int code, unsigned long long limit_ns = kWaitTimeoutNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     uint32_t spins = 0;
@@ -80,7 +94,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 63u) == 0) {
             if (*abort_flag) return false;
-            if (global_ns() - t0 > kWaitTimeoutNs) {
+            if (global_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 return false;
@@ -124,29 +138,37 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 struct SeqArgs {
-    int64_t M, N, K;
+    int64_t M, N, K;   // tokens, output channels, input channels (all blocks)
+    int64_t Kb;        // input channels per block (multiple of 16)
+    int num_blocks;
     int num_cand;
-    int n_ct, n_tt;   // channel tiles, token tiles
-    int loss_kind;    // 0 squared, 1 absolute, 2 squared + square of the second product
-    int lowp;         // 0 none, 1 round like bfloat16, 2 round like float16
+    int n_ct, n_tt;    // channel tiles, token tiles
+    int loss_kind;     // 0 squared, 1 absolute, 2 squared + square of the second product,
+                       // 3 squared + square of the first product
+    int lowp;          // 0 none, 1 round like bfloat16, 2 round like float16
     uint32_t idesc;
-    float *partial;   // [n_tt][num_cand][N][nvals]
+    float *partial;    // [2 * n_tt][num_cand][N][num_blocks][nvals]
     int *status;
+    unsigned long long timeout_ns;
 };
 
 __device__ __forceinline__ float round_lowp(float v, int lowp) {
@@ -155,6 +177,44 @@ __device__ __forceinline__ float round_lowp(float v, int lowp) {
     return v;
 }
 
+// The sequence of passes of one CTA, identical in every role: for each tile the CTA touches, the
+// reference pass (g == -1) when the kernel has one, then its candidates of that tile.
+struct Pass {
+    int ct, tt, blk, g;
+};
+struct PassIter {
+    int64_t i, i1, done_unit;
+    int num_cand, n_tt, num_blocks;
+    bool has_ref;
+    __device__ PassIter(const SeqArgs &a, bool ref) {
+        const int64_t items = (int64_t)a.n_ct * a.n_tt * a.num_blocks * a.num_cand;
+        i = items * blockIdx.x / gridDim.x;
+        i1 = items * (blockIdx.x + 1) / gridDim.x;
+        done_unit = -1;
+        num_cand = a.num_cand;
+        n_tt = a.n_tt;
+        num_blocks = a.num_blocks;
+        has_ref = ref;
+    }
+    __device__ bool next(Pass &p) {
+        if (i >= i1) return false;
+        const int64_t u = i / num_cand;
+        const int64_t t = u / num_blocks;
+        p.blk = (int)(u - t * num_blocks);
+        p.ct = (int)(t / n_tt);
+        p.tt = (int)(t - (int64_t)p.ct * n_tt);
+        if (has_ref && u != done_unit) {
+            done_unit = u;
+            p.g = -1;
+            return true;
+        }
+        p.g = (int)(i - u * num_cand);
+        ++i;
+        return true;
+    }
+};
+
+template <bool HAS_REF>
 __global__ void __launch_bounds__(kSeqThreads, 1)
 k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_wq,
          const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_xq, SeqArgs a) {
@@ -164,12 +224,12 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *aligned = smem_raw + (base - raw);
     uint64_t *bars = reinterpret_cast<uint64_t *>(aligned + (size_t)STAGES * STAGE_BYTES);
-    // bars[0..S) full, [S..2S) empty, [2S] accumulator full, [2S+1] accumulator empty
+    // bars[0..S) full, [S..2S) empty, [2S..2S+2) accumulator full, [2S+2..2S+4) accumulator empty
     const uint32_t bar_full = smem_u32(bars);
     const uint32_t bar_empty = smem_u32(bars + STAGES);
     const uint32_t bar_acc_full = smem_u32(bars + 2 * STAGES);
-    const uint32_t bar_acc_empty = smem_u32(bars + 2 * STAGES + 1);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 2);
+    const uint32_t bar_acc_empty = smem_u32(bars + 2 * STAGES + 2);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -180,8 +240,10 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
         }
-        mbar_init(bar_acc_full, 1);
-        mbar_init(bar_acc_empty, 128);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar_acc_full + 8 * s, 1);
+            mbar_init(bar_acc_empty + 8 * s, 32 * kEpiWarps);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -197,12 +259,8 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    // contiguous range of (channel tile, token tile) units for this CTA
-    const int64_t units = (int64_t)a.n_ct * a.n_tt;
-    const int64_t u0 = units * blockIdx.x / gridDim.x;
-    const int64_t u1 = units * (blockIdx.x + 1) / gridDim.x;
-    const int kblocks = (int)((a.K + BK - 1) / BK);
-    const int passes = a.num_cand + 1;  // pass 0 = x.w^T, pass g = candidate g-1
+    const int kblocks = (int)((a.Kb + BK - 1) / BK);
+    const unsigned long long limit = a.timeout_ns;
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -210,23 +268,23 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int64_t u = u0; u < u1 && ok; ++u) {
-                const int ct = (int)(u / a.n_tt), tt = (int)(u % a.n_tt);
-                for (int g = 0; g < passes && ok; ++g) {
-                    const CUtensorMap *ma = g == 0 ? &tm_w : &tm_wq;
-                    const CUtensorMap *mb = g == 0 ? &tm_x : &tm_xq;
-                    const int row_a = g == 0 ? ct * BM : (int)((int64_t)(g - 1) * a.N) + ct * BM;
-                    for (int kb = 0; kb < kblocks; ++kb) {
-                        ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, a.status, ST_TIMEOUT_PRODUCER);
-                        if (!ok) break;
-                        const uint32_t sa = base + stage * STAGE_BYTES;
-                        mbar_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
-                        tma_load_2d(sa, ma, kb * BK, row_a, bar_full + 8 * stage);
-                        tma_load_2d(sa + A_BYTES, mb, kb * BK, tt * BN, bar_full + 8 * stage);
-                        if (++stage == STAGES) {
-                            stage = 0;
-                            phase ^= 1;
-                        }
+            PassIter it(a, HAS_REF);
+            Pass p;
+            while (ok && it.next(p)) {
+                const CUtensorMap *ma = p.g < 0 ? &tm_w : &tm_wq;
+                const CUtensorMap *mb = p.g < 0 ? &tm_x : &tm_xq;
+                const int row_a = p.g < 0 ? p.ct * BM : (int)((int64_t)p.g * a.N) + p.ct * BM;
+                const int col0 = (int)((int64_t)p.blk * a.Kb);
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, a.status, ST_TIMEOUT_PRODUCER, limit);
+                    if (!ok) break;
+                    const uint32_t sa = base + stage * STAGE_BYTES;
+                    mbar_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
+                    tma_load_2d(sa, ma, col0 + kb * BK, row_a, bar_full + 8 * stage);
+                    tma_load_2d(sa + A_BYTES, mb, col0 + kb * BK, p.tt * BN, bar_full + 8 * stage);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
                     }
                 }
             }
@@ -236,88 +294,119 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
-            int64_t event = 0;  // index of the next accumulator hand-over to the epilogue
+            uint32_t pass = 0;  // passes issued by this CTA: accumulator = pass & 1
             bool ok = true;
-            for (int64_t u = u0; u < u1 && ok; ++u) {
-                for (int g = 0; g < passes && ok; ++g) {
-                    // do not overwrite an accumulator the epilogue may still be reading:
-                    //   pass 0 overwrites x.w^T, last read by the previous unit's final event;
-                    //   pass g >= 2 overwrites the candidate accumulator read by event - 1
-                    if ((g == 0 && event > 0) || g >= 2) {
-                        ok = mbar_wait(bar_acc_empty, (uint32_t)((event - 1) & 1), abort_flag, a.status, ST_TIMEOUT_MMA);
-                        if (!ok) break;
-                    }
+            PassIter it(a, HAS_REF);
+            Pass p;
+            while (ok && it.next(p)) {
+                const uint32_t buf = pass & 1u, use = pass >> 1;
+                // the accumulator must have been read out by the epilogue of its previous pass
+                // (a fresh barrier lets the first use through)
+                ok = mbar_wait(bar_acc_empty + 8 * buf, (use & 1u) ^ 1u, abort_flag, a.status, ST_TIMEOUT_MMA, limit);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, a.status, ST_TIMEOUT_MMA, limit);
+                    if (!ok) break;
                     tc_fence_after();
-                    const uint32_t d_tmem = tmem_base + (g == 0 ? 0 : BN);
-                    for (int kb = 0; kb < kblocks; ++kb) {
-                        ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, a.status, ST_TIMEOUT_MMA);
-                        if (!ok) break;
-                        tc_fence_after();
-                        const uint32_t sa = base + stage * STAGE_BYTES;
-                        const uint64_t da = make_smem_desc(sa);
-                        const uint64_t db = make_smem_desc(sa + A_BYTES);
-#pragma unroll
-                        for (int k = 0; k < BK / UMMA_K; ++k) {
-                            // advance 32 bytes (16 elements) inside the swizzled 128-byte row
-                            umma_f16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), a.idesc,
-                                     (kb > 0 || k > 0) ? 1u : 0u);
-                        }
-                        umma_commit(bar_empty + 8 * stage);  // frees the stage once these MMAs have read it
-                        if (++stage == STAGES) {
-                            stage = 0;
-                            phase ^= 1;
-                        }
+                    const uint32_t sa = base + stage * STAGE_BYTES;
+                    const uint64_t da = make_smem_desc(sa);
+                    const uint64_t db = make_smem_desc(sa + A_BYTES);
+                    // a block's last stage may be partly beyond the block: only its own columns count
+                    // (with a single block the columns beyond K are zero-filled by TMA and harmless)
+                    const int64_t left = a.Kb - (int64_t)kb * BK;
+                    const int ksteps = (left >= BK || a.num_blocks == 1) ? BK / UMMA_K : (int)(left / UMMA_K);
+                    for (int k = 0; k < ksteps; ++k) {
+                        // advance 32 bytes (16 elements) inside the swizzled 128-byte row
+                        umma_f16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), a.idesc,
+                                 (kb > 0 || k > 0) ? 1u : 0u);
                     }
-                    if (ok && g >= 1) {
-                        umma_commit(bar_acc_full);
-                        ++event;
+                    umma_commit(bar_empty + 8 * stage);  // frees the stage once these MMAs have read it
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1;
                     }
                 }
+                if (ok) umma_commit(bar_acc_full + 8 * buf);
+                ++pass;
             }
         }
     } else {
-        // ---------------- epilogue: warps 2..5, one TMEM lane quadrant each ----------------
+        // ---------------- epilogue: warps 2..9 ----------------
+        // a warp may only read the TMEM lanes of its quadrant (warp index mod 4); the two warps of a
+        // quadrant take one half of the accumulator's columns each
         const int quad = warp & 3;
-        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-        const int nvals = a.loss_kind == 2 ? 2 : 1;
-        int64_t event = 0;
+        const int half = (warp - 2) >> 2;
+        const uint32_t lane_base = ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * kHalfCols);
+        const int nvals = a.loss_kind >= 2 ? 2 : 1;
+        const int lowp = a.lowp, kind = a.loss_kind;
+        float xw[HAS_REF ? kHalfCols : 1];  // the reference product of this thread's channel and columns
+        float sref = 0.f;                   // sum of its squares
+        uint32_t pass = 0;
         bool ok = true;
-        for (int64_t u = u0; u < u1 && ok; ++u) {
-            const int ct = (int)(u / a.n_tt), tt = (int)(u % a.n_tt);
-            const int64_t n = (int64_t)ct * BM + quad * 32 + lane;
-            for (int g = 1; g < passes && ok; ++g, ++event) {
-                ok = mbar_wait(bar_acc_full, (uint32_t)(event & 1), abort_flag, a.status, ST_TIMEOUT_EPILOGUE);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
-                float s0 = 0.f, s1 = 0.f;
-#pragma unroll 1
-                for (int chunk = 0; chunk < BN / 32; ++chunk) {
-                    uint32_t rx[32], ry[32];
-                    tmem_ld32(tmem_base + lane_base + chunk * 32, rx);
-                    tmem_ld32(tmem_base + lane_base + BN + chunk * 32, ry);
+        PassIter it(a, HAS_REF);
+        Pass p;
+        while (ok && it.next(p)) {
+            const uint32_t buf = pass & 1u, use = pass >> 1;
+            ++pass;
+            ok = mbar_wait(bar_acc_full + 8 * buf, use & 1u, abort_flag, a.status, ST_TIMEOUT_EPILOGUE, limit);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t t0 = tmem_base + lane_base + buf * BN;
+            if (HAS_REF && p.g < 0) {
+                sref = 0.f;
+#pragma unroll
+                for (int ch = 0; ch < kHalfCols / 16; ++ch) {
+                    uint32_t r[16];
+                    tmem_ld16(t0 + ch * 16, r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float xw = __uint_as_float(rx[j]), y = __uint_as_float(ry[j]);
-                        if (a.lowp) {
-                            xw = round_lowp(xw, a.lowp);
-                            y = round_lowp(y, a.lowp);
-                        }
-                        const float d = xw - y;
-                        float f = a.loss_kind == 1 ? fabsf(d) : d * d;
-                        if (a.lowp) f = round_lowp(f, a.lowp);
-                        s0 += f;
-                        if (a.loss_kind == 2) s1 += a.lowp ? round_lowp(y * y, a.lowp) : y * y;
+                    for (int j = 0; j < 16; ++j) {
+                        float v = __uint_as_float(r[j]);
+                        if (lowp) v = round_lowp(v, lowp);
+                        if (HAS_REF) xw[ch * 16 + j] = v;
+                        sref += lowp ? round_lowp(v * v, lowp) : v * v;
                     }
                 }
                 tc_fence_before();
-                mbar_arrive(bar_acc_empty);
-                if (n < a.N) {
-                    float *p = a.partial + (((int64_t)tt * a.num_cand + (g - 1)) * a.N + n) * nvals;
-                    p[0] = s0;
-                    if (nvals == 2) p[1] = s1;
+                mbar_arrive(bar_acc_empty + 8 * buf);
+                continue;
+            }
+            float s0 = 0.f, s1 = 0.f;
+            constexpr int CW = 8;  // columns per request: two requests' worth of registers beside xw[]
+            uint32_t ca[CW], cb[CW];
+            tmem_ld8(t0, ca);
+#pragma unroll
+            for (int ch = 0; ch < kHalfCols / CW; ++ch) {
+                tmem_ld_wait();  // chunk ch has arrived; the next one is requested before it is used
+                if (ch + 1 < kHalfCols / CW) {
+                    if (ch & 1)
+                        tmem_ld8(t0 + (ch + 1) * CW, ca);
+                    else
+                        tmem_ld8(t0 + (ch + 1) * CW, cb);
                 }
+#pragma unroll
+                for (int j = 0; j < CW; ++j) {
+                    float y = __uint_as_float((ch & 1) ? cb[j] : ca[j]);
+                    if (lowp) y = round_lowp(y, lowp);
+                    const float d = (HAS_REF ? xw[ch * CW + j] : 0.f) - y;
+                    float f = kind == 1 ? fabsf(d) : d * d;
+                    if (lowp) f = round_lowp(f, lowp);
+                    s0 += f;
+                    if (kind == 2) s1 += lowp ? round_lowp(y * y, lowp) : y * y;
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar_acc_empty + 8 * buf);
+            const int64_t n = (int64_t)p.ct * BM + quad * 32 + lane;
+            if (n < a.N) {
+                const int64_t sub = (int64_t)p.tt * 2 + half;
+                float *out = a.partial +
+                             (((sub * a.num_cand + p.g) * a.N + n) * a.num_blocks + p.blk) * nvals;
+                out[0] = s0;
+                if (nvals == 2) out[1] = kind == 3 ? sref : s1;
             }
         }
     }
@@ -331,13 +420,28 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
     }
 }
 
-// out[c][n][v] = sum over token tiles, in tile order (deterministic)
-__global__ void k_seqmse_reduce(const float *partial, float *out, int n_tt, int64_t per_tile) {
+// out[i] = sum over token sub-tiles, in tile order (deterministic)
+__global__ void k_seqmse_reduce(const float *partial, float *out, int n_sub, int64_t per_tile) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= per_tile) return;
     float s = 0.f;
-    for (int t = 0; t < n_tt; ++t) s += partial[(int64_t)t * per_tile + i];
+    for (int t = 0; t < n_sub; ++t) s += partial[(int64_t)t * per_tile + i];
     out[i] = s;
+}
+
+// A wait that nothing completes: exercises the bounded wait's give-up path (status word, return)
+// without any fault.  One warp waits on a barrier no one arrives at.
+__global__ void k_wait_selftest(int *status, unsigned long long limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const bool ok = mbar_wait(smem_u32(&bar), 0, &abort_flag, status, ST_TIMEOUT_EPILOGUE, limit_ns);
+    if (ok) atomicCAS(status, 0, -1);  // the wait claimed a completion that never happened
 }
 
 // ---------------------------------------------------------------------------
@@ -376,55 +480,74 @@ int make_map(CUtensorMap *map, const void *ptr, int64_t rows, int64_t K, int box
     return AB_OK;
 }
 
+int64_t blocks_scratch_bytes(int64_t M, int64_t N, int32_t num_blocks, int32_t num_cand) {
+    const int64_t n_tt = (M + BN - 1) / BN;
+    return 2 * n_tt * num_cand * N * num_blocks * 2 * (int64_t)sizeof(float);
+}
+
 }  // namespace
 }  // namespace ab
 
-extern "C" int64_t aimet_b200_seqmse_scratch_bytes(int64_t M, int64_t N, int64_t K, int32_t num_cand) {
+extern "C" int64_t aimet_b200_seqmse_blocks_scratch_bytes(int64_t M, int64_t N, int64_t K, int32_t num_blocks,
+                                                          int32_t num_cand) {
     (void)K;
-    if (M <= 0 || N <= 0 || num_cand <= 0) return ab::fail(AB_ERR_INVALID, "M, N and num_cand must be positive");
-    const int64_t n_tt = (M + ab::BN - 1) / ab::BN;
-    return n_tt * num_cand * N * 2 * (int64_t)sizeof(float);
+    if (M <= 0 || N <= 0 || num_cand <= 0 || num_blocks <= 0)
+        return ab::fail(AB_ERR_INVALID, "M, N, num_blocks and num_cand must be positive");
+    return ab::blocks_scratch_bytes(M, N, num_blocks, num_cand);
 }
 
-extern "C" int aimet_b200_seqmse_linear_loss(const void *x, const void *xq, const void *w, const void *wq, int64_t M,
-                                             int64_t N, int64_t K, int32_t num_cand, int io_dtype, int loss_kind,
-                                             int lowp_epilogue, float *out, int32_t *status, void *scratch,
-                                             int64_t scratch_bytes, void *stream) {
+extern "C" int64_t aimet_b200_seqmse_scratch_bytes(int64_t M, int64_t N, int64_t K, int32_t num_cand) {
+    return aimet_b200_seqmse_blocks_scratch_bytes(M, N, K, 1, num_cand);
+}
+
+extern "C" int aimet_b200_seqmse_linear_loss_blocks(const void *x, const void *xq, const void *w, const void *wq,
+                                                    int64_t M, int64_t N, int64_t K, int32_t num_blocks,
+                                                    int32_t num_cand, int io_dtype, int loss_kind, int lowp_epilogue,
+                                                    int has_reference, float *out, int32_t *status, void *scratch,
+                                                    int64_t scratch_bytes, void *stream) {
     using namespace ab;
     if (io_dtype != AB_BF16 && io_dtype != AB_F16)
         return fail(AB_ERR_UNSUPPORTED, "seqmse_linear_loss takes bfloat16 or float16 operands");
-    if (M <= 0 || N <= 0 || K <= 0 || num_cand <= 0) return fail(AB_ERR_INVALID, "M, N, K and num_cand must be positive");
+    if (M <= 0 || N <= 0 || K <= 0 || num_cand <= 0 || num_blocks <= 0)
+        return fail(AB_ERR_INVALID, "M, N, K, num_blocks and num_cand must be positive");
+    if (K % num_blocks != 0) return fail(AB_ERR_INVALID, "K (%lld) is not a multiple of num_blocks (%d)", (long long)K, (int)num_blocks);
+    const int64_t Kb = K / num_blocks;
     if (K % 8 != 0) return fail(AB_ERR_UNSUPPORTED, "K must be a multiple of 8 (16-byte rows for TMA), got %lld", (long long)K);
-    if (loss_kind < 0 || loss_kind > 2) return fail(AB_ERR_INVALID, "loss_kind must be 0, 1 or 2");
+    if (num_blocks > 1 && Kb % 16 != 0)
+        return fail(AB_ERR_UNSUPPORTED, "the input channels of one block (%lld) must be a multiple of 16", (long long)Kb);
+    if (loss_kind < 0 || loss_kind > 3) return fail(AB_ERR_INVALID, "loss_kind must be 0, 1, 2 or 3");
+    if (!has_reference && loss_kind == 3) return fail(AB_ERR_INVALID, "loss_kind 3 needs the reference product");
+    if (!has_reference) {  // the first product is absent: its operands are never read
+        x = xq;
+        w = wq;
+    }
     if (!x || !xq || !w || !wq || !out || !status) return fail(AB_ERR_INVALID, "NULL pointer argument");
     for (const void *p : {x, xq, w, wq})
         if (!aligned16(p)) return fail(AB_ERR_INVALID, "operands must be 16-byte aligned");
-    if ((int64_t)num_cand * N >= ((int64_t)1 << 31) || M >= ((int64_t)1 << 31))
-        return fail(AB_ERR_UNSUPPORTED, "row counts must fit 31 bits");
-    const int64_t need = aimet_b200_seqmse_scratch_bytes(M, N, K, num_cand);
+    if ((int64_t)num_cand * N >= ((int64_t)1 << 31) || M >= ((int64_t)1 << 31) || K >= ((int64_t)1 << 31))
+        return fail(AB_ERR_UNSUPPORTED, "row and column counts must fit 31 bits");
+    const int64_t need = blocks_scratch_bytes(M, N, num_blocks, num_cand);
     if (!scratch || scratch_bytes < need)
         return fail(AB_ERR_SCRATCH, "seqmse needs %lld bytes of scratch, got %lld", (long long)need, (long long)scratch_bytes);
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     CUtensorMap tm_w, tm_wq, tm_x, tm_xq;
     int rc;
-    if ((rc = make_map(&tm_w, w, N, K, BM, io_dtype)) != AB_OK) return rc;
+    if ((rc = make_map(&tm_w, w, has_reference ? N : (int64_t)num_cand * N, K, BM, io_dtype)) != AB_OK) return rc;
     if ((rc = make_map(&tm_wq, wq, (int64_t)num_cand * N, K, BM, io_dtype)) != AB_OK) return rc;
     if ((rc = make_map(&tm_x, x, M, K, BN, io_dtype)) != AB_OK) return rc;
     if ((rc = make_map(&tm_xq, xq, M, K, BN, io_dtype)) != AB_OK) return rc;
 
-    static std::once_flag attr_once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(attr_once, []() {
-        attr_err = cudaFuncSetAttribute(k_seqmse, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-    });
-    if (attr_err != cudaSuccess)
-        return fail(AB_ERR_CUDA, "cannot reserve %zu bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(attr_err));
+    // the opt-in to more than 48 KB of shared memory is a per-device attribute of the kernel
+    if ((rc = opt_in_smem<k_seqmse<true>>(SMEM_BYTES)) != AB_OK) return rc;
+    if ((rc = opt_in_smem<k_seqmse<false>>(SMEM_BYTES)) != AB_OK) return rc;
 
     SeqArgs a;
     a.M = M;
     a.N = N;
     a.K = K;
+    a.Kb = Kb;
+    a.num_blocks = num_blocks;
     a.num_cand = num_cand;
     a.n_ct = (int)((N + BM - 1) / BM);
     a.n_tt = (int)((M + BN - 1) / BN);
@@ -434,16 +557,39 @@ extern "C" int aimet_b200_seqmse_linear_loss(const void *x, const void *xq, cons
     a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     a.partial = static_cast<float *>(scratch);
     a.status = status;
+    a.timeout_ns = kWaitTimeoutNs;
 
     AB_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int32_t), st));
-    const int64_t units = (int64_t)a.n_ct * a.n_tt;
+    const int64_t items = (int64_t)a.n_ct * a.n_tt * num_blocks * num_cand;
     int grid = sm_count();
-    if (units < grid) grid = (int)units;
-    k_seqmse<<<grid, kSeqThreads, SMEM_BYTES, st>>>(tm_w, tm_wq, tm_x, tm_xq, a);
+    if (items < grid) grid = (int)items;
+    if (has_reference)
+        k_seqmse<true><<<grid, kSeqThreads, SMEM_BYTES, st>>>(tm_w, tm_wq, tm_x, tm_xq, a);
+    else
+        k_seqmse<false><<<grid, kSeqThreads, SMEM_BYTES, st>>>(tm_w, tm_wq, tm_x, tm_xq, a);
     AB_LAUNCH_OK();
-    const int nvals = loss_kind == 2 ? 2 : 1;
-    const int64_t per_tile = (int64_t)num_cand * N * nvals;
-    k_seqmse_reduce<<<(unsigned)((per_tile + 255) / 256), 256, 0, st>>>(a.partial, out, a.n_tt, per_tile);
+    const int nvals = loss_kind >= 2 ? 2 : 1;
+    const int64_t per_tile = (int64_t)num_cand * N * num_blocks * nvals;
+    k_seqmse_reduce<<<(unsigned)((per_tile + 255) / 256), 256, 0, st>>>(a.partial, out, 2 * a.n_tt, per_tile);
+    AB_LAUNCH_OK();
+    return AB_OK;
+}
+
+extern "C" int aimet_b200_seqmse_linear_loss(const void *x, const void *xq, const void *w, const void *wq, int64_t M,
+                                             int64_t N, int64_t K, int32_t num_cand, int io_dtype, int loss_kind,
+                                             int lowp_epilogue, float *out, int32_t *status, void *scratch,
+                                             int64_t scratch_bytes, void *stream) {
+    return aimet_b200_seqmse_linear_loss_blocks(x, xq, w, wq, M, N, K, 1, num_cand, io_dtype, loss_kind,
+                                                lowp_epilogue, 1, out, status, scratch, scratch_bytes, stream);
+}
+
+extern "C" int aimet_b200_seqmse_wait_selftest(int32_t *status, int64_t limit_us, void *stream) {
+    using namespace ab;
+    if (!status) return fail(AB_ERR_INVALID, "status must not be NULL");
+    if (limit_us <= 0 || limit_us > 1000000) return fail(AB_ERR_INVALID, "limit_us must be in (0, 1000000]");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    AB_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int32_t), st));
+    k_wait_selftest<<<1, 32, 0, st>>>(status, (unsigned long long)limit_us * 1000ull);
     AB_LAUNCH_OK();
     return AB_OK;
 }

@@ -81,16 +81,16 @@ def check_peers(group=None, timeout_s: float = 30.0):
 
 
 def allreduce_minmax(mn: torch.Tensor, mx: torch.Tensor, group=None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Element-wise MIN / MAX over ranks.  16-bit statistics travel as float32 (exact) because not
-    every backend reduces them natively."""
+    """Element-wise MIN / MAX over ranks in ONE collective: MIN over the pair (lo, -hi) -- the
+    exchange is latency-bound, so one call instead of two halves its cost.  16-bit statistics travel
+    as float32 (exact, as is the negation) because not every backend reduces them natively."""
     rank, world = _world(group)
     if world == 1:
         return mn, mx
     dt = mn.dtype
-    lo, hi = mn.to(torch.float32).contiguous(), mx.to(torch.float32).contiguous()
-    _collective(dist.all_reduce, lo, op=dist.ReduceOp.MIN, group=group)
-    _collective(dist.all_reduce, hi, op=dist.ReduceOp.MAX, group=group)
-    return lo.to(dt), hi.to(dt)
+    packed = torch.stack((mn.to(torch.float32), -mx.to(torch.float32))).contiguous()
+    _collective(dist.all_reduce, packed, op=dist.ReduceOp.MIN, group=group)
+    return packed[0].to(dt), (-packed[1]).to(dt)
 
 
 def allreduce_counts(counts: torch.Tensor, group=None) -> torch.Tensor:
@@ -120,26 +120,44 @@ def _default_counts(x, shape, block_size, num_bins, lo, hi):
     return _histogram_counts(_StatLayout(_check_input(x), tuple(shape), block_size), num_bins, lo, hi)
 
 
-def calibrate_minmax(analyzer, batches: Iterable[torch.Tensor], group=None):
+def _stat_device(batches, device):
+    if batches:
+        return batches[0].device
+    if device is not None:
+        return torch.device(device)
+    return torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+
+
+def calibrate_minmax(analyzer, batches: Iterable[torch.Tensor], group=None, device=None):
     """Observe this rank's batches with a min-max analyzer and combine the ranges over all ranks.
     Afterwards ``analyzer.compute_encodings`` gives the same result on every rank, equal to
-    observing all batches in one process."""
+    observing all batches in one process.  A rank without a batch (fewer batches than ranks) takes
+    part in the exchange with an empty range (+inf, -inf) on ``device`` (default: the current CUDA
+    device); if no rank has one, every rank raises together after the exchange."""
     from .encoding_analyzer import _MinMaxRange
 
+    batches = list(batches)
     for x in batches:
         analyzer.update_stats(x)
     st = analyzer.observer.get_stats()
     rank, world = _world(group)
     if world > 1:
-        if st.min is None:
-            raise PeerFailure(f"rank {rank} observed no batch; give every rank at least one")
-        mn, mx = allreduce_minmax(st.min, st.max, group)
+        mn, mx = st.min, st.max
+        if mn is None:
+            dev = _stat_device(batches, device)
+            shape = analyzer.observer.shape
+            mn = torch.full(shape, float("inf"), dtype=torch.float32, device=dev)
+            mx = torch.full(shape, float("-inf"), dtype=torch.float32, device=dev)
+        mn, mx = allreduce_minmax(mn, mx, group)
+        if bool((mn > mx).all()):  # the same on every rank: nobody observed anything
+            raise PeerFailure("no rank observed a calibration batch")
         analyzer.observer.stats = _MinMaxRange(mn, mx)
     return analyzer.observer.get_stats()
 
 
 def calibrate_histogram(analyzer, batches: Sequence[torch.Tensor], group=None, *,
-                        minmax_fn: Callable = _default_minmax, counts_fn: Callable = _default_counts):
+                        minmax_fn: Callable = _default_minmax, counts_fn: Callable = _default_counts, device=None,
+                        timings: Optional[dict] = None):
     """Two-phase histogram calibration of this rank's batches for a histogram-based analyzer
     (percentile / SQNR / TF-enhanced).
 
@@ -148,7 +166,10 @@ def calibrate_histogram(analyzer, batches: Sequence[torch.Tensor], group=None, *
     or infinite go to the edge bins); counts are summed locally and then over ranks.
     The analyzer's observer is left holding the combined statistics.  ``minmax_fn`` / ``counts_fn``
     compute the per-batch statistics (default: the CUDA kernels); they exist so that the exchange
-    logic can be exercised with CPU tensors.
+    logic can be exercised with CPU tensors.  A rank without a batch contributes an empty range and
+    zero counts (on ``device``); if no rank has a batch every rank raises together.
+    ``timings``: a dict that receives CUDA events at the phase boundaries (``t0`` .. ``t4``: start,
+    local ranges done, ranges exchanged, local counts done, counts exchanged).
     """
     from .encoding_analyzer import _HistogramList
 
@@ -156,19 +177,44 @@ def calibrate_histogram(analyzer, batches: Sequence[torch.Tensor], group=None, *
     shape, block, nbins = obs.shape, obs.block_size, obs.num_bins
     batches = list(batches)
     rank, world = _world(group)
-    if not batches:
-        raise PeerFailure(f"rank {rank} has no calibration batch; give every rank at least one")
+    dev = _stat_device(batches, device)
+    if not batches and world == 1:
+        raise PeerFailure("no calibration batch")
+
+    def mark(name):
+        if timings is not None and dev.type == "cuda":
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(torch.cuda.current_stream(dev))
+            timings[name] = ev
+
+    mark("t0")
     # per-batch statistics are kept and combined once (one stack + reduce instead of a small
     # kernel per batch)
-    mins, maxs = zip(*(minmax_fn(x, shape, block, True) for x in batches))
-    mn = torch.stack(mins).amin(dim=0) if len(mins) > 1 else mins[0]
-    mx = torch.stack(maxs).amax(dim=0) if len(maxs) > 1 else maxs[0]
-    mn, mx = allreduce_minmax(mn, mx, group)
+    if batches:
+        mins, maxs = zip(*(minmax_fn(x, shape, block, True) for x in batches))
+        mn = torch.stack(mins).amin(dim=0) if len(mins) > 1 else mins[0]
+        mx = torch.stack(maxs).amax(dim=0) if len(maxs) > 1 else maxs[0]
+    else:
+        mn = torch.full((obs.num_histograms,), float("inf"), dtype=torch.float32, device=dev)
+        mx = torch.full((obs.num_histograms,), float("-inf"), dtype=torch.float32, device=dev)
+    mark("t1")
+    if world > 1:
+        mn, mx = allreduce_minmax(mn, mx, group)
+    mark("t2")
     edges = obs._create_bin_edges(mn, mx)  # pylint: disable=protected-access
     lo, hi = edges[:, 0].contiguous(), edges[:, -1].contiguous()
-    per_batch = [counts_fn(x, shape, block, nbins, lo, hi) for x in batches]
-    counts = torch.stack(per_batch).sum(dim=0) if len(per_batch) > 1 else per_batch[0]
+    if batches:
+        per_batch = [counts_fn(x, shape, block, nbins, lo, hi) for x in batches]
+        counts = torch.stack(per_batch).sum(dim=0) if len(per_batch) > 1 else per_batch[0]
+    else:
+        counts = torch.zeros((obs.num_histograms, nbins), dtype=torch.int64, device=dev)
+    mark("t3")
     counts = allreduce_counts(counts, group)
+    mark("t4")
+    if world > 1 and not batches and int(counts.sum()) == 0:
+        # this rank had nothing; if the sum over all ranks is empty too, nobody had (every rank sees
+        # the same counts and raises the same way)
+        raise PeerFailure("no rank observed a calibration batch")
     obs._state = _HistogramList(counts.to(torch.float32), edges, mn, mx)  # pylint: disable=protected-access
     e0, e1 = edges[:, 0], edges[:, -1]
     span = e1 - e0

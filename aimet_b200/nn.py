@@ -1,7 +1,7 @@
 """Quantized Conv2d / Linear wrappers and a model-level calibration context.
 
-A small mirror of the part of aimet_torch's quantized-module layer that BASELINE config 4
-exercises (nn/base.py:258-325 ``_patch_quantized_parameters``, nn/true_quant.py:600-616
+A small mirror of the part of aimet_torch's quantized-module layer that a QuantSim forward of a
+convolutional model exercises (nn/base.py:258-325 ``_patch_quantized_parameters``, nn/true_quant.py:600-616
 ``_forward_no_dispatch``, nn/__init__.py:22-84 ``compute_encodings``): a wrapped layer quantizes its
 weight with ``param_quantizers["weight"]`` on every forward, its input with ``input_quantizers[0]``
 and its output with ``output_quantizers[0]``.  It is a caller of the hot path, not a QuantSim
@@ -19,7 +19,7 @@ from torch import nn
 from .encoding_analyzer import MinMaxEncodingAnalyzer
 from .quantizer import QuantizeDequantize
 
-__all__ = ["QuantizedLayer", "quantize_model", "compute_encodings", "quantized_layers"]
+__all__ = ["QuantizedLayer", "quantize_model", "compute_encodings", "quantized_layers", "precomputed"]
 
 
 class QuantizedLayer(nn.Module):
@@ -39,20 +39,12 @@ class QuantizedLayer(nn.Module):
         return self.layer.weight
 
     def _quantized_weight(self, qw):
-        """The quantize-dequantized weight.  The reference re-quantizes every weight on every forward
-        (nn/base.py:296-325); without autograd the result only changes when the weight or the
-        quantizer's range does, so it is kept until either is modified (both are versioned tensors)."""
-        weight = self.layer.weight
-        calibrating = getattr(qw, "_observer_hook", None) is not None
-        if torch.is_grad_enabled() or calibrating or not qw.is_initialized():
-            return qw(weight)
-        key = (id(weight), weight._version, id(qw._pinned_encoding), qw._encoding_cache_key())  # pylint: disable=protected-access
-        cached = self.__dict__.get("_wq_cache")
-        if cached is not None and cached[0] == key:
-            return cached[1]
-        out = qw(weight)
-        self.__dict__["_wq_cache"] = (key, out)
-        return out
+        """The quantize-dequantized weight: computed on every forward like the reference
+        (nn/base.py:296-325), unless :func:`precomputed` holds it for the duration of a context."""
+        held = self.__dict__.get("_held_weight")
+        if held is not None and not torch.is_grad_enabled() and getattr(qw, "_observer_hook", None) is None:
+            return held
+        return qw(self.layer.weight)
 
     def forward(self, x):
         qi, qo, qw = self.input_quantizers[0], self.output_quantizers[0], self.param_quantizers["weight"]
@@ -74,7 +66,7 @@ def quantize_model(model: nn.Module, *, param_bw: int = 8, act_bw: int = 8,
                    analyzer_factory: Optional[Callable] = None) -> nn.Module:
     """Replace every Conv2d / Linear of ``model`` in place by a :class:`QuantizedLayer` with a
     per-channel symmetric weight quantizer and per-tensor asymmetric input and output quantizers
-    (the layout BASELINE config 4 asks for).  ``analyzer_factory(shape)`` builds the activation
+    (every conv / linear input and output per-tensor, weights per-channel).  ``analyzer_factory(shape)`` builds the activation
     analyzers (default: min-max)."""
     factory = analyzer_factory or (lambda shape: MinMaxEncodingAnalyzer(shape))
     for name, child in list(model.named_children()):
@@ -111,3 +103,28 @@ def compute_encodings(model: nn.Module):
                 if q is not None:
                     stack.enter_context(q._compute_encodings(passthrough=True))  # pylint: disable=protected-access
         yield
+
+
+@contextlib.contextmanager
+def precomputed(model: nn.Module):
+    """Inference with frozen parameters: inside the context every quantizer derives its scale and
+    offset once (the reference's ``_precompute_encodings``, quantizer.py:790-804, entered for a whole
+    model as in aimet_torch/utils.py:1666) and every layer quantizes its weight once instead of on
+    every forward (what the reference's ``fold_param_quantizers`` achieves, nn/base.py:1103-1155,
+    without giving up the quantizers).  Nothing is cached outside the context, so weights and
+    ranges may be edited freely (in place, through ``.data``, by re-assignment) between contexts."""
+    with contextlib.ExitStack() as stack, torch.no_grad():
+        layers = list(quantized_layers(model))
+        for layer in layers:
+            for q in (*layer.input_quantizers, *layer.output_quantizers, layer.param_quantizers["weight"]):
+                if q is not None and q.is_initialized():
+                    stack.enter_context(q._precompute_encodings())  # pylint: disable=protected-access
+        for layer in layers:
+            qw = layer.param_quantizers["weight"]
+            if qw is not None and qw.is_initialized():
+                layer.__dict__["_held_weight"] = qw(layer.layer.weight).detach()
+        try:
+            yield model
+        finally:
+            for layer in layers:
+                layer.__dict__.pop("_held_weight", None)

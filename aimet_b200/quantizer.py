@@ -152,7 +152,10 @@ class GroupedBlockEncoding(AffineEncoding):
 
 
 def _get_symmetric_offset(qmin, qmax, shape, dtype, device):
-    return torch.full(shape, fill_value=-round((qmin + qmax) / 2), requires_grad=False, dtype=dtype, device=device)
+    value = -round((qmin + qmax) / 2)
+    offset = torch.full(shape, fill_value=value, requires_grad=False, dtype=dtype, device=device)
+    offset._b200_constant = float(value)  # pylint: disable=protected-access  (every element is this host-known value)
+    return offset
 
 
 def _get_scale_offset(min, max, qmin, qmax, symmetric):  # pylint: disable=redefined-builtin
@@ -373,32 +376,32 @@ class AffineQuantizerBase(QuantizerBase):
         if max is not None:
             self.max.copy_(max if isinstance(max, torch.Tensor) else torch.tensor(max))
 
-    def _encoding_cache_key(self):
-        # parameters are versioned tensors: an in-place update or a re-assignment changes the key
-        return (id(self.min), self.min._version, id(self.max), self.max._version, self.min.device, self.min.dtype, self.qmin,  # pylint: disable=protected-access
-                self.qmax, self._symmetric, self.block_size, self.zero_point_shift)
-
     def get_encodings(self) -> Optional[AffineEncoding]:
         if self._pinned_encoding is not None:
             return self._pinned_encoding
-        # inference: scale / offset only change when the parameters do, so they are derived once
-        # (the reference offers the same through its _precompute_encodings context)
-        cacheable = not torch.is_grad_enabled() and type(self).get_scale is AffineQuantizerBase.get_scale
-        if cacheable:
-            key = self._encoding_cache_key()
-            cached = getattr(self, "_encoding_cache", None)
-            if cached is not None and cached[0] == key:
-                return cached[1]
         scale = self.get_scale(dtype=torch.float32)
         if scale is None:
             return None
         offset = self._get_offset(scale=scale, dtype=torch.float32)
-        enc = AffineEncoding(scale, offset, self.qmin, self.qmax, self._symmetric, self.block_size,
-                             self.zero_point_shift, producer=self)
-        if cacheable:
-            enc.scale, enc.offset = scale.detach().contiguous(), offset.detach().contiguous()
-            object.__setattr__(self, "_encoding_cache", (key, enc))
-        return enc
+        return AffineEncoding(scale, offset, self.qmin, self.qmax, self._symmetric, self.block_size,
+                              self.zero_point_shift, producer=self)
+
+    @contextlib.contextmanager
+    def _precompute_encodings(self, dtype: Optional[torch.dtype] = None):
+        """Derive scale / offset once and use them for every forward inside the context
+        (quantizer.py:790-804 of the reference).  Opt-in on purpose: outside it the encoding is
+        re-derived from ``min`` / ``max`` on every forward, like the reference does, so that any
+        way of editing the parameters (``.data`` included, which leaves no trace in the tensor's
+        version counter) takes effect."""
+        with torch.no_grad():
+            enc = self.get_encodings()
+            if enc is not None:
+                enc = enc.to(dtype=dtype or torch.float32)
+                enc.scale, enc.offset = enc.scale.detach().contiguous(), enc.offset.detach().contiguous()
+                if self._symmetric:  # every zero point is this constant: known without reading the device
+                    enc.offset._b200_constant = float(-round((self.qmin + self.qmax) / 2))  # pylint: disable=protected-access
+        with self._set_encodings(enc):
+            yield
 
     def _get_dummy_encoding(self) -> AffineEncoding:
         device = self.min.device

@@ -208,24 +208,45 @@ int aimet_b200_sqnr_sweep(const float *hist, const float *edge0, const float *wi
                           double gamma, float *noise_out, int32_t *best_out, void *stream);
 
 /* ------------------------------------------------------------------------- *
- * SeqMSE reconstruction loss of a Linear layer for all candidates at once:
- *   out[c][n][0] = sum_m f(x[m,:] . w[n,:],  xq[m,:] . wq[c][n,:])
- * with f = squared difference (loss_kind 0), absolute difference (1), or, for
- * loss_kind 2, out[c][n][0] = sum of squared differences and out[c][n][1] = sum
- * of squares of the second product (what neg_sqnr needs).
+ * SeqMSE reconstruction loss of a Linear layer for all candidates and all
+ * input-channel blocks at once:
+ *   out[c][n][b][0] = sum_m f(x[m,Kb] . w[n,Kb],  xq[m,Kb] . wq[c][n,Kb])
+ * where Kb are the K / num_blocks input channels of block b, and f is the
+ * squared difference (loss_kind 0, 2, 3) or the absolute difference (1).
+ * loss_kind 2 also returns out[..][1] = sum of squares of the second product,
+ * loss_kind 3 the sum of squares of the first product (what neg_sqnr needs as
+ * its signal: the Linear path passes (xw, xqwq), seq_mse.py:440-454, the Conv2d
+ * path (xqwq, xw), _base/seq_mse.py:705-720).
  *   x, xq  [M][K] row-major, io_dtype AB_BF16 or AB_F16;  w [N][K];  wq [C][N][K]
- *   out    float32 [C][N][2]
- *   lowp_epilogue != 0 rounds both products, their difference and f() to io_dtype
- *   the way the reference's half-precision aten chain does.
- * SequentialMse._compute_linear_loss (seq_mse.py:403-482) for num_blocks == 1.
+ *   out    float32 [C][N][num_blocks][nvals], nvals = 2 for loss_kind 2 and 3, else 1
+ *   lowp_epilogue != 0 rounds both products and f() to io_dtype the way the
+ *   reference's half-precision aten chain does.
+ *   has_reference == 0 drops the first product (x and w are not read): the loss
+ *   is f(0, xq . wq), which a caller that has formed differences itself uses.
+ * With num_blocks > 1 the channels of one block must be a multiple of 16.
+ * SequentialMse._compute_linear_loss (seq_mse.py:403-482).
  * The contraction runs on the 5th-generation tensor cores (tcgen05, TMEM
  * accumulators, TMA-fed operands).  status is a device int32 the kernel sets to
  * non-zero if one of its bounded waits gives up. */
+int64_t aimet_b200_seqmse_blocks_scratch_bytes(int64_t M, int64_t N, int64_t K, int32_t num_blocks,
+                                               int32_t num_cand);
+int aimet_b200_seqmse_linear_loss_blocks(const void *x, const void *xq, const void *w, const void *wq,
+                                         int64_t M, int64_t N, int64_t K, int32_t num_blocks,
+                                         int32_t num_cand, int io_dtype, int loss_kind,
+                                         int lowp_epilogue, int has_reference, float *out,
+                                         int32_t *status, void *scratch, int64_t scratch_bytes,
+                                         void *stream);
+/* The same with num_blocks == 1 and has_reference == 1: out is float32 [C][N][nvals]. */
 int64_t aimet_b200_seqmse_scratch_bytes(int64_t M, int64_t N, int64_t K, int32_t num_cand);
 int aimet_b200_seqmse_linear_loss(const void *x, const void *xq, const void *w, const void *wq,
                                   int64_t M, int64_t N, int64_t K, int32_t num_cand, int io_dtype,
                                   int loss_kind, int lowp_epilogue, float *out, int32_t *status,
                                   void *scratch, int64_t scratch_bytes, void *stream);
+/* No counterpart in the reference (its GEMMs are library calls without device-side waits).
+ * Launches one warp that waits, with the kernel's bounded wait, on a barrier nothing completes:
+ * after limit_us microseconds the wait gives up, *status becomes 3 and the kernel returns.  Lets
+ * a host check the give-up path of the SeqMSE kernel's waits without provoking any fault. */
+int aimet_b200_seqmse_wait_selftest(int32_t *status, int64_t limit_us, void *stream);
 
 #ifdef __cplusplus
 }

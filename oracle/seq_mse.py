@@ -1,9 +1,10 @@
-"""Oracle for the SeqMSE candidate search of a Linear layer (CPU, PyTorch tensor ops).
+"""Oracle for the SeqMSE candidate search of a Linear or Conv2d layer (CPU, PyTorch tensor ops).
 
 Restates seq_mse.py of the reference: candidate ranges (_get_candidate :360-372), the
 re-calibration of the weight quantizer on a candidate range (compute_param_encodings :263-294),
-the block-wise reconstruction loss (_compute_linear_loss :403-454) and the per-channel arg-min
-(optimize_module :523-578); loss functions from _base/seq_mse.py:69-82, 872-888.
+the block-wise reconstruction loss (_compute_linear_loss :403-454, _compute_conv_loss :485-520 with
+compute_outputs / compute_recon_loss of _base/seq_mse.py:705-720, 753-800) and the per-channel
+arg-min (optimize_module :523-578); loss functions from _base/seq_mse.py:69-82, 872-888.
 Test infrastructure only.
 """
 
@@ -64,9 +65,27 @@ def linear_loss(x, xq, w, wq, block_size, loss_fn="mse"):
     return LOSS_FNS[loss_fn](xw, xqwq, reduction="none").sum(0).view(out_ch, nb)
 
 
+def conv_loss(x, xq, w, wq, block_size, loss_fn="mse", stride=1, padding=0, dilation=1, groups=1):
+    """_compute_conv_loss (:485-520): the weight is cut into blocks of ``block_size`` input channels,
+    the input into pieces of ``block_size * groups`` channels, one pair of convolutions per block;
+    the loss is taken with the quantized output as prediction and summed over all positions
+    (_base/seq_mse.py:705-720, 753-800) -> [C_out, num_blocks]"""
+    w_blocks, wq_blocks = torch.split(w, block_size, dim=1), torch.split(wq, block_size, dim=1)
+    x_blocks, xq_blocks = torch.split(x, block_size * groups, dim=-3), torch.split(xq, block_size * groups, dim=-3)
+    cols = []
+    for i, xb in enumerate(x_blocks):
+        kw = dict(stride=stride, padding=padding, dilation=dilation, groups=groups)
+        xqwq = F.conv2d(xq_blocks[i], wq_blocks[i], **kw).permute(0, 2, 3, 1)
+        xw = F.conv2d(xb, w_blocks[i], **kw).permute(0, 2, 3, 1)
+        ch = xqwq.shape[-1]
+        cols.append(LOSS_FNS[loss_fn](xqwq.reshape(-1, ch), xw.reshape(-1, ch), reduction="none").sum(0))
+    return torch.stack(cols, dim=-1)
+
+
 def optimize_linear(w, xs, xqs, min_t, max_t, qmin, qmax, symmetric, block_size=None, num_candidates=20,
-                    loss_fn="mse", zero_point_shift=0.0, num_batches=None):
-    """optimize_module (:523-578) for a Linear weight.  ``min_t`` / ``max_t`` are the quantizer's
+                    loss_fn="mse", zero_point_shift=0.0, num_batches=None, conv=None):
+    """optimize_module (:523-578) for a Linear weight, or for a Conv2d weight when ``conv`` holds
+    its stride / padding / dilation / groups.  ``min_t`` / ``max_t`` are the quantizer's
     get_min() / get_max() before the search.  Returns (losses [C, out, blocks], best indices,
     final encoding min, final encoding max)."""
     in_block = w.shape[1] if block_size is None else w.shape[1] // min_t.shape[1]
@@ -79,7 +98,10 @@ def optimize_linear(w, xs, xqs, min_t, max_t, qmin, qmax, symmetric, block_size=
         for b, (x, xq) in enumerate(zip(xs, xqs)):
             if num_batches and b >= num_batches:
                 break
-            loss = loss + linear_loss(x, xq, w, wq, in_block, loss_fn)
+            if conv is None:
+                loss = loss + linear_loss(x, xq, w, wq, in_block, loss_fn)
+            else:
+                loss = loss + conv_loss(x, xq, w, wq, in_block, loss_fn, **conv)
         total.append(loss)
     losses = torch.stack(total)
     best = losses.min(0)[1]

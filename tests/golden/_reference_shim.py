@@ -2,7 +2,7 @@
 
 The reference imports a few packages that are not installed (bokeh, onnx, onnxruntime, onnxscript,
 onnx_ir) at module load although the quantization-simulation path never calls them; they are
-replaced by inert stand-ins.  Set AIMET_REFERENCE_ROOT to the checkout (default /root/reference).
+replaced by inert stand-ins.  Set AIMET_REFERENCE_ROOT to the checkout of the reference.
 """
 
 import importlib.abc
@@ -12,7 +12,7 @@ import sys
 from unittest.mock import MagicMock
 
 _STUB_ROOTS = {"bokeh", "onnx", "onnxruntime", "onnxscript", "onnx_ir"}
-REFERENCE_ROOT = os.environ.get("AIMET_REFERENCE_ROOT", "/root/reference")
+REFERENCE_ROOT = os.environ.get("AIMET_REFERENCE_ROOT", "")
 
 
 class _Loader(importlib.abc.Loader):
@@ -33,6 +33,8 @@ class _Finder(importlib.abc.MetaPathFinder):
 
 
 def install():
+    if not REFERENCE_ROOT:
+        raise RuntimeError("set AIMET_REFERENCE_ROOT to the checkout of the reference")
     if not os.path.isdir(REFERENCE_ROOT):
         raise RuntimeError(f"reference checkout not found at {REFERENCE_ROOT}")
     if not any(isinstance(f, _Finder) for f in sys.meta_path):

@@ -2,7 +2,7 @@
 
 Run where the reference checkout is available (CPU is enough):
 
-    python tests/golden/make_golden.py [affine|backend_vectors|analyzers|quantizers|seqmse ...]
+    AIMET_REFERENCE_ROOT=<checkout> python tests/golden/make_golden.py [affine|backend_vectors|analyzers|quantizers|seqmse|seqmse_extra ...]
 
 Every fixture stores the seeded inputs next to the reference's outputs, so the tests that read
 them need neither the reference nor this script.  Nothing here is imported by the product.
@@ -342,12 +342,78 @@ def gen_seqmse():
     _save("seqmse_cases.pt", out)
 
 
+# name, dtype, layer, conv args, quantizer shape, block size, bitwidth, loss, candidates, x shape, xq differs
+SEQMSE_EXTRA_CASES = [
+    ("linear_int4_mse_fp32_distinct_inputs", torch.float32, ("linear", 48, 64), {}, (48, 1), None, 4, "mse", 8,
+     (2, 50, 64), True),
+    ("linear_blockwise16_int4_mse_fp32_distinct_inputs", torch.float32, ("linear", 32, 64), {}, (32, 4), (1, 16), 4,
+     "mse", 6, (2, 40, 64), True),
+    ("conv3x3_per_channel_int4_mse_fp32", torch.float32, ("conv", 24, 16, 3), dict(stride=1, padding=1), (24, 1, 1, 1),
+     None, 4, "mse", 8, (2, 2, 16, 10, 10), True),
+    ("conv3x3_blockwise8_int4_mse_fp32", torch.float32, ("conv", 24, 16, 3), dict(stride=2, padding=1), (24, 2, 1, 1),
+     (1, 8, 3, 3), 4, "mse", 6, (2, 2, 16, 11, 11), False),
+    ("conv3x3_groups2_int4_sqnr_fp32", torch.float32, ("conv", 24, 16, 3), dict(stride=1, padding=0, groups=2),
+     (24, 1, 1, 1), None, 4, "sqnr", 6, (1, 3, 16, 9, 9), True),
+    ("conv1x1_per_channel_int8_l1_fp32", torch.float32, ("conv", 20, 32, 1), dict(stride=1, padding=0), (20, 1, 1, 1),
+     None, 8, "l1", 5, (1, 4, 32, 7, 7), True),
+]
+
+
+def gen_seqmse_extra():
+    """SeqMSE fixtures for Conv2d layers, blockwise Linear and inputs that differ between the
+    floating-point and the quantized model."""
+    from aimet_torch.nn import QuantizationMixin
+    from aimet_torch.quantization.affine import QuantizeDequantize
+    from aimet_torch.seq_mse import SequentialMse, SeqMseParams
+
+    out = {}
+    for idx, (name, dtype, layer, conv, qshape, block, bw, loss_fn, ncand, xshape, distinct) in enumerate(SEQMSE_EXTRA_CASES):
+        g = _gen(1400 + idx)
+        if layer[0] == "linear":
+            mod = torch.nn.Linear(layer[2], layer[1], bias=False)
+        else:
+            mod = torch.nn.Conv2d(layer[2], layer[1], layer[3], bias=False, **conv)
+        w = torch.randn(mod.weight.shape, generator=g) * 0.05
+        x = torch.randn(xshape, generator=g)
+        xq = x + 0.02 * torch.randn(xshape, generator=g) if distinct else x
+        w, x, xq = w.to(dtype), x.to(dtype), xq.to(dtype)
+        with torch.no_grad():
+            mod.weight.copy_(w)
+        qmod = QuantizationMixin.from_module(mod.to(dtype))
+        qtz = QuantizeDequantize(shape=qshape, bitwidth=bw, symmetric=True, block_size=block)
+        qmod.param_quantizers["weight"] = qtz
+        with qtz.compute_encodings():
+            qtz(qmod.weight.data)
+        min_t, max_t = qtz.get_min().detach().clone(), qtz.get_max().detach().clone()
+        captured = []
+        orig = SequentialMse._compute_loss.__func__
+
+        def spy(cls, *a, **k):
+            r = orig(cls, *a, **k)
+            captured.append(r.detach().clone())
+            return r
+
+        SequentialMse._compute_loss = classmethod(spy)
+        try:
+            SequentialMse.optimize_module(qmod, x, xq, SeqMseParams(num_batches=None, num_candidates=ncand, loss_fn=loss_fn))
+        finally:
+            SequentialMse._compute_loss = classmethod(orig)
+        nb = xshape[0]
+        losses = torch.stack([sum(captured[c * nb:(c + 1) * nb]) for c in range(ncand)])
+        out[name] = dict(dtype=dtype, layer=layer, conv=conv, w=w, x=x, xq=xq, qshape=qshape, block_size=block,
+                         bitwidth=bw, loss_fn=loss_fn, num_candidates=ncand, min_before=min_t, max_before=max_t,
+                         losses=losses, best=losses.min(0)[1], min_after=qtz.min.detach().clone(),
+                         max_after=qtz.max.detach().clone())
+    _save("seqmse_extra_cases.pt", out)
+
+
 GENERATORS = {
     "backend_vectors": gen_backend_vectors,
     "affine": gen_affine,
     "analyzers": gen_analyzers,
     "quantizers": gen_quantizers,
     "seqmse": gen_seqmse,
+    "seqmse_extra": gen_seqmse_extra,
 }
 
 

@@ -276,3 +276,26 @@ def test_fake_quantize_large_per_channel():
     offset = torch.zeros(96, 1, 1)
     y = B.quantize_dequantize(x.cuda(), scale.cuda(), offset.cuda(), -128, 127)
     assert_same(y, O.fake_quantize(x, scale, offset, -128, 127), "per-channel fake-quantize")
+
+
+def test_per_channel_zero_point_outside_the_grid_takes_the_division_arithmetic():
+    """torch.fake_quantize_per_channel_affine refuses zero points outside [qmin, qmax] and the reference
+    then runs QuantDequantFunc (true division) for the whole tensor (torch_builtins.py:418-425); so does
+    this backend, whether it learns the zero points from the device or from a host-known constant."""
+    B = _backend()
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(7, 12, 33, generator=g) * 3
+    scale = torch.rand(12, 1, generator=g) * 0.05 + 0.01
+    inside = torch.full((12, 1), -100.0)
+    outside = inside.clone()
+    outside[5] = 40.0  # zero point -40 < qmin = 0
+    with torch.no_grad():
+        y_in = B.quantize_dequantize(x.cuda(), scale.cuda(), inside.cuda(), 0, 255)
+        y_out = B.quantize_dequantize(x.cuda(), scale.cuda(), outside.cuda(), 0, 255)
+        tagged = outside.cuda()
+        tagged[:] = 40.0
+        tagged._b200_constant = 40.0
+        y_tag = B.quantize_dequantize(x.cuda(), scale.cuda(), tagged, 0, 255)
+    assert_same(y_in, O.fake_quantize(x, scale, inside, 0, 255), "zero points inside: fake-quantize arithmetic")
+    assert_same(y_out, O.quantize_dequantize(x, scale, outside, 0, 255), "a zero point outside: division arithmetic")
+    assert_same(y_tag, O.quantize_dequantize(x, scale, torch.full((12, 1), 40.0), 0, 255), "host-known constant")

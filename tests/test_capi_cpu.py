@@ -46,7 +46,9 @@ def test_layout_errors_and_scratch_queries_without_a_gpu():
     n = lib.aimet_b200_backward_scratch_bytes(_lib.make_layout([4096, 4096], [4096, 4096]), _lib.AB_F32)
     assert n % 16 == 0 and 4096 * 4096 // 32768 * 16 <= n <= (4096 * 4096 // 2048) * 16
     assert lib.aimet_b200_backward_scratch_bytes(_lib.make_layout([0, 4], [1, 4]), _lib.AB_F32) == 0
-    assert lib.aimet_b200_seqmse_scratch_bytes(8192, 4096, 4096, 20) == 32 * 20 * 4096 * 2 * 4
+    # two column halves per 256-token tile, up to two values per (candidate, channel, block)
+    assert lib.aimet_b200_seqmse_scratch_bytes(8192, 4096, 4096, 20) == 2 * 32 * 20 * 4096 * 2 * 4
+    assert lib.aimet_b200_seqmse_blocks_scratch_bytes(8192, 4096, 4096, 64, 20) == 64 * 2 * 32 * 20 * 4096 * 2 * 4
     assert lib.aimet_b200_fixed_scratch_capacity() == 1 << 20
     with pytest.raises(RuntimeError):
         _lib.make_layout([1] * 9, [1] * 9)

@@ -75,6 +75,20 @@ def _worker(rank, world, port, mode, ret):
             an = EA.SqnrEncodingAnalyzer((16,), num_bins=64)
             st = D.calibrate_histogram(an, mine, minmax_fn=_cpu_minmax, counts_fn=_cpu_counts)
             ret[rank] = ("ok", st.histogram.clone(), st.bin_edges.clone(), st.min.clone(), st.max.clone())
+        elif mode == "one_rank_empty":
+            # fewer batches than ranks: rank 1 has nothing, takes part with an empty range and zero
+            # counts, and ends with the same statistics as rank 0
+            mine = batches[:1] if rank == 0 else []
+            an = EA.SqnrEncodingAnalyzer((16,), num_bins=64)
+            st = D.calibrate_histogram(an, mine, minmax_fn=_cpu_minmax, counts_fn=_cpu_counts, device="cpu")
+            ret[rank] = ("ok", st.histogram.clone(), st.bin_edges.clone(), st.min.clone(), st.max.clone())
+        elif mode == "all_ranks_empty":
+            an = EA.SqnrEncodingAnalyzer((16,), num_bins=64)
+            try:
+                D.calibrate_histogram(an, [], minmax_fn=_cpu_minmax, counts_fn=_cpu_counts, device="cpu")
+                ret[rank] = ("no error",)
+            except D.PeerFailure as e:
+                ret[rank] = ("peer failure", str(e)[:60])
         elif mode == "minmax":
             mn = torch.stack([b.amin() for b in mine]).amin()
             mx = torch.stack([b.amax() for b in mine]).amax()
@@ -130,6 +144,23 @@ def test_sharded_histogram_equals_single_process_collect():
             assert torch.equal(edges[i], w["bin_edges"])
             assert torch.equal(mn[i], w["min"]) and torch.equal(mx[i], w["max"])
     assert torch.equal(ret[0][1], ret[1][1])
+
+
+def test_rank_without_a_batch_takes_part_instead_of_raising_alone():
+    """A rank that received no batch must not leave the others waiting inside the collective: it
+    contributes an empty range and zero counts; only when no rank has a batch do all raise, together."""
+    from oracle import encoding_analyzer as OA
+
+    ret = _run("one_rank_empty")
+    want = OA.hist_collect(_batches()[0], (16,), 64)
+    for rank in (0, 1):
+        status, hist, edges, mn, mx = ret[rank]
+        assert status == "ok"
+        for i, w in enumerate(want):
+            assert torch.equal(hist[i], w["histogram"]) and torch.equal(edges[i], w["bin_edges"])
+            assert float(mn[i]) == float(w["min"]) and float(mx[i]) == float(w["max"])
+    ret = _run("all_ranks_empty")
+    assert ret[0][0] == "peer failure" and ret[1][0] == "peer failure"
 
 
 def test_minmax_allreduce_and_row_gather():

@@ -39,12 +39,12 @@ def test_two_phase_histogram_equals_concatenated_collect(shape):
     emin, emax = an.compute_encodings(255, False)
     omin, omax = OA.sqnr_encodings(want, shape, 255, False)
     assert torch.allclose(emin.cpu().float(), omin.float(), rtol=1e-5) and torch.allclose(emax.cpu().float(), omax.float(), rtol=1e-5)
-    # the large-tensor path (pattern table) gives the same counts as the arithmetic kernel
+    # the large-tensor kernel (replicated shared-memory counters) gives the same counts as the plain one
     big = torch.cat([b.flatten() for b in batches] * 40)[: 1 << 20].cuda().contiguous()
     an2 = EA.SqnrEncodingAnalyzer((), num_bins=128)
     st2 = D.calibrate_histogram(an2, [big, big[: 1 << 19]])
     ref = OA.hist_collect(torch.cat([big.cpu(), big[: 1 << 19].cpu()]), (), 128)[0]
-    assert_same(st2[0].histogram, ref["histogram"], "table-path histogram")
+    assert_same(st2[0].histogram, ref["histogram"], "large-tensor histogram")
 
 
 def test_seqmse_on_row_shards_equals_unsharded():

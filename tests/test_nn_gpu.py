@@ -44,13 +44,28 @@ def test_quantized_cnn_matches_oracle_layer_by_layer():
     hooks = [spy(q) for layer in layers
              for q in (layer.input_quantizers[0], layer.output_quantizers[0], layer.param_quantizers["weight"])]
     with torch.no_grad():
-        for layer in layers:
-            layer.layer.weight.add_(0)  # an in-place update: the kept quantized weight must be refreshed
         y = model(x)
         assert y.shape == (5, 10) and len(seen) == 9
-        # a second forward reuses the quantized weights (6 activation quantizer calls only), same result
+        # like the reference, every forward quantizes every weight again ...
         y2 = model(x)
-        assert len(seen) == 15 and torch.equal(y, y2)
+        assert len(seen) == 18 and torch.equal(y, y2)
+        del seen[9:]
+        # ... unless the caller opts in to frozen parameters for the duration of a context: then only
+        # the 6 activation quantizers run per forward, with the same result
+        with qnn.precomputed(model):
+            y3 = model(x)
+            y4 = model(x)
+        assert len(seen) == 9 + 3 + 6 + 6 and torch.equal(y, y3) and torch.equal(y, y4)
+        del seen[9:]
+        # nothing outlives the context: edits that leave no trace in a tensor's version counter
+        # (writes through .data, as batch-norm folding and cross-layer equalisation do) take effect
+        layers[1].layer.weight.data.mul_(2.0)
+        layers[0].input_quantizers[0].max.data.mul_(0.5)
+        y5 = model(x)
+        assert not torch.equal(y, y5)
+        layers[1].layer.weight.data.mul_(0.5)
+        layers[0].input_quantizers[0].max.data.mul_(2.0)
+        assert torch.equal(model(x), y)
         del seen[9:]
     for h in hooks:
         h.remove()

@@ -63,6 +63,15 @@ def test_fixed_scratch_matches_ordinary_entry_point_twice_in_a_row():
         assert torch.equal(gs0, gs1) and not torch.isnan(gs1).any()
         if want_go:
             assert torch.equal(go0, go1) and not torch.isnan(go1).any()
+        # and both agree with the CPU oracle of the reference's backward pass
+        from oracle import affine as O
+
+        ogx, ogs, ogo = O.quantize_dequantize_backward(x.cpu(), gy.cpu(), scale.cpu(), offset.cpu(), qmin, qmax)
+        assert torch.equal(gx1.cpu(), ogx)
+        for got, want in ((gs1, ogs), (go1, ogo) if want_go else (None, None)):
+            if got is not None:  # sums in another order than torch's: 1e-5 of the largest magnitude
+                want = want.reshape(got.shape).double()
+                assert (got.cpu().double() - want).abs().max() <= 1e-5 * want.abs().max().clamp_min(1e-30)
 
 
 def test_fixed_scratch_refuses_oversized_layouts():
