@@ -51,6 +51,7 @@ template <> struct StatT<AB_F64> { using T = double; };
 
 template <typename T, typename E> __device__ __forceinline__ T stat_load(E v) { return (T)to_f32(v); }
 template <> __device__ __forceinline__ double stat_load<double, double>(double v) { return v; }
+template <> __device__ __forceinline__ double stat_load<double, float>(float v) { return (double)v; }
 
 template <typename E> __device__ __forceinline__ E stat_store(double v);
 template <> __device__ __forceinline__ float stat_store<float>(double v) { return (float)v; }
@@ -110,6 +111,7 @@ struct MinMaxArgs {
     int group, direct;
     int64_t rows, row_len, rows_per_tile;
     int finite_only;
+    int merge;  // direct mode: also take the values already in min_out / max_out
 };
 
 template <int IO, bool VECT> __global__ void __launch_bounds__(kThreads) k_minmax_seg(MinMaxArgs a) {
@@ -200,6 +202,9 @@ template <int IO, bool VECT> __global__ void __launch_bounds__(kThreads) k_minma
     }
     if (valid && lane == 0) {
         if (a.direct) {
+            if (a.merge)
+                mm_merge(m, stat_load<T, E>(static_cast<E *>(a.min_out)[param]),
+                         stat_load<T, E>(static_cast<E *>(a.max_out)[param]));
             static_cast<E *>(a.min_out)[param] = stat_store<E>((double)m.lo);
             static_cast<E *>(a.max_out)[param] = stat_store<E>((double)m.hi);
         } else {
@@ -253,6 +258,7 @@ struct MinMaxFinishArgs {
     const double *partial;
     void *min_out, *max_out;
     int64_t nparam, na, sa, sc, nb;
+    int merge;  // also take the values already in min_out / max_out (a running min / max over calls)
 };
 
 template <int IO, bool PER_CTA> __global__ void __launch_bounds__(kThreads) k_minmax_finish(MinMaxFinishArgs a) {
@@ -287,6 +293,8 @@ template <int IO, bool PER_CTA> __global__ void __launch_bounds__(kThreads) k_mi
         for (int w = 1; w < kThreads / 32; ++w) mm_merge(m, sh[0][w], sh[1][w]);
     }
     if (lane == 0) {
+        if (a.merge) mm_merge(m, (double)stat_load<double, E>(static_cast<E *>(a.min_out)[c]),
+                              (double)stat_load<double, E>(static_cast<E *>(a.max_out)[c]));
         static_cast<E *>(a.min_out)[c] = stat_store<E>(m.lo);
         static_cast<E *>(a.max_out)[c] = stat_store<E>(m.hi);
     }
@@ -302,7 +310,7 @@ template <int IO> void launch_minmax_finish(const MinMaxFinishArgs &f, cudaStrea
 }
 
 template <int IO>
-int launch_minmax(const void *x, const Canon &canon, int finite_only, void *min_out, void *max_out,
+int launch_minmax(const void *x, const Canon &canon, int finite_only, int merge, void *min_out, void *max_out,
                   void *scratch, int64_t scratch_bytes, cudaStream_t stream) {
     const ReducePlan p = plan_reduce(canon, IO, aligned16(x), kStatChunkMult);
     if (p.mode == ReducePlan::GEN)
@@ -326,6 +334,7 @@ int launch_minmax(const void *x, const Canon &canon, int finite_only, void *min_
     a.row_len = canon.C * canon.I;
     a.rows_per_tile = p.rows_per_tile;
     a.finite_only = finite_only;
+    a.merge = merge;
     if (p.mode == ReducePlan::SEG) {
         const int gpc = kThreads / p.group;
         const int64_t grid = (p.nseg + gpc - 1) / gpc;
@@ -345,7 +354,7 @@ int launch_minmax(const void *x, const Canon &canon, int finite_only, void *min_
     }
     AB_LAUNCH_OK();
     if (p.npartial > 0) {
-        MinMaxFinishArgs f{a.partial, min_out, max_out, canon.nparam, p.na, p.sa, p.sc, p.nb};
+        MinMaxFinishArgs f{a.partial, min_out, max_out, canon.nparam, p.na, p.sa, p.sc, p.nb, merge};
         launch_minmax_finish<IO>(f, stream);
         AB_LAUNCH_OK();
     }
@@ -532,47 +541,75 @@ template <int IO, bool VECT> __global__ void __launch_bounds__(kThreads) k_histo
 constexpr int kPrivThreads = 1024;
 constexpr int kPrivCopies = 16;
 constexpr int kPrivMaxBins = 3072;                    // (bins + 1) * 64 B of counters: 192 KB
+constexpr size_t kPrivSmemMax = 232448 - 1024;        // dynamic shared memory one CTA may ask for
 constexpr int64_t kPrivMinElems = 1 << 20;            // per histogram; below this the plain kernel
 
 struct HistPrivArgs {
     const void *x;
     const float *lo, *hi, *below, *above;
     unsigned long long *counts;
+    double *mm_partial;  // [C][tiles][2] finite min / max of each CTA's tile, or NULL
     int64_t O, C, I;
     int64_t chan_elems, tile_elems;
     int num_bins;
+    int tiles;
 };
 
-// all values of the vector inside [plo, phi] (false if any is NaN)
-__device__ __forceinline__ bool vec_inside(const Vec16<float> &v, float plo, float phi) {
-    float mn, mx;
-    asm("min.NaN.f32 %0, %1, %2;" : "=f"(mn) : "f"(v.v[0]), "f"(v.v[1]));
-    asm("max.NaN.f32 %0, %1, %2;" : "=f"(mx) : "f"(v.v[0]), "f"(v.v[1]));
-    float mn2, mx2;
-    asm("min.NaN.f32 %0, %1, %2;" : "=f"(mn2) : "f"(v.v[2]), "f"(v.v[3]));
-    asm("max.NaN.f32 %0, %1, %2;" : "=f"(mx2) : "f"(v.v[2]), "f"(v.v[3]));
-    asm("min.NaN.f32 %0, %1, %2;" : "=f"(mn) : "f"(mn), "f"(mn2));
-    asm("max.NaN.f32 %0, %1, %2;" : "=f"(mx) : "f"(mx), "f"(mx2));
-    return mn >= plo && mx <= phi;
-}
-template <typename E> __device__ __forceinline__ bool vec_inside(const Vec16<E> &v, float plo, float phi) {
+// all values of the vector inside [plo, phi] (false if any is NaN); the packed minimum and maximum
+// of a 16-bit vector are handed back for the running min / max
+struct RangeF32 {
+    float plo, phi;
+    __device__ __forceinline__ void init(float lo, float hi) {
+        plo = lo;
+        phi = hi;
+    }
+    __device__ __forceinline__ bool inside(const Vec16<float> &v, float &mn, float &mx) const {
+        float mn2, mx2;
+        asm("min.NaN.f32 %0, %1, %2;" : "=f"(mn) : "f"(v.v[0]), "f"(v.v[1]));
+        asm("max.NaN.f32 %0, %1, %2;" : "=f"(mx) : "f"(v.v[0]), "f"(v.v[1]));
+        asm("min.NaN.f32 %0, %1, %2;" : "=f"(mn2) : "f"(v.v[2]), "f"(v.v[3]));
+        asm("max.NaN.f32 %0, %1, %2;" : "=f"(mx2) : "f"(v.v[2]), "f"(v.v[3]));
+        asm("min.NaN.f32 %0, %1, %2;" : "=f"(mn) : "f"(mn), "f"(mn2));
+        asm("max.NaN.f32 %0, %1, %2;" : "=f"(mx) : "f"(mx), "f"(mx2));
+        return mn >= plo && mx <= phi;
+    }
+};
+// For 16-bit elements the thresholds are moved onto the element grid (the lower one rounded up, the
+// upper one rounded down): a 16-bit value is >= plo exactly when it is >= the smallest 16-bit value
+// that is, so the whole test is two packed comparisons.
+template <typename E> struct Range16 {
     using H2 = typename std::conditional<std::is_same<E, __half>::value, __half2, __nv_bfloat162>::type;
-    const H2 *w = reinterpret_cast<const H2 *>(&v);
-    const H2 mn = __hmin2_nan(__hmin2_nan(w[0], w[1]), __hmin2_nan(w[2], w[3]));
-    const H2 mx = __hmax2_nan(__hmax2_nan(w[0], w[1]), __hmax2_nan(w[2], w[3]));
-    const float2 fmn = std::is_same<E, __half>::value ? __half22float2(*reinterpret_cast<const __half2 *>(&mn))
-                                                       : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&mn));
-    const float2 fmx = std::is_same<E, __half>::value ? __half22float2(*reinterpret_cast<const __half2 *>(&mx))
-                                                       : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&mx));
-    return fmn.x >= plo && fmn.y >= plo && fmx.x <= phi && fmx.y <= phi;
-}
+    H2 plo, phi;
+    __device__ __forceinline__ void init(float lo, float hi) {
+        if constexpr (std::is_same<E, __half>::value) {
+            plo = __half2half2(__float2half_ru(lo));
+            phi = __half2half2(__float2half_rd(hi));
+        } else {
+            plo = __bfloat162bfloat162(__float2bfloat16_ru(lo));
+            phi = __bfloat162bfloat162(__float2bfloat16_rd(hi));
+        }
+    }
+    __device__ __forceinline__ bool inside(const Vec16<E> &v, H2 &mn, H2 &mx) const {
+        const H2 *w = reinterpret_cast<const H2 *>(&v);
+        mn = __hmin2_nan(__hmin2_nan(w[0], w[1]), __hmin2_nan(w[2], w[3]));
+        mx = __hmax2_nan(__hmax2_nan(w[0], w[1]), __hmax2_nan(w[2], w[3]));
+        return __hbge2(mn, plo) && __hble2(mx, phi);
+    }
+};
 
-template <int IO> __global__ void __launch_bounds__(kPrivThreads, 1) k_hist_private(HistPrivArgs a) {
+// MM: also produce the finite minimum and maximum of the tile (for the pass that bins a batch
+// against a range known beforehand and learns the batch's own range on the way).
+template <int IO, bool MM, bool POW2, int RING>
+__global__ void __launch_bounds__(kPrivThreads, 1) k_hist_private(HistPrivArgs a) {
     pdl_prologue();
     using E = typename Elem<IO>::type;
     constexpr int NV = 16 / (int)sizeof(E);
+    constexpr bool F32 = std::is_same<E, float>::value;
+    using Range = typename std::conditional<F32, RangeF32, Range16<E>>::type;
+    using Ext = typename std::conditional<F32, float, typename Range16<typename std::conditional<F32, __half, E>::type>::H2>::type;
     extern __shared__ __align__(16) unsigned int sh_cnt[];  // [num_bins + 1][16]; row num_bins: v == hi
     __shared__ unsigned long long sh_edge[2];
+    __shared__ float sh_mm[2][kPrivThreads / 32];
     const int64_t c = blockIdx.y;
     for (int i = threadIdx.x; i < (a.num_bins + 1) * kPrivCopies; i += kPrivThreads) sh_cnt[i] = 0;
     if (threadIdx.x < 2) sh_edge[threadIdx.x] = 0;
@@ -580,102 +617,218 @@ template <int IO> __global__ void __launch_bounds__(kPrivThreads, 1) k_hist_priv
 
     const float lo = a.lo[c], hi = a.hi[c], below = a.below[c], above = a.above[c];
     const float range = __fsub_rn(hi, lo), nbf = (float)a.num_bins;
-    const float r = __frcp_rn(range);
-    // the quick body needs a moderate range (exact reciprocal division)
-    const bool quick = range > 7.888609e-31f && range < 1.2676506e30f && fabsf(lo) < 1.2676506e30f &&
+    // a power-of-two bin count scales exactly: (v - lo) * bins / range == (v - lo) / (range / bins)
+    const float dvs = POW2 ? __fdiv_rn(range, nbf) : range;  // divisor of the quick body
+    const float mul = POW2 ? 1.0f : nbf;
+    const float r = __frcp_rn(dvs);
+    // the quick body needs a moderate range (exact reciprocal division, no underflow in the remainder)
+    const bool quick = range > 1.0e-25f && range < 1.2676506e30f && fabsf(lo) < 1.2676506e30f &&
                        fabsf(hi) < 1.2676506e30f;
     // "plain" values lie inside the binning range and inside the outlier thresholds: they count in
     // their bin and nowhere else
-    const float plo = fmaxf(lo, below), phi = fminf(hi, above);
+    Range rng;
+    rng.init(fmaxf(lo, below), fminf(hi, above));
     const int lane = threadIdx.x & 31;
+    // counter (bin, lane mod 16) lives at base + 64 * bin + 4 * (lane mod 16).  The quick body gets the
+    // bin as the low bits of the float 2^23 + bin (0x4B000000 + bin), so the address is one
+    // multiply-add on those bits with the constant part folded into the base.
     const unsigned base = (unsigned)__cvta_generic_to_shared(sh_cnt) + 4u * (lane & (kPrivCopies - 1));
+    const unsigned base_q = base - (0x4B000000u << 6);
     unsigned int n_below = 0, n_above = 0;
+    float fmn = INFINITY, fmx = -INFINITY;  // general body's finite min / max
+    Ext rmn, rmx;                            // quick body's running (packed) min / max
+    if constexpr (F32) {
+        rmn = INFINITY;
+        rmx = -INFINITY;
+    } else if constexpr (std::is_same<E, __half>::value) {
+        rmn = __float2half2_rn(INFINITY);
+        rmx = __float2half2_rn(-INFINITY);
+    } else {
+        rmn = __float2bfloat162_rn(INFINITY);
+        rmx = __float2bfloat162_rn(-INFINITY);
+    }
 
     auto count = [&](int b) {  // b in [0, num_bins]
         asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(base + ((unsigned)b << 6)), "r"(1u) : "memory");
     };
-    auto quick_vec = [&](const float (&f)[NV]) {
-#pragma unroll
-        for (int i = 0; i < NV; i += 2) {
-            const float2 t = __fmul2_rn(__fadd2_rn(make_float2(f[i], f[i + 1]), make_float2(-lo, -lo)), make_float2(nbf, nbf));
-            const float2 q0 = __fmul2_rn(t, make_float2(r, r));
-            const float2 rem = __ffma2_rn(q0, make_float2(-range, -range), t);
-            const float2 q = __ffma2_rn(rem, make_float2(r, r), q0);
-            const float2 tb = __ffma2_rz(q, make_float2(1.0f, 1.0f), make_float2(8388608.0f, 8388608.0f));
-            count(__float_as_int(tb.x) & 0x7fffff);
-            count(__float_as_int(tb.y) & 0x7fffff);
-        }
+    const float2 nlo2 = make_float2(-lo, -lo), mul2 = make_float2(mul, mul), r2 = make_float2(r, r),
+                 ndv2 = make_float2(-dvs, -dvs), one2 = make_float2(1.0f, 1.0f),
+                 magic2 = make_float2(8388608.0f, 8388608.0f);
+    auto quick_pair = [&](float fx, float fy) {
+        float2 t = __fadd2_rn(make_float2(fx, fy), nlo2);
+        if (!POW2) t = __fmul2_rn(t, mul2);
+        const float2 q0 = __fmul2_rn(t, r2);
+        const float2 rem = __ffma2_rn(q0, ndv2, t);
+        const float2 q = __ffma2_rn(rem, r2, q0);
+        const float2 tb = __ffma2_rz(q, one2, magic2);
+        asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(__float_as_uint(tb.x) * 64u + base_q), "r"(1u) : "memory");
+        asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(__float_as_uint(tb.y) * 64u + base_q), "r"(1u) : "memory");
     };
-    auto general_vec = [&](const Vec16<E> &w) {  // rare: its own copy of the vector, indexed in a loop
-        const Vec16<E> tmp = w;
+    auto general_vec = [&](unsigned slot_addr) {  // rare: the vector is read back from its ring slot
 #pragma unroll 1
         for (int i = 0; i < NV; ++i) {
-            const float v = to_f32(tmp.v[i]);
+            E e;
+            if constexpr (F32) {
+                asm volatile("ld.shared.f32 %0, [%1];" : "=f"(e) : "r"(slot_addr + 4u * i) : "memory");
+            } else {
+                unsigned short bits;
+                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(bits) : "r"(slot_addr + 2u * i) : "memory");
+                e = *reinterpret_cast<const E *>(&bits);
+            }
+            const float v = to_f32(e);
             if (v >= lo && v <= hi) count(histc_bin(v, lo, range, nbf, a.num_bins));
             n_below += v < below;
             n_above += v > above;
+            if (MM && isfinite(v)) {
+                fmn = fminf(fmn, v);
+                fmx = fmaxf(fmx, v);
+            }
         }
     };
-    auto feed = [&](const Vec16<E> &w) {
-        if (quick && vec_inside(w, plo, phi)) {
-            float f[NV];
-            VecCvt<float, E>::unpack(w, f);
-            quick_vec(f);
+    auto feed = [&](const Vec16<E> &w, unsigned slot_addr) {
+        Ext mn, mx;
+        if (quick && rng.inside(w, mn, mx)) {
+            if constexpr (MM) {
+                if constexpr (F32) {
+                    rmn = fminf(rmn, mn);
+                    rmx = fmaxf(rmx, mx);
+                } else {
+                    rmn = __hmin2(rmn, mn);
+                    rmx = __hmax2(rmx, mx);
+                }
+            }
+            if constexpr (F32) {
+                quick_pair(w.v[0], w.v[1]);
+                quick_pair(w.v[2], w.v[3]);
+            } else if constexpr (std::is_same<E, __nv_bfloat16>::value) {
+                const uint32_t *u = reinterpret_cast<const uint32_t *>(&w);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) quick_pair(__uint_as_float(u[i] << 16), __uint_as_float(u[i] & 0xffff0000u));
+            } else {
+                const __half2 *h = reinterpret_cast<const __half2 *>(&w);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __half22float2(h[i]);
+                    quick_pair(f.x, f.y);
+                }
+            }
         } else {
-            general_vec(w);
+            general_vec(slot_addr);
         }
     };
 
-    const Vec16<E> *xp = static_cast<const Vec16<E> *>(a.x);
-    const int64_t e0 = (int64_t)blockIdx.x * a.tile_elems;
-    int64_t e1 = e0 + a.tile_elems;
+    // Which vectors this CTA bins.  A single histogram over one contiguous run (the usual case: a
+    // per-tensor statistic) is dealt out in rounds of RING * 1024 vectors, round r going to CTA
+    // r mod gridDim.x: every SM then reads from all over the tensor and sees the same mix of
+    // memory channels as the others (with one contiguous tile per CTA some SMs finished 15 % early).
+    // Otherwise a CTA walks its own tile of the channel.
+    const bool flat = a.C == 1;
+    const int64_t e0 = flat ? 0 : (int64_t)blockIdx.x * a.tile_elems;
+    int64_t e1 = flat ? a.chan_elems : e0 + a.tile_elems;
     if (e1 > a.chan_elems) e1 = a.chan_elems;
     const int64_t nvec = (e1 - e0) / NV;
-    const bool flat = a.C == 1;
-    auto addr_of = [&](int64_t v) -> int64_t {
-        if (flat) return e0 / NV + v;
+    const int64_t G = flat ? gridDim.x : 1, bidx = flat ? blockIdx.x : 0;
+    const Vec16<E> *xp = static_cast<const Vec16<E> *>(a.x);
+    auto src = [&](int64_t v) -> const Vec16<E> * {
+        if (flat) return xp + v;
         const int64_t e = e0 + v * NV;
         const int64_t o = e / a.I;
-        return ((o * a.C + c) * a.I + (e - o * a.I)) / NV;
+        return xp + ((o * a.C + c) * a.I + (e - o * a.I)) / NV;
     };
-    // two vectors per iteration; the next iteration's loads are issued before this one's arithmetic
-    // (the warps of the CTA run in step, so without this all of them would wait on memory together)
-    Vec16<E> wa, wb, na, nb;
-    int64_t v0 = threadIdx.x;
-    if (v0 < nvec) wa = xp[addr_of(v0)];
-    if (v0 + kPrivThreads < nvec) wb = xp[addr_of(v0 + kPrivThreads)];
-    for (; v0 < nvec; v0 += 2 * kPrivThreads) {
-        const bool hb = v0 + kPrivThreads < nvec;
-        const int64_t n0 = v0 + 2 * kPrivThreads, n1 = n0 + kPrivThreads;
-        if (n0 < nvec) na = xp[addr_of(n0)];
-        if (n1 < nvec) nb = xp[addr_of(n1)];
-        feed(wa);
-        if (hb) feed(wb);
-        wa = na;
-        wb = nb;
+    // The input reaches the thread through its own ring of RING 16-byte slots in shared memory,
+    // filled by cp.async: RING - 1 vectors per thread (80 KB per SM with six slots) are in flight
+    // while one is binned, however the compiler orders the rest -- the pass is bound by memory
+    // latency otherwise, the warps of the one 1024-thread CTA per SM running in step.  A thread only
+    // ever touches its own slots, so no barrier is involved.
+    constexpr int T = kPrivThreads;
+    constexpr unsigned kSlotBytes = T * 16u;
+    const unsigned ring = (unsigned)__cvta_generic_to_shared(sh_cnt) + (unsigned)(a.num_bins + 1) * (kPrivCopies * 4u) +
+                          16u * threadIdx.x;
+    auto fill = [&](unsigned slot_addr, int64_t v) {
+        if (v < nvec) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(slot_addr), "l"(src(v)) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");  // one group per slot, empty or not
+    };
+    auto take = [&](unsigned slot_addr, int64_t v) {  // the oldest group has landed: bin its vector
+        asm volatile("cp.async.wait_group %0;" ::"n"(RING - 1) : "memory");
+        if (v < nvec) {
+            Vec16<E> w;
+            uint32_t *wr = reinterpret_cast<uint32_t *>(&w);
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(wr[0]), "=r"(wr[1]), "=r"(wr[2]), "=r"(wr[3])
+                         : "r"(slot_addr)
+                         : "memory");
+            feed(w, slot_addr);
+        }
+    };
+    // vector j of the CTA's round rl, for this thread
+    auto vec_of = [&](int64_t rl, int j) -> int64_t { return ((rl * G + bidx) * RING + j) * T + threadIdx.x; };
+#pragma unroll
+    for (int j = 0; j < RING - 1; ++j) fill(ring + j * kSlotBytes, vec_of(0, j));
+    for (int64_t rl = 0; vec_of(rl, 0) - threadIdx.x < nvec; ++rl) {
+        const int64_t base = vec_of(rl, 0), next = vec_of(rl + 1, 0);
+#pragma unroll
+        for (int j = 0; j < RING; ++j) {
+            // the slot emptied one step ago takes the vector RING - 1 steps ahead
+            const int rs = (j + RING - 1) % RING;
+            fill(ring + rs * kSlotBytes, j == 0 ? base + (RING - 1) * T : next + (j - 1) * T);
+            take(ring + j * kSlotBytes, base + j * T);
+        }
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+
     n_below = __reduce_add_sync(0xffffffffu, n_below);
     n_above = __reduce_add_sync(0xffffffffu, n_above);
     if (lane == 0) {
         if (n_below) atomicAdd(&sh_edge[0], (unsigned long long)n_below);
         if (n_above) atomicAdd(&sh_edge[1], (unsigned long long)n_above);
     }
+    if constexpr (MM) {
+        if constexpr (F32) {
+            fmn = fminf(fmn, rmn);
+            fmx = fmaxf(fmx, rmx);
+        } else if constexpr (std::is_same<E, __half>::value) {
+            fmn = fminf(fmn, fminf(__low2float(rmn), __high2float(rmn)));
+            fmx = fmaxf(fmx, fmaxf(__low2float(rmx), __high2float(rmx)));
+        } else {
+            fmn = fminf(fmn, fminf(__low2float(rmn), __high2float(rmn)));
+            fmx = fmaxf(fmx, fmaxf(__low2float(rmx), __high2float(rmx)));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            fmn = fminf(fmn, __shfl_xor_sync(0xffffffffu, fmn, o));
+            fmx = fmaxf(fmx, __shfl_xor_sync(0xffffffffu, fmx, o));
+        }
+        if (lane == 0) {
+            sh_mm[0][threadIdx.x >> 5] = fmn;
+            sh_mm[1][threadIdx.x >> 5] = fmx;
+        }
+    }
     __syncthreads();
     // merge the replicas: half a warp per bin
     unsigned long long *out = a.counts + c * (int64_t)a.num_bins;
     const int last = a.num_bins - 1;
-    for (int b0 = (threadIdx.x >> 5) * 2; b0 <= a.num_bins; b0 += kPrivThreads / 16) {
-        const int b = b0 + (lane >> 4);
-        unsigned int v = b <= a.num_bins ? sh_cnt[b * kPrivCopies + (lane & 15)] : 0u;
+    for (int b0i = (threadIdx.x >> 5) * 2; b0i <= a.num_bins; b0i += kPrivThreads / 16) {
+        const int b = b0i + (lane >> 4);
+        unsigned int n32 = b <= a.num_bins ? sh_cnt[b * kPrivCopies + (lane & 15)] : 0u;
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        for (int o = 8; o > 0; o >>= 1) n32 += __shfl_xor_sync(0xffffffffu, n32, o);
         if ((lane & 15) == 0 && b <= a.num_bins) {
-            unsigned long long n = v;
+            unsigned long long n = n32;
             const int dst = b > last ? last : b;  // row num_bins (v == hi) belongs to the last bin
             if (b == 0) n += sh_edge[0];
             if (b == last) n += sh_edge[1];
             if (n) atomicAdd(out + dst, n);
         }
+    }
+    if (MM && threadIdx.x == 0) {
+        float mn = sh_mm[0][0], mx = sh_mm[1][0];
+        for (int w = 1; w < kPrivThreads / 32; ++w) {
+            mn = fminf(mn, sh_mm[0][w]);
+            mx = fmaxf(mx, sh_mm[1][w]);
+        }
+        double *p = a.mm_partial + 2 * (c * (int64_t)a.tiles + blockIdx.x);
+        p[0] = (double)mn;
+        p[1] = (double)mx;
     }
 }
 
@@ -693,10 +846,13 @@ inline int zero_counts(int64_t *counts, int64_t n, cudaStream_t stream) {
     return AB_OK;
 }
 
+constexpr int AB_HIST_ACCUMULATE = 1;   // add to counts instead of overwriting them
+constexpr int AB_HIST_MERGE_MINMAX = 2; // fin_min / fin_max: running values over calls
+
 template <int IO>
 int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const float *lo, const float *hi,
                      const float *below, const float *above, int64_t *counts, void *fin_min, void *fin_max,
-                     void *scratch, int64_t scratch_bytes, cudaStream_t stream) {
+                     int flags, void *scratch, int64_t scratch_bytes, cudaStream_t stream) {
     if (!canon.oci)
         return fail(AB_ERR_UNSUPPORTED, "statistics need a layout that reduces to (outer, channel, inner)");
     if (canon.C > 65535) return fail(AB_ERR_UNSUPPORTED, "at most 65535 histograms per call, got %lld", (long long)canon.C);
@@ -714,19 +870,41 @@ int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const 
     tiles = (chan_elems + tile_elems - 1) / tile_elems;
 
     const bool want_mm = fin_min && fin_max;
+    const bool accumulate = (flags & AB_HIST_ACCUMULATE) != 0;
+    const int merge_mm = (flags & AB_HIST_MERGE_MINMAX) ? 1 : 0;
     // lane-private counters for large histograms
     if constexpr (IO == AB_BF16 || IO == AB_F16 || IO == AB_F32) {
-        if (vect && !want_mm && num_bins <= kPrivMaxBins && chan_elems >= kPrivMinElems && canon.C <= 1024) {
-            const size_t smem = (size_t)(num_bins + 1) * kPrivCopies * sizeof(unsigned int);
-            int rc = opt_in_smem<k_hist_private<IO>>((size_t)(kPrivMaxBins + 1) * kPrivCopies * sizeof(unsigned int));
-            if (rc != AB_OK) return rc;
-            rc = zero_counts(counts, canon.C * (int64_t)num_bins, stream);
+        if (vect && num_bins <= kPrivMaxBins && chan_elems >= kPrivMinElems && canon.C <= 1024) {
+            // counters, then the input ring: six slots of 16 bytes per thread when they fit, else two
+            const size_t counters = (size_t)(num_bins + 1) * kPrivCopies * sizeof(unsigned int);
+            const int ring = counters + 6 * (size_t)kPrivThreads * 16 <= kPrivSmemMax ? 6 : 2;
+            const size_t smem = counters + (size_t)ring * kPrivThreads * 16;
+            const bool pow2 = (num_bins & (num_bins - 1)) == 0;
+            using KernelFn = void (*)(HistPrivArgs);
+            KernelFn kernel = nullptr;
+            int rc = AB_OK;
+#define AB_PICK(MMV, P2V, RV)                                                       \
+    if (want_mm == MMV && pow2 == P2V && ring == RV) {                              \
+        kernel = k_hist_private<IO, MMV, P2V, RV>;                                  \
+        rc = opt_in_smem<k_hist_private<IO, MMV, P2V, RV>>(kPrivSmemMax);           \
+    }
+            AB_PICK(false, false, 2) AB_PICK(false, false, 6) AB_PICK(false, true, 2) AB_PICK(false, true, 6)
+            AB_PICK(true, false, 2) AB_PICK(true, false, 6) AB_PICK(true, true, 2) AB_PICK(true, true, 6)
+#undef AB_PICK
             if (rc != AB_OK) return rc;
             int64_t ptiles = (sm_count() + canon.C - 1) / canon.C;
             if (ptiles < 1) ptiles = 1;
             int64_t pt_elems = (chan_elems + ptiles - 1) / ptiles;
             pt_elems = ((pt_elems + 15) / 16) * 16;
             ptiles = (chan_elems + pt_elems - 1) / pt_elems;
+            const int64_t need = want_mm ? canon.C * ptiles * 2 * (int64_t)sizeof(double) : 0;
+            if (need > 0 && (!scratch || scratch_bytes < need))
+                return fail(AB_ERR_SCRATCH, "histogram needs %lld bytes of scratch, got %lld", (long long)need,
+                            (long long)scratch_bytes);
+            if (!accumulate) {
+                rc = zero_counts(counts, canon.C * (int64_t)num_bins, stream);
+                if (rc != AB_OK) return rc;
+            }
             HistPrivArgs h;
             h.x = x;
             h.lo = lo;
@@ -734,15 +912,22 @@ int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const 
             h.below = below;
             h.above = above;
             h.counts = reinterpret_cast<unsigned long long *>(counts);
+            h.mm_partial = want_mm ? static_cast<double *>(scratch) : nullptr;
             h.O = canon.O;
             h.C = canon.C;
             h.I = canon.I;
             h.chan_elems = chan_elems;
             h.tile_elems = pt_elems;
             h.num_bins = num_bins;
+            h.tiles = (int)ptiles;
             dim3 grid((unsigned)ptiles, (unsigned)canon.C);
-            launch_pdl(k_hist_private<IO>, grid, kPrivThreads, smem, stream, h);
+            launch_pdl(kernel, grid, kPrivThreads, smem, stream, h);
             AB_LAUNCH_OK();
+            if (want_mm) {
+                MinMaxFinishArgs f{h.mm_partial, fin_min, fin_max, canon.C, 1, 0, ptiles, ptiles, merge_mm};
+                launch_minmax_finish<IO>(f, stream);
+                AB_LAUNCH_OK();
+            }
             return AB_OK;
         }
     }
@@ -751,7 +936,7 @@ int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const 
         return fail(AB_ERR_SCRATCH, "histogram needs %lld bytes of scratch, got %lld", (long long)need,
                     (long long)scratch_bytes);
 
-    {
+    if (!accumulate) {
         const int zrc = zero_counts(counts, canon.C * (int64_t)num_bins, stream);
         if (zrc != AB_OK) return zrc;
     }
@@ -778,7 +963,7 @@ int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const 
         launch_pdl(k_histogram<IO, false>, grid, kThreads, smem, stream, a);
     AB_LAUNCH_OK();
     if (want_mm) {
-        MinMaxFinishArgs f{a.mm_partial, fin_min, fin_max, canon.C, 1, 0, tiles, tiles};
+        MinMaxFinishArgs f{a.mm_partial, fin_min, fin_max, canon.C, 1, 0, tiles, tiles, merge_mm};
         launch_minmax_finish<IO>(f, stream);
         AB_LAUNCH_OK();
     }
@@ -952,9 +1137,8 @@ extern "C" int64_t aimet_b200_stats_scratch_bytes(const ab_layout *layout, int i
     return bytes;
 }
 
-extern "C" int aimet_b200_minmax(const void *x, const ab_layout *layout, int io_dtype, int finite_only,
-                                 void *min_out, void *max_out, void *scratch, int64_t scratch_bytes,
-                                 void *stream) {
+static int minmax_entry(const void *x, const ab_layout *layout, int io_dtype, int finite_only, int merge,
+                        void *min_out, void *max_out, void *scratch, int64_t scratch_bytes, void *stream) {
     ab::Canon canon;
     int rc = ab::canonicalize(layout, &canon);
     if (rc != AB_OK) return rc;
@@ -962,18 +1146,30 @@ extern "C" int aimet_b200_minmax(const void *x, const ab_layout *layout, int io_
     if (!x || !min_out || !max_out) return ab::fail(AB_ERR_INVALID, "x, min_out and max_out must not be NULL");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (io_dtype) {
-        case AB_F32: return ab::launch_minmax<AB_F32>(x, canon, finite_only, min_out, max_out, scratch, scratch_bytes, st);
-        case AB_F16: return ab::launch_minmax<AB_F16>(x, canon, finite_only, min_out, max_out, scratch, scratch_bytes, st);
-        case AB_BF16: return ab::launch_minmax<AB_BF16>(x, canon, finite_only, min_out, max_out, scratch, scratch_bytes, st);
-        case AB_F64: return ab::launch_minmax<AB_F64>(x, canon, finite_only, min_out, max_out, scratch, scratch_bytes, st);
+        case AB_F32: return ab::launch_minmax<AB_F32>(x, canon, finite_only, merge, min_out, max_out, scratch, scratch_bytes, st);
+        case AB_F16: return ab::launch_minmax<AB_F16>(x, canon, finite_only, merge, min_out, max_out, scratch, scratch_bytes, st);
+        case AB_BF16: return ab::launch_minmax<AB_BF16>(x, canon, finite_only, merge, min_out, max_out, scratch, scratch_bytes, st);
+        case AB_F64: return ab::launch_minmax<AB_F64>(x, canon, finite_only, merge, min_out, max_out, scratch, scratch_bytes, st);
     }
     return ab::fail(AB_ERR_INVALID, "unknown io_dtype %d", io_dtype);
 }
 
-extern "C" int aimet_b200_histogram(const void *x, const ab_layout *layout, int io_dtype, int32_t num_bins,
-                                    const float *lo, const float *hi, const float *below,
-                                    const float *above, int64_t *counts, void *fin_min, void *fin_max,
-                                    void *scratch, int64_t scratch_bytes, void *stream) {
+extern "C" int aimet_b200_minmax(const void *x, const ab_layout *layout, int io_dtype, int finite_only,
+                                 void *min_out, void *max_out, void *scratch, int64_t scratch_bytes,
+                                 void *stream) {
+    return minmax_entry(x, layout, io_dtype, finite_only, 0, min_out, max_out, scratch, scratch_bytes, stream);
+}
+
+extern "C" int aimet_b200_minmax_running(const void *x, const ab_layout *layout, int io_dtype, int finite_only,
+                                         void *min_io, void *max_io, void *scratch, int64_t scratch_bytes,
+                                         void *stream) {
+    return minmax_entry(x, layout, io_dtype, finite_only, 1, min_io, max_io, scratch, scratch_bytes, stream);
+}
+
+extern "C" int aimet_b200_histogram_ex(const void *x, const ab_layout *layout, int io_dtype, int32_t num_bins,
+                                       const float *lo, const float *hi, const float *below,
+                                       const float *above, int64_t *counts, void *fin_min, void *fin_max,
+                                       int32_t flags, void *scratch, int64_t scratch_bytes, void *stream) {
     ab::Canon canon;
     int rc = ab::canonicalize(layout, &canon);
     if (rc != AB_OK) return rc;
@@ -982,16 +1178,25 @@ extern "C" int aimet_b200_histogram(const void *x, const ab_layout *layout, int 
     if (canon.numel == 0) return ab::fail(AB_ERR_INVALID, "histogram of an empty tensor is undefined");
     if (!x || !lo || !hi || !below || !above || !counts)
         return ab::fail(AB_ERR_INVALID, "x, lo, hi, below, above and counts must not be NULL");
+    if (flags & ~3) return ab::fail(AB_ERR_INVALID, "unknown flags %d", (int)flags);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (io_dtype) {
         case AB_F32:
-            return ab::launch_histogram<AB_F32>(x, canon, num_bins, lo, hi, below, above, counts, fin_min, fin_max, scratch, scratch_bytes, st);
+            return ab::launch_histogram<AB_F32>(x, canon, num_bins, lo, hi, below, above, counts, fin_min, fin_max, flags, scratch, scratch_bytes, st);
         case AB_F16:
-            return ab::launch_histogram<AB_F16>(x, canon, num_bins, lo, hi, below, above, counts, fin_min, fin_max, scratch, scratch_bytes, st);
+            return ab::launch_histogram<AB_F16>(x, canon, num_bins, lo, hi, below, above, counts, fin_min, fin_max, flags, scratch, scratch_bytes, st);
         case AB_BF16:
-            return ab::launch_histogram<AB_BF16>(x, canon, num_bins, lo, hi, below, above, counts, fin_min, fin_max, scratch, scratch_bytes, st);
+            return ab::launch_histogram<AB_BF16>(x, canon, num_bins, lo, hi, below, above, counts, fin_min, fin_max, flags, scratch, scratch_bytes, st);
     }
     return ab::fail(AB_ERR_UNSUPPORTED, "histogram supports float32, float16 and bfloat16 inputs");
+}
+
+extern "C" int aimet_b200_histogram(const void *x, const ab_layout *layout, int io_dtype, int32_t num_bins,
+                                    const float *lo, const float *hi, const float *below,
+                                    const float *above, int64_t *counts, void *fin_min, void *fin_max,
+                                    void *scratch, int64_t scratch_bytes, void *stream) {
+    return aimet_b200_histogram_ex(x, layout, io_dtype, num_bins, lo, hi, below, above, counts, fin_min, fin_max, 0,
+                                   scratch, scratch_bytes, stream);
 }
 
 extern "C" int aimet_b200_sqnr_sweep(const float *hist, const float *edge0, const float *width,

@@ -159,6 +159,13 @@ int aimet_b200_minmax(const void *x, const ab_layout *layout, int io_dtype, int 
                       void *min_out, void *max_out, void *scratch, int64_t scratch_bytes,
                       void *stream);
 
+/* The same, as a running min / max over calls: min_io / max_io are read and updated (start them
+ * at +inf / -inf).  Lets a calibration loop keep one pair of statistics on the device instead of
+ * one pair per batch (_MinMaxObserver.merge_stats, encoding_analyzer.py:95-112). */
+int aimet_b200_minmax_running(const void *x, const ab_layout *layout, int io_dtype, int finite_only,
+                              void *min_io, void *max_io, void *scratch, int64_t scratch_bytes,
+                              void *stream);
+
 /* counts[c][b] (int64, overwritten): torch.histc binning of float(x) over
  * [lo[c], hi[c]], i.e. bin = (int)((x - lo) * num_bins / (hi - lo)) with x == hi
  * in the last bin and values outside [lo, hi] or NaN ignored; then the number of
@@ -172,6 +179,15 @@ int aimet_b200_histogram(const void *x, const ab_layout *layout, int io_dtype, i
                          const float *lo, const float *hi, const float *below, const float *above,
                          int64_t *counts, void *fin_min, void *fin_max, void *scratch,
                          int64_t scratch_bytes, void *stream);
+
+/* The same with options (flags, or-ed together):
+ *   1  add to counts instead of overwriting them (several batches binned over one range, the
+ *      second phase of a calibration whose range was agreed on first)
+ *   2  fin_min / fin_max are running values over calls, as in aimet_b200_minmax_running */
+int aimet_b200_histogram_ex(const void *x, const ab_layout *layout, int io_dtype, int32_t num_bins,
+                            const float *lo, const float *hi, const float *below, const float *above,
+                            int64_t *counts, void *fin_min, void *fin_max, int32_t flags,
+                            void *scratch, int64_t scratch_bytes, void *stream);
 
 /* Moves accumulated histograms into the range that also covers a new batch, one launch for
  * what _HistogramObserver.merge_stats (encoding_analyzer.py:231-323) does with tensor
