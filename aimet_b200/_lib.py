@@ -111,6 +111,18 @@ SIGNATURES = {
         _i32,
         [_vp, _lay, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _i64, _vp],
     ),
+    "aimet_b200_minmax_batches": (_i32, [_vp, _i32, _lay, _i32, _i32, _i32, _vp, _vp, _vp, _i64, _vp]),
+    "aimet_b200_histogram_batches": (
+        _i32,
+        [_vp, _i32, _lay, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _vp, _vp, _i64, _vp],
+    ),
+    "aimet_b200_histogram_edges": (_i32, [_vp, _vp, _i32, _i32, _i32, _f64, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "aimet_b200_histogram_merge_ex": (_i32, [_vp] * 7 + [_i32, _i32] + [_vp] * 6),
+    "aimet_b200_sqnr_encodings": (
+        _i32,
+        [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _f64, _f64, _f64, _vp, _vp, _vp, _vp, _vp, _vp,
+         _vp],
+    ),
     "aimet_b200_histogram": (
         _i32,
         [_vp, _lay, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp],
@@ -152,6 +164,11 @@ def check(rc: int) -> None:
     if rc == AB_ERR_UNSUPPORTED:
         raise NotImplementedError(msg)
     raise RuntimeError(f"aimet_b200: {msg} (status {rc})")
+
+
+def ptr_array(tensors) -> ctypes.Array:
+    """A host array of the tensors' device pointers (``const void *const *`` on the C side)."""
+    return (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
 
 
 def ptr(t: torch.Tensor | None) -> int | None:

@@ -18,6 +18,7 @@ namespace {
 // min / max
 // ---------------------------------------------------------------------------
 constexpr int kStatChunkMult = 4;  // read-only passes take longer runs per thread group
+constexpr int kMaxBatch = 32;       // tensors of the same shape that one launch can take
 
 template <typename T> struct MinMax {
     T lo, hi;
@@ -309,6 +310,138 @@ template <int IO> void launch_minmax_finish(const MinMaxFinishArgs &f, cudaStrea
     }
 }
 
+// One statistic over whole contiguous tensors (a per-tensor quantizer's calibration), several
+// tensors of the same size per launch: chunks of 1024 vectors are dealt out round-robin to the
+// CTAs, four loads in flight per thread, one partial pair per CTA.
+struct MinMaxFlatArgs {
+    const void *xs[kMaxBatch];
+    int num_x;
+    int64_t numel;
+    int finite_only;
+    double *partial;  // [gridDim.x][2]
+};
+
+template <int IO> __global__ void __launch_bounds__(kThreads) k_minmax_flat(MinMaxFlatArgs a) {
+    pdl_prologue();
+    using E = typename Elem<IO>::type;
+    using T = typename StatT<IO>::T;
+    constexpr int VEC = 16 / (int)sizeof(E);
+    constexpr int U = 4;
+    const int64_t nvec = a.numel / VEC;
+    const int64_t chunk = (int64_t)kThreads * U;
+    const int64_t chunks_per_x = (nvec + chunk - 1) / chunk;
+    const int64_t total = chunks_per_x * a.num_x;
+    const bool fin = a.finite_only != 0;
+    MinMax<T> m = mm_init<T>();
+    [[maybe_unused]] auto packed = [&]() {
+        if constexpr (PackedMM<E>::ok) {
+            using PM = PackedMM<E>;
+            const typename PM::H2 pinf = PM::dup(INFINITY), ninf = PM::dup(-INFINITY);
+            typename PM::H2 pmin = pinf, pmax = ninf;
+            for (int64_t ch = blockIdx.x; ch < total; ch += gridDim.x) {
+                const int64_t xi = ch / chunks_per_x, lc = ch - xi * chunks_per_x;
+                const Vec16<E> *xp = static_cast<const Vec16<E> *>(a.xs[xi]);
+                const int64_t base = lc * chunk + threadIdx.x;
+                Vec16<E> v[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (base + (int64_t)u * kThreads < nvec) v[u] = xp[base + (int64_t)u * kThreads];
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (base + (int64_t)u * kThreads < nvec) mm_update_packed<E>(pmin, pmax, v[u], fin, pinf, ninf);
+            }
+            mm_merge(m, (T)PM::lo(pmin), (T)PM::lo(pmax));
+            mm_merge(m, (T)PM::hi(pmin), (T)PM::hi(pmax));
+        }
+    };
+    if constexpr (PackedMM<E>::ok) {
+        packed();
+    } else {
+        for (int64_t ch = blockIdx.x; ch < total; ch += gridDim.x) {
+            const int64_t xi = ch / chunks_per_x, lc = ch - xi * chunks_per_x;
+            const Vec16<E> *xp = static_cast<const Vec16<E> *>(a.xs[xi]);
+            const int64_t base = lc * chunk + threadIdx.x;
+            Vec16<E> v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (base + (int64_t)u * kThreads < nvec) v[u] = xp[base + (int64_t)u * kThreads];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (base + (int64_t)u * kThreads < nvec) {
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) mm_update(m, stat_load<T, E>(v[u].v[i]), fin);
+                }
+        }
+    }
+    // elements beyond the last whole vector of each tensor
+    const int tail = (int)(a.numel - nvec * VEC);
+    if (blockIdx.x == 0 && (int)threadIdx.x < tail * a.num_x) {
+        const int xi = threadIdx.x / tail, i = threadIdx.x - xi * tail;
+        mm_update(m, stat_load<T, E>(static_cast<const E *>(a.xs[xi])[nvec * VEC + i]), fin);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        T lo = __shfl_xor_sync(0xffffffffu, m.lo, o);
+        T hi = __shfl_xor_sync(0xffffffffu, m.hi, o);
+        mm_merge(m, lo, hi);
+    }
+    __shared__ double sh[2][kThreads / 32];
+    if ((threadIdx.x & 31) == 0) {
+        sh[0][threadIdx.x >> 5] = (double)m.lo;
+        sh[1][threadIdx.x >> 5] = (double)m.hi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        MinMax<double> r = mm_init<double>();
+        for (int w = 0; w < kThreads / 32; ++w) mm_merge(r, sh[0][w], sh[1][w]);
+        a.partial[2 * blockIdx.x] = r.lo;
+        a.partial[2 * blockIdx.x + 1] = r.hi;
+    }
+}
+
+template <int IO>
+int launch_minmax(const void *x, const Canon &canon, int finite_only, int merge, void *min_out, void *max_out,
+                  void *scratch, int64_t scratch_bytes, cudaStream_t stream);
+
+// a list of tensors of the same layout: min_out / max_out run over all of them
+template <int IO>
+int launch_minmax_list(const void *const *xs, int num_x, const Canon &canon, int finite_only, int merge, void *min_out,
+                       void *max_out, void *scratch, int64_t scratch_bytes, cudaStream_t stream) {
+    bool flat = canon.oci && canon.nparam == 1 && canon.numel >= (1 << 16);
+    for (int i = 0; i < num_x; ++i) flat = flat && aligned16(xs[i]);
+    if (!flat) {
+        for (int i = 0; i < num_x; ++i) {
+            const int rc = launch_minmax<IO>(xs[i], canon, finite_only, merge || i > 0, min_out, max_out, scratch,
+                                             scratch_bytes, stream);
+            if (rc != AB_OK) return rc;
+        }
+        return AB_OK;
+    }
+    const int vec = 16 / dtype_size(IO);
+    for (int i0 = 0; i0 < num_x; i0 += kMaxBatch) {
+        MinMaxFlatArgs a;
+        a.num_x = num_x - i0 < kMaxBatch ? num_x - i0 : kMaxBatch;
+        for (int i = 0; i < a.num_x; ++i) a.xs[i] = xs[i0 + i];
+        a.numel = canon.numel;
+        a.finite_only = finite_only;
+        a.partial = static_cast<double *>(scratch);
+        const int64_t chunks = ((canon.numel / vec + (int64_t)kThreads * 4 - 1) / ((int64_t)kThreads * 4)) * a.num_x;
+        int64_t grid = (int64_t)sm_count() * 8;
+        if (grid > chunks) grid = chunks;
+        if (grid < 1) grid = 1;
+        const int64_t need = grid * 2 * (int64_t)sizeof(double);
+        if (!scratch || scratch_bytes < need)
+            return fail(AB_ERR_SCRATCH, "min/max needs %lld bytes of scratch, got %lld", (long long)need,
+                        (long long)scratch_bytes);
+        launch_pdl(k_minmax_flat<IO>, (unsigned)grid, kThreads, 0, stream, a);
+        AB_LAUNCH_OK();
+        MinMaxFinishArgs f{a.partial, min_out, max_out, 1, 1, 0, grid, grid, (merge || i0 > 0) ? 1 : 0};
+        launch_minmax_finish<IO>(f, stream);
+        AB_LAUNCH_OK();
+    }
+    return AB_OK;
+}
+
 template <int IO>
 int launch_minmax(const void *x, const Canon &canon, int finite_only, int merge, void *min_out, void *max_out,
                   void *scratch, int64_t scratch_bytes, cudaStream_t stream) {
@@ -376,6 +509,7 @@ struct HistArgs {
     int64_t tile_elems;          // elements of one channel handled by one CTA (multiple of 16)
     int num_bins;
     int tiles;                   // CTAs per channel
+    const int *run_if;           // NULL, or a device flag: the launch does nothing when it is zero
 };
 
 // torch.histc's bin of v over [lo, hi] (CPU and CUDA kernels agree):
@@ -396,6 +530,7 @@ template <int IO, bool VECT> __global__ void __launch_bounds__(kThreads) k_histo
     __shared__ unsigned long long sh_edge[2];
     __shared__ float sh_mm[2][kThreads / 32];
 
+    if (a.run_if && *a.run_if == 0) return;
     const int64_t c = blockIdx.y;
     const int tile = blockIdx.x;
     for (int b = threadIdx.x; b < a.num_bins; b += kThreads) sh_hist[b] = 0;
@@ -546,6 +681,8 @@ constexpr int64_t kPrivMinElems = 1 << 20;            // per histogram; below th
 
 struct HistPrivArgs {
     const void *x;
+    const void *xs[kMaxBatch];  // num_x tensors of the same shape (a single contiguous statistic only)
+    int num_x;
     const float *lo, *hi, *below, *above;
     unsigned long long *counts;
     double *mm_partial;  // [C][tiles][2] finite min / max of each CTA's tile, or NULL
@@ -553,6 +690,7 @@ struct HistPrivArgs {
     int64_t chan_elems, tile_elems;
     int num_bins;
     int tiles;
+    const int *run_if;   // NULL, or a device flag: the launch does nothing when it is zero
 };
 
 // all values of the vector inside [plo, phi] (false if any is NaN); the packed minimum and maximum
@@ -610,6 +748,7 @@ __global__ void __launch_bounds__(kPrivThreads, 1) k_hist_private(HistPrivArgs a
     extern __shared__ __align__(16) unsigned int sh_cnt[];  // [num_bins + 1][16]; row num_bins: v == hi
     __shared__ unsigned long long sh_edge[2];
     __shared__ float sh_mm[2][kPrivThreads / 32];
+    if (a.run_if && *a.run_if == 0) return;
     const int64_t c = blockIdx.y;
     for (int i = threadIdx.x; i < (a.num_bins + 1) * kPrivCopies; i += kPrivThreads) sh_cnt[i] = 0;
     if (threadIdx.x < 2) sh_edge[threadIdx.x] = 0;
@@ -718,34 +857,53 @@ __global__ void __launch_bounds__(kPrivThreads, 1) k_hist_private(HistPrivArgs a
     };
 
     // Which vectors this CTA bins.  A single histogram over one contiguous run (the usual case: a
-    // per-tensor statistic) is dealt out in rounds of RING * 1024 vectors, round r going to CTA
-    // r mod gridDim.x: every SM then reads from all over the tensor and sees the same mix of
-    // memory channels as the others (with one contiguous tile per CTA some SMs finished 15 % early).
-    // Otherwise a CTA walks its own tile of the channel.
+    // per-tensor statistic), possibly of several tensors of the same shape, is dealt out in rounds of
+    // RING * 1024 vectors, round r going to CTA r mod gridDim.x: every SM then reads from all over
+    // the tensors and sees the same mix of memory channels as the others (with one contiguous tile
+    // per CTA some SMs finished 15 % early).  Otherwise a CTA walks its own tile of the channel.
     const bool flat = a.C == 1;
     const int64_t e0 = flat ? 0 : (int64_t)blockIdx.x * a.tile_elems;
     int64_t e1 = flat ? a.chan_elems : e0 + a.tile_elems;
     if (e1 > a.chan_elems) e1 = a.chan_elems;
     const int64_t nvec = (e1 - e0) / NV;
+    constexpr int T = kPrivThreads;
+    const int64_t rounds_per_x = (nvec + RING * T - 1) / (RING * T);
+    const int64_t total_rounds = rounds_per_x * (flat ? a.num_x : 1);
     const int64_t G = flat ? gridDim.x : 1, bidx = flat ? blockIdx.x : 0;
-    const Vec16<E> *xp = static_cast<const Vec16<E> *>(a.x);
-    auto src = [&](int64_t v) -> const Vec16<E> * {
-        if (flat) return xp + v;
-        const int64_t e = e0 + v * NV;
-        const int64_t o = e / a.I;
-        return xp + ((o * a.C + c) * a.I + (e - o * a.I)) / NV;
-    };
     // The input reaches the thread through its own ring of RING 16-byte slots in shared memory,
     // filled by cp.async: RING - 1 vectors per thread (80 KB per SM with six slots) are in flight
     // while one is binned, however the compiler orders the rest -- the pass is bound by memory
     // latency otherwise, the warps of the one 1024-thread CTA per SM running in step.  A thread only
     // ever touches its own slots, so no barrier is involved.
-    constexpr int T = kPrivThreads;
     constexpr unsigned kSlotBytes = T * 16u;
     const unsigned ring = (unsigned)__cvta_generic_to_shared(sh_cnt) + (unsigned)(a.num_bins + 1) * (kPrivCopies * 4u) +
                           16u * threadIdx.x;
-    auto fill = [&](unsigned slot_addr, int64_t v) {
-        if (v < nvec) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(slot_addr), "l"(src(v)) : "memory");
+    // a round: the tensor it reads and this thread's first vector in it
+    struct Round {
+        const Vec16<E> *x;
+        int64_t v;
+    };
+    auto round_of = [&](int64_t rl) -> Round {
+        const int64_t r = rl * G + bidx;
+        Round rd;
+        if (r >= total_rounds) {
+            rd.x = nullptr;
+            rd.v = nvec;  // beyond the end: nothing is fetched or binned
+            return rd;
+        }
+        const int64_t xi = r / rounds_per_x, lr = r - xi * rounds_per_x;
+        rd.x = static_cast<const Vec16<E> *>(flat ? a.xs[xi] : a.x);
+        rd.v = lr * (RING * T) + threadIdx.x;
+        return rd;
+    };
+    auto src = [&](const Round &rd, int64_t v) -> const Vec16<E> * {
+        if (flat) return rd.x + v;
+        const int64_t e = e0 + v * NV;
+        const int64_t o = e / a.I;
+        return rd.x + ((o * a.C + c) * a.I + (e - o * a.I)) / NV;
+    };
+    auto fill = [&](unsigned slot_addr, const Round &rd, int64_t v) {
+        if (v < nvec) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(slot_addr), "l"(src(rd, v)) : "memory");
         asm volatile("cp.async.commit_group;" ::: "memory");  // one group per slot, empty or not
     };
     auto take = [&](unsigned slot_addr, int64_t v) {  // the oldest group has landed: bin its vector
@@ -760,19 +918,22 @@ __global__ void __launch_bounds__(kPrivThreads, 1) k_hist_private(HistPrivArgs a
             feed(w, slot_addr);
         }
     };
-    // vector j of the CTA's round rl, for this thread
-    auto vec_of = [&](int64_t rl, int j) -> int64_t { return ((rl * G + bidx) * RING + j) * T + threadIdx.x; };
+    Round cur = round_of(0);
 #pragma unroll
-    for (int j = 0; j < RING - 1; ++j) fill(ring + j * kSlotBytes, vec_of(0, j));
-    for (int64_t rl = 0; vec_of(rl, 0) - threadIdx.x < nvec; ++rl) {
-        const int64_t base = vec_of(rl, 0), next = vec_of(rl + 1, 0);
+    for (int j = 0; j < RING - 1; ++j) fill(ring + j * kSlotBytes, cur, cur.v + j * T);
+    for (int64_t rl = 0; cur.x != nullptr; ++rl) {
+        const Round nxt = round_of(rl + 1);
 #pragma unroll
         for (int j = 0; j < RING; ++j) {
             // the slot emptied one step ago takes the vector RING - 1 steps ahead
             const int rs = (j + RING - 1) % RING;
-            fill(ring + rs * kSlotBytes, j == 0 ? base + (RING - 1) * T : next + (j - 1) * T);
-            take(ring + j * kSlotBytes, base + j * T);
+            if (j == 0)
+                fill(ring + rs * kSlotBytes, cur, cur.v + (RING - 1) * T);
+            else
+                fill(ring + rs * kSlotBytes, nxt, nxt.v + (j - 1) * T);
+            take(ring + j * kSlotBytes, cur.v + j * T);
         }
+        cur = nxt;
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 
@@ -850,12 +1011,14 @@ constexpr int AB_HIST_ACCUMULATE = 1;   // add to counts instead of overwriting 
 constexpr int AB_HIST_MERGE_MINMAX = 2; // fin_min / fin_max: running values over calls
 
 template <int IO>
-int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const float *lo, const float *hi,
-                     const float *below, const float *above, int64_t *counts, void *fin_min, void *fin_max,
-                     int flags, void *scratch, int64_t scratch_bytes, cudaStream_t stream) {
-    if (!canon.oci)
-        return fail(AB_ERR_UNSUPPORTED, "statistics need a layout that reduces to (outer, channel, inner)");
-    if (canon.C > 65535) return fail(AB_ERR_UNSUPPORTED, "at most 65535 histograms per call, got %lld", (long long)canon.C);
+int launch_histogram_one(const void *const *xs, int num_x, const Canon &canon, int32_t num_bins, const float *lo,
+                         const float *hi, const float *below, const float *above, int64_t *counts, void *fin_min,
+                         void *fin_max, int flags, const int *run_if, void *scratch, int64_t scratch_bytes,
+                         cudaStream_t stream, int *consumed) {
+    // bins xs[0] (and, where one launch can take several tensors, up to kMaxBatch of them);
+    // *consumed tells how many
+    *consumed = 1;
+    const void *x = xs[0];
     const int vecw = 16 / dtype_size(IO);
     const bool vect = aligned16(x) && (canon.I % vecw == 0);
     const int v = vect ? vecw : 1;
@@ -907,6 +1070,14 @@ int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const 
             }
             HistPrivArgs h;
             h.x = x;
+            h.num_x = 1;
+            h.xs[0] = x;
+            if (canon.C == 1) {  // one contiguous statistic: several tensors in one launch
+                int n = 1;
+                for (; n < num_x && n < kMaxBatch && aligned16(xs[n]); ++n) h.xs[n] = xs[n];
+                h.num_x = n;
+                *consumed = n;
+            }
             h.lo = lo;
             h.hi = hi;
             h.below = below;
@@ -920,6 +1091,7 @@ int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const 
             h.tile_elems = pt_elems;
             h.num_bins = num_bins;
             h.tiles = (int)ptiles;
+            h.run_if = run_if;
             dim3 grid((unsigned)ptiles, (unsigned)canon.C);
             launch_pdl(kernel, grid, kPrivThreads, smem, stream, h);
             AB_LAUNCH_OK();
@@ -955,6 +1127,7 @@ int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const 
     a.tile_elems = tile_elems;
     a.num_bins = num_bins;
     a.tiles = (int)tiles;
+    a.run_if = run_if;
     dim3 grid((unsigned)tiles, (unsigned)canon.C);
     const size_t smem = sizeof(unsigned int) * (size_t)num_bins;
     if (vect)
@@ -966,6 +1139,28 @@ int launch_histogram(const void *x, const Canon &canon, int32_t num_bins, const 
         MinMaxFinishArgs f{a.mm_partial, fin_min, fin_max, canon.C, 1, 0, tiles, tiles, merge_mm};
         launch_minmax_finish<IO>(f, stream);
         AB_LAUNCH_OK();
+    }
+    return AB_OK;
+}
+
+// all tensors of the list, the counts (and the min / max) running over them
+template <int IO>
+int launch_histogram(const void *const *xs, int num_x, const Canon &canon, int32_t num_bins, const float *lo,
+                     const float *hi, const float *below, const float *above, int64_t *counts, void *fin_min,
+                     void *fin_max, int flags, const int *run_if, void *scratch, int64_t scratch_bytes,
+                     cudaStream_t stream) {
+    if (!canon.oci)
+        return fail(AB_ERR_UNSUPPORTED, "statistics need a layout that reduces to (outer, channel, inner)");
+    if (canon.C > 65535) return fail(AB_ERR_UNSUPPORTED, "at most 65535 histograms per call, got %lld", (long long)canon.C);
+    if (run_if && (fin_min || fin_max))
+        return fail(AB_ERR_INVALID, "a conditional launch cannot also produce min / max");
+    for (int i = 0; i < num_x;) {
+        int used = 1;
+        const int rc = launch_histogram_one<IO>(xs + i, num_x - i, canon, num_bins, lo, hi, below, above, counts, fin_min,
+                                                fin_max, flags, run_if, scratch, scratch_bytes, stream, &used);
+        if (rc != AB_OK) return rc;
+        i += used;
+        flags |= AB_HIST_ACCUMULATE | AB_HIST_MERGE_MINMAX;  // the rest of the list adds to what is there
     }
     return AB_OK;
 }
@@ -988,6 +1183,7 @@ struct MergeArgs {
     float *out_carry;        // [H][n]
     float *out_edges;        // [H][n + 1]
     int num_bins;
+    int *out_moved;          // [H] or NULL: 1 when the updated range differs from the current edges
 };
 
 __device__ __forceinline__ float min_prop(float a, float b) {  // torch.minimum: NaN propagates
@@ -1038,6 +1234,9 @@ __global__ void __launch_bounds__(kThreads) k_hist_merge(MergeArgs a) {
     if (threadIdx.x == 0) {
         a.out_min[h] = umin;
         a.out_max[h] = umax;
+        // counts taken over [edges[0], edges[n]] are the counts over the updated range exactly when
+        // the range still ends where the edges do
+        if (a.out_moved) a.out_moved[h] = (umin == e0 && umax == e_last) ? 0 : 1;
     }
 }
 
@@ -1118,6 +1317,183 @@ __global__ void __launch_bounds__(kSweepThreads) k_argmin(const float *noise, in
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// Small-tensor bookkeeping of a calibration as single launches (it is what a many-GPU calibration
+// spends its time on once the passes over the data are short)
+// ---------------------------------------------------------------------------
+// round to the dtype the statistics are kept in, as a tensor operation on that dtype would
+__device__ __forceinline__ float rnd_dt(float v, int dt) {
+    if (dt == AB_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+    if (dt == AB_F16) return __half2float(__float2half_rn(v));
+    return v;
+}
+
+struct EdgesArgs {
+    const float *mn, *mx;  // [H] observed range (finite min / max), exact in the statistics dtype
+    int num_hist, num_bins, stat_dtype;
+    float growth;          // range limit = edges -/+ span * growth / 2
+    float *edges;          // [H][num_bins + 1]
+    float *lo, *hi, *below, *above, *limit;  // [H], [H], [H], [H], [H][2]; limit may be NULL
+};
+
+// _HistogramObserver._create_bin_edges (encoding_analyzer.py:221-229) and what the histogram pass
+// needs from it: first / last edge, the same two rounded to the tensor dtype for the outlier
+// comparisons, and the growth limit of the range (:244-257).  One thread per edge.
+__global__ void __launch_bounds__(kThreads) k_hist_edges(EdgesArgs a) {
+    pdl_prologue();
+    const int h = blockIdx.y;
+    const float mn = a.mn[h], mx = a.mx[h];
+    const bool same = mn == mx;
+    const float lo = same ? rnd_dt(__fsub_rn(mn, 0.5f), a.stat_dtype) : mn;
+    const float hi = same ? rnd_dt(__fadd_rn(mx, 0.5f), a.stat_dtype) : mx;
+    const float step = __fdiv_rn(__fsub_rn(hi, lo), (float)a.num_bins);
+    const int j = blockIdx.x * kThreads + threadIdx.x;
+    if (j <= a.num_bins) a.edges[(int64_t)h * (a.num_bins + 1) + j] = __fadd_rn(__fmul_rn((float)j, step), lo);
+    if (j == 0) {
+        const float e0 = __fadd_rn(__fmul_rn(0.0f, step), lo);
+        const float e1 = __fadd_rn(__fmul_rn((float)a.num_bins, step), lo);
+        a.lo[h] = e0;
+        a.hi[h] = e1;
+        a.below[h] = rnd_dt(e0, a.stat_dtype);
+        a.above[h] = rnd_dt(e1, a.stat_dtype);
+        if (a.limit) {
+            const float half = __fmul_rn(__fmul_rn(__fsub_rn(e1, e0), a.growth), 0.5f);
+            a.limit[2 * h] = __fsub_rn(e0, half);
+            a.limit[2 * h + 1] = __fadd_rn(e1, half);
+        }
+    }
+}
+
+// The (delta, offset) test candidates of the SQNR / TF-enhanced analyzers, formed on the device with
+// the reference's operations in the reference's order (_pick_test_candidates,
+// _pick_test_candidates_asymmetric / _symmetric, _clamp_delta_offset_values,
+// encoding_analyzer.py:728-820).
+struct CandArgs {
+    const float *stat_min, *stat_max;  // [H]
+    const float *base_offsets;         // [n_base] asymmetric offsets before the observed one is appended
+    int n_base, n_delta, symmetric, stat_dtype;
+    float num_steps, min_scale, widen;  // widen = (float)(min_scale * num_steps)
+    float sym_offset;
+};
+
+__device__ __forceinline__ void sqnr_candidate(const CandArgs &c, int h, int cand, float &delta, float &offset) {
+    const int dt = c.stat_dtype;
+    float mn = fminf(c.stat_min[h], 0.0f), mx = fmaxf(c.stat_max[h], 0.0f);
+    mx = fmaxf(mx, rnd_dt(__fadd_rn(mn, c.widen), dt));
+    if (c.symmetric) {
+        const float max_delta = __fdiv_rn(rnd_dt(__fmul_rn(2.0f, fmaxf(mx, -mn)), dt), c.num_steps);
+        const float d = __fdiv_rn(__fmul_rn(max_delta, (float)(cand + 1)), (float)(c.n_delta - 1));
+        delta = fmaxf(d, c.min_scale);
+        offset = c.sym_offset;
+        return;
+    }
+    const int n_off = c.n_base + 1;
+    const int k = cand / n_off, o = cand - k * n_off;
+    const float max_delta = __fdiv_rn(rnd_dt(__fsub_rn(mx, mn), dt), c.num_steps);
+    const float obs_offset = rintf(__fdiv_rn(mn, max_delta));
+    const float obs_min = __fmul_rn(max_delta, obs_offset);
+    const float obs_max = __fadd_rn(obs_min, __fmul_rn(max_delta, c.num_steps));
+    const float dk = __fdiv_rn(__fmul_rn(max_delta, (float)(k + 1)), (float)(c.n_delta - 1));
+    const float off = o < c.n_base ? c.base_offsets[o] : obs_offset;
+    float tmin = __fmul_rn(dk, off);
+    float tmax = __fadd_rn(tmin, __fmul_rn(dk, c.num_steps));
+    tmin = fmaxf(obs_min, tmin);
+    tmax = fminf(obs_max, tmax);
+    delta = fmaxf(__fdiv_rn(__fsub_rn(tmax, tmin), c.num_steps), c.min_scale);
+    offset = rintf(__fdiv_rn(tmin, delta));
+}
+
+struct SweepGenArgs {
+    CandArgs cand;
+    const float *hist;   // [H][num_bins]
+    const float *edges;  // [H][num_bins + 1]
+    int num_bins, num_cand;
+    float gamma;
+    int use_gamma;
+    float *noise;              // [H][num_cand]
+    float *deltas, *offsets;   // [H][num_cand] or NULL
+    float *enc_min, *enc_max;  // [H]
+    int *best;                 // [H]
+};
+
+__global__ void __launch_bounds__(kSweepThreads) k_sqnr_sweep_gen(SweepGenArgs a) {
+    pdl_prologue();
+    const int cand = blockIdx.x, h = blockIdx.y;
+    float delta, offset;
+    sqnr_candidate(a.cand, h, cand, delta, offset);
+    if (threadIdx.x == 0 && a.deltas) {
+        a.deltas[(int64_t)h * a.num_cand + cand] = delta;
+        a.offsets[(int64_t)h * a.num_cand + cand] = offset;
+    }
+    const float *edges = a.edges + (int64_t)h * (a.num_bins + 1);
+    const float width = __fsub_rn(edges[1], edges[0]);
+    const float mid0 = __fadd_rn(edges[0], __fdiv_rn(width, 2.0f));
+    const float *hist = a.hist + (int64_t)h * a.num_bins;
+    const float num_steps = a.cand.num_steps;
+    double acc = 0.0;
+    for (int b = threadIdx.x; b < a.num_bins; b += kSweepThreads) {
+        const float mid = __fadd_rn(mid0, __fmul_rn(width, (float)b));
+        float q = rintf(__fsub_rn(__fdiv_rn(mid, delta), offset));
+        const bool clipped = (q < 0.0f) || (q > num_steps);
+        q = clamp_nan(q, 0.0f, num_steps);
+        q = __fmul_rn(__fadd_rn(q, offset), delta);
+        float err = fabsf(__fsub_rn(q, mid));
+        err = __fmul_rn(__fmul_rn(err, err), hist[b]);
+        if (a.use_gamma && clipped) err = __fmul_rn(err, a.gamma);
+        acc += (double)err;
+    }
+    acc = warp_sum(acc);
+    __shared__ double sh[kSweepThreads / 32];
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0;
+        for (int w = 0; w < kSweepThreads / 32; ++w) t += sh[w];
+        a.noise[(int64_t)h * a.num_cand + cand] = (float)t;
+    }
+}
+
+// arg-min over the candidates of one histogram (lowest index among equal minima) and the encoding
+// range of the winner: min = offset * delta, max = min + num_steps * delta (:718-726)
+__global__ void __launch_bounds__(kSweepThreads) k_sqnr_pick(SweepGenArgs a) {
+    pdl_prologue();
+    const int h = blockIdx.x;
+    const float *n = a.noise + (int64_t)h * a.num_cand;
+    float bv = INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < a.num_cand; i += kSweepThreads) {
+        const float v = n[i];
+        if (v < bv || (v == bv && i < bi)) {
+            bv = v;
+            bi = i;
+        }
+    }
+    __shared__ float sv[kSweepThreads];
+    __shared__ int si[kSweepThreads];
+    sv[threadIdx.x] = bv;
+    si[threadIdx.x] = bi;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int t = 1; t < kSweepThreads; ++t) {
+            const float v = sv[t];
+            const int i = si[t];
+            if (i == 0x7fffffff) continue;
+            if (bi == 0x7fffffff || v < bv || (v == bv && i < bi)) {
+                bv = v;
+                bi = i;
+            }
+        }
+        if (bi == 0x7fffffff) bi = 0;
+        float delta, offset;
+        sqnr_candidate(a.cand, h, bi, delta, offset);
+        const float emin = __fmul_rn(offset, delta);
+        a.best[h] = bi;
+        a.enc_min[h] = emin;
+        a.enc_max[h] = __fadd_rn(emin, __fmul_rn(a.cand.num_steps, delta));
+    }
+}
+
 }  // namespace
 }  // namespace ab
 
@@ -1154,6 +1530,27 @@ static int minmax_entry(const void *x, const ab_layout *layout, int io_dtype, in
     return ab::fail(AB_ERR_INVALID, "unknown io_dtype %d", io_dtype);
 }
 
+extern "C" int aimet_b200_minmax_batches(const void *const *xs, int32_t num_tensors, const ab_layout *layout,
+                                         int io_dtype, int finite_only, int merge, void *min_io, void *max_io,
+                                         void *scratch, int64_t scratch_bytes, void *stream) {
+    ab::Canon canon;
+    int rc = ab::canonicalize(layout, &canon);
+    if (rc != AB_OK) return rc;
+    if (canon.numel == 0) return ab::fail(AB_ERR_INVALID, "min/max of an empty tensor is undefined");
+    if (num_tensors <= 0 || !xs || !min_io || !max_io)
+        return ab::fail(AB_ERR_INVALID, "need at least one tensor and both outputs");
+    for (int i = 0; i < num_tensors; ++i)
+        if (!xs[i]) return ab::fail(AB_ERR_INVALID, "tensor %d of the list is NULL", i);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (io_dtype) {
+        case AB_F32: return ab::launch_minmax_list<AB_F32>(xs, num_tensors, canon, finite_only, merge, min_io, max_io, scratch, scratch_bytes, st);
+        case AB_F16: return ab::launch_minmax_list<AB_F16>(xs, num_tensors, canon, finite_only, merge, min_io, max_io, scratch, scratch_bytes, st);
+        case AB_BF16: return ab::launch_minmax_list<AB_BF16>(xs, num_tensors, canon, finite_only, merge, min_io, max_io, scratch, scratch_bytes, st);
+        case AB_F64: return ab::launch_minmax_list<AB_F64>(xs, num_tensors, canon, finite_only, merge, min_io, max_io, scratch, scratch_bytes, st);
+    }
+    return ab::fail(AB_ERR_INVALID, "unknown io_dtype %d", io_dtype);
+}
+
 extern "C" int aimet_b200_minmax(const void *x, const ab_layout *layout, int io_dtype, int finite_only,
                                  void *min_out, void *max_out, void *scratch, int64_t scratch_bytes,
                                  void *stream) {
@@ -1166,29 +1563,42 @@ extern "C" int aimet_b200_minmax_running(const void *x, const ab_layout *layout,
     return minmax_entry(x, layout, io_dtype, finite_only, 1, min_io, max_io, scratch, scratch_bytes, stream);
 }
 
-extern "C" int aimet_b200_histogram_ex(const void *x, const ab_layout *layout, int io_dtype, int32_t num_bins,
-                                       const float *lo, const float *hi, const float *below,
-                                       const float *above, int64_t *counts, void *fin_min, void *fin_max,
-                                       int32_t flags, void *scratch, int64_t scratch_bytes, void *stream) {
+extern "C" int aimet_b200_histogram_batches(const void *const *xs, int32_t num_tensors, const ab_layout *layout,
+                                            int io_dtype, int32_t num_bins, const float *lo, const float *hi,
+                                            const float *below, const float *above, int64_t *counts, void *fin_min,
+                                            void *fin_max, int32_t flags, const int32_t *run_if_nonzero, void *scratch,
+                                            int64_t scratch_bytes, void *stream) {
     ab::Canon canon;
     int rc = ab::canonicalize(layout, &canon);
     if (rc != AB_OK) return rc;
     if (num_bins <= 0 || num_bins > 8192)
         return ab::fail(AB_ERR_UNSUPPORTED, "num_bins must be in [1, 8192], got %d", num_bins);
     if (canon.numel == 0) return ab::fail(AB_ERR_INVALID, "histogram of an empty tensor is undefined");
-    if (!x || !lo || !hi || !below || !above || !counts)
-        return ab::fail(AB_ERR_INVALID, "x, lo, hi, below, above and counts must not be NULL");
+    if (num_tensors <= 0 || !xs) return ab::fail(AB_ERR_INVALID, "need at least one tensor");
+    for (int i = 0; i < num_tensors; ++i)
+        if (!xs[i]) return ab::fail(AB_ERR_INVALID, "tensor %d of the list is NULL", i);
+    if (!lo || !hi || !below || !above || !counts)
+        return ab::fail(AB_ERR_INVALID, "lo, hi, below, above and counts must not be NULL");
     if (flags & ~3) return ab::fail(AB_ERR_INVALID, "unknown flags %d", (int)flags);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (io_dtype) {
         case AB_F32:
-            return ab::launch_histogram<AB_F32>(x, canon, num_bins, lo, hi, below, above, counts, fin_min, fin_max, flags, scratch, scratch_bytes, st);
+            return ab::launch_histogram<AB_F32>(xs, num_tensors, canon, num_bins, lo, hi, below, above, counts, fin_min, fin_max, flags, run_if_nonzero, scratch, scratch_bytes, st);
         case AB_F16:
-            return ab::launch_histogram<AB_F16>(x, canon, num_bins, lo, hi, below, above, counts, fin_min, fin_max, flags, scratch, scratch_bytes, st);
+            return ab::launch_histogram<AB_F16>(xs, num_tensors, canon, num_bins, lo, hi, below, above, counts, fin_min, fin_max, flags, run_if_nonzero, scratch, scratch_bytes, st);
         case AB_BF16:
-            return ab::launch_histogram<AB_BF16>(x, canon, num_bins, lo, hi, below, above, counts, fin_min, fin_max, flags, scratch, scratch_bytes, st);
+            return ab::launch_histogram<AB_BF16>(xs, num_tensors, canon, num_bins, lo, hi, below, above, counts, fin_min, fin_max, flags, run_if_nonzero, scratch, scratch_bytes, st);
     }
     return ab::fail(AB_ERR_UNSUPPORTED, "histogram supports float32, float16 and bfloat16 inputs");
+}
+
+extern "C" int aimet_b200_histogram_ex(const void *x, const ab_layout *layout, int io_dtype, int32_t num_bins,
+                                       const float *lo, const float *hi, const float *below,
+                                       const float *above, int64_t *counts, void *fin_min, void *fin_max,
+                                       int32_t flags, void *scratch, int64_t scratch_bytes, void *stream) {
+    if (!x) return ab::fail(AB_ERR_INVALID, "x must not be NULL");
+    return aimet_b200_histogram_batches(&x, 1, layout, io_dtype, num_bins, lo, hi, below, above, counts, fin_min,
+                                        fin_max, flags, nullptr, scratch, scratch_bytes, stream);
 }
 
 extern "C" int aimet_b200_histogram(const void *x, const ab_layout *layout, int io_dtype, int32_t num_bins,
@@ -1230,19 +1640,89 @@ extern "C" int aimet_b200_sqnr_sweep(const float *hist, const float *edge0, cons
     return AB_OK;
 }
 
-extern "C" int aimet_b200_histogram_merge(const float *new_min, const float *new_max, const float *cur_min,
-                                          const float *cur_max, const float *cur_edges, const float *cur_hist,
-                                          const float *range_limit, int32_t num_hist, int32_t num_bins, float *out_min,
-                                          float *out_max, float *out_carry, float *out_edges, void *stream) {
+extern "C" int aimet_b200_histogram_merge_ex(const float *new_min, const float *new_max, const float *cur_min,
+                                             const float *cur_max, const float *cur_edges, const float *cur_hist,
+                                             const float *range_limit, int32_t num_hist, int32_t num_bins,
+                                             float *out_min, float *out_max, float *out_carry, float *out_edges,
+                                             int32_t *out_moved, void *stream) {
     if (num_hist <= 0 || num_bins <= 0) return ab::fail(AB_ERR_INVALID, "num_hist and num_bins must be positive");
     if (num_bins > 8192) return ab::fail(AB_ERR_UNSUPPORTED, "at most 8192 bins, got %d", (int)num_bins);
     if (!new_min || !new_max || !cur_min || !cur_max || !cur_edges || !cur_hist || !range_limit || !out_min || !out_max ||
         !out_carry || !out_edges)
         return ab::fail(AB_ERR_INVALID, "NULL pointer argument");
     ab::MergeArgs a{new_min, new_max, cur_min, cur_max, cur_edges, cur_hist, range_limit,
-                    out_min, out_max, out_carry, out_edges, num_bins};
+                    out_min, out_max, out_carry, out_edges, num_bins, out_moved};
     ab::launch_pdl(ab::k_hist_merge, (unsigned)num_hist, ab::kThreads, sizeof(float) * (size_t)num_bins,
                    static_cast<cudaStream_t>(stream), a);
     AB_LAUNCH_OK();
     return AB_OK;
+}
+
+extern "C" int aimet_b200_histogram_edges(const float *min, const float *max, int32_t num_hist, int32_t num_bins,
+                                          int stat_dtype, double growth_limit, float *edges, float *lo, float *hi,
+                                          float *below, float *above, float *range_limit, void *stream) {
+    if (num_hist <= 0 || num_bins <= 0) return ab::fail(AB_ERR_INVALID, "num_hist and num_bins must be positive");
+    if (num_hist > 65535) return ab::fail(AB_ERR_UNSUPPORTED, "at most 65535 histograms per call");
+    if (!min || !max || !edges || !lo || !hi || !below || !above) return ab::fail(AB_ERR_INVALID, "NULL pointer argument");
+    ab::EdgesArgs a{min, max, num_hist, num_bins, stat_dtype, (float)growth_limit, edges, lo, hi, below, above, range_limit};
+    dim3 grid((unsigned)((num_bins + 1 + ab::kThreads - 1) / ab::kThreads), (unsigned)num_hist);
+    ab::launch_pdl(ab::k_hist_edges, grid, ab::kThreads, 0, static_cast<cudaStream_t>(stream), a);
+    AB_LAUNCH_OK();
+    return AB_OK;
+}
+
+extern "C" int aimet_b200_sqnr_encodings(const float *hist, const float *edges, const float *stat_min,
+                                         const float *stat_max, const float *base_offsets, int32_t num_base_offsets,
+                                         int32_t num_deltas, int32_t symmetric, int stat_dtype, int32_t num_hist,
+                                         int32_t num_bins, double num_steps, double gamma, double min_scale,
+                                         float *noise_out, float *deltas_out, float *offsets_out, float *enc_min_out,
+                                         float *enc_max_out, int32_t *best_out, void *stream) {
+    if (num_hist <= 0 || num_bins <= 0 || num_deltas < 2)
+        return ab::fail(AB_ERR_INVALID, "num_hist and num_bins must be positive, num_deltas at least 2");
+    if (num_hist > 65535) return ab::fail(AB_ERR_UNSUPPORTED, "at most 65535 histograms per call");
+    if (!symmetric && (num_base_offsets <= 0 || !base_offsets))
+        return ab::fail(AB_ERR_INVALID, "asymmetric candidates need the offset grid");
+    if (!hist || !edges || !stat_min || !stat_max || !noise_out || !enc_min_out || !enc_max_out || !best_out)
+        return ab::fail(AB_ERR_INVALID, "NULL pointer argument");
+    if ((deltas_out == nullptr) != (offsets_out == nullptr))
+        return ab::fail(AB_ERR_INVALID, "deltas_out and offsets_out go together");
+    ab::SweepGenArgs a;
+    a.cand.stat_min = stat_min;
+    a.cand.stat_max = stat_max;
+    a.cand.base_offsets = base_offsets;
+    a.cand.n_base = symmetric ? 0 : num_base_offsets;
+    a.cand.n_delta = num_deltas;
+    a.cand.symmetric = symmetric;
+    a.cand.stat_dtype = stat_dtype;
+    a.cand.num_steps = (float)num_steps;
+    a.cand.min_scale = (float)min_scale;
+    a.cand.widen = (float)(min_scale * num_steps);
+    a.cand.sym_offset = (float)floor(-num_steps / 2.0);
+    a.hist = hist;
+    a.edges = edges;
+    a.num_bins = num_bins;
+    a.num_cand = symmetric ? num_deltas : num_deltas * (num_base_offsets + 1);
+    a.gamma = (float)gamma;
+    a.use_gamma = gamma != 1.0;
+    a.noise = noise_out;
+    a.deltas = deltas_out;
+    a.offsets = offsets_out;
+    a.enc_min = enc_min_out;
+    a.enc_max = enc_max_out;
+    a.best = best_out;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    dim3 grid((unsigned)a.num_cand, (unsigned)num_hist);
+    ab::launch_pdl(ab::k_sqnr_sweep_gen, grid, ab::kSweepThreads, 0, st, a);
+    AB_LAUNCH_OK();
+    ab::launch_pdl(ab::k_sqnr_pick, (unsigned)num_hist, ab::kSweepThreads, 0, st, a);
+    AB_LAUNCH_OK();
+    return AB_OK;
+}
+
+extern "C" int aimet_b200_histogram_merge(const float *new_min, const float *new_max, const float *cur_min,
+                                          const float *cur_max, const float *cur_edges, const float *cur_hist,
+                                          const float *range_limit, int32_t num_hist, int32_t num_bins, float *out_min,
+                                          float *out_max, float *out_carry, float *out_edges, void *stream) {
+    return aimet_b200_histogram_merge_ex(new_min, new_max, cur_min, cur_max, cur_edges, cur_hist, range_limit, num_hist,
+                                         num_bins, out_min, out_max, out_carry, out_edges, nullptr, stream);
 }

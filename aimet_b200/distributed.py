@@ -156,7 +156,7 @@ def calibrate_minmax(analyzer, batches: Iterable[torch.Tensor], group=None, devi
 
 
 def calibrate_histogram(analyzer, batches: Sequence[torch.Tensor], group=None, *,
-                        minmax_fn: Callable = _default_minmax, counts_fn: Callable = _default_counts, device=None,
+                        minmax_fn: Optional[Callable] = None, counts_fn: Optional[Callable] = None, device=None,
                         timings: Optional[dict] = None):
     """Two-phase histogram calibration of this rank's batches for a histogram-based analyzer
     (percentile / SQNR / TF-enhanced).
@@ -164,9 +164,12 @@ def calibrate_histogram(analyzer, batches: Sequence[torch.Tensor], group=None, *
     Phase 1: finite min / max of every local batch, combined locally and then over ranks.
     Phase 2: every batch is binned over the common range (integer counts, values outside the range
     or infinite go to the edge bins); counts are summed locally and then over ranks.
-    The analyzer's observer is left holding the combined statistics.  ``minmax_fn`` / ``counts_fn``
-    compute the per-batch statistics (default: the CUDA kernels); they exist so that the exchange
-    logic can be exercised with CPU tensors.  A rank without a batch contributes an empty range and
+    The analyzer's observer is left holding the combined statistics.  By default every phase is a
+    handful of launches however many batches there are (the kernels take lists of tensors, the
+    bin edges come from one launch): with the passes over the data cut eight ways, per-batch
+    launches and small tensor operations are what a calibration would otherwise spend its time
+    on.  ``minmax_fn`` / ``counts_fn`` replace the per-batch statistics; they exist so that the
+    exchange logic can be exercised with CPU tensors.  A rank without a batch contributes an empty range and
     zero counts (on ``device``); if no rank has a batch every rank raises together.
     ``timings``: a dict that receives CUDA events at the phase boundaries (``t0`` .. ``t4``: start,
     local ranges done, ranges exchanged, local counts done, counts exchanged).
@@ -188,9 +191,26 @@ def calibrate_histogram(analyzer, batches: Sequence[torch.Tensor], group=None, *
             timings[name] = ev
 
     mark("t0")
-    # per-batch statistics are kept and combined once (one stack + reduce instead of a small
-    # kernel per batch)
-    if batches:
+    fast = minmax_fn is None and counts_fn is None and dev.type == "cuda" and all(
+        x.dtype != torch.float64 for x in batches)
+    minmax_fn, counts_fn = minmax_fn or _default_minmax, counts_fn or _default_counts
+    lays = None
+    if batches and fast:
+        from .encoding_analyzer import _check_input, _minmax_batches, _same_layout, _StatLayout
+
+        lays = [_StatLayout(_check_input(x), tuple(shape), block) for x in batches]
+        if not _same_layout(lays):
+            lays = None
+    if lays is not None:
+        try:
+            mn, mx = _minmax_batches(lays, True)
+        except NotImplementedError:
+            for lay in lays:
+                lay.densify()
+            mn, mx = _minmax_batches(lays, True)
+    elif batches:
+        # per-batch statistics are kept and combined once (one stack + reduce instead of a small
+        # kernel per batch)
         mins, maxs = zip(*(minmax_fn(x, shape, block, True) for x in batches))
         mn = torch.stack(mins).amin(dim=0) if len(mins) > 1 else mins[0]
         mx = torch.stack(maxs).amax(dim=0) if len(maxs) > 1 else maxs[0]
@@ -201,13 +221,20 @@ def calibrate_histogram(analyzer, batches: Sequence[torch.Tensor], group=None, *
     if world > 1:
         mn, mx = allreduce_minmax(mn, mx, group)
     mark("t2")
-    edges = obs._create_bin_edges(mn, mx)  # pylint: disable=protected-access
-    lo, hi = edges[:, 0].contiguous(), edges[:, -1].contiguous()
-    if batches:
-        per_batch = [counts_fn(x, shape, block, nbins, lo, hi) for x in batches]
-        counts = torch.stack(per_batch).sum(dim=0) if len(per_batch) > 1 else per_batch[0]
+    limit = None
+    if lays is not None:
+        from .encoding_analyzer import _histogram_batches, _range_edges
+
+        edges, lo, hi, below, above, limit = _range_edges(mn, mx, nbins, obs.growth_limit)
+        counts = _histogram_batches(lays, nbins, lo, hi, below, above)
     else:
-        counts = torch.zeros((obs.num_histograms, nbins), dtype=torch.int64, device=dev)
+        edges = obs._create_bin_edges(mn, mx)  # pylint: disable=protected-access
+        lo, hi = edges[:, 0].contiguous(), edges[:, -1].contiguous()
+        if batches:
+            per_batch = [counts_fn(x, shape, block, nbins, lo, hi) for x in batches]
+            counts = torch.stack(per_batch).sum(dim=0) if len(per_batch) > 1 else per_batch[0]
+        else:
+            counts = torch.zeros((obs.num_histograms, nbins), dtype=torch.int64, device=dev)
     mark("t3")
     counts = allreduce_counts(counts, group)
     mark("t4")
@@ -216,10 +243,11 @@ def calibrate_histogram(analyzer, batches: Sequence[torch.Tensor], group=None, *
         # the same counts and raises the same way)
         raise PeerFailure("no rank observed a calibration batch")
     obs._state = _HistogramList(counts.to(torch.float32), edges, mn, mx)  # pylint: disable=protected-access
-    e0, e1 = edges[:, 0], edges[:, -1]
-    span = e1 - e0
-    obs._histogram_range_limit = torch.stack(  # pylint: disable=protected-access
-        (e0 - span * obs.growth_limit / 2, e1 + span * obs.growth_limit / 2), dim=1)
+    if limit is None:
+        e0, e1 = edges[:, 0], edges[:, -1]
+        span = e1 - e0
+        limit = torch.stack((e0 - span * obs.growth_limit / 2, e1 + span * obs.growth_limit / 2), dim=1)
+    obs._histogram_range_limit = limit  # pylint: disable=protected-access
     return obs.get_stats()
 
 

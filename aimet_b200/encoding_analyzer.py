@@ -112,14 +112,25 @@ class _HistogramList(_SequenceABC):
 
 
 class _LazyHistogramList(_HistogramList):
-    """Statistics of one batch whose histogram is computed when it is first read.  Merging into an
-    accumulated histogram only needs the batch's range (the counts are taken again over the merged
-    range), so a caller that does not look at the per-batch histogram saves a pass over the tensor.
-    The observed tensor must not be modified before the histogram is read."""
+    """Statistics of one batch whose histogram (and bin edges) are computed when they are first
+    read.  Merging into an accumulated histogram only needs the batch's range (the counts are taken
+    again over the merged range), so a caller that does not look at the per-batch histogram saves a
+    pass over the tensor.  The observed tensor must not be modified before the histogram is read."""
 
     def __init__(self, compute, bin_edges, min, max):  # pylint: disable=redefined-builtin,super-init-not-called
         self._compute, self._hist = compute, None
-        self.bin_edges, self.min, self.max = bin_edges, min, max
+        self._edges = bin_edges  # a tensor, or a callable that makes it
+        self.min, self.max = min, max
+
+    @property
+    def bin_edges(self):
+        if callable(self._edges):
+            self._edges = self._edges()
+        return self._edges
+
+    @bin_edges.setter
+    def bin_edges(self, value):
+        self._edges = value
 
     @property
     def histogram(self):
@@ -132,7 +143,7 @@ class _LazyHistogramList(_HistogramList):
         self._hist, self._compute = value, None
 
     def __len__(self):
-        return self.bin_edges.shape[0]
+        return self.min.shape[0]
 
 
 # --------------------------------------------------------------------------------------------
@@ -262,7 +273,86 @@ def _histogram(lay: _StatLayout, num_bins: int, lo: torch.Tensor, hi: torch.Tens
     return _histogram_counts(lay, num_bins, lo, hi).to(torch.float32)
 
 
-def _merge_histograms(new: "_HistogramList", cur: "_HistogramList", limit: torch.Tensor, num_bins: int):
+def _same_layout(lays) -> bool:
+    first = lays[0]
+    return all(l.size == first.size and l.block == first.block and l.io == first.io and l.x.device == first.x.device
+               for l in lays[1:])
+
+
+def _minmax_batches(lays, finite_only: bool):
+    """Min / max over a list of observed tensors of one layout, one statistic pair for the whole list;
+    tensors of a single contiguous statistic share launches."""
+    if not _same_layout(lays):
+        raise RuntimeError("the tensors of one calibration phase must share shape, dtype and device")
+    lay = lays[0]
+    x = lay.x
+    mn = torch.empty(lay.count, dtype=x.dtype, device=x.device)
+    mx = torch.empty(lay.count, dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        nbytes = lib.aimet_b200_stats_scratch_bytes(lay.layout, lay.io)
+        _lib.check(nbytes)
+        scratch = _lib.scratch.get(x.device, max(nbytes, 1))
+        rc = lib.aimet_b200_minmax_batches(_lib.ptr_array([l.x for l in lays]), len(lays), lay.layout, lay.io,
+                                           int(finite_only), 0, mn.data_ptr(), mx.data_ptr(), _lib.ptr(scratch),
+                                           scratch.numel(), _lib.stream_ptr(x.device))
+    _lib.check(rc)
+    return mn, mx
+
+
+def _stat_dtype_code(dtype) -> int:
+    return _lib.DTYPE_CODE[dtype] if dtype in (torch.float16, torch.bfloat16) else _lib.AB_F32
+
+
+def _range_edges(mn: torch.Tensor, mx: torch.Tensor, num_bins: int, growth_limit: float, want_limit: bool = True):
+    """Everything a histogram pass over [mn, mx] needs, in one launch: bin edges [H, bins + 1] (a
+    degenerate range widened by 0.5 on each side), first / last edge, the two rounded to the tensor
+    dtype (for the outlier comparisons) and the growth limit of the range."""
+    dev = mn.device
+    h = mn.numel()
+    f32 = lambda t: t.detach().reshape(-1).to(torch.float32).contiguous()  # noqa: E731
+    edges = torch.empty((h, num_bins + 1), dtype=torch.float32, device=dev)
+    lo, hi, below, above = (torch.empty(h, dtype=torch.float32, device=dev) for _ in range(4))
+    limit = torch.empty((h, 2), dtype=torch.float32, device=dev) if want_limit else None
+    a, b = f32(mn), f32(mx)
+    with torch.cuda.device(dev):
+        rc = lib.aimet_b200_histogram_edges(a.data_ptr(), b.data_ptr(), h, num_bins, _stat_dtype_code(mn.dtype),
+                                            float(growth_limit), edges.data_ptr(), lo.data_ptr(), hi.data_ptr(),
+                                            below.data_ptr(), above.data_ptr(), _lib.ptr(limit), _lib.stream_ptr(dev))
+    _lib.check(rc)
+    return edges, lo, hi, below, above, limit
+
+
+def _histogram_batches(lays, num_bins: int, lo, hi, below, above, counts=None, want_minmax=False, run_if=None):
+    """int64 counts [count, num_bins] of a list of tensors of one layout over [lo, hi] (added to
+    ``counts`` when given), optionally with the finite min / max of the list from the same pass;
+    ``run_if``: a device int32 flag -- the pass is skipped on the device when it is zero."""
+    if not _same_layout(lays):
+        raise RuntimeError("the tensors of one calibration phase must share shape, dtype and device")
+    lay = lays[0]
+    x = lay.x
+    flags = 0
+    if counts is None:
+        counts = torch.empty((lay.count, num_bins), dtype=torch.int64, device=x.device)
+    else:
+        flags |= 1
+    mn = mx = None
+    if want_minmax:
+        mn = torch.empty(lay.count, dtype=x.dtype, device=x.device)
+        mx = torch.empty(lay.count, dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        nbytes = lib.aimet_b200_stats_scratch_bytes(lay.layout, lay.io)
+        _lib.check(nbytes)
+        scratch = _lib.scratch.get(x.device, max(nbytes, 1))
+        rc = lib.aimet_b200_histogram_batches(_lib.ptr_array([l.x for l in lays]), len(lays), lay.layout, lay.io, num_bins,
+                                              lo.data_ptr(), hi.data_ptr(), below.data_ptr(), above.data_ptr(),
+                                              counts.data_ptr(), _lib.ptr(mn), _lib.ptr(mx), flags, _lib.ptr(run_if),
+                                              _lib.ptr(scratch), scratch.numel(), _lib.stream_ptr(x.device))
+    _lib.check(rc)
+    return (counts, mn, mx) if want_minmax else counts
+
+
+def _merge_histograms(new: "_HistogramList", cur: "_HistogramList", limit: torch.Tensor, num_bins: int,
+                      want_moved: bool = False):
     """(updated min, updated max, carried counts, updated edges) of ``cur`` widened to cover ``new``."""
     dev = cur.histogram.device
     f32 = lambda t: t.detach().to(torch.float32).contiguous()  # noqa: E731  (exact for 16-bit statistics)
@@ -272,11 +362,13 @@ def _merge_histograms(new: "_HistogramList", cur: "_HistogramList", limit: torch
     carry = torch.empty((h, num_bins), dtype=torch.float32, device=dev)
     edges = torch.empty((h, num_bins + 1), dtype=torch.float32, device=dev)
     args = [f32(new.min), f32(new.max), f32(cur.min), f32(cur.max), f32(cur.bin_edges), f32(cur.histogram), f32(limit)]
+    moved = torch.empty(h, dtype=torch.int32, device=dev) if want_moved else None
     with torch.cuda.device(dev):
-        rc = lib.aimet_b200_histogram_merge(*[t.data_ptr() for t in args], h, num_bins, out_min.data_ptr(),
-                                            out_max.data_ptr(), carry.data_ptr(), edges.data_ptr(), _lib.stream_ptr(dev))
+        rc = lib.aimet_b200_histogram_merge_ex(*[t.data_ptr() for t in args], h, num_bins, out_min.data_ptr(),
+                                               out_max.data_ptr(), carry.data_ptr(), edges.data_ptr(), _lib.ptr(moved),
+                                               _lib.stream_ptr(dev))
     _lib.check(rc)
-    return out_min, out_max, carry, edges
+    return (out_min, out_max, carry, edges, moved) if want_moved else (out_min, out_max, carry, edges)
 
 
 # --------------------------------------------------------------------------------------------
@@ -385,6 +477,52 @@ class _HistogramObserver(_Observer):
         hist += carry
         self._state = _HistogramList(hist, edges, umin, umax)
 
+    @torch.no_grad()
+    def observe(self, input_tensor: torch.Tensor):
+        """``collect_stats`` + ``merge_stats`` of one batch with a single pass over the tensor where
+        that is possible (what ``update_stats`` of the histogram analyzers runs).
+
+        Once statistics exist, one kernel bins the batch against the *current* range and finds the
+        batch's own finite min / max on the way.  The merge kernel then decides, on the device,
+        whether the range had to move (growth, or a first range that the batch exceeds); only then
+        are the counts wrong, and a second binning pass over the moved range runs -- launched
+        always, skipped on the device when the flag says so, so the host never waits.  The batch's
+        own histogram (which the reference computes on every update and most callers never read)
+        is produced only when someone asks for it."""
+        x = _check_input(input_tensor)
+        if x.numel() == 0:
+            raise RuntimeError("cannot collect statistics of an empty tensor")
+        if self._state is None:
+            new = self.collect_stats(x)
+            self.merge_stats(new, x)
+            return new
+        n = self.num_bins
+        cur = self._state
+        lay = _StatLayout(x, self.shape, self.block_size)
+        if lay.x.dtype == torch.float64:
+            new = self.collect_stats(x)
+            self.merge_stats(new, x)
+            return new
+        e0, e1 = cur.bin_edges[:, 0].contiguous(), cur.bin_edges[:, -1].contiguous()
+        below, above = e0.to(lay.x.dtype).to(torch.float32), e1.to(lay.x.dtype).to(torch.float32)
+        try:
+            counts, bmin, bmax = _histogram_batches([lay], n, e0, e1, below, above, want_minmax=True)
+        except NotImplementedError:
+            lay.densify()
+            counts, bmin, bmax = _histogram_batches([lay], n, e0, e1, below, above, want_minmax=True)
+        batch = _LazyHistogramList(None, None, bmin, bmax)
+        batch._edges = lambda: self._create_bin_edges(bmin, bmax)  # pylint: disable=protected-access
+        batch._compute = lambda: _histogram(lay, n, batch.bin_edges[:, 0], batch.bin_edges[:, -1])  # pylint: disable=protected-access
+        umin, umax, carry, edges, moved = _merge_histograms(batch, cur, self._histogram_range_limit, n, want_moved=True)
+        # the second pass: over the moved range, skipped on the device when no range moved
+        any_moved = moved.amax().reshape(1)
+        redo = torch.zeros_like(counts)
+        _histogram_batches([lay], n, umin, umax, umin.to(lay.x.dtype).to(torch.float32),
+                           umax.to(lay.x.dtype).to(torch.float32), counts=redo, run_if=any_moved)
+        hist = torch.where(any_moved.bool(), redo, counts).to(torch.float32) + carry
+        self._state = _HistogramList(hist, edges, umin, umax)
+        return batch
+
     def reset_stats(self):
         self._state = None
         self._histogram_range_limit = None
@@ -469,9 +607,7 @@ class _HistogramAnalyzer(EncodingAnalyzer):
 
     @torch.no_grad()
     def update_stats(self, input_tensor: torch.Tensor):
-        new_stats = self.observer.collect_stats(input_tensor)
-        self.observer.merge_stats(new_stats, input_tensor)
-        return new_stats
+        return self.observer.observe(input_tensor)
 
     @staticmethod
     def _batched(stats) -> _HistogramList:
@@ -557,12 +693,52 @@ class _LpNormEncodingAnalyzer(_HistogramAnalyzer):
     def compute_encodings_from_stats(self, stats, num_steps: int, is_symmetric: bool):
         st = self._batched(stats)
         _check_num_steps(num_steps)
-        deltas, offsets = self._pick_test_candidates(st, num_steps, is_symmetric)
-        best_delta, best_offset = self._select_best_candidates(deltas, offsets, st, num_steps)
-        emin = best_offset * best_delta
-        emax = emin + num_steps * best_delta
+        emin, emax, _ = self._search(st, num_steps, is_symmetric)
         shape = self.observer.shape
         return emin.to(st.min.dtype).view(shape), emax.to(st.max.dtype).view(shape)
+
+    _OFFSET_GRIDS = {}
+
+    def _offset_grid(self, num_steps, device) -> torch.Tensor:
+        """round(arange(-num_steps, step, step)), step = num_steps / (O - 2): the asymmetric offset
+        candidates before the observed offset is appended (:754-766).  Built on the host (so that every
+        device sees the CPU kernel's values) once per (num_steps, O, device)."""
+        n_off = min(num_steps + 2, self.num_offset_candidates)
+        key = (num_steps, n_off, str(device))
+        grid = self._OFFSET_GRIDS.get(key)
+        if grid is None:
+            step = num_steps / (n_off - 2)
+            grid = torch.round(torch.arange(start=-num_steps, end=step, step=step, dtype=torch.float32)).to(device)
+            self._OFFSET_GRIDS[key] = grid
+        return grid
+
+    def _search(self, st: _HistogramList, num_steps, symmetric, want_candidates: bool = False):
+        """Candidates, their noise and the winner's range in two launches (the candidates are formed on
+        the device).  Returns (min, max, details): float32 [H] each; ``details`` holds the noise and,
+        on request, the candidate grids for inspection."""
+        hist = st.histogram.to(torch.float32).contiguous()
+        edges = st.bin_edges.to(torch.float32).contiguous()
+        h, bins = hist.shape
+        dev = hist.device
+        smin, smax = st.min.reshape(-1).to(torch.float32).contiguous(), st.max.reshape(-1).to(torch.float32).contiguous()
+        k = self.sym_delta_candidates if symmetric else self.asym_delta_candidates
+        grid = None if symmetric else self._offset_grid(num_steps, dev)
+        ncand = k if symmetric else k * (grid.numel() + 1)
+        noise = torch.empty((h, ncand), dtype=torch.float32, device=dev)
+        deltas = torch.empty((h, ncand), dtype=torch.float32, device=dev) if want_candidates else None
+        offsets = torch.empty((h, ncand), dtype=torch.float32, device=dev) if want_candidates else None
+        emin = torch.empty(h, dtype=torch.float32, device=dev)
+        emax = torch.empty(h, dtype=torch.float32, device=dev)
+        best = torch.empty(h, dtype=torch.int32, device=dev)
+        with torch.cuda.device(dev):
+            rc = lib.aimet_b200_sqnr_encodings(hist.data_ptr(), edges.data_ptr(), smin.data_ptr(), smax.data_ptr(),
+                                               _lib.ptr(grid), 0 if grid is None else grid.numel(), k, int(symmetric),
+                                               _stat_dtype_code(st.min.dtype), h, bins, float(num_steps),
+                                               float(self.gamma), _get_minimum_scale(num_steps), noise.data_ptr(),
+                                               _lib.ptr(deltas), _lib.ptr(offsets), emin.data_ptr(), emax.data_ptr(),
+                                               best.data_ptr(), _lib.stream_ptr(dev))
+        _lib.check(rc)
+        return emin, emax, dict(noise=noise, deltas=deltas, offsets=offsets, best=best)
 
     # candidate grids -----------------------------------------------------------------------
     def _pick_test_candidates(self, st: _HistogramList, num_steps, symmetric):

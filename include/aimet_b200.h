@@ -166,6 +166,14 @@ int aimet_b200_minmax_running(const void *x, const ab_layout *layout, int io_dty
                               void *min_io, void *max_io, void *scratch, int64_t scratch_bytes,
                               void *stream);
 
+/* The same over a list of num_tensors tensors of one layout (a host array of device pointers):
+ * the statistics run over all of them, and, where the layout is a single statistic over contiguous
+ * tensors (a per-tensor quantizer's calibration batches), up to 32 tensors share one launch.
+ * merge != 0 also takes in the values already in min_io / max_io. */
+int aimet_b200_minmax_batches(const void *const *xs, int32_t num_tensors, const ab_layout *layout,
+                              int io_dtype, int finite_only, int merge, void *min_io, void *max_io,
+                              void *scratch, int64_t scratch_bytes, void *stream);
+
 /* counts[c][b] (int64, overwritten): torch.histc binning of float(x) over
  * [lo[c], hi[c]], i.e. bin = (int)((x - lo) * num_bins / (hi - lo)) with x == hi
  * in the last bin and values outside [lo, hi] or NaN ignored; then the number of
@@ -189,6 +197,30 @@ int aimet_b200_histogram_ex(const void *x, const ab_layout *layout, int io_dtype
                             int64_t *counts, void *fin_min, void *fin_max, int32_t flags,
                             void *scratch, int64_t scratch_bytes, void *stream);
 
+/* The same over a list of tensors of one layout (see aimet_b200_minmax_batches), all binned over
+ * the same range with the counts running over the list.  run_if_nonzero, if not NULL, is a device
+ * flag read by the kernel: when it is zero the launch does nothing (counts keep their contents) --
+ * for a pass that a preceding kernel may find unnecessary, decided without the host waiting. */
+int aimet_b200_histogram_batches(const void *const *xs, int32_t num_tensors, const ab_layout *layout,
+                                 int io_dtype, int32_t num_bins, const float *lo, const float *hi,
+                                 const float *below, const float *above, int64_t *counts,
+                                 void *fin_min, void *fin_max, int32_t flags,
+                                 const int32_t *run_if_nonzero, void *scratch, int64_t scratch_bytes,
+                                 void *stream);
+
+/* Bin edges of histograms over [min, max] and what a histogram pass needs from them, one launch
+ * for _HistogramObserver._create_bin_edges (encoding_analyzer.py:221-229): a degenerate range is
+ * widened by 0.5 on each side in the statistics dtype (stat_dtype: AB_F32 / AB_F16 / AB_BF16),
+ * edges = ticks * ((hi - lo) / num_bins) + lo.
+ *   min, max      float32 [H] (the statistics, exact in stat_dtype)
+ *   edges         float32 [H][num_bins + 1]
+ *   lo, hi        float32 [H] first and last edge
+ *   below, above  float32 [H] the same rounded to stat_dtype (for the outlier comparisons)
+ *   range_limit   float32 [H][2] or NULL: edges -/+ (hi - lo) * growth_limit / 2 (:244-257) */
+int aimet_b200_histogram_edges(const float *min, const float *max, int32_t num_hist, int32_t num_bins,
+                               int stat_dtype, double growth_limit, float *edges, float *lo, float *hi,
+                               float *below, float *above, float *range_limit, void *stream);
+
 /* Moves accumulated histograms into the range that also covers a new batch, one launch for
  * what _HistogramObserver.merge_stats (encoding_analyzer.py:231-323) does with tensor
  * expressions: updated range = batch range clamped between the growth limit and the current
@@ -208,6 +240,15 @@ int aimet_b200_histogram_merge(const float *new_min, const float *new_max, const
                                float *out_min, float *out_max, float *out_carry, float *out_edges,
                                void *stream);
 
+/* The same, and out_moved [H] (int32, may be NULL) = 1 where the updated range no longer ends at
+ * the current edges, i.e. where counts taken over the current edges are not the counts over the
+ * updated range. */
+int aimet_b200_histogram_merge_ex(const float *new_min, const float *new_max, const float *cur_min,
+                                  const float *cur_max, const float *cur_edges, const float *cur_hist,
+                                  const float *range_limit, int32_t num_hist, int32_t num_bins,
+                                  float *out_min, float *out_max, float *out_carry, float *out_edges,
+                                  int32_t *out_moved, void *stream);
+
 /* Expected clipping + rounding noise of every (delta, offset) candidate against
  * a histogram, and the arg-min per histogram.
  *   hist        float32 [H][num_bins]
@@ -222,6 +263,26 @@ int aimet_b200_sqnr_sweep(const float *hist, const float *edge0, const float *wi
                           const float *deltas, const float *offsets, int32_t offsets_per_hist,
                           int32_t num_hist, int32_t num_bins, int32_t num_cand, double num_steps,
                           double gamma, float *noise_out, int32_t *best_out, void *stream);
+
+/* The whole SQNR / TF-enhanced range search in two launches: the candidates are formed on the
+ * device with the reference's operations in the reference's order, evaluated against the
+ * histogram, and the winner's range min = offset * delta, max = min + num_steps * delta is written.
+ * _pick_test_candidates, _clamp_delta_offset_values, _select_best_candidates,
+ * compute_encodings_from_stats (encoding_analyzer.py:700-899).
+ *   hist          float32 [H][num_bins];  edges float32 [H][num_bins + 1]
+ *   stat_min/max  float32 [H] observed range (exact in stat_dtype, the dtype of the statistics)
+ *   asymmetric: num_deltas deltas x (num_base_offsets + 1) offsets; base_offsets float32
+ *     [num_base_offsets] is round(arange(-num_steps, step, step)), step = num_steps / (O - 2), the
+ *     observed offset is appended;  symmetric: num_deltas deltas, offset floor(-num_steps / 2)
+ *   noise_out     float32 [H][num_cand];  deltas_out / offsets_out float32 [H][num_cand] or both NULL
+ *   enc_min_out / enc_max_out float32 [H];  best_out int32 [H] (lowest index among equal minima) */
+int aimet_b200_sqnr_encodings(const float *hist, const float *edges, const float *stat_min,
+                              const float *stat_max, const float *base_offsets,
+                              int32_t num_base_offsets, int32_t num_deltas, int32_t symmetric,
+                              int stat_dtype, int32_t num_hist, int32_t num_bins, double num_steps,
+                              double gamma, double min_scale, float *noise_out, float *deltas_out,
+                              float *offsets_out, float *enc_min_out, float *enc_max_out,
+                              int32_t *best_out, void *stream);
 
 /* ------------------------------------------------------------------------- *
  * SeqMSE reconstruction loss of a Linear layer for all candidates and all

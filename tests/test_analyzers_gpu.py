@@ -173,3 +173,111 @@ def test_large_histograms_with_outliers_and_non_finite_values(dtype, channels):
         want[0] += int((v < below).sum())
         want[-1] += int((v > above).sum())
         assert torch.equal(got[c], want), f"channel {c}: {(got[c] != want).sum()} bins differ"
+
+
+@pytest.mark.parametrize("name", sorted(n for n, c in CASES.items() if c["kind"] in ("sqnr", "tfe")))
+@pytest.mark.parametrize("grid", [(255, False), (255, True), (15, True), (65535, False)])
+def test_candidates_formed_on_the_device_equal_the_reference_grids(name, grid):
+    """The search kernel forms its (delta, offset) candidates itself.  They must be, bit for bit, the
+    grids the reference builds with tensor operations (checked against the oracle in
+    test_sqnr_noise_vs_oracle), the noise must be what the stand-alone noise kernel returns for
+    those grids, and the range it reports the one of its own arg-min."""
+    case = CASES[name]
+    num_steps, sym = grid
+    an = make_analyzer(case)
+    for x in case["batches"]:
+        an.update_stats(x.cuda())
+    st = an._batched(an.observer.get_stats())
+    deltas, offsets = an._pick_test_candidates(st, num_steps, sym)
+    noise, best = an._estimate_clip_and_quant_noise(st, deltas, offsets, num_steps, 2.0, an.gamma, return_best=True)
+    emin, emax, det = an._search(st, num_steps, sym, want_candidates=True)
+    shape = torch.broadcast_shapes(deltas.shape, offsets.shape)
+    h = st.histogram.shape[0]
+    assert_same(det["deltas"], deltas.expand(shape).reshape(h, -1), "deltas")
+    assert_same(det["offsets"], offsets.expand(shape).reshape(h, -1), "offsets")
+    assert_same(det["noise"], noise.reshape(h, -1), "noise")
+    assert torch.equal(det["best"], best)
+    idx = best.long()[:, None]
+    bd = torch.gather(det["deltas"], 1, idx)[:, 0]
+    bo = torch.gather(det["offsets"], 1, idx)[:, 0]
+    assert_same(emin, bo * bd, "range min")
+    assert_same(emax, bo * bd + num_steps * bd, "range max")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_bin_edges_in_one_launch(dtype):
+    """aimet_b200_histogram_edges against the tensor expression of _create_bin_edges, including a
+    degenerate range (widened by 0.5 in the statistics dtype) and the growth limit."""
+    from aimet_b200 import encoding_analyzer as EA
+
+    mn = torch.tensor([-3.17, 0.0, 5.5, -1e-3, 2048.0], device="cuda").to(dtype)
+    mx = torch.tensor([7.01, 0.0, 5.5, 9e4 if dtype != torch.float16 else 6e4, 2050.0], device="cuda").to(dtype)
+    for bins, growth in ((2048, float("inf")), (512, 3.0), (7, 1.0)):
+        obs = EA._HistogramObserver((5,), num_bins=bins, growth_limit=growth)
+        want = obs._create_bin_edges(mn, mx)
+        edges, lo, hi, below, above, limit = EA._range_edges(mn, mx, bins, growth)
+        assert_same(edges, want, "edges")
+        assert_same(lo, want[:, 0].contiguous(), "first edge")
+        assert_same(hi, want[:, -1].contiguous(), "last edge")
+        assert_same(below, want[:, 0].to(dtype).float(), "below")
+        assert_same(above, want[:, -1].to(dtype).float(), "above")
+        span = want[:, -1] - want[:, 0]
+        assert_same(limit[:, 0].contiguous(), want[:, 0] - EA._div(span * growth, 2), "lower limit")
+        assert_same(limit[:, 1].contiguous(), want[:, -1] + EA._div(span * growth, 2), "upper limit")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_lists_of_tensors_in_one_launch(dtype):
+    """Min / max and counts of a list of batches (one launch for up to 32 tensors of a per-tensor
+    statistic) equal the per-tensor results combined; more than 32 tensors, a tensor whose size is
+    not a multiple of the vector width, and a per-channel layout (one launch per tensor)."""
+    from aimet_b200 import encoding_analyzer as EA
+
+    g = torch.Generator().manual_seed(9)
+    for shape, qshape, count in (((1 << 20) + 3, (), 3), ((1 << 18), (), 35), ((64, 1 << 15), (64, 1), 3)):
+        xs = [(torch.randn(shape, generator=g) * (1 + i)).to(dtype).cuda() for i in range(count)]
+        xs[1].view(-1)[5] = float("inf")
+        xs[0].view(-1)[7] = float("nan")
+        lays = [EA._StatLayout(x, qshape, None) for x in xs]
+        mn, mx = EA._minmax_batches(lays, True)
+        singles = [EA._minmax(EA._StatLayout(x, qshape, None), True) for x in xs]
+        assert_same(mn, torch.stack([s[0] for s in singles]).amin(0), "min over the list")
+        assert_same(mx, torch.stack([s[1] for s in singles]).amax(0), "max over the list")
+        edges, lo, hi, below, above, _ = EA._range_edges(mn * 0.5, mx * 0.5, 256, float("inf"))  # narrower than the data
+        counts, fmn, fmx = EA._histogram_batches(lays, 256, lo, hi, below, above, want_minmax=True)
+        want = sum(EA._histogram_counts(EA._StatLayout(x, qshape, None), 256, lo, hi) for x in xs)
+        assert torch.equal(counts, want)
+        assert_same(fmn, mn, "min from the histogram pass")
+        assert_same(fmx, mx, "max from the histogram pass")
+        # a conditional launch that is switched off leaves the counts alone
+        keep = counts.clone()
+        EA._histogram_batches(lays, 256, lo, hi, below, above, counts=counts, run_if=torch.zeros(1, dtype=torch.int32, device="cuda"))
+        assert torch.equal(counts, keep)
+        EA._histogram_batches(lays, 256, lo, hi, below, above, counts=counts, run_if=torch.ones(1, dtype=torch.int32, device="cuda"))
+        assert torch.equal(counts, 2 * keep)
+
+
+def test_sequential_updates_in_one_pass_when_the_range_holds():
+    """update_stats after the first batch bins against the current range and learns the batch's own
+    range in the same pass; batches that stay inside the range, that exceed it, and (with a growth
+    limit) that exceed what the range may grow to -- every intermediate state equals the oracle's
+    (the reference's two-pass procedure)."""
+    from aimet_b200 import encoding_analyzer as EA
+
+    g = torch.Generator().manual_seed(21)
+    n = (1 << 20) + 64
+    scales = [4.0, 1.0, 2.0, 9.0, 3.0, 40.0, 1.0]
+    batches = [(torch.randn(n, generator=g) * s).to(torch.bfloat16) for s in scales]
+    for growth in (None, 3.0):
+        an = EA.SqnrEncodingAnalyzer((), num_bins=2048, histogram_growth_limit=growth)
+        state = None
+        for i, x in enumerate(batches):
+            ret = an.update_stats(x.cuda())
+            new = OA.hist_collect(x, (), 2048)
+            state = OA.hist_merge(state, new, x, (), 2048, growth if growth is not None else float("inf"))
+            got = an.observer.get_stats()
+            merged = state["stats"] if isinstance(state, dict) else state
+            assert_stats_same(got, merged, f"growth {growth} update {i} merged")
+            assert_same(ret.min, torch.stack([w["min"] for w in new]), "returned min")
+            if i in (2, 5):  # the batch's own histogram on request
+                assert_stats_same(ret, new, f"update {i} returned")
