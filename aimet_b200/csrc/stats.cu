@@ -509,7 +509,7 @@ struct HistArgs {
     int64_t tile_elems;          // elements of one channel handled by one CTA (multiple of 16)
     int num_bins;
     int tiles;                   // CTAs per channel
-    const int *run_if;           // NULL, or a device flag: the launch does nothing when it is zero
+    const int *run_if;           // NULL, or one device flag per histogram: nothing is done for those that are zero
 };
 
 // torch.histc's bin of v over [lo, hi] (CPU and CUDA kernels agree):
@@ -530,7 +530,7 @@ template <int IO, bool VECT> __global__ void __launch_bounds__(kThreads) k_histo
     __shared__ unsigned long long sh_edge[2];
     __shared__ float sh_mm[2][kThreads / 32];
 
-    if (a.run_if && *a.run_if == 0) return;
+    if (a.run_if && a.run_if[blockIdx.y] == 0) return;
     const int64_t c = blockIdx.y;
     const int tile = blockIdx.x;
     for (int b = threadIdx.x; b < a.num_bins; b += kThreads) sh_hist[b] = 0;
@@ -690,7 +690,7 @@ struct HistPrivArgs {
     int64_t chan_elems, tile_elems;
     int num_bins;
     int tiles;
-    const int *run_if;   // NULL, or a device flag: the launch does nothing when it is zero
+    const int *run_if;   // NULL, or one device flag per histogram: nothing is done for those that are zero
 };
 
 // all values of the vector inside [plo, phi] (false if any is NaN); the packed minimum and maximum
@@ -748,7 +748,7 @@ __global__ void __launch_bounds__(kPrivThreads, 1) k_hist_private(HistPrivArgs a
     extern __shared__ __align__(16) unsigned int sh_cnt[];  // [num_bins + 1][16]; row num_bins: v == hi
     __shared__ unsigned long long sh_edge[2];
     __shared__ float sh_mm[2][kPrivThreads / 32];
-    if (a.run_if && *a.run_if == 0) return;
+    if (a.run_if && a.run_if[blockIdx.y] == 0) return;
     const int64_t c = blockIdx.y;
     for (int i = threadIdx.x; i < (a.num_bins + 1) * kPrivCopies; i += kPrivThreads) sh_cnt[i] = 0;
     if (threadIdx.x < 2) sh_edge[threadIdx.x] = 0;
@@ -1174,6 +1174,13 @@ int launch_histogram(const void *const *xs, int num_x, const Canon &canon, int32
 // straddles a destination edge is split proportionally, the first part rounded half to even;
 // the new edges are ticks * step + lo.
 // ---------------------------------------------------------------------------
+// round to the dtype the statistics are kept in, as a tensor operation on that dtype would
+__device__ __forceinline__ float rnd_dt(float v, int dt) {
+    if (dt == AB_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+    if (dt == AB_F16) return __half2float(__float2half_rn(v));
+    return v;
+}
+
 struct MergeArgs {
     const float *new_min, *new_max, *cur_min, *cur_max;
     const float *cur_edges;  // [H][n + 1]
@@ -1184,6 +1191,8 @@ struct MergeArgs {
     float *out_edges;        // [H][n + 1]
     int num_bins;
     int *out_moved;          // [H] or NULL: 1 when the updated range differs from the current edges
+    float *out_range;        // [H][4] or NULL: first edge, last edge, and the two rounded to stat_dtype
+    int stat_dtype;
 };
 
 __device__ __forceinline__ float min_prop(float a, float b) {  // torch.minimum: NaN propagates
@@ -1237,7 +1246,27 @@ __global__ void __launch_bounds__(kThreads) k_hist_merge(MergeArgs a) {
         // counts taken over [edges[0], edges[n]] are the counts over the updated range exactly when
         // the range still ends where the edges do
         if (a.out_moved) a.out_moved[h] = (umin == e0 && umax == e_last) ? 0 : 1;
+        if (a.out_range) {
+            const float first = __fadd_rn(__fmul_rn(0.0f, step), lo), last = __fadd_rn(__fmul_rn(nf, step), lo);
+            a.out_range[4 * h] = first;
+            a.out_range[4 * h + 1] = last;
+            a.out_range[4 * h + 2] = rnd_dt(first, a.stat_dtype);
+            a.out_range[4 * h + 3] = rnd_dt(last, a.stat_dtype);
+        }
     }
+}
+
+// hist[h][b] = carry[h][b] + (moved[h] ? redo : counts)[h][b]: the accumulated counts moved into the
+// updated range plus the batch's counts from whichever pass is valid for it
+__global__ void __launch_bounds__(kThreads) k_hist_combine(const long long *counts, const long long *redo, const float *carry,
+                                                           const int *moved, float *hist, int num_bins) {
+    pdl_prologue();
+    const int h = blockIdx.y;
+    const int b = blockIdx.x * kThreads + threadIdx.x;
+    if (b >= num_bins) return;
+    const int64_t i = (int64_t)h * num_bins + b;
+    const long long n = moved[h] ? redo[i] : counts[i];
+    hist[i] = __fadd_rn((float)n, carry[i]);
 }
 
 // ---------------------------------------------------------------------------
@@ -1322,13 +1351,6 @@ __global__ void __launch_bounds__(kSweepThreads) k_argmin(const float *noise, in
 // Small-tensor bookkeeping of a calibration as single launches (it is what a many-GPU calibration
 // spends its time on once the passes over the data are short)
 // ---------------------------------------------------------------------------
-// round to the dtype the statistics are kept in, as a tensor operation on that dtype would
-__device__ __forceinline__ float rnd_dt(float v, int dt) {
-    if (dt == AB_BF16) return __bfloat162float(__float2bfloat16_rn(v));
-    if (dt == AB_F16) return __half2float(__float2half_rn(v));
-    return v;
-}
-
 struct EdgesArgs {
     const float *mn, *mx;  // [H] observed range (finite min / max), exact in the statistics dtype
     int num_hist, num_bins, stat_dtype;
@@ -1644,14 +1666,14 @@ extern "C" int aimet_b200_histogram_merge_ex(const float *new_min, const float *
                                              const float *cur_max, const float *cur_edges, const float *cur_hist,
                                              const float *range_limit, int32_t num_hist, int32_t num_bins,
                                              float *out_min, float *out_max, float *out_carry, float *out_edges,
-                                             int32_t *out_moved, void *stream) {
+                                             int32_t *out_moved, float *out_range, int stat_dtype, void *stream) {
     if (num_hist <= 0 || num_bins <= 0) return ab::fail(AB_ERR_INVALID, "num_hist and num_bins must be positive");
     if (num_bins > 8192) return ab::fail(AB_ERR_UNSUPPORTED, "at most 8192 bins, got %d", (int)num_bins);
     if (!new_min || !new_max || !cur_min || !cur_max || !cur_edges || !cur_hist || !range_limit || !out_min || !out_max ||
         !out_carry || !out_edges)
         return ab::fail(AB_ERR_INVALID, "NULL pointer argument");
     ab::MergeArgs a{new_min, new_max, cur_min, cur_max, cur_edges, cur_hist, range_limit,
-                    out_min, out_max, out_carry, out_edges, num_bins, out_moved};
+                    out_min, out_max, out_carry, out_edges, num_bins, out_moved, out_range, stat_dtype};
     ab::launch_pdl(ab::k_hist_merge, (unsigned)num_hist, ab::kThreads, sizeof(float) * (size_t)num_bins,
                    static_cast<cudaStream_t>(stream), a);
     AB_LAUNCH_OK();
@@ -1724,5 +1746,19 @@ extern "C" int aimet_b200_histogram_merge(const float *new_min, const float *new
                                           const float *range_limit, int32_t num_hist, int32_t num_bins, float *out_min,
                                           float *out_max, float *out_carry, float *out_edges, void *stream) {
     return aimet_b200_histogram_merge_ex(new_min, new_max, cur_min, cur_max, cur_edges, cur_hist, range_limit, num_hist,
-                                         num_bins, out_min, out_max, out_carry, out_edges, nullptr, stream);
+                                         num_bins, out_min, out_max, out_carry, out_edges, nullptr, nullptr, AB_F32, stream);
+}
+
+extern "C" int aimet_b200_histogram_combine(const int64_t *counts, const int64_t *redo, const float *carry,
+                                            const int32_t *moved, int32_t num_hist, int32_t num_bins, float *hist_out,
+                                            void *stream) {
+    if (num_hist <= 0 || num_bins <= 0) return ab::fail(AB_ERR_INVALID, "num_hist and num_bins must be positive");
+    if (num_hist > 65535) return ab::fail(AB_ERR_UNSUPPORTED, "at most 65535 histograms per call");
+    if (!counts || !redo || !carry || !moved || !hist_out) return ab::fail(AB_ERR_INVALID, "NULL pointer argument");
+    dim3 grid((unsigned)((num_bins + ab::kThreads - 1) / ab::kThreads), (unsigned)num_hist);
+    ab::launch_pdl(ab::k_hist_combine, grid, ab::kThreads, 0, static_cast<cudaStream_t>(stream),
+                   reinterpret_cast<const long long *>(counts), reinterpret_cast<const long long *>(redo), carry, moved,
+                   hist_out, num_bins);
+    AB_LAUNCH_OK();
+    return AB_OK;
 }

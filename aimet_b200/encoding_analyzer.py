@@ -351,24 +351,33 @@ def _histogram_batches(lays, num_bins: int, lo, hi, below, above, counts=None, w
     return (counts, mn, mx) if want_minmax else counts
 
 
+def _f32c(t: torch.Tensor) -> torch.Tensor:
+    """float32 contiguous (exact for 16-bit statistics); the tensor itself when it already is."""
+    t = t.detach()
+    return t if t.dtype == torch.float32 and t.is_contiguous() else t.to(torch.float32).contiguous()
+
+
 def _merge_histograms(new: "_HistogramList", cur: "_HistogramList", limit: torch.Tensor, num_bins: int,
-                      want_moved: bool = False):
-    """(updated min, updated max, carried counts, updated edges) of ``cur`` widened to cover ``new``."""
+                      want_moved: bool = False, stat_dtype=torch.float32):
+    """(updated min, updated max, carried counts, updated edges) of ``cur`` widened to cover ``new``;
+    with ``want_moved`` also the per-histogram flag "the range no longer ends at the current edges"
+    and [H, 4] = (first edge, last edge, both rounded to ``stat_dtype``) of the updated range."""
     dev = cur.histogram.device
-    f32 = lambda t: t.detach().to(torch.float32).contiguous()  # noqa: E731  (exact for 16-bit statistics)
     h = cur.histogram.shape[0]
     out_min = torch.empty(h, dtype=torch.float32, device=dev)
     out_max = torch.empty(h, dtype=torch.float32, device=dev)
     carry = torch.empty((h, num_bins), dtype=torch.float32, device=dev)
     edges = torch.empty((h, num_bins + 1), dtype=torch.float32, device=dev)
-    args = [f32(new.min), f32(new.max), f32(cur.min), f32(cur.max), f32(cur.bin_edges), f32(cur.histogram), f32(limit)]
+    args = [_f32c(new.min), _f32c(new.max), _f32c(cur.min), _f32c(cur.max), _f32c(cur.bin_edges), _f32c(cur.histogram),
+            _f32c(limit)]
     moved = torch.empty(h, dtype=torch.int32, device=dev) if want_moved else None
+    rng = torch.empty((h, 4), dtype=torch.float32, device=dev) if want_moved else None
     with torch.cuda.device(dev):
         rc = lib.aimet_b200_histogram_merge_ex(*[t.data_ptr() for t in args], h, num_bins, out_min.data_ptr(),
                                                out_max.data_ptr(), carry.data_ptr(), edges.data_ptr(), _lib.ptr(moved),
-                                               _lib.stream_ptr(dev))
+                                               _lib.ptr(rng), _stat_dtype_code(stat_dtype), _lib.stream_ptr(dev))
     _lib.check(rc)
-    return (out_min, out_max, carry, edges, moved) if want_moved else (out_min, out_max, carry, edges)
+    return (out_min, out_max, carry, edges, moved, rng) if want_moved else (out_min, out_max, carry, edges)
 
 
 # --------------------------------------------------------------------------------------------
@@ -503,24 +512,40 @@ class _HistogramObserver(_Observer):
             new = self.collect_stats(x)
             self.merge_stats(new, x)
             return new
-        e0, e1 = cur.bin_edges[:, 0].contiguous(), cur.bin_edges[:, -1].contiguous()
-        below, above = e0.to(lay.x.dtype).to(torch.float32), e1.to(lay.x.dtype).to(torch.float32)
-        try:
-            counts, bmin, bmax = _histogram_batches([lay], n, e0, e1, below, above, want_minmax=True)
-        except NotImplementedError:
-            lay.densify()
-            counts, bmin, bmax = _histogram_batches([lay], n, e0, e1, below, above, want_minmax=True)
+        # first / last edge of the current range and the two rounded to the tensor dtype: kept from
+        # the previous update (the merge kernel writes them) as long as the dtype stays the same
+        rng = getattr(cur, "_range", None)
+        if rng is None or rng[1] != lay.x.dtype:
+            e0, e1 = cur.bin_edges[:, 0], cur.bin_edges[:, -1]
+            rng = (torch.stack((e0, e1, e0.to(lay.x.dtype).to(torch.float32), e1.to(lay.x.dtype).to(torch.float32)),
+                               dim=1).contiguous(), lay.x.dtype)
+        r = rng[0]
+        lo, hi, below, above = r[:, 0], r[:, 1], r[:, 2], r[:, 3]  # strided views: only their first element is read per histogram
+
+        def bin_over(lo, hi, below, above, **kw):
+            cols = [c.contiguous() for c in (lo, hi, below, above)] if r.shape[0] > 1 else [lo, hi, below, above]
+            try:
+                return _histogram_batches([lay], n, *cols, **kw)
+            except NotImplementedError:
+                lay.densify()
+                return _histogram_batches([lay], n, *cols, **kw)
+
+        counts, bmin, bmax = bin_over(lo, hi, below, above, want_minmax=True)
         batch = _LazyHistogramList(None, None, bmin, bmax)
         batch._edges = lambda: self._create_bin_edges(bmin, bmax)  # pylint: disable=protected-access
         batch._compute = lambda: _histogram(lay, n, batch.bin_edges[:, 0], batch.bin_edges[:, -1])  # pylint: disable=protected-access
-        umin, umax, carry, edges, moved = _merge_histograms(batch, cur, self._histogram_range_limit, n, want_moved=True)
-        # the second pass: over the moved range, skipped on the device when no range moved
-        any_moved = moved.amax().reshape(1)
+        umin, umax, carry, edges, moved, nr = _merge_histograms(batch, cur, self._histogram_range_limit, n, want_moved=True,
+                                                                stat_dtype=lay.x.dtype)
+        # the second pass: over the moved range, skipped on the device for histograms whose range held
         redo = torch.zeros_like(counts)
-        _histogram_batches([lay], n, umin, umax, umin.to(lay.x.dtype).to(torch.float32),
-                           umax.to(lay.x.dtype).to(torch.float32), counts=redo, run_if=any_moved)
-        hist = torch.where(any_moved.bool(), redo, counts).to(torch.float32) + carry
+        bin_over(nr[:, 0], nr[:, 1], nr[:, 2], nr[:, 3], counts=redo, run_if=moved)
+        hist = torch.empty((counts.shape[0], n), dtype=torch.float32, device=counts.device)
+        with torch.cuda.device(counts.device):
+            rc = lib.aimet_b200_histogram_combine(counts.data_ptr(), redo.data_ptr(), carry.data_ptr(), moved.data_ptr(),
+                                                  counts.shape[0], n, hist.data_ptr(), _lib.stream_ptr(counts.device))
+        _lib.check(rc)
         self._state = _HistogramList(hist, edges, umin, umax)
+        self._state._range = (nr, lay.x.dtype)  # pylint: disable=protected-access
         return batch
 
     def reset_stats(self):

@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE config 2): the weight of a Llama-3-8B MLP linear, [14336, 4096] bfloat16,
+Workload: the weight of a Llama-3-8B MLP linear, [14336, 4096] bfloat16,
 N(0, 0.02) with 0.1 % of the entries scaled 20x; one *step* is quantize-dequantize forward +
 backward (input, scale and offset gradients) of that weight under three encodings: per-channel
 symmetric int8, blockwise int4 (block 64) and LPBQ (int4 blocks, 8-bit per-channel scale).
@@ -15,11 +15,16 @@ Metric: algorithmic GB/s = 10 bytes per element and encoding / time (2 read + 2 
   back, inside the timed region.
 * ``roofline``: the dominant kernel (backward), timed with CUDA events inside the timed region.
 * ``cpu_baseline`` / ``--impl reference``: the CPU oracle (a restatement of the reference's torch
-  path) on the host cores, on a bounded row-sample of the same weight.
+  path) on the host cores, on a bounded row-sample of the same weight; only the quantize-dequantize
+  forward + backward is timed (inputs and encodings are prepared before).
+* ``parity``: after each timed leg, outside the timed region, one step's results are compared with
+  the CPU oracle on a sample, and, with N > 1, the sharded result with the unsharded one.
 
 With N > 1 every rank runs the same step on its own weight (independent layers: no collective),
 reported as weak scaling; the calibration figure shards its batches over the ranks and
-all-reduces min/max and histogram counts.
+all-reduces min/max and histogram counts; the SeqMSE figure shards the output channels.
+Further objects of the JSON line: ``per_tensor_fp32`` (a [4096, 4096] float32 tensor under a
+per-tensor asymmetric 8-bit encoding), ``calibration``, ``seqmse``, ``quantsim_resnet50``.
 """
 
 from __future__ import annotations
@@ -300,43 +305,219 @@ class HostStep:
 # --------------------------------------------------------------------------------------------
 # CPU oracle leg
 # --------------------------------------------------------------------------------------------
-def cpu_step(sample_rows):
-    """One step of the workload on a row sample through the CPU oracle.  Returns seconds."""
+CPU_SAMPLE_ROWS = 1024
+
+
+class CpuStep:
+    """The workload on a row sample through the CPU oracle: the weight, the upstream gradient and the
+    three encodings are prepared once; ``run`` is one quantize-dequantize forward + backward under
+    each encoding and returns the seconds it took."""
+
+    def __init__(self, sample_rows=CPU_SAMPLE_ROWS):
+        from oracle import encoding_analyzer as OE
+        from oracle import quantizer as OQ
+
+        self.rows = sample_rows
+        self.w, self.dy = make_weight(sample_rows, COLS, seed=2000)
+        nblk = COLS // BLOCK
+        self.encs = []
+        for i, (shape, bw, block) in enumerate((((sample_rows, 1), 8, None), ((sample_rows, nblk), 4, (1, BLOCK)),
+                                               ((sample_rows, nblk), 4, (1, BLOCK)))):
+            steps = 2**bw - 1
+            qmin, qmax = -((steps + 1) // 2), steps // 2
+            mn, mx = OE.minmax_collect(self.w, shape, block)
+            mn, mx = OE.minmax_encodings(mn, mx, steps, True)
+            scale, offset = OQ.scale_offset_from_min_max(mn.float(), mx.float(), qmin, qmax, True)
+            if i == 2:
+                scale, _ = OQ.lpbq_scale(scale, 4, 8, (1, -1))
+            self.encs.append((scale, offset, qmin, qmax, block))
+
+    def run(self):
+        from oracle import affine as OA
+
+        t0 = time.perf_counter()
+        self.out = []
+        for scale, offset, qmin, qmax, block in self.encs:
+            y = OA.quantize_dequantize(self.w, scale, offset, qmin, qmax, block)
+            gx, gs, _ = OA.quantize_dequantize_backward(self.w, self.dy, scale, offset, qmin, qmax, block)
+            self.out.append((y, gx, gs))
+        return time.perf_counter() - t0
+
+    def gbps(self, seconds):
+        return 3 * self.rows * COLS * BYTES_PER_ELEM / seconds / 1e9
+
+    @property
+    def sample(self):
+        return (f"{self.rows} of {ROWS} rows of the weight, all three encodings; weight, gradient and encodings "
+                "prepared beforehand, only forward + backward timed")
+
+
+def cpu_baseline(repeats=3):
+    torch.set_num_threads(os.cpu_count() or 1)
+    step = CpuStep()
+    step.run()
+    t = statistics.median(step.run() for _ in range(repeats))
+    return {"value": step.gbps(t), "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": step.sample + f", median of {repeats} runs"}
+
+
+def _bits_equal(a, b):
+    a, b = a.detach().cpu(), b.detach().cpu()
+    return bool(a.shape == b.shape and a.dtype == b.dtype and ((a == b) | (a.isnan() & b.isnan())).all())
+
+
+def _rel_err(got, want):
+    got, want = got.detach().double().cpu().flatten(), want.detach().double().cpu().flatten()
+    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
+def qdq_parity(resident, rows=256):
+    """One step's outputs on the first ``rows`` rows against the CPU oracle: y and dx bit for bit,
+    the scale gradients to 1e-5 of their largest value (or one unit in the last place of the 16-bit
+    dtype the reference sums them in)."""
+    from oracle import affine as OA
+
+    lib, p, L = resident.lib, torch.Tensor.data_ptr, resident._lib
+    w, dy = resident.w[:rows].contiguous(), resident.dy[:rows].contiguous()
+    y, gx = torch.empty_like(w), torch.empty_like(w)
+    out = {"rows": rows}
+    ok = True
+    for name in VARIANTS:
+        e = resident.enc[name]
+        scale, offset = e["scale"][:rows].contiguous(), e["offset"][:rows].contiguous()
+        gs = torch.empty_like(scale)
+        lay = L.make_layout([rows, COLS], [1, COLS] if name == "per_channel_int8" else [1, BLOCK])
+        scratch = torch.empty(max(lib.aimet_b200_backward_scratch_bytes(lay, resident.io), 16), dtype=torch.uint8,
+                              device=w.device)
+        st = torch.cuda.current_stream(w.device).cuda_stream
+        resident._ok(lib.aimet_b200_quantize_dequantize(p(w), p(y), p(scale), p(offset), lay, resident.io, e["ct"], 0,
+                                                        e["qmin"], e["qmax"], 0.0, st))
+        resident._ok(lib.aimet_b200_quantize_dequantize_backward(
+            p(w), p(dy), p(scale), p(offset), lay, resident.io, e["ct"], 0, e["qmin"], e["qmax"], 0.0, p(gx), p(gs),
+            None, p(scratch), scratch.numel(), st))
+        block = None if name == "per_channel_int8" else (1, BLOCK)
+        oy = OA.quantize_dequantize(w.cpu(), scale.cpu(), offset.cpu(), e["qmin"], e["qmax"], block)
+        ogx, ogs, _ = OA.quantize_dequantize_backward(w.cpu(), dy.cpu(), scale.cpu(), offset.cpu(), e["qmin"], e["qmax"], block)
+        tol = 1e-5 if name == "per_channel_int8" else 2.0 ** -7  # float32 sums / bfloat16 sums (one ulp)
+        rec = {"y_bit_exact": _bits_equal(y, oy), "dx_bit_exact": _bits_equal(gx, ogx),
+               "dscale_max_rel_err": _rel_err(gs, ogs.reshape(gs.shape).float()), "dscale_tolerance": tol}
+        rec["ok"] = rec["y_bit_exact"] and rec["dx_bit_exact"] and rec["dscale_max_rel_err"] <= tol
+        ok = ok and rec["ok"]
+        out[name] = rec
+    out["ok"] = ok
+    return out
+
+
+def qdq_shard_parity(dev, rank, world):
+    """N > 1: the rows of one weight split over the ranks, quantize-dequantized shard by shard and
+    gathered, equal the unsharded result (no reduction crosses rows)."""
+    import torch.distributed as dist
+
+    from aimet_b200 import distributed as D
+    from aimet_b200.quantizer import QuantizeDequantize
+
+    w, _ = make_weight(ROWS, COLS, seed=2000)
+    w = w.to(dev)
+    q = QuantizeDequantize((ROWS, COLS // BLOCK), 4, True, block_size=(1, BLOCK)).to(dev)
+    with q.compute_encodings():
+        q(w)
+    with torch.no_grad():
+        full = q(w)
+        lo, hi = D.shard_range(ROWS, rank, world)
+        part = QuantizeDequantize((hi - lo, COLS // BLOCK), 4, True, block_size=(1, BLOCK)).to(dev)
+        part.set_range(q.min[lo:hi], q.max[lo:hi])
+        mine = part(w[lo:hi].contiguous())
+    gathered = D.gather_rows(mine, ROWS, dist.group.WORLD)
+    ok = torch.tensor([int(torch.equal(gathered, full))], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    return bool(ok.item())
+
+
+# --------------------------------------------------------------------------------------------
+# a float32 tensor under a per-tensor asymmetric 8-bit encoding
+# --------------------------------------------------------------------------------------------
+def per_tensor_figure(dev, reps=20, cpu=True):
+    """[4096, 4096] float32, N(0, 1), per-tensor asymmetric 8-bit encoding from a min-max calibration;
+    forward + backward with range gradients.  The tensors (64 MB each) would partly stay in the
+    126 MB L2, so a 256 MB buffer is overwritten between timed iterations."""
+    from aimet_b200 import _lib
+    from aimet_b200.quantizer import QuantizeDequantize
     from oracle import affine as OA
     from oracle import encoding_analyzer as OE
     from oracle import quantizer as OQ
 
-    w, dy = make_weight(sample_rows, COLS, seed=2000)
-    nblk = COLS // BLOCK
-    encs = []
-    for shape, bw, block in (((sample_rows, 1), 8, None), ((sample_rows, nblk), 4, (1, BLOCK)), ((sample_rows, nblk), 4, (1, BLOCK))):
-        steps = 2**bw - 1
-        qmin, qmax = -((steps + 1) // 2), steps // 2
-        mn, mx = OE.minmax_collect(w, shape, block)
-        mn, mx = OE.minmax_encodings(mn, mx, steps, True)
-        encs.append((mn.float(), mx.float(), qmin, qmax, block))
+    g = torch.Generator().manual_seed(1000)
+    x_cpu, dy_cpu = torch.randn(4096, 4096, generator=g), torch.randn(4096, 4096, generator=g)
+    x, dy = x_cpu.to(dev), dy_cpu.to(dev)
+    q = QuantizeDequantize((), 8, False).to(dev)
+    with q.compute_encodings():
+        q(x)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    lib, p = _lib.lib, torch.Tensor.data_ptr
+    with torch.no_grad():
+        scale, offset = q.get_scale().contiguous(), q.get_offset().contiguous()
+    lay = _lib.make_layout([4096, 4096], [4096, 4096])
+    y, gx, gs, go = torch.empty_like(x), torch.empty_like(x), torch.empty_like(scale), torch.empty_like(scale)
+    scratch = torch.empty(max(lib.aimet_b200_backward_scratch_bytes(lay, _lib.AB_F32), 16), dtype=torch.uint8, device=dev)
+    st = torch.cuda.current_stream(dev).cuda_stream
+
+    def fwd():
+        assert lib.aimet_b200_quantize_dequantize(p(x), p(y), p(scale), p(offset), lay, _lib.AB_F32, _lib.AB_F32, 0,
+                                                  q.qmin, q.qmax, 0.0, st) == 0, _lib.last_error()
+
+    def bwd():
+        assert lib.aimet_b200_quantize_dequantize_backward(p(x), p(dy), p(scale), p(offset), lay, _lib.AB_F32, _lib.AB_F32,
+                                                           0, q.qmin, q.qmax, 0.0, p(gx), p(gs), p(go), p(scratch),
+                                                           scratch.numel(), st) == 0, _lib.last_error()
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        return statistics.median(ts), min(ts)
+
+    f_med, f_best = timed(fwd)
+    b_med, b_best = timed(bwd)
+    peaks, kind = measured_peaks()
+    n = x.numel()
+    # parity: calibration, forward, backward against the oracle (whole tensor)
+    omn, omx = OE.minmax_collect(x_cpu, (), None)
+    omn, omx = OE.minmax_encodings(omn, omx, 255, False)
+    osc, oof = OQ.scale_offset_from_min_max(omn.float(), omx.float(), q.qmin, q.qmax, False)
     t0 = time.perf_counter()
-    for i, (mn, mx, qmin, qmax, block) in enumerate(encs):
-        scale, offset = OQ.scale_offset_from_min_max(mn, mx, qmin, qmax, True)
-        if i == 2:
-            scale, _ = OQ.lpbq_scale(scale, 4, 8, (1, -1))
-        OA.quantize_dequantize(w, scale, offset, qmin, qmax, block)
-        OA.quantize_dequantize_backward(w, dy, scale, offset, qmin, qmax, block)
-    return time.perf_counter() - t0
-
-
-def cpu_baseline(sample_rows=1024, repeats=3):
-    torch.set_num_threads(os.cpu_count() or 1)
-    cpu_step(sample_rows)
-    times = [cpu_step(sample_rows) for _ in range(repeats)]
-    t = statistics.median(times)
-    gbs = 3 * sample_rows * COLS * BYTES_PER_ELEM / t / 1e9
-    return {"value": gbs, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{sample_rows} of {ROWS} rows of the weight, all three encodings, median of {repeats} runs"}
+    oy = OA.quantize_dequantize(x_cpu, osc, oof, q.qmin, q.qmax)
+    ogx, ogs, ogo = OA.quantize_dequantize_backward(x_cpu, dy_cpu, osc, oof, q.qmin, q.qmax)
+    cpu_s = time.perf_counter() - t0
+    parity = {"encoding_bit_exact": _bits_equal(q.min.detach(), omn.float().reshape(q.min.shape)) and
+              _bits_equal(q.max.detach(), omx.float().reshape(q.max.shape)),
+              "y_bit_exact": _bits_equal(y, oy), "dx_bit_exact": _bits_equal(gx, ogx),
+              "dscale_rel_err": _rel_err(gs, ogs.reshape(gs.shape)), "doffset_abs_err": float((go.cpu() - ogo.reshape(go.shape)).abs().max())}
+    parity["ok"] = (parity["encoding_bit_exact"] and parity["y_bit_exact"] and parity["dx_bit_exact"]
+                    and parity["dscale_rel_err"] <= 1e-5 and parity["doffset_abs_err"] <= 1e-5 * max(1.0, float(ogo.abs().max())))
+    out = {"shape": [4096, 4096], "dtype": "float32", "encoding": "per-tensor asymmetric 8-bit (min-max calibration)",
+           "algorithmic_bytes": {"forward": 8 * n, "backward": 12 * n},
+           "forward_us": f_med, "forward_best_us": f_best, "backward_us": b_med, "backward_best_us": b_best,
+           "backward_includes": "the finishing kernel that sums the partial scale / offset gradients",
+           "fwd_bwd_GBps": 20 * n / ((f_med + b_med) * 1e-6) / 1e9,
+           "frac_of_" + kind + "_hbm": 20 * n / ((f_med + b_med) * 1e-6) / 1e9 / peaks["hbm_gbs"],
+           "l2": "a 256 MB buffer is overwritten between timed iterations (the tensors alone would fit L2)",
+           "parity": parity}
+    if cpu:
+        out["cpu_baseline"] = {"value": 20 * n / cpu_s / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+                               "sample": "the whole tensor, one forward + backward through the CPU oracle"}
+    return out
 
 
 # --------------------------------------------------------------------------------------------
-# secondary figures: calibration (config 3) and SeqMSE (config 5)
+# calibration and SeqMSE
 # --------------------------------------------------------------------------------------------
 def student_t_batch(gen, hot, dev, tokens=16 * 2048, channels=4096, df=3):
     z = torch.randn((tokens, channels), device=dev, generator=gen)
@@ -346,10 +527,10 @@ def student_t_batch(gen, hot, dev, tokens=16 * 2048, channels=4096, df=3):
     return x.to(torch.bfloat16).view(16, 2048, channels)
 
 
-def calibration_figure(dev, rank, world, num_batches=64):
-    """SQNR calibration of config 3: ``num_batches`` activation batches [16,2048,4096] bf16 (Student-t,
-    df 3, 32 channels x50) dealt round-robin to the ranks; two-phase exact histogram (min/max
-    all-reduce, 2048-bin int64 count all-reduce), then the 17x21 asymmetric candidate sweep."""
+def calibration_figure(dev, rank, world, num_batches=64, cpu=True):
+    """SQNR calibration: ``num_batches`` activation batches [16,2048,4096] bf16 (Student-t, df 3, 32
+    channels x50) dealt round-robin to the ranks; two-phase exact histogram (min/max all-reduce,
+    2048-bin int64 count all-reduce), then the 17x21 asymmetric candidate search."""
     import torch.distributed as dist
 
     from aimet_b200 import distributed as D
@@ -358,36 +539,84 @@ def calibration_figure(dev, rank, world, num_batches=64):
     gen = torch.Generator(device=dev).manual_seed(3000)
     hot = torch.randperm(4096, device=dev, generator=gen)[:32]
     mine = D.my_batches(num_batches, rank, world)
-    batches = []
-    for b in range(num_batches):  # every rank draws the same stream and keeps its own share
-        x = student_t_batch(gen, hot, dev)
-        if b in mine:
-            batches.append(x)
+    everything = [student_t_batch(gen, hot, dev) for _ in range(num_batches)]  # every rank draws the same stream
+    batches = [everything[b] for b in mine]
     group = dist.group.WORLD if world > 1 else None
 
-    def run():
+    def run(timings=None):
         an = EA.SqnrEncodingAnalyzer((), num_bins=2048)
-        D.calibrate_histogram(an, batches, group)
-        return an.compute_encodings(255, False)
+        D.calibrate_histogram(an, batches, group, timings=timings)
+        enc = an.compute_encodings(255, False)
+        if timings is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            timings["t5"] = ev
+        return an, enc
 
     run()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = 3
+    reps = 5
     e0.record()
     for _ in range(reps):
-        enc = run()
+        an, enc = run()
     e1.record()
     torch.cuda.synchronize()
     t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
+    # where the time goes: CUDA events at the phase boundaries of one more run
+    tm = {}
+    run(tm)
+    torch.cuda.synchronize()
+    phases = {"minmax_pass_ms": tm["t0"].elapsed_time(tm["t1"]), "allreduce_range_us": tm["t1"].elapsed_time(tm["t2"]) * 1e3,
+              "histogram_pass_ms": tm["t2"].elapsed_time(tm["t3"]), "allreduce_counts_us": tm["t3"].elapsed_time(tm["t4"]) * 1e3,
+              "search_us": tm["t4"].elapsed_time(tm["t5"]) * 1e3}
     tokens = num_batches * 16 * 2048
     peaks, kind = measured_peaks()
     bytes_moved = num_batches * 16 * 2048 * 4096 * 2 * 2  # two passes over every batch
+
+    # parity.  (1) the statistics of this rank's first batch against the CPU oracle, bit for bit;
+    # (2) N > 1: the combined histogram equals one collect over all batches on one GPU
+    from oracle import encoding_analyzer as OE
+
+    one = EA.SqnrEncodingAnalyzer((), num_bins=2048)
+    st = one.observer.collect_stats(batches[0])
+    x_cpu = batches[0].cpu()
+    t0 = time.perf_counter()
+    want = OE.hist_collect(x_cpu, (), 2048)
+    omin, omax = OE.sqnr_encodings(want, (), 255, False)
+    cpu_s = time.perf_counter() - t0
+    gmin, gmax = one.compute_encodings_from_stats(st, 255, False)
+    # torch.histc keeps its counts in float32: bins holding more than 2^24 values are not exact in
+    # the oracle itself (this library counts in integers), so those are compared to float32 accuracy
+    oh, gh = want[0]["histogram"].double(), st.histogram[0].double().cpu()
+    small = oh < 2 ** 24
+    parity = {"histogram_bit_exact": bool((gh[small] == oh[small]).all()) and float(gh.sum()) == float(batches[0].numel()),
+              "bins_beyond_float32_exact_range": int((~small).sum()),
+              "their_max_rel_diff": float(((gh[~small] - oh[~small]).abs() / oh[~small]).max()) if bool((~small).any()) else 0.0,
+              "edges_bit_exact": _bits_equal(st.bin_edges[0], want[0]["bin_edges"]),
+              "min_max_bit_exact": _bits_equal(st.min[0], want[0]["min"]) and _bits_equal(st.max[0], want[0]["max"]),
+              "sqnr_encoding_rel_err": max(_rel_err(gmin, omin), _rel_err(gmax, omax)),
+              "what": "one batch: collect_stats + SQNR encodings against the CPU oracle"}
+    parity["ok"] = (parity["histogram_bit_exact"] and parity["their_max_rel_diff"] <= 1e-6 and parity["edges_bit_exact"]
+                    and parity["min_max_bit_exact"] and parity["sqnr_encoding_rel_err"] <= 1e-5)
+    if world > 1:
+        whole = EA.SqnrEncodingAnalyzer((), num_bins=2048)
+        D.calibrate_histogram(whole, everything, None)
+        a, b = an.observer.get_stats(), whole.observer.get_stats()
+        same = (torch.equal(a.histogram, b.histogram) and torch.equal(a.bin_edges, b.bin_edges)
+                and torch.equal(a.min, b.min) and torch.equal(a.max, b.max))
+        wenc = whole.compute_encodings(255, False)
+        same = same and torch.equal(enc[0], wenc[0]) and torch.equal(enc[1], wenc[1])
+        ok = torch.tensor([int(same)], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        parity["sharded_equals_unsharded"] = bool(ok.item())
+        parity["ok"] = parity["ok"] and parity["sharded_equals_unsharded"]
+    del everything
     # the reference's own calling pattern: update_stats batch after batch (range growth + merge)
     seq = EA.SqnrEncodingAnalyzer((), num_bins=2048)
     seq.update_stats(batches[0])
@@ -400,29 +629,41 @@ def calibration_figure(dev, rank, world, num_batches=64):
     torch.cuda.synchronize()
     seq_ms = s0.elapsed_time(s1)
     sequential = {"tokens_per_s_per_gpu": len(batches) * 16 * 2048 / (seq_ms * 1e-3), "ms_per_batch": seq_ms / len(batches),
-                  "what": "analyzer.update_stats on this rank's batches one after the other (no exchange)"}
-    return {"sequential_update_stats": sequential, "metric": "calibration_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "ms": ms,
-            "batches": num_batches, "batch_shape": [16, 2048, 4096], "analyzer": "SQNR, 2048 bins, 17x21 asymmetric candidates",
-            "algorithmic_bytes": bytes_moved, "achieved_GBps_per_gpu": bytes_moved / world / (ms * 1e-3) / 1e9,
-            "frac_of_" + kind + "_hbm": bytes_moved / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-            "encoding_min_max": [float(enc[0]), float(enc[1])]}
+                  "achieved_GBps": len(batches) * 16 * 2048 * 4096 * 2 / (seq_ms * 1e-3) / 1e9,
+                  "what": "analyzer.update_stats on this rank's batches one after the other (no exchange): one pass "
+                          "per batch (histogram against the current range + the batch's min/max), a second one only "
+                          "when the range moved"}
+    out = {"sequential_update_stats": sequential, "metric": "calibration_tokens_per_s", "value": tokens / (ms * 1e-3),
+           "unit": "tokens/s", "ms": ms, "batches": num_batches, "batch_shape": [16, 2048, 4096],
+           "analyzer": "SQNR, 2048 bins, 17x21 asymmetric candidates", "algorithmic_bytes": bytes_moved,
+           "achieved_GBps_per_gpu": bytes_moved / world / (ms * 1e-3) / 1e9,
+           "frac_of_" + kind + "_hbm": bytes_moved / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+           "phases_rank0": phases, "encoding_min_max": [float(enc[0]), float(enc[1])], "parity": parity}
+    if cpu and rank == 0:
+        out["cpu_baseline"] = {"value": 16 * 2048 / cpu_s, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                               "sample": "one batch of 32768 tokens: histogram collection + SQNR search through the CPU oracle"}
+    return out
 
 
-def seqmse_figure(dev, rank, world, m=8192, n=4096, k=4096, cands=20):
-    """Config 5: reconstruction loss of 20 candidates for a [4096,4096] bf16 weight on 8192 tokens;
-    output channels split across ranks."""
+def seqmse_figure(dev, rank, world, m=8192, n=4096, k=4096, cands=20, cpu=True):
+    """SeqMSE for the Llama-3-8B q_proj shape: reconstruction loss of 20 candidates of a [4096,4096]
+    bf16 weight on 8192 tokens; output channels split across ranks.  Two figures: the loss kernel
+    alone on candidates spread over [0.5 max, max], and the whole search (candidate weights, loss,
+    arg-min, final encodings, all-gather of the winners) through ``optimize_module_sharded``."""
     import torch.distributed as dist
 
     from aimet_b200 import distributed as D
-    from aimet_b200.seq_mse import linear_loss_all_candidates
+    from aimet_b200.quantizer import QuantizeDequantize
+    from aimet_b200.seq_mse import QuantizedLinear, SeqMseParams, SequentialMse, linear_loss_all_candidates
 
     gen = torch.Generator(device=dev).manual_seed(5000)
     x = torch.randn((m, k), device=dev, generator=gen)
     x[:, torch.randperm(k, device=dev, generator=gen)[:20]] *= 30
     x = x.to(torch.bfloat16)
     lo, hi = D.shard_range(n, rank, world)
-    w = (torch.randn((n, k), device=dev, generator=gen) * 0.02).to(torch.bfloat16)[lo:hi].contiguous()
-    fr = torch.linspace(0.5, 1.0, cands, device=dev)  # BASELINE's candidate grid: [0.5 max, max]
+    w_full = (torch.randn((n, k), device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+    w = w_full[lo:hi].contiguous()
+    fr = torch.linspace(0.5, 1.0, cands, device=dev)  # candidates spread over [0.5 max, max]
     smax = w.float().abs().amax(1, keepdim=True) / 7
     wq = torch.stack([(torch.clamp(torch.round(w.float() / (smax * f)), -8, 7) * (smax * f)).to(torch.bfloat16) for f in fr])
     for _ in range(2):
@@ -444,18 +685,93 @@ def seqmse_figure(dev, rank, world, m=8192, n=4096, k=4096, cands=20):
     flops = 2.0 * m * n * k * cands
     peaks, kind = measured_peaks()
     tf = flops / (ms * 1e-3) / 1e12
-    return {"metric": "seqmse_candidate_TFLOPs", "value": tf, "unit": "TFLOP/s (whole job)", "ms": ms,
-            "shape": {"tokens": m, "out": n, "in": k, "candidates": cands}, "per_gpu_TFLOPs": tf / world,
-            "frac_of_" + kind + "_bf16_burst": tf / world / peaks["bf16_tflops"],
-            "frac_of_sustained": tf / world / peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]),
-            "best_index_histogram": torch.bincount(loss.argmin(0), minlength=cands).tolist()}
+
+    # the whole search through the module API, the reference's candidate grid (i + 1) / 20 of the range
+    group = dist.group.WORLD if world > 1 else None
+
+    def build():
+        lin = QuantizedLinear(k, n, bias=False, device=dev, dtype=torch.bfloat16)
+        with torch.no_grad():
+            lin.weight.copy_(w_full)
+        q = QuantizeDequantize((n, 1), 4, True).to(dev)
+        lin.param_quantizers["weight"] = q
+        with q.compute_encodings():
+            q(lin.weight.data)
+        return lin, q
+
+    params = SeqMseParams(num_batches=None, num_candidates=cands, loss_fn="mse")
+    xb = x[None]
+    lin, q = build()
+    D.optimize_module_sharded(lin, xb, xb, params, group)
+    times = []
+    for _ in range(3):
+        lin, q = build()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        best = D.optimize_module_sharded(lin, xb, xb, params, group)
+        s1.record()
+        torch.cuda.synchronize()
+        times.append(s0.elapsed_time(s1))
+    tt = torch.tensor([statistics.median(times)], device=dev)
+    if world > 1:
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    e2e_ms = float(tt.item())
+
+    # parity.  (1) losses of the first rows of this rank's shard against a float64 evaluation of the
+    # same bf16 operands; (2) N > 1: the gathered winners and encodings equal an unsharded search
+    rows = 64
+    xw = x.double() @ w[:rows].double().T
+    want = torch.stack([((xw - x.double() @ wq[c, :rows].double().T) ** 2).sum(0) for c in range(cands)])
+    # bf16 operands: the tensor core truncates its float32 accumulator after each of the K / 16 steps,
+    # which shrinks both products by up to K / 16 * 2^-25 (8e-6 at K = 4096) and the loss by a few
+    # times that; float32 operands take the segmented path and meet 1e-5 (see the parity tests).  The
+    # reference's own bf16 evaluation rounds products and loss terms to bf16 (1e-2 off this value).
+    parity = {"loss_max_rel_err_vs_float64": float(((loss[:, :rows].double() - want).abs() / want).max()),
+              "rows_checked": rows, "tolerance": 1e-4,
+              "tolerance_note": "bf16 operands, K = 4096: accumulator truncation of the tensor core; float32 operands: 1e-5"}
+    parity["ok"] = parity["loss_max_rel_err_vs_float64"] <= 1e-4
+    if world > 1:
+        lin1, q1 = build()
+        best1 = SequentialMse.optimize_module(lin1, xb, xb, params)
+        same = (torch.equal(best.reshape(-1), best1.reshape(-1)) and torch.equal(q.min.detach(), q1.min.detach())
+                and torch.equal(q.max.detach(), q1.max.detach()))
+        ok = torch.tensor([int(same)], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        parity["sharded_equals_unsharded"] = bool(ok.item())
+        parity["ok"] = parity["ok"] and parity["sharded_equals_unsharded"]
+    out = {"metric": "seqmse_candidate_TFLOPs", "value": tf, "unit": "TFLOP/s (whole job)", "ms": ms,
+           "shape": {"tokens": m, "out": n, "in": k, "candidates": cands}, "per_gpu_TFLOPs": tf / world,
+           "frac_of_" + kind + "_bf16_burst": tf / world / peaks["bf16_tflops"],
+           "frac_of_sustained": tf / world / peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]),
+           "best_index_histogram": torch.bincount(loss.argmin(0), minlength=cands).tolist(),
+           "whole_search": {"ms": e2e_ms, "TFLOPs": flops / (e2e_ms * 1e-3) / 1e12,
+                            "what": "optimize_module_sharded: candidate weights (one quantize-dequantize launch), loss "
+                                    "kernel, arg-min, final encodings, all-gather of the winners; X replicated"},
+           "parity": parity}
+    if cpu and rank == 0:
+        from oracle import seq_mse as OS
+
+        crow, ccand = 32, 4
+        wc, xc = w_full[:crow].cpu(), x.cpu()
+        mn, mx = -wc.float().abs().amax(1, keepdim=True), wc.float().abs().amax(1, keepdim=True)
+        t0 = time.perf_counter()
+        OS.optimize_linear(wc, [xc], [xc], mn, mx, -8, 7, True, num_candidates=ccand)
+        cpu_s = time.perf_counter() - t0
+        out["cpu_baseline"] = {"value": 2.0 * m * crow * k * ccand / cpu_s / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                               "kind": "port", "sample": f"{crow} output channels, {ccand} candidates, all {m} tokens through the CPU "
+                                                         "oracle (candidate weights + two products + loss per candidate)"}
+    return out
 
 
-def resnet50_figure(dev, batch=256):
-    """Config 4: forward of a random-init ResNet-50 at batch 256 (224x224 fp32, N(0,1)) with per-channel
-    int8 weight QDQ and per-tensor int8 QDQ on the input and output of all 54 conv / linear layers
-    (the reference's QuantSim model builder is replaced by ``aimet_b200.nn.quantize_model``).
-    QDQ share = 1 - plain forward time / quantized forward time."""
+def resnet50_figure(dev, batch=256, cpu=True):
+    """QuantSim-style forward of a random-init ResNet-50 at batch 256 (224x224 fp32, N(0,1)) with
+    per-channel int8 weight quantize-dequantize and per-tensor int8 quantize-dequantize on the input
+    and output of all 54 conv / linear layers (``aimet_b200.nn.quantize_model`` stands in for the
+    reference's model builder).  The quantize-dequantize time is measured directly: CUDA events
+    around every quantizer call of one forward."""
     try:
         import torchvision
     except ImportError:
@@ -490,32 +806,93 @@ def resnet50_figure(dev, batch=256):
         qmodel(x[64:128])
     torch.cuda.synchronize()
     calib_ms = (time.perf_counter() - t0) * 1e3
-    quant_ms = timed(qmodel)
     layers = list(qnn.quantized_layers(qmodel))
-    act_elems, w_elems = 0, 0
-    hooks = []
+    with qnn.precomputed(qmodel):  # frozen parameters: encodings and quantized weights derived once
+        quant_ms = timed(qmodel)
+        # quantize-dequantize time of one forward: events around every activation quantizer call
+        spans, hooks, act_elems = [], [], 0
 
-    def count(_m, inp, out):
-        nonlocal act_elems
-        act_elems += inp[0].numel() + out.numel()
+        def pre(_m, _inp):
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            spans.append([ev, None])
 
-    for layer in layers:
-        hooks.append(layer.register_forward_hook(count))
-        w_elems += layer.weight.numel()
-    with torch.no_grad():
-        qmodel(x)
-    for h in hooks:
-        h.remove()
-    qdq_bytes = act_elems * 8  # the quantized weights are kept across forwards (25.5 M elements, once)
+        def post(_m, inp, _out):
+            nonlocal act_elems
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            spans[-1][1] = ev
+            act_elems += inp[0].numel()
+
+        for layer in layers:
+            for qz in (layer.input_quantizers[0], layer.output_quantizers[0]):
+                hooks.append(qz.register_forward_pre_hook(pre))
+                hooks.append(qz.register_forward_hook(post))
+        with torch.no_grad():
+            qmodel(x)
+        torch.cuda.synchronize()
+        for h in hooks:
+            h.remove()
+        qdq_ms = sum(a.elapsed_time(b) for a, b in spans)
+    w_elems = sum(layer.weight.numel() for layer in layers)
+    every_ms = timed(qmodel)  # the reference's behaviour: every weight quantized again on every forward
+    qdq_bytes = act_elems * 8
     peaks, kind = measured_peaks()
-    qdq_ms = quant_ms - plain_ms
-    return {"metric": "quantsim_resnet50_images_per_s", "value": batch / (quant_ms * 1e-3), "unit": "images/s",
-            "batch": batch, "quantized_layers": len(layers), "forward_ms": quant_ms, "plain_forward_ms": plain_ms,
-            "qdq_ms": qdq_ms, "qdq_share": qdq_ms / quant_ms, "qdq_algorithmic_bytes": qdq_bytes,
-            "weight_elements": w_elems, "weight_qdq": "kept across forwards while weight and range are unchanged",
-            "calibration_ms_128_images": calib_ms,
-            "qdq_achieved_GBps": qdq_bytes / (qdq_ms * 1e-3) / 1e9,
-            "qdq_frac_of_" + kind + "_hbm": qdq_bytes / (qdq_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    out = {"metric": "quantsim_resnet50_images_per_s", "value": batch / (quant_ms * 1e-3), "unit": "images/s",
+           "batch": batch, "quantized_layers": len(layers), "forward_ms": quant_ms, "plain_forward_ms": plain_ms,
+           "qdq_ms": qdq_ms, "qdq_share": qdq_ms / quant_ms, "qdq_launches": len(spans),
+           "qdq_measured": "CUDA events around each of the activation quantizer calls of one forward",
+           "qdq_algorithmic_bytes": qdq_bytes, "weight_elements": w_elems,
+           "weight_qdq": "inside the precomputed() context the quantized weights are derived once",
+           "forward_ms_weights_quantized_every_forward": every_ms,
+           "images_per_s_weights_quantized_every_forward": batch / (every_ms * 1e-3),
+           "calibration_ms_128_images": calib_ms,
+           "qdq_achieved_GBps": qdq_bytes / (qdq_ms * 1e-3) / 1e9,
+           "qdq_frac_of_" + kind + "_hbm": qdq_bytes / (qdq_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    if cpu:
+        out["cpu_baseline"] = resnet50_cpu_baseline(torchvision)
+    return out
+
+
+def resnet50_cpu_baseline(torchvision, batch=4):
+    """The same forward on the host cores: torch CPU convolutions with the oracle's fake-quantize on
+    the input and output of every conv / linear layer and per-channel weights."""
+    from oracle import affine as OA
+    from oracle import encoding_analyzer as OE
+    from oracle import quantizer as OQ
+
+    torch.manual_seed(4000)
+    model = torchvision.models.resnet50(weights=None).eval()
+    x = torch.randn(batch, 3, 224, 224)
+    enc = {}
+
+    def qdq(t, key):
+        if key not in enc:
+            mn, mx = OE.minmax_collect(t, (), None)
+            mn, mx = OE.minmax_encodings(mn, mx, 255, False)
+            enc[key] = OQ.scale_offset_from_min_max(mn.float(), mx.float(), 0, 255, False)
+        s, o = enc[key]
+        return OA.fake_quantize(t, s, o, 0, 255)
+
+    hooks = []
+    for name, mod in model.named_modules():
+        if isinstance(mod, (torch.nn.Conv2d, torch.nn.Linear)):
+            shape = (mod.weight.shape[0],) + (1,) * (mod.weight.dim() - 1)
+            mn, mx = OE.minmax_collect(mod.weight.detach(), shape, None)
+            mn, mx = OE.minmax_encodings(mn, mx, 255, True)
+            s, o = OQ.scale_offset_from_min_max(mn.float(), mx.float(), -128, 127, True)
+            with torch.no_grad():
+                mod.weight.copy_(OA.fake_quantize(mod.weight.detach(), s, o, -128, 127))
+            hooks.append(mod.register_forward_pre_hook(lambda m, inp, n=name: (qdq(inp[0], n + ".in"),)))
+            hooks.append(mod.register_forward_hook(lambda m, inp, out, n=name: qdq(out, n + ".out")))
+    with torch.no_grad():
+        model(x)  # calibrates the activation encodings on the first pass
+        t0 = time.perf_counter()
+        model(x)
+        dt = time.perf_counter() - t0
+    return {"value": batch / dt, "unit": "images/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"batch {batch}: torch CPU ResNet-50 with the oracle's fake-quantize on every conv / linear "
+                      "input and output, weights quantized beforehand"}
 
 
 def base_config(n_gpus):
@@ -523,7 +900,8 @@ def base_config(n_gpus):
                         "blockwise int4 (block 64) + LPBQ (int4, 8-bit per-channel scale), scale grads on",
             "elements_per_step": 3 * ROWS * COLS, "algorithmic_bytes_per_element": BYTES_PER_ELEM,
             "l2": "inputs larger than L2: 470 MB touched per encoding vs 126 MB L2",
-            "parallelism": f"replicated layers x{n_gpus}"}
+            "parallelism": f"replicated layers x{n_gpus}",
+            "reference_arm_sample": f"the CPU arm runs {CPU_SAMPLE_ROWS} of the {ROWS} rows per step (figures are per byte)"}
 
 
 def run_reference(args):
@@ -531,15 +909,12 @@ def run_reference(args):
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
-    rows = 512
-    for _ in range(args.warmup):
-        cpu_step(rows)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        cpu_step(rows)
-    dt = (time.perf_counter() - t0) / args.steps
-    gbs = 3 * rows * COLS * BYTES_PER_ELEM / dt / 1e9
-    sample = f"each step = {rows} of {ROWS} rows of the weight, all three encodings, CPU oracle (restated torch path)"
+    step = CpuStep()  # weight, gradient and encodings are prepared once, outside the timed steps
+    for _ in range(max(args.warmup, 1)):
+        step.run()
+    dt = sum(step.run() for _ in range(args.steps)) / args.steps
+    gbs = step.gbps(dt)
+    sample = "each step = " + step.sample + ", CPU oracle (restated torch path)"
     print(json.dumps({
         "impl": "reference", "metric": "qdq_fwd_bwd_algorithmic_GBps", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
@@ -666,16 +1041,26 @@ def run_ours(args):
         }
         if world == 1 and not args.no_cpu:
             out["cpu_baseline"] = cpu_baseline()
+    # parity of the measured step, outside the timed region
+    parity = qdq_parity(resident)
+    if world > 1:
+        parity["row_shards_equal_unsharded"] = qdq_shard_parity(dev, rank, world)
+        parity["ok"] = parity["ok"] and parity["row_shards_equal_unsharded"]
+    if rank == 0:
+        out["parity"] = parity
     extras = {}
     if not args.no_extras:
+        cpu = not args.no_cpu
         del resident, host
         torch.cuda.empty_cache()
-        extras["calibration"] = calibration_figure(dev, rank, world)
+        if world == 1:  # a single per-tensor scale: nothing to shard (replicas only)
+            extras["per_tensor_fp32"] = per_tensor_figure(dev, cpu=cpu)
+        extras["calibration"] = calibration_figure(dev, rank, world, cpu=cpu)
         torch.cuda.empty_cache()
-        extras["seqmse"] = seqmse_figure(dev, rank, world)
+        extras["seqmse"] = seqmse_figure(dev, rank, world, cpu=cpu)
         if world == 1:  # a model forward does not shard: replicas only
             torch.cuda.empty_cache()
-            extras["quantsim_resnet50"] = resnet50_figure(dev)
+            extras["quantsim_resnet50"] = resnet50_figure(dev, cpu=cpu)
     if rank == 0:
         out.update(extras)
         print(json.dumps(out))

@@ -198,9 +198,9 @@ int aimet_b200_histogram_ex(const void *x, const ab_layout *layout, int io_dtype
                             void *scratch, int64_t scratch_bytes, void *stream);
 
 /* The same over a list of tensors of one layout (see aimet_b200_minmax_batches), all binned over
- * the same range with the counts running over the list.  run_if_nonzero, if not NULL, is a device
- * flag read by the kernel: when it is zero the launch does nothing (counts keep their contents) --
- * for a pass that a preceding kernel may find unnecessary, decided without the host waiting. */
+ * the same range with the counts running over the list.  run_if_nonzero, if not NULL, holds one
+ * device flag per histogram, read by the kernel: histograms whose flag is zero are left alone -- for
+ * a pass that a preceding kernel may find unnecessary, decided without the host waiting. */
 int aimet_b200_histogram_batches(const void *const *xs, int32_t num_tensors, const ab_layout *layout,
                                  int io_dtype, int32_t num_bins, const float *lo, const float *hi,
                                  const float *below, const float *above, int64_t *counts,
@@ -242,12 +242,21 @@ int aimet_b200_histogram_merge(const float *new_min, const float *new_max, const
 
 /* The same, and out_moved [H] (int32, may be NULL) = 1 where the updated range no longer ends at
  * the current edges, i.e. where counts taken over the current edges are not the counts over the
- * updated range. */
+ * updated range; out_range [H][4] (may be NULL) = first edge, last edge of the updated range and
+ * the two rounded to stat_dtype (what a histogram pass over the updated range takes as lo, hi,
+ * below, above). */
 int aimet_b200_histogram_merge_ex(const float *new_min, const float *new_max, const float *cur_min,
                                   const float *cur_max, const float *cur_edges, const float *cur_hist,
                                   const float *range_limit, int32_t num_hist, int32_t num_bins,
                                   float *out_min, float *out_max, float *out_carry, float *out_edges,
-                                  int32_t *out_moved, void *stream);
+                                  int32_t *out_moved, float *out_range, int stat_dtype, void *stream);
+
+/* hist_out[h][b] = carry[h][b] + (moved[h] ? redo : counts)[h][b] as float32: the last step of a
+ * sequential update (encoding_analyzer.py:313-323), taking the batch's counts from the pass that is
+ * valid for the updated range. */
+int aimet_b200_histogram_combine(const int64_t *counts, const int64_t *redo, const float *carry,
+                                 const int32_t *moved, int32_t num_hist, int32_t num_bins,
+                                 float *hist_out, void *stream);
 
 /* Expected clipping + rounding noise of every (delta, offset) candidate against
  * a histogram, and the arg-min per histogram.

@@ -249,11 +249,11 @@ def test_lists_of_tensors_in_one_launch(dtype):
         assert torch.equal(counts, want)
         assert_same(fmn, mn, "min from the histogram pass")
         assert_same(fmx, mx, "max from the histogram pass")
-        # a conditional launch that is switched off leaves the counts alone
+        # a conditional launch leaves the counts of switched-off histograms alone
         keep = counts.clone()
-        EA._histogram_batches(lays, 256, lo, hi, below, above, counts=counts, run_if=torch.zeros(1, dtype=torch.int32, device="cuda"))
+        EA._histogram_batches(lays, 256, lo, hi, below, above, counts=counts, run_if=torch.zeros(lays[0].count, dtype=torch.int32, device="cuda"))
         assert torch.equal(counts, keep)
-        EA._histogram_batches(lays, 256, lo, hi, below, above, counts=counts, run_if=torch.ones(1, dtype=torch.int32, device="cuda"))
+        EA._histogram_batches(lays, 256, lo, hi, below, above, counts=counts, run_if=torch.ones(lays[0].count, dtype=torch.int32, device="cuda"))
         assert torch.equal(counts, 2 * keep)
 
 
