@@ -27,6 +27,7 @@ import torch
 import torch.distributed as dist
 
 __all__ = [
+    "ALONE",
     "PeerFailure",
     "shard_range",
     "my_batches",
@@ -43,8 +44,19 @@ class PeerFailure(RuntimeError):
     """A collective did not complete because another rank failed, left or timed out."""
 
 
+class _Alone:
+    """Stands for "no exchange: this process alone" where a process group is expected (``None`` means
+    the default group once one is initialised)."""
+
+    def __repr__(self):
+        return "aimet_b200.distributed.ALONE"
+
+
+ALONE = _Alone()
+
+
 def _world(group) -> Tuple[int, int]:
-    if not dist.is_available() or not dist.is_initialized():
+    if group is ALONE or not dist.is_available() or not dist.is_initialized():
         return 0, 1
     return dist.get_rank(group), dist.get_world_size(group)
 

@@ -597,16 +597,17 @@ def calibration_figure(dev, rank, world, num_batches=64, cpu=True):
     small = oh < 2 ** 24
     parity = {"histogram_bit_exact": bool((gh[small] == oh[small]).all()) and float(gh.sum()) == float(batches[0].numel()),
               "bins_beyond_float32_exact_range": int((~small).sum()),
-              "their_max_rel_diff": float(((gh[~small] - oh[~small]).abs() / oh[~small]).max()) if bool((~small).any()) else 0.0,
+              "their_max_rel_diff_to_the_float32_oracle": float(((gh[~small] - oh[~small]).abs() / oh[~small]).max()) if bool((~small).any()) else 0.0,
               "edges_bit_exact": _bits_equal(st.bin_edges[0], want[0]["bin_edges"]),
               "min_max_bit_exact": _bits_equal(st.min[0], want[0]["min"]) and _bits_equal(st.max[0], want[0]["max"]),
               "sqnr_encoding_rel_err": max(_rel_err(gmin, omin), _rel_err(gmax, omax)),
               "what": "one batch: collect_stats + SQNR encodings against the CPU oracle"}
-    parity["ok"] = (parity["histogram_bit_exact"] and parity["their_max_rel_diff"] <= 1e-6 and parity["edges_bit_exact"]
-                    and parity["min_max_bit_exact"] and parity["sqnr_encoding_rel_err"] <= 1e-5)
+    # (no condition on the bins beyond 2^24: single-threaded, torch.histc's float32 counters stop there)
+    parity["ok"] = (parity["histogram_bit_exact"] and parity["edges_bit_exact"] and parity["min_max_bit_exact"]
+                    and parity["sqnr_encoding_rel_err"] <= 1e-5)
     if world > 1:
         whole = EA.SqnrEncodingAnalyzer((), num_bins=2048)
-        D.calibrate_histogram(whole, everything, None)
+        D.calibrate_histogram(whole, everything, D.ALONE)
         a, b = an.observer.get_stats(), whole.observer.get_stats()
         same = (torch.equal(a.histogram, b.histogram) and torch.equal(a.bin_edges, b.bin_edges)
                 and torch.equal(a.min, b.min) and torch.equal(a.max, b.max))
