@@ -4,6 +4,7 @@
   (aimet_torch's backend protocol); :func:`register_backend` plugs them into an installed aimet_torch.
 * :mod:`aimet_b200.quantizer` -- ``Quantize``, ``QuantizeDequantize``, ``Dequantize``,
   ``GroupedBlockQuantizeDequantize`` modules with learnable ranges.
+* :mod:`aimet_b200.float_quantizer` -- ``FloatQuantizeDequantize`` (fp16 / bf16 / fp8 / fp4 fake-cast), MXFP4, NVFP4.
 * :mod:`aimet_b200.encoding_analyzer` -- MinMax / Percentile / SQNR / TF-enhanced analyzers.
 * :mod:`aimet_b200.seq_mse` -- SeqMSE candidate search for Linear layers.
 * :mod:`aimet_b200.distributed` -- sharded calibration and output-channel sharding helpers.
@@ -15,11 +16,12 @@ fails if that library has not been built (``python -m aimet_b200.build``).
 import importlib
 
 __all__ = [
-    "backend", "quantizer", "encoding_analyzer", "seq_mse", "distributed",
+    "backend", "quantizer", "float_quantizer", "encoding_analyzer", "seq_mse", "distributed", "nn",
     "quantize", "dequantize", "quantize_dequantize", "register_backend",
 ]
 
-_SUBMODULES = ("_lib", "backend", "quantizer", "encoding_analyzer", "seq_mse", "distributed", "build")
+_SUBMODULES = ("_lib", "backend", "quantizer", "float_quantizer", "encoding_analyzer", "seq_mse", "distributed", "nn",
+               "build")
 _FUNCTIONS = ("quantize", "dequantize", "quantize_dequantize")
 
 

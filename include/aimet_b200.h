@@ -143,6 +143,24 @@ int aimet_b200_quantize_dequantize_backward_fixed_scratch(
     int io_dtype, int compute_dtype, int param_dtype, int64_t qmin, int64_t qmax,
     double zero_point_shift, void *grad_x, void *grad_scale, void *grad_offset, void *stream);
 
+/* Floating-point fake-cast: y = fake_cast(clamp(x / scale, -maxval, maxval)) * scale, simulating a
+ * float format with exponent_bits / mantissa_bits on a wider tensor; scale is float32 of the
+ * layout's parameter shape (per-tensor, per-channel or blockwise).
+ * replaces _float_quantize_dequantize (quantization/float/quantizer.py:619-705).
+ *   io_dtype / compute_dtype  AB_F32, AB_F16 or AB_BF16 (equal): the tensor dtype, in which every
+ *                  step is evaluated and rounded as the reference's tensor operations are
+ *   exponent_bias  bias of the format's exponent field (smallest normal number 2^(1 - bias))
+ *   maxval         largest finite value of the format
+ *   flags          1: formats without a torch dtype -- repeat fake_cast_to_ieee_float
+ *                     (fp_quantization.py:157-214) step by step, else round to nearest even onto
+ *                     the format's grid, subnormals included (_cast_decast :704-705)
+ *                  2: the format has infinities: an infinite x / scale passes through (flag 1 only)
+ *                  4: the format's zero is unsigned: zero results are +0 */
+int aimet_b200_float_fake_cast(const void *x, void *y, const float *scale, const ab_layout *layout,
+                               int io_dtype, int compute_dtype, int32_t exponent_bits,
+                               int32_t mantissa_bits, int32_t exponent_bias, double maxval,
+                               int32_t flags, void *stream);
+
 /* ------------------------------------------------------------------------- *
  * Calibration statistics.  The layout must reduce to (outer, channel, inner):
  * one statistic per parameter element, taken over everything that shares it.

@@ -2,7 +2,7 @@
 
 Run where the reference checkout is available (CPU is enough):
 
-    AIMET_REFERENCE_ROOT=<checkout> python tests/golden/make_golden.py [affine|backend_vectors|analyzers|quantizers|seqmse|seqmse_extra ...]
+    AIMET_REFERENCE_ROOT=<checkout> python tests/golden/make_golden.py [affine|backend_vectors|analyzers|quantizers|seqmse|seqmse_extra|float ...]
 
 Every fixture stores the seeded inputs next to the reference's outputs, so the tests that read
 them need neither the reference nor this script.  Nothing here is imported by the product.
@@ -407,6 +407,58 @@ def gen_seqmse_extra():
     _save("seqmse_extra_cases.pt", out)
 
 
+# name, constructor kwargs, input dtype, input shape, quantizer shape, block size, class
+FLOAT_CASES = [
+    ("fp16_per_tensor", dict(dtype=torch.float16), torch.float32, (64, 96), (), None, "float"),
+    ("bf16_per_tensor", dict(dtype=torch.bfloat16), torch.float32, (64, 96), (), None, "float"),
+    ("e4m3fn_per_tensor", dict(dtype=torch.float8_e4m3fn), torch.float32, (64, 96), (), None, "float"),
+    ("e4m3fn_per_tensor_bf16_input", dict(dtype=torch.float8_e4m3fn), torch.bfloat16, (64, 96), (), None, "float"),
+    ("e4m3fn_per_tensor_fp16_input", dict(dtype=torch.float8_e4m3fn), torch.float16, (64, 96), (), None, "float"),
+    ("e5m2_per_channel", dict(dtype=torch.float8_e5m2), torch.float32, (48, 80), (48, 1), None, "float"),
+    ("e5m2_per_channel_bf16_input", dict(dtype=torch.float8_e5m2), torch.bfloat16, (48, 80), (48, 1), None, "float"),
+    ("e4m3fnuz_blockwise", dict(dtype=torch.float8_e4m3fnuz), torch.float32, (32, 128), (32, 4), (1, 32), "float"),
+    ("e5m2fnuz_per_tensor", dict(dtype=torch.float8_e5m2fnuz), torch.float32, (64, 96), (), None, "float"),
+    ("e4m3_ieee_per_tensor", dict(exponent_bits=4, mantissa_bits=3), torch.float32, (64, 96), (), None, "float"),
+    ("e4m3_ieee_per_tensor_bf16_input", dict(exponent_bits=4, mantissa_bits=3), torch.bfloat16, (64, 96), (), None, "float"),
+    ("e3m4_ieee_per_channel", dict(exponent_bits=3, mantissa_bits=4), torch.float32, (48, 80), (48, 1), None, "float"),
+    ("e5m6_ieee_per_tensor_fp16_input", dict(exponent_bits=5, mantissa_bits=6), torch.float16, (64, 96), (), None, "float"),
+    ("fp4_e2m1_blockwise", dict(exponent_bits=2, mantissa_bits=1, finite=True), torch.float32, (32, 128), (32, 4), (1, 32), "float"),
+    ("mxfp4_blocks_of_32", {}, torch.float32, (16, 256), (16, 8), (1, 32), "mxfp4"),
+    ("nvfp4_blocks_of_16", {}, torch.float32, (16, 256), (16, 16), (1, 16), "nvfp4"),
+]
+
+
+def gen_float():
+    """Float fake-cast quantizers: calibrated on the input, then applied to it and to a second tensor
+    with values beyond the calibrated range, infinities, NaN, zeros of both signs and tiny values."""
+    from aimet_torch.quantization.float import FloatQuantizeDequantize
+    from aimet_torch.quantization.float.quantizer import _MXFP4QuantizeDequantize, _NVFP4QuantizeDequantize
+
+    out = {}
+    for idx, (name, kw, in_dtype, xshape, qshape, block, kind) in enumerate(FLOAT_CASES):
+        g = _gen(1500 + idx)
+        x = torch.randn(xshape, generator=g) * torch.exp(torch.randn(xshape[0], 1, generator=g))
+        x2 = torch.randn(xshape, generator=g) * 4
+        flat = x2.view(-1)
+        flat[:12] = torch.tensor([float("inf"), -float("inf"), float("nan"), 0.0, -0.0, 1e-30, -1e-30, 1e30, -1e30, 1e-6,
+                                  1.0, -2.0])
+        x, x2 = x.to(in_dtype), x2.to(in_dtype)
+        if kind == "mxfp4":
+            q = _MXFP4QuantizeDequantize(qshape, block)
+        elif kind == "nvfp4":
+            q = _NVFP4QuantizeDequantize(qshape, block)
+        else:
+            q = FloatQuantizeDequantize(shape=qshape, block_size=block, **kw)
+        with q.compute_encodings():
+            dyn = q(x)
+        y, y2 = q(x), q(x2)
+        out[name] = dict(kwargs=kw, kind=kind, in_dtype=in_dtype, x=x, x2=x2, qshape=qshape, block_size=block,
+                         maxval=q.maxval.detach().clone(), scale=q.get_scale().detach().clone(),
+                         dynamic=dyn.as_subclass(torch.Tensor).detach().clone(),
+                         y=y.as_subclass(torch.Tensor).detach().clone(), y2=y2.as_subclass(torch.Tensor).detach().clone())
+    _save("float_cases.pt", out)
+
+
 GENERATORS = {
     "backend_vectors": gen_backend_vectors,
     "affine": gen_affine,
@@ -414,6 +466,7 @@ GENERATORS = {
     "quantizers": gen_quantizers,
     "seqmse": gen_seqmse,
     "seqmse_extra": gen_seqmse_extra,
+    "float": gen_float,
 }
 
 
