@@ -105,11 +105,12 @@ class AffineEncoding:
 
     @property
     def min(self) -> torch.Tensor:
-        return (self.offset + self.qmin + self.zero_point_shift) * self.scale
+        """(offset + qmin) * scale, without the zero-point shift (quantization/affine/encoding.py:140-152)."""
+        return (self.offset + self.qmin) * self.scale
 
     @property
     def max(self) -> torch.Tensor:
-        return (self.offset + self.qmax + self.zero_point_shift) * self.scale
+        return (self.offset + self.qmax) * self.scale
 
     @property
     def bitwidth(self) -> int:
@@ -126,6 +127,127 @@ class AffineEncoding:
     def to(self, *args, **kwargs):
         return type(self)(self.scale.to(*args, **kwargs), self.offset.to(*args, **kwargs), self.qmin, self.qmax,
                           self.symmetry, self.block_size, self.zero_point_shift, self.producer)
+
+    # ---- the encodings wire format (quantization/affine/encoding.py:332-454) --------------
+    @property
+    def granularity(self) -> str:
+        """(quantization/base/encoding.py:116-128)"""
+        if self.scale.dim() == 0:
+            return "pertensor"
+        if self.block_size is not None:
+            return "blockwise"
+        return "perchannel" if sum(1 for d in self.scale.shape if d > 1) <= 1 else "unknown"
+
+    def _hint_input_shape(self, input_shape) -> "AffineEncoding":
+        """The shape of the tensor this encoding quantizes: needed to name channel and block axes."""
+        self._input_shape_hint = tuple(input_shape)
+        return self
+
+    def _safe_get_channel_and_block_axis(self):
+        """(channel axis, block axis) as negative axes of the scale (quantization/base/encoding.py:142-213)."""
+        hint = getattr(self, "_input_shape_hint", None)
+        if hint is None:
+            raise RuntimeError("Could not safely infer channel and block axes because input shape hint is not provided. "
+                               "Call `_hint_input_shape` before calling this function.")
+        blocks = _concretize_block_size(hint, tuple(self.scale.shape), tuple(self.block_size or ()))
+        chan = [a for a, (n, b) in enumerate(zip(self.scale.shape, blocks)) if n > 1 and b <= 1]
+        blk = [a for a, (n, b) in enumerate(zip(self.scale.shape, blocks)) if n > 1 and b > 1]
+        if len(blk) > 1:
+            raise RuntimeError(f"Multiple non-trivial block axes found: {blk}. Cannot determine a unique block axis.")
+        block_axis = blk[0] if blk else None
+        if not chan and block_axis is not None:  # a singleton dimension can be the channel axis if its block size is 1
+            chan = [a for a, b in enumerate(blocks) if b == 1]
+        if len(chan) > 1:
+            raise RuntimeError(f"Multiple non-trivial channel axes found: {chan}. Cannot determine a unique channel axis.")
+        channel_axis = chan[0] if chan else None
+        if channel_axis is None and block_axis is not None:
+            raise RuntimeError(f"Block axis {block_axis} found without a corresponding channel axis. "
+                               "Cannot determine a unique channel axis.")
+        nd = self.scale.dim()
+        return (None if channel_axis is None else channel_axis - nd, None if block_axis is None else block_axis - nd)
+
+    def _get_export_dtype(self) -> str:
+        nbits = math.ceil(math.log2(self.qmax - self.qmin + 1))
+        return f"int{nbits}" if self.qmin < 0 <= self.qmax else f"uint{nbits}"
+
+    def _to_legacy_format(self):
+        mn, mx, scale = self.min.flatten(), self.max.flatten(), self.scale.flatten()
+        offset = self.offset.flatten() + self.qmin  # the legacy format shifts the offset by qmin
+        encs = [{"min": float(a), "max": float(b), "scale": float(c), "offset": int(d), "bitwidth": self.bitwidth,
+                 "dtype": "int", "is_symmetric": str(self.symmetry)}
+                for a, b, c, d in zip(mn.tolist(), mx.tolist(), scale.tolist(), offset.tolist())]
+        if self.zero_point_shift:
+            encs = [{**e, "zero_point_shift": self.zero_point_shift} for e in encs]
+        return encs
+
+    def to_qnn_encoding_dict(self, encoding_version=None):
+        """The encoding as the reference's exported dictionary, versions "0.6.1", "1.0.0", "2.0.0" and
+        "2.1.0" (quantization/affine/encoding.py:362-454)."""
+        if encoding_version == "0.6.1":
+            return self._to_legacy_format()
+        if encoding_version == "1.0.0":
+            out = {"dtype": "INT", "bw": self.bitwidth, "is_sym": self.symmetry, "scale": self.scale.flatten().tolist()}
+            offset = self.offset - 2 ** (self.bitwidth - 1) if self.signed else self.offset
+            out["offset"] = offset.to(torch.int).flatten().tolist()
+            if self.zero_point_shift != 0.0:
+                assert self.zero_point_shift == 0.5 and self.symmetry
+                out["zero_point_shift"] = [self.zero_point_shift] * len(out["offset"])
+            assert self.granularity != "unknown"
+            if self.granularity == "pertensor":
+                out["enc_type"] = "PER_TENSOR"
+            elif self.granularity == "perchannel":
+                out["enc_type"] = "PER_CHANNEL"
+            else:
+                _, block_axis = self._safe_get_channel_and_block_axis()
+                out["enc_type"] = "PER_BLOCK"
+                out["block_size"] = self.block_size[block_axis]
+                if out["block_size"] == -1:
+                    raise NotImplementedError("Exporting encodings to 1.0.0 format with block size -1 is not "
+                                              "supported yet. Export using sim.export() instead.")
+            return out
+        if encoding_version in ("2.0.0", "2.1.0"):
+            y_scale = self.scale
+            if self.symmetry:
+                zp = torch.full_like(y_scale, math.ceil((self.qmax + self.qmin) / 2), dtype=torch.int32)
+            else:
+                zp = -self.offset.to(torch.int32)
+            if self.zero_point_shift:
+                zp = zp - self.zero_point_shift
+            channel_axis = block_axis = block_size = None
+            if self.granularity != "pertensor":
+                channel_axis, block_axis = self._safe_get_channel_and_block_axis()
+            if block_axis is not None:
+                axis, block_size = block_axis, self.block_size[block_axis]
+            elif channel_axis is not None:
+                axis, y_scale, zp = channel_axis, y_scale.flatten(), zp.flatten()
+            else:
+                axis, y_scale, zp = None, y_scale.squeeze(), zp.squeeze()
+            ret = {"output_dtype": self._get_export_dtype(), "y_scale": y_scale.tolist()}
+            if not bool(torch.all(zp == 0)):
+                ret["y_zero_point"] = zp.tolist()
+            if axis is not None:
+                ret["axis"] = axis
+            if block_size is not None:
+                ret["block_size"] = block_size
+            return ret
+        raise AssertionError(f"Export encoding version {encoding_version} not supported."
+                             "Expected one of: ['0.6.1', '1.0.0', '2.0.0', '2.1.0']")
+
+    @classmethod
+    def _from_qnn_encoding_dict(cls, encoding_dict, version=None) -> "AffineEncoding":
+        """Per-tensor encodings of the 2.x format back into an encoding object (:457-498)."""
+        if version is None:
+            version = "2.0.0" if "y_scale" in encoding_dict or "per_block_int_scale" in encoding_dict else "unknown"
+        if version not in ("2.0.0", "2.1.0"):
+            raise NotImplementedError(f"Only 2.0.0 and 2.1.0 encodings are supported; got {version}")
+        if "per_block_int_scale" in encoding_dict or "axis" in encoding_dict:
+            raise NotImplementedError("Only per-tensor encodings are supported")
+        unsigned, bw = encoding_dict["output_dtype"].split("int")
+        bw = int(bw)
+        qmin, qmax = (0, 2**bw - 1) if unsigned else (-(2 ** (bw - 1)), 2 ** (bw - 1) - 1)
+        offset = -encoding_dict.get("y_zero_point", 0)
+        return cls(torch.tensor(encoding_dict["y_scale"], dtype=torch.float32), torch.tensor(offset, dtype=torch.float32),
+                   qmin, qmax, symmetry=(not unsigned) and offset == 0)
 
     def quantize(self, input: torch.Tensor) -> torch.Tensor:  # pylint: disable=redefined-builtin
         return backend.quantize(input, self.scale.to(input.dtype), self.offset.to(input.dtype), self.qmin, self.qmax,
@@ -149,6 +271,41 @@ class GroupedBlockEncoding(AffineEncoding):
         self.block_grouping = block_grouping
         self.decompressed_bw = decompressed_bw
         self.per_channel_scale = per_channel_scale
+
+    @property
+    def per_block_int_scale(self) -> torch.Tensor:
+        """The integer factor of every block scale: ``scale = per_block_int_scale * per_channel_scale``
+        (quantization/affine/encoding.py:605-620)."""
+        return backend.quantize(self.scale, self.per_channel_scale, torch.zeros_like(self.per_channel_scale), 1,
+                                2 ** (self.decompressed_bw - self.bitwidth), self.block_grouping)
+
+    def to_qnn_encoding_dict(self, encoding_version=None):
+        """(quantization/affine/encoding.py:622-686)"""
+        out = super().to_qnn_encoding_dict(encoding_version)
+        if all(g == 1 for g in self.block_grouping) or encoding_version == "0.6.1":
+            return out  # equivalent to a plain blockwise encoding
+        if encoding_version == "1.0.0":
+            out["bw"] = self.decompressed_bw
+            out["compressed_bw"] = self.bitwidth
+            out["scale"] = self.per_channel_scale.flatten().tolist()
+            out["offset"] = [-(2 ** (self.decompressed_bw - 1)) for _ in out["scale"]]
+            out["enc_type"] = "LPBQ"
+            out["per_block_int_scale"] = self.per_block_int_scale.to(torch.int32).flatten().tolist()
+        elif encoding_version in ("2.0.0", "2.1.0"):
+            zp = out.pop("y_zero_point", None)
+            if zp is not None and bool(torch.any(torch.tensor(zp) != 0)):
+                raise RuntimeError(f"LPBQ only supports symmetric quantization; got non-zero y_zero_point {zp}")
+            output_dtype = f"int{self.bitwidth}" if self.signed else f"uint{self.bitwidth}"
+            int_scale = self.per_block_int_scale.to(torch.int32).tolist()
+            if encoding_version == "2.0.0":
+                del out["y_scale"], out["output_dtype"]
+                out.update({"per_block_int_scale": int_scale, "per_channel_float_scale": self.per_channel_scale.tolist(),
+                            "output_dtype": output_dtype})
+            else:
+                channel_axis, _ = self._safe_get_channel_and_block_axis()
+                out.update({"y_scale": {"x": int_scale, "x_scale": self.per_channel_scale.flatten().tolist(),
+                                        "axis": channel_axis}, "output_dtype": output_dtype})
+        return out
 
 
 def _get_symmetric_offset(qmin, qmax, shape, dtype, device):

@@ -2,7 +2,7 @@
 
 Run where the reference checkout is available (CPU is enough):
 
-    AIMET_REFERENCE_ROOT=<checkout> python tests/golden/make_golden.py [affine|backend_vectors|analyzers|quantizers|seqmse|seqmse_extra|float ...]
+    AIMET_REFERENCE_ROOT=<checkout> python tests/golden/make_golden.py [affine|backend_vectors|analyzers|quantizers|seqmse|seqmse_extra|float|wire ...]
 
 Every fixture stores the seeded inputs next to the reference's outputs, so the tests that read
 them need neither the reference nor this script.  Nothing here is imported by the product.
@@ -459,6 +459,46 @@ def gen_float():
     _save("float_cases.pt", out)
 
 
+# name, class, ctor args, ctor kwargs, weight shape
+WIRE_CASES = [
+    ("per_tensor_asym_uint8", "qdq", ((), 8, False), {}, (16, 24)),
+    ("per_tensor_sym_int8", "qdq", ((), 8, True), {}, (16, 24)),
+    ("per_channel_sym_int4", "qdq", ((16, 1), 4, True), {}, (16, 24)),
+    ("per_channel_asym_uint8_axis1", "qdq", ((1, 24), 8, False), {}, (16, 24)),
+    ("blockwise_sym_int4", "qdq", ((16, 3), 4, True), dict(block_size=(1, 8)), (16, 24)),
+    ("blockwise_conv_sym_int8", "qdq", ((8, 2, 1, 1), 8, True), dict(block_size=(1, 4, 3, 3)), (8, 8, 3, 3)),
+    ("sym_int4_half_step_shift", "qdq", ((), 4, True), dict(zero_point_shift=0.5), (16, 24)),
+    ("lpbq_int4_in_int8", "lpbq", ((16, 3), 4, True, 8), dict(block_size=(1, 8), block_grouping=(1, -1)), (16, 24)),
+    ("lpbq_ungrouped", "lpbq", ((16, 3), 4, True, 8), dict(block_size=(1, 8), block_grouping=(1, 1)), (16, 24)),
+]
+
+
+def gen_wire():
+    """Exported encoding dictionaries (all four versions of the format) of calibrated quantizers."""
+    from aimet_torch.quantization.affine import GroupedBlockQuantizeDequantize, QuantizeDequantize
+
+    out = {}
+    for idx, (name, kind, args, kw, wshape) in enumerate(WIRE_CASES):
+        g = _gen(1600 + idx)
+        w = torch.randn(wshape, generator=g) * 0.3 + 0.05
+        q = (QuantizeDequantize if kind == "qdq" else GroupedBlockQuantizeDequantize)(*args, **kw)
+        with q.compute_encodings():
+            q(w)
+        enc = q.get_encodings()._hint_input_shape(w.shape)
+        dicts = {}
+        for version in ("0.6.1", "1.0.0", "2.0.0", "2.1.0"):
+            try:
+                dicts[version] = enc.to_qnn_encoding_dict(version)
+            except Exception as e:  # noqa: BLE001  the reference refuses some combinations
+                dicts[version] = ("error", type(e).__name__)
+        extra = {}
+        if kind == "lpbq":
+            extra["per_block_int_scale"] = enc.per_block_int_scale.as_subclass(torch.Tensor).detach().clone()
+        out[name] = dict(kind=kind, args=args, kwargs=kw, w=w, min=q.min.detach().clone(), max=q.max.detach().clone(),
+                         granularity=enc.granularity, dicts=dicts, **extra)
+    _save("wire_cases.pt", out)
+
+
 GENERATORS = {
     "backend_vectors": gen_backend_vectors,
     "affine": gen_affine,
@@ -467,6 +507,7 @@ GENERATORS = {
     "seqmse": gen_seqmse,
     "seqmse_extra": gen_seqmse_extra,
     "float": gen_float,
+    "wire": gen_wire,
 }
 
 
