@@ -415,6 +415,45 @@ class _MinMaxObserver(_Observer):
             new_max = stats.max.clone() if new_max is None else torch.maximum(new_max, stats.max)
         self.stats = _MinMaxRange(new_min, new_max)
 
+    @torch.no_grad()
+    def observe(self, input_tensor: torch.Tensor) -> None:
+        """``collect_stats`` + ``merge_stats`` for a caller that does not want the batch's own
+        statistics back (a model-level calibration in pass-through mode observes a hundred tensors per
+        forward): the kernel updates the running min / max in place, two launches and no temporary
+        tensors, and the description of the tensor's layout is kept between calls."""
+        x = _check_input(input_tensor)
+        if x.numel() == 0:
+            raise RuntimeError("cannot collect statistics of an empty tensor")
+        key = (tuple(x.shape), x.stride(), x.dtype, x.device)
+        cached = self.__dict__.get("_layout_cache")
+        if cached is None or cached[0] != key:
+            lay = _StatLayout(x, self.shape, self.block_size)
+            with torch.cuda.device(x.device):
+                nbytes = lib.aimet_b200_stats_scratch_bytes(lay.layout, lay.io)
+            _lib.check(nbytes)
+            in_place = lay.x.data_ptr() == x.data_ptr()  # a permuted view of x itself (no copy was needed)
+            cached = (key, lay, nbytes, in_place)
+            self.__dict__["_layout_cache"] = cached
+        _, lay, nbytes, in_place = cached
+        if not in_place:
+            lay = _StatLayout(x, self.shape, self.block_size)
+        st = self.stats
+        if st.min is None or st.min.dtype != x.dtype or st.min.device != x.device:
+            if st.min is not None:  # statistics of another dtype exist: fall back to the general path
+                return self.merge_stats(self.collect_stats(x))
+            st = _MinMaxRange(torch.full(self.shape, float("inf"), dtype=x.dtype, device=x.device),
+                              torch.full(self.shape, float("-inf"), dtype=x.dtype, device=x.device))
+            self.stats = st
+        with torch.cuda.device(x.device):
+            scratch = _lib.scratch.get(x.device, nbytes)
+            rc = lib.aimet_b200_minmax_running(x.data_ptr() if in_place else lay.x.data_ptr(), lay.layout, lay.io, 0,
+                                               st.min.data_ptr(), st.max.data_ptr(), _lib.ptr(scratch),
+                                               0 if scratch is None else scratch.numel(), _lib.stream_ptr(x.device))
+        if rc == _lib.AB_ERR_UNSUPPORTED:
+            return self.merge_stats(self.collect_stats(x))
+        _lib.check(rc)
+        return None
+
     def reset_stats(self):
         self.stats = _MinMaxRange()
 
@@ -576,6 +615,15 @@ class EncodingAnalyzer:
         new_stats = self.observer.collect_stats(input_tensor)
         self.observer.merge_stats(new_stats)
         return new_stats
+
+    @torch.no_grad()
+    def observe(self, input_tensor: torch.Tensor) -> None:
+        """``update_stats`` for callers that do not use the returned per-batch statistics."""
+        fast = getattr(self.observer, "observe", None)
+        if fast is not None:
+            fast(input_tensor)
+        else:
+            self.update_stats(input_tensor)
 
     def reset_stats(self):
         self.observer.reset_stats()

@@ -11,6 +11,7 @@ replacement: no config files, no graph analysis, no supergroups.
 from __future__ import annotations
 
 import contextlib
+import math
 from typing import Callable, Iterable, Optional
 
 import torch
@@ -89,10 +90,18 @@ def quantized_layers(model: nn.Module) -> Iterable[QuantizedLayer]:
 
 
 @contextlib.contextmanager
-def compute_encodings(model: nn.Module):
-    """Calibrate every quantizer of the model from the forward passes run inside the context:
-    weights are calibrated on entry, activation quantizers observe (pass-through) and get their
-    ranges on exit."""
+def compute_encodings(model: nn.Module, group=None):
+    """Calibrate every quantizer of the model from the forward passes run inside the context
+    (nn/__init__.py:22-84, nn/base.py:331-427): weights are calibrated on entry, activation quantizers
+    observe in pass-through mode and get their ranges on exit.
+
+    An observing quantizer costs two kernel launches per forward (the running min / max is updated
+    on the device, nothing is allocated or copied; the reference clones every observed activation).
+    ``group``: a ``torch.distributed`` process group whose ranks each run a share of the calibration
+    batches through their replica of the model (data-parallel calibration): on exit the min / max
+    statistics of all quantizers travel in one all-reduce, so every rank ends with the encodings of
+    the whole calibration set."""
+    quantizers = []
     with contextlib.ExitStack() as stack:
         for layer in quantized_layers(model):
             qw = layer.param_quantizers["weight"]
@@ -101,9 +110,45 @@ def compute_encodings(model: nn.Module):
                     qw(layer.layer.weight.detach())
             for q in (*layer.input_quantizers, *layer.output_quantizers):
                 if q is not None:
-                    stack.enter_context(q._compute_encodings(passthrough=True))  # pylint: disable=protected-access
+                    stack.enter_context(q._compute_encodings(passthrough=True, clone=False))  # pylint: disable=protected-access
+                    quantizers.append(q)
         yield
+        if group is not None:
+            _allreduce_minmax_statistics(quantizers, group)
 
+
+def _allreduce_minmax_statistics(quantizers, group):
+    """One MIN all-reduce over the concatenation of every quantizer's (min, -max)."""
+    from . import distributed as D
+    from .encoding_analyzer import _MinMaxObserver, _MinMaxRange
+
+    obs = [q.encoding_analyzer.observer for q in quantizers]
+    if not all(isinstance(o, _MinMaxObserver) for o in obs):
+        raise NotImplementedError("data-parallel model calibration combines min-max statistics; histogram analyzers "
+                                  "need their range before binning (see distributed.calibrate_histogram)")
+    dev = next((o.get_stats().min.device for o in obs if o.get_stats().min is not None), None)
+    if dev is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    parts = []
+    for o in obs:
+        st = o.get_stats()
+        n = math.prod(o.shape)
+        if st.min is None:  # this rank saw nothing for this quantizer
+            parts += [torch.full((n,), float("inf"), device=dev), torch.full((n,), float("inf"), device=dev)]
+        else:
+            parts += [st.min.reshape(-1).float(), -st.max.reshape(-1).float()]
+    packed = torch.cat(parts)
+    D._collective(torch.distributed.all_reduce, packed, op=torch.distributed.ReduceOp.MIN, group=group)  # pylint: disable=protected-access
+    at = 0
+    for o in obs:
+        st = o.get_stats()
+        n = math.prod(o.shape)
+        mn, mx = packed[at:at + n], -packed[at + n:at + 2 * n]
+        at += 2 * n
+        dtype = st.min.dtype if st.min is not None else torch.float32
+        if bool(torch.isinf(mn).all()):
+            continue  # no rank observed this quantizer
+        o.stats = _MinMaxRange(mn.to(dtype).reshape(o.shape), mx.to(dtype).reshape(o.shape))
 
 @contextlib.contextmanager
 def precomputed(model: nn.Module):

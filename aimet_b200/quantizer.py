@@ -582,7 +582,10 @@ class AffineQuantizerBase(QuantizerBase):
             yield
 
     @contextlib.contextmanager
-    def _compute_encodings(self, passthrough: bool = False):
+    def _compute_encodings(self, passthrough: bool = False, clone: bool = True):
+        """``passthrough``: observe without quantizing, returning a copy of the input like the
+        reference does (quantizer.py:628-667) or, with ``clone=False``, the input itself (for callers
+        that know nothing downstream needs a private copy)."""
         if not any(self._is_overwrite_allowed.values()):
             yield
             return
@@ -590,12 +593,17 @@ class AffineQuantizerBase(QuantizerBase):
         dtype, device = self.min.dtype, self.min.device
 
         def observe(input: torch.Tensor) -> torch.Tensor:  # pylint: disable=redefined-builtin
-            run = torch.Tensor.clone if passthrough else self._forward
+            run = (torch.Tensor.clone if clone else (lambda t: t)) if passthrough else self._forward
             if input.numel() == 0:
                 return run(input)
-            batch_stats = self.encoding_analyzer.update_stats(input)
-            if passthrough:  # nothing is quantized while observing: no per-batch encoding needed
+            if passthrough:  # nothing is quantized while observing: no per-batch statistics or encoding needed
+                watch = getattr(self.encoding_analyzer, "observe", None)
+                if watch is not None:
+                    watch(input)
+                else:
+                    self.encoding_analyzer.update_stats(input)
                 return run(input)
+            batch_stats = self.encoding_analyzer.update_stats(input)
             dyn_min, dyn_max = self.encoding_analyzer.compute_encodings_from_stats(
                 batch_stats, self._calibration_steps(), self.symmetric
             )

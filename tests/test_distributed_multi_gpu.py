@@ -77,6 +77,29 @@ def _worker(rank, world, port, ret):
         best1 = SequentialMse.optimize_module(lin1, x, x, params)
         ok["seqmse"] = (torch.equal(best.reshape(-1), best1.reshape(-1)) and torch.equal(q.min, q1.min)
                         and torch.equal(q.max, q1.max))
+        # data-parallel calibration of a model: each rank runs its share of the images through its
+        # replica; one all-reduce combines the min / max statistics of all quantizers
+        from torch import nn as tnn
+
+        from aimet_b200 import nn as qnn
+
+        def make_model():
+            torch.manual_seed(5)
+            net = tnn.Sequential(tnn.Conv2d(3, 8, 3, padding=1), tnn.ReLU(), tnn.Conv2d(8, 8, 3, padding=1), tnn.Flatten(),
+                                 tnn.Linear(8 * 12 * 12, 10)).to(dev).eval()
+            return qnn.quantize_model(net)
+
+        images = torch.randn(8, 3, 12, 12, generator=g).to(dev)
+        sharded, whole = make_model(), make_model()
+        with torch.no_grad(), qnn.compute_encodings(sharded, group=dist.group.WORLD):
+            sharded(images[rank::world])
+        with torch.no_grad(), qnn.compute_encodings(whole):
+            whole(images)
+        same = True
+        for a, b in zip(qnn.quantized_layers(sharded), qnn.quantized_layers(whole)):
+            for qa, qb in ((a.input_quantizers[0], b.input_quantizers[0]), (a.output_quantizers[0], b.output_quantizers[0])):
+                same = same and torch.equal(qa.min, qb.min) and torch.equal(qa.max, qb.max)
+        ok["model_calibration"] = same
         ret[rank] = ok
     finally:
         dist.destroy_process_group()
