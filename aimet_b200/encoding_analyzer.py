@@ -444,11 +444,17 @@ class _MinMaxObserver(_Observer):
             st = _MinMaxRange(torch.full(self.shape, float("inf"), dtype=x.dtype, device=x.device),
                               torch.full(self.shape, float("-inf"), dtype=x.dtype, device=x.device))
             self.stats = st
-        with torch.cuda.device(x.device):
+        def launch():
             scratch = _lib.scratch.get(x.device, nbytes)
-            rc = lib.aimet_b200_minmax_running(x.data_ptr() if in_place else lay.x.data_ptr(), lay.layout, lay.io, 0,
-                                               st.min.data_ptr(), st.max.data_ptr(), _lib.ptr(scratch),
-                                               0 if scratch is None else scratch.numel(), _lib.stream_ptr(x.device))
+            return lib.aimet_b200_minmax_running(x.data_ptr() if in_place else lay.x.data_ptr(), lay.layout, lay.io, 0,
+                                                 st.min.data_ptr(), st.max.data_ptr(), _lib.ptr(scratch),
+                                                 0 if scratch is None else scratch.numel(), _lib.stream_ptr(x.device))
+
+        if x.device.index == torch.cuda.current_device():  # the usual case: no device switch to pay for
+            rc = launch()
+        else:
+            with torch.cuda.device(x.device):
+                rc = launch()
         if rc == _lib.AB_ERR_UNSUPPORTED:
             return self.merge_stats(self.collect_stats(x))
         _lib.check(rc)

@@ -101,20 +101,27 @@ def compute_encodings(model: nn.Module, group=None):
     batches through their replica of the model (data-parallel calibration): on exit the min / max
     statistics of all quantizers travel in one all-reduce, so every rank ends with the encodings of
     the whole calibration set."""
-    quantizers = []
-    with contextlib.ExitStack() as stack:
+    from .quantizer import finish_calibration
+
+    quantizers, weight_quantizers = [], []
+    with torch.no_grad(), contextlib.ExitStack() as stack:  # weights: observed once, in pass-through mode
         for layer in quantized_layers(model):
             qw = layer.param_quantizers["weight"]
-            if qw is not None:
-                with qw.compute_encodings():
-                    qw(layer.layer.weight.detach())
+            if qw is not None and qw.is_overwrite_allowed():
+                stack.enter_context(qw._compute_encodings(passthrough=True, clone=False, finish=False))  # pylint: disable=protected-access
+                qw(layer.layer.weight.detach())
+                weight_quantizers.append(qw)
+    finish_calibration(weight_quantizers)
+    with contextlib.ExitStack() as stack:
+        for layer in quantized_layers(model):
             for q in (*layer.input_quantizers, *layer.output_quantizers):
-                if q is not None:
-                    stack.enter_context(q._compute_encodings(passthrough=True, clone=False))  # pylint: disable=protected-access
+                if q is not None and q.is_overwrite_allowed():
+                    stack.enter_context(q._compute_encodings(passthrough=True, clone=False, finish=False))  # pylint: disable=protected-access
                     quantizers.append(q)
         yield
-        if group is not None:
-            _allreduce_minmax_statistics(quantizers, group)
+    if group is not None:
+        _allreduce_minmax_statistics(quantizers, group)
+    finish_calibration(quantizers)
 
 
 def _allreduce_minmax_statistics(quantizers, group):

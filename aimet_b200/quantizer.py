@@ -33,6 +33,7 @@ from .encoding_analyzer import (
 )
 
 __all__ = [
+    "finish_calibration",
     "AffineEncoding",
     "AffineQuantizerBase",
     "Quantize",
@@ -582,10 +583,12 @@ class AffineQuantizerBase(QuantizerBase):
             yield
 
     @contextlib.contextmanager
-    def _compute_encodings(self, passthrough: bool = False, clone: bool = True):
+    def _compute_encodings(self, passthrough: bool = False, clone: bool = True, finish: bool = True):
         """``passthrough``: observe without quantizing, returning a copy of the input like the
         reference does (quantizer.py:628-667) or, with ``clone=False``, the input itself (for callers
-        that know nothing downstream needs a private copy)."""
+        that know nothing downstream needs a private copy).  ``finish=False`` leaves the statistics
+        in the analyzer on exit: the caller turns them into ranges itself, for many quantizers at
+        once (:func:`finish_calibration`)."""
         if not any(self._is_overwrite_allowed.values()):
             yield
             return
@@ -627,6 +630,12 @@ class AffineQuantizerBase(QuantizerBase):
             yield
         finally:
             self._observer_hook = prev_hook
+        if finish:
+            self._finish_calibration()
+
+    def _finish_calibration(self):
+        """Set ``min`` / ``max`` from the statistics gathered so far (quantizer.py:669-698)."""
+        shape = self.shape
         try:
             enc_min, enc_max = self.encoding_analyzer.compute_encodings(self._calibration_steps(), self.symmetric)
         except StatisticsNotFoundError:
@@ -689,6 +698,41 @@ class AffineQuantizerBase(QuantizerBase):
         if "zero_point_shift" in state:
             self.zero_point_shift = float(state["zero_point_shift"])
         self.shape = tuple(self.min.shape)
+
+
+def finish_calibration(quantizers) -> None:
+    """``_finish_calibration`` of many quantizers with a handful of launches: the statistics of all
+    min-max calibrated quantizers that share a grid (steps, symmetry, dtype) are laid end to end,
+    turned into ranges by one evaluation of the analyzer's rule (elementwise over the statistics, so
+    the values are those of per-quantizer evaluation) and copied back.  A model has a hundred
+    quantizers; one by one their few small tensor operations each dominate a calibration."""
+    from .encoding_analyzer import _MinMaxRange
+
+    groups = {}
+    for q in quantizers:
+        an = q.encoding_analyzer
+        st = an.observer.get_stats() if isinstance(an, MinMaxEncodingAnalyzer) and type(q)._finish_calibration is \
+            AffineQuantizerBase._finish_calibration else None
+        if st is None or st.min is None:
+            q._finish_calibration()  # pylint: disable=protected-access  (another analyzer, or nothing observed)
+            continue
+        key = (q._calibration_steps(), q.symmetric, st.min.dtype, st.min.device)  # pylint: disable=protected-access
+        groups.setdefault(key, []).append((q, st))
+    for (steps, symmetric, _, _), members in groups.items():
+        if len(members) == 1:
+            members[0][0]._finish_calibration()  # pylint: disable=protected-access
+            continue
+        mins = torch.cat([st.min.reshape(-1) for _, st in members])
+        maxs = torch.cat([st.max.reshape(-1) for _, st in members])
+        lo, hi = MinMaxEncodingAnalyzer(()).compute_encodings_from_stats(_MinMaxRange(mins, maxs), steps, symmetric)
+        _flag_extreme_min_max(lo, hi)
+        sizes = [st.min.numel() for _, st in members]
+        with torch.no_grad():
+            for (q, _), a, b in zip(members, lo.split(sizes), hi.split(sizes)):
+                if q._is_overwrite_allowed["min"]:  # pylint: disable=protected-access
+                    q.min.copy_(a.view(q.shape))
+                if q._is_overwrite_allowed["max"]:  # pylint: disable=protected-access
+                    q.max.copy_(b.view(q.shape))
 
 
 class Quantize(AffineQuantizerBase):
