@@ -41,15 +41,19 @@ constexpr int BM = 128;      // output channels per tile (MMA M, TMEM lanes)
 constexpr int BN = 256;      // tokens per tile (MMA N, TMEM columns per accumulator)
 constexpr int BK = 64;       // K elements per pipeline stage: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;   // K elements per tcgen05.mma (16-bit operands)
-constexpr int STAGES = 4;
 constexpr int kEpiWarps = 8;                 // two per TMEM lane quadrant
 constexpr int kSeqThreads = 64 + 32 * kEpiWarps;
 constexpr int kHalfCols = BN / 2;            // columns of one epilogue thread
 constexpr uint32_t A_BYTES = BM * BK * 2;
-constexpr uint32_t B_BYTES = BN * BK * 2;
-constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr uint32_t TMEM_COLS = 512;          // two accumulators of BN columns
-constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+// A CTA on its own stages the whole token tile; a CTA of a pair stages half of it (the tensor cores
+// of both read both halves), which leaves room for a deeper ring.
+template <bool PAIR> struct Ring {
+    static constexpr int kStages = PAIR ? 6 : 4;
+    static constexpr int kTokenRows = PAIR ? BN / 2 : BN;  // rows of the token operand per CTA and stage
+    static constexpr uint32_t kStageBytes = A_BYTES + kTokenRows * BK * 2;
+    static constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
 constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // 2 s per wait
 constexpr int64_t kSegLen = 512;  // columns per segment of a contraction without reference product
 
@@ -111,6 +115,49 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         : "memory");
 }
 
+// --- a pair of CTAs (cluster of two) working on one tile with the tensor cores of both SMs ---
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// the address, in the cluster's shared window, of `addr` in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+// a tile into this CTA's shared memory, completion counted on a barrier of either CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1,
+                                                 uint32_t bar_cluster) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// one arrival on the barrier at this offset in both CTAs of the pair, once the MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"((uint16_t)3)
+        : "memory");
+}
+
 // K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle: 8-row groups are
 // 1024 bytes apart (stride byte offset), the leading byte offset is unused for swizzled K-major
 // layouts (encoded as 1), descriptor version 1 (Blackwell), layout type 2 (SWIZZLE_128B).
@@ -135,6 +182,30 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+template <bool PAIR>
+__device__ __forceinline__ void umma_issue(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    if (PAIR)
+        umma_f16_pair(d_tmem, adesc, bdesc, idesc, accumulate);
+    else
+        umma_f16(d_tmem, adesc, bdesc, idesc, accumulate);
+}
+template <bool PAIR> __device__ __forceinline__ void umma_commit_to(uint32_t bar) {
+    if (PAIR)
+        umma_commit_pair(bar);
+    else
+        umma_commit(bar);
+}
+// true in exactly one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -211,17 +282,22 @@ struct PassIter {
     int wave_g, cur_g, seg_left;
     int num_cand, n_tt, num_blocks, num_seg;
     bool has_ref, ref_pending;
-    int n_ct;
-    __device__ PassIter(const SeqArgs &a, bool ref) {
-        n_ct = a.n_ct;
-        const int64_t units = (int64_t)a.n_ct * a.n_tt * a.num_blocks;
-        const int64_t G = gridDim.x;
+    int n_ct, width, rank;
+    int64_t G;
+    // `pair`: the workers are pairs of CTAs; a pair's unit spans two channel tiles, one per CTA
+    __device__ PassIter(const SeqArgs &a, bool ref, bool pair) {
+        width = pair ? 2 : 1;
+        rank = pair ? (int)(blockIdx.x & 1u) : 0;
+        n_ct = (a.n_ct + width - 1) / width;
+        const int64_t units = (int64_t)n_ct * a.n_tt * a.num_blocks;
+        G = gridDim.x / width;
+        const int64_t me = blockIdx.x / width;
         full_units = units / G * G;
-        wave_unit = blockIdx.x;
+        wave_unit = me;
         wave_g = 0;
         const int64_t items = (units - full_units) * a.num_cand;
-        i = items * blockIdx.x / G;
-        i1 = items * (blockIdx.x + 1) / G;
+        i = items * me / G;
+        i1 = items * (me + 1) / G;
         done_unit = -1;
         cur_unit = 0;
         cur_g = 0;
@@ -239,7 +315,7 @@ struct PassIter {
             cur_g = wave_g;
             if (++wave_g == num_cand) {
                 wave_g = 0;
-                wave_unit += gridDim.x;
+                wave_unit += G;
             }
             return true;
         }
@@ -266,7 +342,7 @@ struct PassIter {
         // token-tile major: the CTAs of a wave share few token tiles (the larger operand tile) and
         // spread over the channel tiles (measured: 4 % faster than channel-tile major)
         p.tt = (int)(t / n_ct);
-        p.ct = (int)(t - (int64_t)p.tt * n_ct);
+        p.ct = (int)(t - (int64_t)p.tt * n_ct) * width + rank;
         if (ref_pending) {
             ref_pending = false;
             p.g = -1;
@@ -280,10 +356,13 @@ struct PassIter {
     }
 };
 
-template <bool HAS_REF>
+template <bool HAS_REF, bool PAIR>
 __global__ void __launch_bounds__(kSeqThreads, 1)
 k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_wq,
          const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_xq, SeqArgs a) {
+    using R = Ring<PAIR>;
+    constexpr int STAGES = R::kStages;
+    constexpr uint32_t STAGE_BYTES = R::kStageBytes;
     extern __shared__ uint8_t smem_raw[];
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
     const uint32_t raw = smem_u32(smem_raw);
@@ -300,6 +379,13 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // In a pair the CTA of rank 0 leads: it issues the MMAs for both, so the barriers that the MMA
+    // thread waits on (operands landed, accumulator read out) are the leader's and collect the
+    // arrivals of both CTAs; the barriers that the MMA thread signals (stage free, accumulator
+    // complete) exist in both CTAs and are signalled together.
+    const uint32_t rank = PAIR ? cluster_rank() : 0u;
+    const uint32_t lead_full = PAIR ? map_to_rank(bar_full, 0) : bar_full;
+    const uint32_t lead_acc_empty = PAIR ? map_to_rank(bar_acc_empty, 0) : bar_acc_empty;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -308,36 +394,46 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(bar_acc_full + 8 * s, 1);
-            mbar_init(bar_acc_empty + 8 * s, 32 * kEpiWarps);
+            mbar_init(bar_acc_empty + 8 * s, (PAIR ? 2 : 1) * 32 * kEpiWarps);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"(TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (warp == 1) {  // one warp of each CTA of a pair allocates: both get the same columns
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                         "r"(TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                         "r"(TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();  // the partner's barriers are initialised before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const unsigned long long limit = a.timeout_ns;
 
     if (warp == 0) {
-        // ---------------- TMA producer ----------------
+        // ---------------- TMA producer (in a pair: each CTA loads its own channel tile and its half
+        // of the token tile) ----------------
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            PassIter it(a, HAS_REF);
+            PassIter it(a, HAS_REF, PAIR);
             Pass p;
             while (ok && it.next(p)) {
                 const CUtensorMap *ma = p.g < 0 ? &tm_w : &tm_wq;
                 const CUtensorMap *mb = p.g < 0 ? &tm_x : &tm_xq;
                 const int row_a = p.g < 0 ? p.ct * BM : (int)((int64_t)p.g * a.N) + p.ct * BM;
+                const int row_b = p.tt * BN + (int)rank * R::kTokenRows;
                 const int64_t seg0 = (int64_t)p.seg * a.seg_len;
                 const int64_t len = a.Kb - seg0 < a.seg_len ? a.Kb - seg0 : a.seg_len;
                 const int col0 = (int)((int64_t)p.blk * a.Kb + seg0);
@@ -346,9 +442,18 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
                     ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, a.status, ST_TIMEOUT_PRODUCER, limit);
                     if (!ok) break;
                     const uint32_t sa = base + stage * STAGE_BYTES;
-                    mbar_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
-                    tma_load_2d(sa, ma, col0 + kb * BK, row_a, bar_full + 8 * stage);
-                    tma_load_2d(sa + A_BYTES, mb, col0 + kb * BK, p.tt * BN, bar_full + 8 * stage);
+                    if (PAIR) {
+                        // the leader's barrier counts the bytes of both CTAs (a partner's bytes may
+                        // land before the leader has announced them: the phase cannot complete
+                        // without the leader's arrival)
+                        if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * STAGE_BYTES);
+                        tma_load_2d_pair(sa, ma, col0 + kb * BK, row_a, lead_full + 8 * stage);
+                        tma_load_2d_pair(sa + A_BYTES, mb, col0 + kb * BK, row_b, lead_full + 8 * stage);
+                    } else {
+                        mbar_expect_tx(bar_full + 8 * stage, STAGE_BYTES);
+                        tma_load_2d(sa, ma, col0 + kb * BK, row_a, bar_full + 8 * stage);
+                        tma_load_2d(sa + A_BYTES, mb, col0 + kb * BK, row_b, bar_full + 8 * stage);
+                    }
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1;
@@ -357,19 +462,24 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
             }
         }
     } else if (warp == 1) {
-        // ---------------- MMA issue ----------------
-        if (lane == 0) {
+        // ---------------- MMA issue (in a pair: by the leader, for both CTAs) ----------------
+        // The whole warp walks the loop and one elected lane issues: all the loop's values are then
+        // uniform over the warp, which lets the operand descriptors be formed where the MMA
+        // instruction reads them.  (Issued from a one-lane branch, every MMA cost about 200 cycles
+        // whatever its size; a 128 x 256 x 16 MMA takes 128 at full rate.)
+        if (rank == 0) {
             int stage = 0;
             uint32_t phase = 0;
             uint32_t pass = 0;  // passes issued by this CTA: accumulator = pass & 1
             bool ok = true;
-            PassIter it(a, HAS_REF);
+            PassIter it(a, HAS_REF, PAIR);
             Pass p;
             while (ok && it.next(p)) {
                 const uint32_t buf = pass & 1u, use = pass >> 1;
                 // the accumulator must have been read out by the epilogue of its previous pass
                 // (a fresh barrier lets the first use through)
                 ok = mbar_wait(bar_acc_empty + 8 * buf, (use & 1u) ^ 1u, abort_flag, a.status, ST_TIMEOUT_MMA, limit);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
@@ -378,6 +488,7 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
                 const int kblocks = (int)((len + BK - 1) / BK);
                 for (int kb = 0; kb < kblocks; ++kb) {
                     ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, a.status, ST_TIMEOUT_MMA, limit);
+                    ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t sa = base + stage * STAGE_BYTES;
@@ -388,18 +499,30 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
                     // columns beyond it are zero-filled by TMA)
                     const int64_t left = len - (int64_t)kb * BK;
                     const int ksteps = left >= BK ? BK / UMMA_K : (int)((left + UMMA_K - 1) / UMMA_K);
-                    for (int k = 0; k < ksteps; ++k) {
-                        // advance 32 bytes (16 elements) inside the swizzled 128-byte row
-                        umma_f16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), a.idesc,
-                                 (kb > 0 || k > 0) ? 1u : 0u);
+                    if (elect_one()) {
+                        // a step advances 32 bytes (16 elements) inside the swizzled 128-byte row; a
+                        // whole stage is straight-line code
+                        if (ksteps == BK / UMMA_K) {
+#pragma unroll
+                            for (int k = 0; k < BK / UMMA_K; ++k)
+                                umma_issue<PAIR>(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), a.idesc,
+                                                 (kb > 0 || k > 0) ? 1u : 0u);
+                        } else {
+                            for (int k = 0; k < ksteps; ++k)
+                                umma_issue<PAIR>(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), a.idesc,
+                                                 (kb > 0 || k > 0) ? 1u : 0u);
+                        }
+                        // frees the stage (in both CTAs) once these MMAs have read it
+                        umma_commit_to<PAIR>(bar_empty + 8 * stage);
                     }
-                    umma_commit(bar_empty + 8 * stage);  // frees the stage once these MMAs have read it
+                    __syncwarp();
                     if (++stage == STAGES) {
                         stage = 0;
                         phase ^= 1;
                     }
                 }
-                if (ok) umma_commit(bar_acc_full + 8 * buf);
+                if (ok && elect_one()) umma_commit_to<PAIR>(bar_acc_full + 8 * buf);
+                __syncwarp();
                 ++pass;
             }
         }
@@ -418,7 +541,7 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
         float sref = 0.f;  // sum of squares of the reference product
         uint32_t pass = 0;
         bool ok = true;
-        PassIter it(a, HAS_REF);
+        PassIter it(a, HAS_REF, PAIR);
         Pass p;
         while (ok && it.next(p)) {
             const uint32_t buf = pass & 1u, use = pass >> 1;
@@ -450,7 +573,10 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
                     }
                 }
                 tc_fence_before();
-                mbar_arrive(bar_acc_empty + 8 * buf);
+                if (PAIR)
+                    mbar_arrive_cluster(lead_acc_empty + 8 * buf);
+                else
+                    mbar_arrive(bar_acc_empty + 8 * buf);
                 continue;
             }
             float s0 = 0.f, s1 = 0.f;
@@ -483,7 +609,10 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
                 }
             }
             tc_fence_before();
-            mbar_arrive(bar_acc_empty + 8 * buf);
+            if (PAIR)
+                mbar_arrive_cluster(lead_acc_empty + 8 * buf);
+            else
+                mbar_arrive(bar_acc_empty + 8 * buf);
             const int64_t n = (int64_t)p.ct * BM + quad * 32 + lane;
             if (n < a.N) {
                 const int64_t sub = (int64_t)p.tt * 2 + half;
@@ -496,11 +625,16 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
     }
 
     // teardown: every role has left its loop (normally or through the abort flag)
+    // (in a pair: in both CTAs, so neither leaves while the other may still signal its barriers)
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();
     tc_fence_after();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        if (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -564,6 +698,44 @@ int make_map(CUtensorMap *map, const void *ptr, int64_t rows, int64_t K, int box
     return AB_OK;
 }
 
+// How many CTA pairs the device runs at once (0: the paired kernel cannot be used), per device.
+int pair_cluster_count(int *out) {
+    static int cached[64];
+    static bool known[64];
+    static std::mutex mu;
+    int dev = 0;
+    AB_CUDA_OK(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 0 || dev >= 64) {
+        *out = 0;
+        return AB_OK;
+    }
+    if (!known[dev]) {
+        int rc = opt_in_smem<k_seqmse<true, true>>(Ring<true>::kSmemBytes);
+        if (rc != AB_OK) return rc;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * (unsigned)sm_count());
+        cfg.blockDim = dim3(kSeqThreads);
+        cfg.dynamicSmemBytes = Ring<true>::kSmemBytes;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, k_seqmse<true, true>, &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            n = 0;
+        }
+        cached[dev] = n;
+        known[dev] = true;
+    }
+    *out = cached[dev];
+    return AB_OK;
+}
+
 int64_t blocks_scratch_bytes(int64_t M, int64_t N, int32_t num_blocks, int32_t num_cand) {
     const int64_t n_tt = (M + BN - 1) / BN;
     return 2 * n_tt * num_cand * N * num_blocks * 2 * (int64_t)sizeof(float);
@@ -615,17 +787,6 @@ extern "C" int aimet_b200_seqmse_linear_loss_blocks(const void *x, const void *x
         return fail(AB_ERR_SCRATCH, "seqmse needs %lld bytes of scratch, got %lld", (long long)need, (long long)scratch_bytes);
 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    CUtensorMap tm_w, tm_wq, tm_x, tm_xq;
-    int rc;
-    if ((rc = make_map(&tm_w, w, has_reference ? N : (int64_t)num_cand * N, K, BM, io_dtype)) != AB_OK) return rc;
-    if ((rc = make_map(&tm_wq, wq, (int64_t)num_cand * N, K, BM, io_dtype)) != AB_OK) return rc;
-    if ((rc = make_map(&tm_x, x, M, K, BN, io_dtype)) != AB_OK) return rc;
-    if ((rc = make_map(&tm_xq, xq, M, K, BN, io_dtype)) != AB_OK) return rc;
-
-    // the opt-in to more than 48 KB of shared memory is a per-device attribute of the kernel
-    if ((rc = opt_in_smem<k_seqmse<true>>(SMEM_BYTES)) != AB_OK) return rc;
-    if ((rc = opt_in_smem<k_seqmse<false>>(SMEM_BYTES)) != AB_OK) return rc;
-
     SeqArgs a;
     a.M = M;
     a.N = N;
@@ -637,8 +798,6 @@ extern "C" int aimet_b200_seqmse_linear_loss_blocks(const void *x, const void *x
     a.n_tt = (int)((M + BN - 1) / BN);
     a.loss_kind = loss_kind;
     a.lowp = lowp_epilogue ? (io_dtype == AB_BF16 ? 1 : 2) : 0;
-    const uint32_t fmt = io_dtype == AB_BF16 ? 1u : 0u;
-    a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     a.partial = static_cast<float *>(scratch);
     a.status = status;
     a.timeout_ns = kWaitTimeoutNs;
@@ -649,14 +808,58 @@ extern "C" int aimet_b200_seqmse_linear_loss_blocks(const void *x, const void *x
     a.seg_len = has_reference ? ((Kb + BK - 1) / BK) * BK : kSegLen;
     a.num_seg = (int)((Kb + a.seg_len - 1) / a.seg_len);
 
+    // With a reference product and at least two channel tiles, pairs of CTAs share a token tile:
+    // each CTA stages half of it and the tensor cores of both SMs read both halves, which takes a
+    // third off the operand bytes an SM has to pull in per pass (the kernel's bound).
+    int pair_clusters = 0;
+    if (has_reference && a.n_ct >= 2) {
+        int rc2 = pair_cluster_count(&pair_clusters);
+        if (rc2 != AB_OK) return rc2;
+    }
+    const bool pair = pair_clusters > 0;
+
+    CUtensorMap tm_w, tm_wq, tm_x, tm_xq;
+    int rc;
+    const int token_rows = pair ? Ring<true>::kTokenRows : Ring<false>::kTokenRows;
+    if ((rc = make_map(&tm_w, w, has_reference ? N : (int64_t)num_cand * N, K, BM, io_dtype)) != AB_OK) return rc;
+    if ((rc = make_map(&tm_wq, wq, (int64_t)num_cand * N, K, BM, io_dtype)) != AB_OK) return rc;
+    if ((rc = make_map(&tm_x, x, M, K, token_rows, io_dtype)) != AB_OK) return rc;
+    if ((rc = make_map(&tm_xq, xq, M, K, token_rows, io_dtype)) != AB_OK) return rc;
+
+    const uint32_t fmt = io_dtype == AB_BF16 ? 1u : 0u;
+    const uint32_t mma_m = pair ? 2 * BM : BM;  // a pair's MMA spans the channel tiles of both CTAs
+    a.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((mma_m >> 4) << 24);
+
     AB_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int32_t), st));
-    const int64_t items = (int64_t)a.n_ct * a.n_tt * num_blocks * num_cand;
-    int grid = sm_count();
-    if (items < grid) grid = (int)items;
-    if (has_reference)
-        k_seqmse<true><<<grid, kSeqThreads, SMEM_BYTES, st>>>(tm_w, tm_wq, tm_x, tm_xq, a);
-    else
-        k_seqmse<false><<<grid, kSeqThreads, SMEM_BYTES, st>>>(tm_w, tm_wq, tm_x, tm_xq, a);
+    if (pair) {
+        const int64_t items = (int64_t)((a.n_ct + 1) / 2) * a.n_tt * num_blocks * num_cand;
+        int clusters = pair_clusters;
+        if (items < clusters) clusters = (int)items;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(2 * clusters));
+        cfg.blockDim = dim3(kSeqThreads);
+        cfg.dynamicSmemBytes = Ring<true>::kSmemBytes;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        AB_CUDA_OK(cudaLaunchKernelEx(&cfg, k_seqmse<true, true>, tm_w, tm_wq, tm_x, tm_xq, a));
+    } else {
+        // the opt-in to more than 48 KB of shared memory is a per-device attribute of the kernel
+        if ((rc = opt_in_smem<k_seqmse<true, false>>(Ring<false>::kSmemBytes)) != AB_OK) return rc;
+        if ((rc = opt_in_smem<k_seqmse<false, false>>(Ring<false>::kSmemBytes)) != AB_OK) return rc;
+        const int64_t items = (int64_t)a.n_ct * a.n_tt * num_blocks * num_cand;
+        int grid = sm_count();
+        if (items < grid) grid = (int)items;
+        if (has_reference)
+            k_seqmse<true, false><<<grid, kSeqThreads, Ring<false>::kSmemBytes, st>>>(tm_w, tm_wq, tm_x, tm_xq, a);
+        else
+            k_seqmse<false, false><<<grid, kSeqThreads, Ring<false>::kSmemBytes, st>>>(tm_w, tm_wq, tm_x, tm_xq, a);
+    }
     AB_LAUNCH_OK();
     const int nvals = loss_kind >= 2 ? 2 : 1;
     const int64_t per_tile = (int64_t)num_cand * N * num_blocks * nvals;
