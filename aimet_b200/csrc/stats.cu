@@ -868,7 +868,7 @@ __global__ void __launch_bounds__(kPrivThreads, 1) k_hist_private(HistPrivArgs a
     const int64_t nvec = (e1 - e0) / NV;
     constexpr int T = kPrivThreads;
     const int64_t rounds_per_x = (nvec + RING * T - 1) / (RING * T);
-    const int64_t total_rounds = rounds_per_x * (flat ? a.num_x : 1);
+    const int64_t num_runs = flat ? (int64_t)a.num_x : 1;  // tensors walked one after the other
     const int64_t G = flat ? gridDim.x : 1, bidx = flat ? blockIdx.x : 0;
     // The input reaches the thread through its own ring of RING 16-byte slots in shared memory,
     // filled by cp.async: RING - 1 vectors per thread (80 KB per SM with six slots) are in flight
@@ -883,17 +883,24 @@ __global__ void __launch_bounds__(kPrivThreads, 1) k_hist_private(HistPrivArgs a
         const Vec16<E> *x;
         int64_t v;
     };
-    auto round_of = [&](int64_t rl) -> Round {
-        const int64_t r = rl * G + bidx;
+    // rounds are walked in steps of G: the tensor index and the round inside it advance by
+    // additions (a 64-bit division per round costs about two instructions per element)
+    int64_t r_xi = rounds_per_x > 0 ? bidx / rounds_per_x : num_runs;
+    int64_t r_lr = rounds_per_x > 0 ? bidx - r_xi * rounds_per_x : 0;
+    auto next_round = [&]() -> Round {
         Round rd;
-        if (r >= total_rounds) {
+        if (r_xi >= num_runs) {
             rd.x = nullptr;
             rd.v = nvec;  // beyond the end: nothing is fetched or binned
             return rd;
         }
-        const int64_t xi = r / rounds_per_x, lr = r - xi * rounds_per_x;
-        rd.x = static_cast<const Vec16<E> *>(flat ? a.xs[xi] : a.x);
-        rd.v = lr * (RING * T) + threadIdx.x;
+        rd.x = static_cast<const Vec16<E> *>(flat ? a.xs[r_xi] : a.x);
+        rd.v = r_lr * (RING * T) + threadIdx.x;
+        r_lr += G;
+        while (r_lr >= rounds_per_x && r_xi < num_runs) {
+            r_lr -= rounds_per_x;
+            ++r_xi;
+        }
         return rd;
     };
     auto src = [&](const Round &rd, int64_t v) -> const Vec16<E> * {
@@ -918,11 +925,11 @@ __global__ void __launch_bounds__(kPrivThreads, 1) k_hist_private(HistPrivArgs a
             feed(w, slot_addr);
         }
     };
-    Round cur = round_of(0);
+    Round cur = next_round();
 #pragma unroll
     for (int j = 0; j < RING - 1; ++j) fill(ring + j * kSlotBytes, cur, cur.v + j * T);
-    for (int64_t rl = 0; cur.x != nullptr; ++rl) {
-        const Round nxt = round_of(rl + 1);
+    while (cur.x != nullptr) {
+        const Round nxt = next_round();
 #pragma unroll
         for (int j = 0; j < RING; ++j) {
             // the slot emptied one step ago takes the vector RING - 1 steps ahead
