@@ -449,3 +449,50 @@ def _takes_fake_quantize_path(tensor, scale, offset, block_size, zero_point_shif
     if sum(1 for d in sshape if d != 1) != 1:
         return False
     return qmin is None or _zero_points_in_grid(offset, qmin, qmax)
+
+
+def quantize_dequantize_stack(input: torch.Tensor, scale: torch.Tensor, offset: torch.Tensor, qmin: int, qmax: int,  # pylint: disable=redefined-builtin
+                              block_size: Optional[List] = None, zero_point_shift: float = 0.0,
+                              parameter_gradients: bool = False) -> torch.Tensor:
+    """``out[c] = quantize_dequantize(input, scale[c], offset[c], ...)`` for every leading index ``c``
+    of the parameters, without autograd: one allocation and one launch per ``c`` on the same input
+    (SeqMSE's candidate weights, seq_mse.py:544-553 of the reference, which quantizes the weight
+    once per candidate).  Each slice takes the arithmetic :func:`quantize_dequantize` would take for
+    it: the fake-quantize fast path unless ``parameter_gradients`` says that the caller's quantizer
+    would have asked for scale / offset gradients."""
+    block_size = _normalize_block_size(block_size)
+    count = scale.shape[0]
+    s0, o0 = scale[0].detach(), offset[0].detach()
+    _validate(input, s0, o0, qmin, qmax, block_size)
+    qmin, qmax = int(qmin), int(qmax)
+    zero_point_shift = zero_point_shift or 0.0
+    fast = (not parameter_gradients and _takes_fake_quantize_path(input, s0, o0, block_size, zero_point_shift)
+            and _zero_points_in_grid(offset, qmin, qmax))
+    internal = torch.float32 if fast else _internal_dtype(input.dtype, qmin, qmax)
+    if not fast and not _is_grid_representable(internal, qmin, qmax):
+        raise RuntimeError(f"{internal} is unable to represent quantized output of range [{qmin}, {qmax}].")
+    x, plan = _prepare(input.detach(), s0, o0, None if fast else block_size, internal)
+    if plan.upcast or list(plan.perm) != list(range(input.dim())):
+        # rare layouts: one ordinary call per slice
+        return torch.stack([quantize_dequantize(input.detach(), scale[c].detach(), offset[c].detach(), qmin, qmax,
+                                                block_size, zero_point_shift) for c in range(count)])
+    s_all = scale.detach().expand((count,) + plan.pshape).to(plan.pt).contiguous()
+    o_all = offset.detach().expand((count,) + plan.pshape).to(plan.pt).contiguous()
+    out = torch.empty((count,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+    if x.numel() == 0:
+        return out
+    pt = _lib.DTYPE_CODE[plan.pt]
+    step_y, step_p = x.numel() * x.element_size(), s_all[0].numel() * s_all.element_size()
+    with torch.cuda.device(x.device):
+        st = _lib.stream_ptr(x.device)
+        for c in range(count):
+            if fast:
+                rc = lib.aimet_b200_fake_quantize(x.data_ptr(), out.data_ptr() + c * step_y, s_all.data_ptr() + c * step_p,
+                                                  o_all.data_ptr() + c * step_p, plan.layout, plan.io, qmin, qmax, st)
+            else:
+                rc = lib.aimet_b200_quantize_dequantize(x.data_ptr(), out.data_ptr() + c * step_y,
+                                                        s_all.data_ptr() + c * step_p, o_all.data_ptr() + c * step_p,
+                                                        plan.layout, plan.io, plan.ct, pt, qmin, qmax,
+                                                        float(zero_point_shift), st)
+            _lib.check(rc)
+    return out

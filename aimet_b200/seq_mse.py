@@ -24,7 +24,7 @@ from typing import Callable, Optional, Tuple
 import torch
 from torch import nn
 
-from . import _lib
+from . import _lib, backend
 from ._lib import lib
 from .encoding_analyzer import _div
 from .quantizer import AffineQuantizerBase, QuantizeDequantize
@@ -272,11 +272,12 @@ class SequentialMse:
 
     @classmethod
     def _all_candidate_weights(cls, quantizer: AffineQuantizerBase, w: torch.Tensor, min_t, max_t, num_candidates: int):
-        """The weight quantize-dequantized under every candidate range, [C, out, in], with one kernel
-        launch: the candidates' ranges are formed with the same element-wise operations as
-        :meth:`_get_candidate` / :meth:`_candidate_encodings` (a leading candidate dimension added),
-        and a quantizer of shape (C, *shape) applies them to the weight repeated along that
-        dimension -- the same arithmetic per element as C separate calls."""
+        """The weight quantize-dequantized under every candidate range, [C, out, in]: the candidates'
+        ranges are formed with the same element-wise operations as :meth:`_get_candidate` /
+        :meth:`_candidate_encodings` (a leading candidate dimension added), a quantizer of shape
+        (C, *shape) turns them into scales and offsets, and one launch per candidate writes its
+        slice of the result from the one weight (the reference quantizes the weight once per
+        candidate too, seq_mse.py:544-553; nothing is repeated or copied here)."""
         from .encoding_analyzer import MinMaxEncodingAnalyzer, _MinMaxRange
 
         c = num_candidates
@@ -293,14 +294,21 @@ class SequentialMse:
         lo, hi = lo.reshape(wide), hi.reshape(wide)
         steps = quantizer.qmax - quantizer.qmin - (1 if quantizer.zero_point_shift == 0.5 else 0)
         lo, hi = MinMaxEncodingAnalyzer(wide).compute_encodings_from_stats(_MinMaxRange(lo, hi), steps, quantizer.symmetric)
-        block = None
-        if quantizer.block_size:
-            block = (1,) * (len(wide) - len(quantizer.block_size)) + tuple(quantizer.block_size)
-        probe = QuantizeDequantize(wide, quantizer.bitwidth, quantizer.symmetric, block_size=block,
+        probe = QuantizeDequantize(wide, quantizer.bitwidth, quantizer.symmetric,
                                    zero_point_shift=quantizer.zero_point_shift).to(w.device)
         probe.signed = quantizer.signed
         probe.set_range(lo, hi)
-        return probe(w.unsqueeze(0).expand((c,) + tuple(w.shape))).detach()
+        with torch.no_grad():
+            scale, offset = probe.get_scale(), probe.get_offset()
+        pshape = (c,) + shape  # per candidate: the quantizer's own parameter shape
+        wants_grad = torch.is_grad_enabled() and any(p.requires_grad for p in quantizer.parameters())
+        offsets = offset.reshape(pshape)
+        const = getattr(offset, "_b200_constant", None)
+        if const is not None:  # a symmetric grid: every zero point is this constant (no device round trip)
+            offsets._b200_constant = const  # pylint: disable=protected-access
+        return backend.quantize_dequantize_stack(w, scale.reshape(pshape), offsets, quantizer.qmin,
+                                                 quantizer.qmax, quantizer.block_size, quantizer.zero_point_shift,
+                                                 parameter_gradients=wants_grad)
 
     @classmethod
     def _freeze_quantizer_encoding(cls, quantizer):
