@@ -259,6 +259,24 @@ __device__ __forceinline__ void fwd_seg_loop(uint32_t ring, const Vec16<typename
     }
 }
 
+// A thread whose whole share is one iteration (short runs: a block of 64 elements is eight vectors
+// for two threads): its vectors were loaded into registers before its parameters, so the two memory
+// latencies overlap.
+template <int IO, int CT, int OP, int PATH, bool PRE>
+__device__ __forceinline__ void fwd_seg_single(const Vec16<typename Elem<IO>::type> (&xv)[kFwdU],
+                                               Vec16<typename Elem<IO>::type> *__restrict__ py, int lane, int nv, int G,
+                                               const Enc<CT> &e, const Grid<typename Arith<CT>::T> &g, uint32_t big2) {
+    using E = typename Elem<IO>::type;
+#pragma unroll
+    for (int u = 0; u < kFwdU; ++u) {
+        if (lane + u * G < nv) {
+            Vec16<E> yv;
+            fwd_vec<IO, CT, OP, PATH, PRE>(xv[u], yv, e, g, big2);
+            py[u * G] = yv;
+        }
+    }
+}
+
 template <int IO, int CT, int OP>
 __global__ void __launch_bounds__(kThreads, 5) k_fwd_seg(FwdSegArgs a) {
     pdl_launch_dependents();
@@ -279,29 +297,36 @@ __global__ void __launch_bounds__(kThreads, 5) k_fwd_seg(FwdSegArgs a) {
     // worth it when the thread has further iterations; a single-iteration thread (short runs) is
     // better off with plain loads
     const bool ringed = p.nv > kFwdU * a.group;
-    if (ringed) fwd_first_issue<E>(ring, px, p.lane, p.nv, a.group);
+    Vec16<E> xv[kFwdU];
+    if (ringed) {
+        fwd_first_issue<E>(ring, px, p.lane, p.nv, a.group);
+    } else {
+#pragma unroll
+        for (int u = 0; u < kFwdU; ++u)
+            if (p.lane + u * a.group < p.nv) xv[u] = px[u * a.group];
+    }
     const Enc<CT> e = load_enc<CT>(a.scale, a.offset, p.param, g);
+#define AB_FWD_RUN(PATH, PRE, BIG)                                                                       \
+    do {                                                                                                 \
+        if (ringed)                                                                                      \
+            fwd_seg_loop<IO, CT, OP, PATH, PRE>(ring, px, py, p.lane, p.nv, a.group, e, g, BIG, true);   \
+        else                                                                                             \
+            fwd_seg_single<IO, CT, OP, PATH, PRE>(xv, py, p.lane, p.nv, a.group, e, g, BIG);             \
+        return;                                                                                          \
+    } while (0)
     if constexpr (kQuant && kIo16) {
         uint32_t big2;
         if (abs_bound16<IO, CT>(e, big2)) {
             if constexpr (CT == IO) {
-                if (vec_packed_ok<CT>(e, g)) {
-                    fwd_seg_loop<IO, CT, OP, PATH_PACKED, true>(ring, px, py, p.lane, p.nv, a.group, e, g, big2, ringed);
-                    return;
-                }
+                if (vec_packed_ok<CT>(e, g)) AB_FWD_RUN(PATH_PACKED, true, big2);
             }
-            if (vec_fast_ok<CT>(e, g)) {
-                fwd_seg_loop<IO, CT, OP, PATH_FAST, true>(ring, px, py, p.lane, p.nv, a.group, e, g, big2, ringed);
-                return;
-            }
+            if (vec_fast_ok<CT>(e, g)) AB_FWD_RUN(PATH_FAST, true, big2);
         }
     } else if constexpr (kQuant && CT != AB_F64) {
-        if (vec_fast_ok<CT>(e, g)) {
-            fwd_seg_loop<IO, CT, OP, PATH_FAST, false>(ring, px, py, p.lane, p.nv, a.group, e, g, 0u, ringed);
-            return;
-        }
+        if (vec_fast_ok<CT>(e, g)) AB_FWD_RUN(PATH_FAST, false, 0u);
     }
-    fwd_seg_loop<IO, CT, OP, PATH_GENERIC, false>(ring, px, py, p.lane, p.nv, a.group, e, g, 0u, ringed);
+    AB_FWD_RUN(PATH_GENERIC, false, 0u);
+#undef AB_FWD_RUN
 }
 
 struct FwdGenArgs {
