@@ -275,7 +275,8 @@ class HostStep:
     def run_many(self, steps):
         """``steps`` steps with the copies of step i+1 (a second stream, a second pair of device
         buffers) overlapping the kernels of step i.  Every step still copies its own inputs from
-        pinned host memory and reads its own result back."""
+        pinned host memory and reads its own result (parameter gradients and checksums) back into
+        pinned host memory; returns the last checksum of every step."""
         self.prepare()
         main = torch.cuda.current_stream(self.dev)
         copier, bufs, pinned = self._copier, self._bufs, self._pinned
@@ -303,12 +304,13 @@ class HostStep:
             free[b].record(main)
             pinned[b].copy_(out, non_blocking=True)  # this step's result, read back asynchronously
             done[b].record(main)
-            if i >= 1:  # the host picks up the previous step's result while this one runs
+            if i >= 1:  # the host picks up the previous step's result while this one runs: it is read
+                # where the copy put it (the pinned buffer is rewritten two steps later)
                 done[1 - b].synchronize()
-                results.append(pinned[1 - b].clone())
+                results.append(float(pinned[1 - b][-1]))
         done[(steps - 1) % 2].synchronize()
-        results.append(pinned[(steps - 1) % 2].clone())
-        self.d2h = results[-1].numel() * 4
+        results.append(float(pinned[(steps - 1) % 2][-1]))
+        self.d2h = pinned[0].numel() * 4
         return results
 
 
@@ -954,6 +956,8 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    # host-side tensor work of a rank (the launcher's default is one thread per process)
+    torch.set_num_threads(max(1, (os.cpu_count() or 1) // world))
 
     from aimet_b200 import _lib
 
