@@ -2,6 +2,8 @@
 
 * :mod:`aimet_b200.backend` -- ``quantize`` / ``dequantize`` / ``quantize_dequantize`` functionals
   (aimet_torch's backend protocol); :func:`register_backend` plugs them into an installed aimet_torch.
+* :mod:`aimet_b200.functional` -- the same three functions for stand-alone use, with the reference's
+  ``(qmin, qmax)`` / ``(bitwidth, signed)`` / ``num_steps=`` call forms (``aimet_b200.quantize`` ...).
 * :mod:`aimet_b200.quantizer` -- ``Quantize``, ``QuantizeDequantize``, ``Dequantize``,
   ``GroupedBlockQuantizeDequantize`` modules with learnable ranges.
 * :mod:`aimet_b200.float_quantizer` -- ``FloatQuantizeDequantize`` (fp16 / bf16 / fp8 / fp4 fake-cast), MXFP4, NVFP4.
@@ -16,11 +18,11 @@ fails if that library has not been built (``python -m aimet_b200.build``).
 import importlib
 
 __all__ = [
-    "backend", "quantizer", "float_quantizer", "encoding_analyzer", "seq_mse", "distributed", "nn",
+    "backend", "functional", "quantizer", "float_quantizer", "encoding_analyzer", "seq_mse", "distributed", "nn",
     "quantize", "dequantize", "quantize_dequantize", "register_backend",
 ]
 
-_SUBMODULES = ("_lib", "backend", "quantizer", "float_quantizer", "encoding_analyzer", "seq_mse", "distributed", "nn",
+_SUBMODULES = ("_lib", "backend", "functional", "quantizer", "float_quantizer", "encoding_analyzer", "seq_mse", "distributed", "nn",
                "build")
 _FUNCTIONS = ("quantize", "dequantize", "quantize_dequantize")
 
@@ -31,7 +33,7 @@ def __getattr__(name):
     if name in _SUBMODULES:
         return importlib.import_module(f"{__name__}.{name}")
     if name in _FUNCTIONS:
-        return getattr(importlib.import_module(f"{__name__}.backend"), name)
+        return getattr(importlib.import_module(f"{__name__}.functional"), name)
     raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
 
 

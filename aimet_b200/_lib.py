@@ -122,8 +122,8 @@ SIGNATURES = {
     "aimet_b200_histogram_combine": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp]),
     "aimet_b200_sqnr_encodings": (
         _i32,
-        [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _f64, _f64, _f64, _vp, _vp, _vp, _vp, _vp, _vp,
-         _vp],
+        [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _f64, _f64, _f64, _f64, _vp, _vp, _vp, _vp, _vp,
+         _vp, _vp],
     ),
     "aimet_b200_histogram": (
         _i32,
@@ -132,7 +132,7 @@ SIGNATURES = {
     "aimet_b200_histogram_merge": (_i32, [_vp] * 7 + [_i32, _i32] + [_vp] * 5),
     "aimet_b200_sqnr_sweep": (
         _i32,
-        [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f64, _f64, _vp, _vp, _vp],
+        [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _f64, _f64, _f64, _vp, _vp, _vp],
     ),
     "aimet_b200_seqmse_blocks_scratch_bytes": (_i64, [_i64, _i64, _i64, _i32, _i32]),
     "aimet_b200_seqmse_linear_loss_blocks": (

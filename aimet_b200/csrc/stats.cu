@@ -1285,10 +1285,21 @@ struct SweepArgs {
     int num_bins, num_cand;
     float num_steps, gamma;
     int use_gamma;
+    float p;  // exponent of the error
     float *noise;
 };
 
 constexpr int kSweepThreads = 128;
+
+// |err|^p the way torch.pow evaluates a scalar exponent: 2 and 3 by multiplication, 0.5 as a
+// square root, 1 as the value itself, anything else through pow
+__device__ __forceinline__ float lp_error(float err, float p) {
+    if (p == 2.0f) return __fmul_rn(err, err);
+    if (p == 1.0f) return err;
+    if (p == 3.0f) return __fmul_rn(__fmul_rn(err, err), err);
+    if (p == 0.5f) return __fsqrt_rn(err);
+    return powf(err, p);
+}
 
 __global__ void __launch_bounds__(kSweepThreads) k_sqnr_sweep(SweepArgs a) {
     pdl_prologue();
@@ -1306,7 +1317,7 @@ __global__ void __launch_bounds__(kSweepThreads) k_sqnr_sweep(SweepArgs a) {
         q = clamp_nan(q, 0.0f, a.num_steps);
         q = __fmul_rn(__fadd_rn(q, offset), delta);
         float err = fabsf(__fsub_rn(q, mid));
-        err = __fmul_rn(__fmul_rn(err, err), hist[b]);
+        err = __fmul_rn(lp_error(err, a.p), hist[b]);
         if (a.use_gamma && clipped) err = __fmul_rn(err, a.gamma);
         acc += (double)err;
     }
@@ -1440,6 +1451,7 @@ struct SweepGenArgs {
     int num_bins, num_cand;
     float gamma;
     int use_gamma;
+    float p;                   // exponent of the error
     float *noise;              // [H][num_cand]
     float *deltas, *offsets;   // [H][num_cand] or NULL
     float *enc_min, *enc_max;  // [H]
@@ -1468,7 +1480,7 @@ __global__ void __launch_bounds__(kSweepThreads) k_sqnr_sweep_gen(SweepGenArgs a
         q = clamp_nan(q, 0.0f, num_steps);
         q = __fmul_rn(__fadd_rn(q, offset), delta);
         float err = fabsf(__fsub_rn(q, mid));
-        err = __fmul_rn(__fmul_rn(err, err), hist[b]);
+        err = __fmul_rn(lp_error(err, a.p), hist[b]);
         if (a.use_gamma && clipped) err = __fmul_rn(err, a.gamma);
         acc += (double)err;
     }
@@ -1641,9 +1653,10 @@ extern "C" int aimet_b200_histogram(const void *x, const ab_layout *layout, int 
 extern "C" int aimet_b200_sqnr_sweep(const float *hist, const float *edge0, const float *width,
                                      const float *deltas, const float *offsets, int32_t offsets_per_hist,
                                      int32_t num_hist, int32_t num_bins, int32_t num_cand, double num_steps,
-                                     double gamma, float *noise_out, int32_t *best_out, void *stream) {
+                                     double gamma, double p, float *noise_out, int32_t *best_out, void *stream) {
     if (num_hist <= 0 || num_bins <= 0 || num_cand <= 0)
         return ab::fail(AB_ERR_INVALID, "num_hist, num_bins and num_cand must be positive");
+    if (!(p > 0)) return ab::fail(AB_ERR_INVALID, "the error exponent p must be positive");
     if (num_hist > 65535) return ab::fail(AB_ERR_UNSUPPORTED, "at most 65535 histograms per call");
     if (!hist || !edge0 || !width || !deltas || !offsets || !noise_out || !best_out)
         return ab::fail(AB_ERR_INVALID, "NULL pointer argument");
@@ -1660,6 +1673,7 @@ extern "C" int aimet_b200_sqnr_sweep(const float *hist, const float *edge0, cons
     a.num_steps = (float)num_steps;
     a.gamma = (float)gamma;
     a.use_gamma = gamma != 1.0;
+    a.p = (float)p;
     a.noise = noise_out;
     dim3 grid((unsigned)num_cand, (unsigned)num_hist);
     ab::launch_pdl(ab::k_sqnr_sweep, grid, ab::kSweepThreads, 0, st, a);
@@ -1703,11 +1717,12 @@ extern "C" int aimet_b200_histogram_edges(const float *min, const float *max, in
 extern "C" int aimet_b200_sqnr_encodings(const float *hist, const float *edges, const float *stat_min,
                                          const float *stat_max, const float *base_offsets, int32_t num_base_offsets,
                                          int32_t num_deltas, int32_t symmetric, int stat_dtype, int32_t num_hist,
-                                         int32_t num_bins, double num_steps, double gamma, double min_scale,
+                                         int32_t num_bins, double num_steps, double gamma, double p, double min_scale,
                                          float *noise_out, float *deltas_out, float *offsets_out, float *enc_min_out,
                                          float *enc_max_out, int32_t *best_out, void *stream) {
     if (num_hist <= 0 || num_bins <= 0 || num_deltas < 2)
         return ab::fail(AB_ERR_INVALID, "num_hist and num_bins must be positive, num_deltas at least 2");
+    if (!(p > 0)) return ab::fail(AB_ERR_INVALID, "the error exponent p must be positive");
     if (num_hist > 65535) return ab::fail(AB_ERR_UNSUPPORTED, "at most 65535 histograms per call");
     if (!symmetric && (num_base_offsets <= 0 || !base_offsets))
         return ab::fail(AB_ERR_INVALID, "asymmetric candidates need the offset grid");
@@ -1733,6 +1748,7 @@ extern "C" int aimet_b200_sqnr_encodings(const float *hist, const float *edges, 
     a.num_cand = symmetric ? num_deltas : num_deltas * (num_base_offsets + 1);
     a.gamma = (float)gamma;
     a.use_gamma = gamma != 1.0;
+    a.p = (float)p;
     a.noise = noise_out;
     a.deltas = deltas_out;
     a.offsets = offsets_out;

@@ -757,8 +757,8 @@ class _LpNormEncodingAnalyzer(_HistogramAnalyzer):
                  histogram_growth_limit: Optional[float] = None, block_size=None):
         if num_bins <= 0:
             raise ValueError("Number of bins cannot be less than or equal to 0.")
-        if p != 2.0:
-            raise NotImplementedError("the sweep kernel evaluates the squared error (p = 2) only")
+        if not p > 0:
+            raise ValueError("The exponent p of the error must be positive.")
         super().__init__(_HistogramObserver(shape=shape, num_bins=num_bins, growth_limit=histogram_growth_limit,
                                             block_size=block_size))
         self.p = p
@@ -813,7 +813,8 @@ class _LpNormEncodingAnalyzer(_HistogramAnalyzer):
             rc = lib.aimet_b200_sqnr_encodings(hist.data_ptr(), edges.data_ptr(), smin.data_ptr(), smax.data_ptr(),
                                                _lib.ptr(grid), 0 if grid is None else grid.numel(), k, int(symmetric),
                                                _stat_dtype_code(st.min.dtype), h, bins, float(num_steps),
-                                               float(self.gamma), _get_minimum_scale(num_steps), noise.data_ptr(),
+                                               float(self.gamma), float(self.p), _get_minimum_scale(num_steps),
+                                               noise.data_ptr(),
                                                _lib.ptr(deltas), _lib.ptr(offsets), emin.data_ptr(), emax.data_ptr(),
                                                best.data_ptr(), _lib.stream_ptr(dev))
         _lib.check(rc)
@@ -885,8 +886,6 @@ class _LpNormEncodingAnalyzer(_HistogramAnalyzer):
     @staticmethod
     def _estimate_clip_and_quant_noise(stats, test_deltas, test_offsets, num_steps, p, gamma=1.0, return_best=False):
         """Noise of every candidate, shape (hists, deltas, offsets): one kernel over the histogram."""
-        if p != 2.0:
-            raise NotImplementedError("the sweep kernel evaluates the squared error (p = 2) only")
         st = _HistogramList.from_stats(stats)
         hist = st.histogram.to(torch.float32).contiguous()
         h, bins = hist.shape
@@ -904,7 +903,8 @@ class _LpNormEncodingAnalyzer(_HistogramAnalyzer):
         with torch.cuda.device(dev):
             rc = lib.aimet_b200_sqnr_sweep(hist.data_ptr(), edge0.data_ptr(), width.data_ptr(), deltas.data_ptr(),
                                            offs.data_ptr(), int(per_hist), h, bins, ncand, float(num_steps),
-                                           float(gamma), noise.data_ptr(), best.data_ptr(), _lib.stream_ptr(dev))
+                                           float(gamma), float(p), noise.data_ptr(), best.data_ptr(),
+                                           _lib.stream_ptr(dev))
         _lib.check(rc)
         noise = noise.view(out_shape)
         return (noise, best) if return_best else noise

@@ -285,11 +285,12 @@ int aimet_b200_histogram_combine(const int64_t *counts, const int64_t *redo, con
  *   noise_out   float32 [H][num_cand]
  *   best_out    int32   [H]  (lowest index among equal minima)
  * _LpNormEncodingAnalyzer._estimate_clip_and_quant_noise / _select_best_candidates
- * (encoding_analyzer.py:822-899) with p = 2 */
+ * (encoding_analyzer.py:822-899); the error of a bin is |quantized midpoint - midpoint|^p times
+ * its count, times gamma where the midpoint was clipped */
 int aimet_b200_sqnr_sweep(const float *hist, const float *edge0, const float *width,
                           const float *deltas, const float *offsets, int32_t offsets_per_hist,
                           int32_t num_hist, int32_t num_bins, int32_t num_cand, double num_steps,
-                          double gamma, float *noise_out, int32_t *best_out, void *stream);
+                          double gamma, double p, float *noise_out, int32_t *best_out, void *stream);
 
 /* The whole SQNR / TF-enhanced range search in two launches: the candidates are formed on the
  * device with the reference's operations in the reference's order, evaluated against the
@@ -307,7 +308,7 @@ int aimet_b200_sqnr_encodings(const float *hist, const float *edges, const float
                               const float *stat_max, const float *base_offsets,
                               int32_t num_base_offsets, int32_t num_deltas, int32_t symmetric,
                               int stat_dtype, int32_t num_hist, int32_t num_bins, double num_steps,
-                              double gamma, double min_scale, float *noise_out, float *deltas_out,
+                              double gamma, double p, double min_scale, float *noise_out, float *deltas_out,
                               float *offsets_out, float *enc_min_out, float *enc_max_out,
                               int32_t *best_out, void *stream);
 

@@ -252,14 +252,14 @@ def sqnr_noise(stats, deltas, offsets, num_steps, gamma=3.0, p=2.0):
 
 
 def sqnr_encodings(stats, shape, num_steps, symmetric, gamma=3.0, asym_deltas=17, sym_deltas=101,
-                   num_offsets=21, return_details=False):
+                   num_offsets=21, return_details=False, p=2.0):
     """_LpNormEncodingAnalyzer.compute_encodings_from_stats (:685-726) for one chunk of histograms
     (the reference processes at most ``max_parallelism`` histograms per chunk; chunks are
     independent, so one chunk restates all of them)."""
     if num_steps <= 0:
         raise ValueError("The number of quantization bins cannot be less than or equal to 0.")
     deltas, offsets = sqnr_candidates(stats, num_steps, symmetric, asym_deltas, sym_deltas, num_offsets)
-    noise = sqnr_noise(stats, deltas, offsets, num_steps, gamma)
+    noise = sqnr_noise(stats, deltas, offsets, num_steps, gamma, p)
     _, idx = torch.min(noise.flatten(start_dim=1), dim=1)
     best_delta = torch.gather(deltas.flatten(start_dim=1), 1, idx[:, None])
     best_offset = offsets if offsets.numel() == 1 else torch.gather(offsets.flatten(start_dim=1), 1, idx[:, None])

@@ -237,6 +237,37 @@ def gen_analyzers():
     _save("analyzer_cases.pt", out)
 
 
+LPNORM_CASES = [
+    # name, p, num_bins, shape, data kind, dtype
+    ("lp1_per_tensor_fp32", 1.0, 512, (), "activation", torch.float32),
+    ("lp3_per_tensor_bf16", 3.0, 512, (), "activation", torch.bfloat16),
+    ("lp2p5_per_channel_fp32", 2.5, 128, (12, 1), "weight", torch.float32),
+    ("lp0p5_per_tensor_fp32", 0.5, 256, (), "shrinking", torch.float32),
+]
+
+
+def gen_lpnorm():
+    """The range search with an error exponent other than 2 (the analyzer behind SqnrEncodingAnalyzer
+    with ``p`` set freely): histograms, the noise of every candidate, the chosen range."""
+    out = {}
+    for idx, (name, p, bins, shape, data, dtype) in enumerate(LPNORM_CASES):
+        batches = _analyzer_batches(data, dtype, 900 + idx)
+        an = ref_ea._LpNormEncodingAnalyzer(shape, bins, p=p, asymmetric_delta_candidates=17, symmetric_delta_candidates=101,
+                                            offset_candidates=21, max_parallelism=64, gamma=3.0)
+        for x in batches:
+            an.update_stats(x)
+        stats = an.observer.get_stats()
+        rec = dict(p=p, num_bins=bins, shape=shape, batches=batches, stats=_stats_to_plain(stats), grids={})
+        for num_steps, sym in ((255, False), (255, True), (15, False)):
+            deltas, offsets = an._pick_test_candidates(stats, num_steps, sym)
+            noise = an._estimate_clip_and_quant_noise(stats, deltas, offsets, num_steps, p, 3.0)
+            mn, mx = an.compute_encodings(num_steps, sym)
+            rec["grids"][(num_steps, sym)] = dict(deltas=deltas.clone(), offsets=offsets.clone(), noise=noise.clone(),
+                                                  min=mn.clone(), max=mx.clone())
+        out[name] = rec
+    _save("lpnorm_cases.pt", out)
+
+
 # --------------------------------------------------------------------------------------------
 # quantizer modules: calibrate, forward, backward
 # --------------------------------------------------------------------------------------------
@@ -503,6 +534,7 @@ GENERATORS = {
     "backend_vectors": gen_backend_vectors,
     "affine": gen_affine,
     "analyzers": gen_analyzers,
+    "lpnorm": gen_lpnorm,
     "quantizers": gen_quantizers,
     "seqmse": gen_seqmse,
     "seqmse_extra": gen_seqmse_extra,

@@ -299,3 +299,25 @@ def test_per_channel_zero_point_outside_the_grid_takes_the_division_arithmetic()
     assert_same(y_in, O.fake_quantize(x, scale, inside, 0, 255), "zero points inside: fake-quantize arithmetic")
     assert_same(y_out, O.quantize_dequantize(x, scale, outside, 0, 255), "a zero point outside: division arithmetic")
     assert_same(y_tag, O.quantize_dequantize(x, scale, torch.full((12, 1), 40.0), 0, 255), "host-known constant")
+
+
+def test_functional_call_forms():
+    """``aimet_b200.quantize`` / ``quantize_dequantize`` / ``dequantize`` with the reference's three
+    ways of naming the grid (backends/__init__.py:50-175, 215-369) give what the explicit
+    ``qmin, qmax`` form gives, and that is the oracle's result."""
+    import aimet_b200
+
+    x = torch.arange(-0.3, 1.3, 0.05).cuda()
+    scale, offset = torch.tensor(1 / 15).cuda(), torch.tensor(0.0).cuda()
+    want_q = O.quantize(x.cpu(), scale.cpu(), offset.cpu(), 0, 15)
+    for got in (aimet_b200.quantize(x, scale, offset, 0, 15), aimet_b200.quantize(x, scale, offset, bitwidth=4),
+                aimet_b200.quantize(x, scale, offset, 4), aimet_b200.quantize(x, scale, offset, num_steps=15, signed=False),
+                aimet_b200.quantize(x, scale, offset, qmin=0, qmax=15)):
+        assert_same(got, want_q)
+    want = O.fake_quantize(x.cpu(), scale.cpu(), offset.cpu(), -8, 7)  # no parameter gradient: the fast path
+    for got in (aimet_b200.quantize_dequantize(x, scale, offset, -8, 7),
+                aimet_b200.quantize_dequantize(x, scale, offset, 4, True),
+                aimet_b200.quantize_dequantize(x, scale, offset, bitwidth=4, signed=True),
+                aimet_b200.quantize_dequantize(x, scale, offset, num_steps=15, signed=True)):
+        assert_same(got, want)
+    assert_same(aimet_b200.dequantize(want_q.cuda(), scale, offset), O.dequantize(want_q, scale.cpu(), offset.cpu()))

@@ -281,3 +281,34 @@ def test_sequential_updates_in_one_pass_when_the_range_holds():
             assert_same(ret.min, torch.stack([w["min"] for w in new]), "returned min")
             if i in (2, 5):  # the batch's own histogram on request
                 assert_stats_same(ret, new, f"update {i} returned")
+
+
+LP_CASES = load_golden("lpnorm_cases.pt")
+
+
+@pytest.mark.parametrize("name", sorted(LP_CASES))
+def test_lp_norm_search(name):
+    """Error exponents other than 2: per-candidate noise within 1e-5 of the reference's, the
+    reference's range wherever the two best candidates are further apart than that."""
+    from aimet_b200 import encoding_analyzer as EA
+
+    case = LP_CASES[name]
+    an = EA._LpNormEncodingAnalyzer(case["shape"], case["num_bins"], p=case["p"], asymmetric_delta_candidates=17,
+                                    symmetric_delta_candidates=101, offset_candidates=21, max_parallelism=64, gamma=3.0)
+    for x in case["batches"]:
+        an.update_stats(x.cuda())
+    st = an.observer.get_stats()
+    for (num_steps, sym), want in case["grids"].items():
+        deltas, offsets = an._pick_test_candidates(st, num_steps, sym)
+        assert_same(deltas, want["deltas"], "candidate deltas")
+        assert_same(offsets, want["offsets"], "candidate offsets")
+        noise = an._estimate_clip_and_quant_noise(st, deltas, offsets, num_steps, case["p"], 3.0)
+        assert torch.allclose(noise.cpu().double(), want["noise"].double(), rtol=1e-5, atol=0), (num_steps, sym)
+        flat = want["noise"].flatten(start_dim=1).double()
+        top2 = flat.topk(2, dim=1, largest=False).values
+        decisive = ((top2[:, 1] - top2[:, 0]) > 1e-5 * top2[:, 1].abs()).reshape(want["min"].shape)
+        mn, mx = an.compute_encodings(num_steps, sym)
+        assert torch.equal(mn.cpu()[decisive], want["min"][decisive]) and torch.equal(mx.cpu()[decisive], want["max"][decisive])
+    with pytest.raises(ValueError):
+        EA._LpNormEncodingAnalyzer((), 16, p=0.0, asymmetric_delta_candidates=17, symmetric_delta_candidates=101,
+                                   offset_candidates=21, max_parallelism=64, gamma=3.0)

@@ -96,3 +96,60 @@ def test_behaviour_under_torch_compile(monkeypatch):
         compiled = torch.compile(fn, backend="eager")(x)
     assert seen == ["fq", "qdq"]
     assert torch.equal(eager, compiled)
+
+
+# (args after (tensor, scale, offset), kwargs) -> (qmin, qmax, block_size, zero_point_shift)
+_CALL_FORMS = [
+    ((0, 255), {}, (0, 255, None, 0.0)),
+    ((-8, 7, (1, 64)), {}, (-8, 7, (1, 64), 0.0)),
+    ((-128, 127, None, 0.5), {}, (-128, 127, None, 0.5)),
+    ((), {"qmin": -4, "qmax": 3}, (-4, 3, None, 0.0)),
+    ((8,), {}, (0, 255, None, 0.0)),
+    ((8, True), {}, (-128, 127, None, 0.0)),
+    ((4, False, (1, 32)), {}, (0, 15, (1, 32), 0.0)),
+    ((), {"bitwidth": 4, "signed": True}, (-8, 7, None, 0.0)),
+    ((), {"bitwidth": 2}, (0, 3, None, 0.0)),
+    ((), {"num_steps": 15, "signed": False}, (0, 15, None, 0.0)),
+    ((), {"num_steps": 15, "signed": True}, (-8, 7, None, 0.0)),
+    ((), {"num_steps": 254, "signed": True, "block_size": (2, 2)}, (-127, 127, (2, 2), 0.0)),
+    ((), {"num_steps": 3, "signed": True, "zero_point_shift": 0.5}, (-2, 1, None, 0.5)),
+    ((16, True), {"block_size": [1, -1]}, (-32768, 32767, [1, -1], 0.0)),
+]
+
+
+def test_call_forms_of_the_functionals():
+    """(qmin, qmax) / (bitwidth, signed) / num_steps= resolve like the reference's ``_parse_args``
+    (backends/__init__.py:408-445)."""
+    from aimet_b200 import functional as F
+
+    for args, kwargs, want in _CALL_FORMS:
+        assert F.parse_grid_arguments(args, kwargs) == want, (args, kwargs)
+    with pytest.raises(KeyError):
+        F.parse_grid_arguments((), {"num_steps": 15})  # signed is required in this form, as in the reference
+    with pytest.raises(RuntimeError, match="zero_point_shift"):
+        F.quantize(torch.zeros(4), torch.tensor(1.0), torch.tensor(0.0), 0, 15, None, 0.5)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        F.quantize_dequantize(torch.zeros(4), torch.tensor(1.0), torch.tensor(0.0), bitwidth=8, signed=True)
+
+
+def test_call_forms_agree_with_the_reference_parser():
+    ref = _reference_checkout()
+    if ref is None:
+        pytest.skip("no checkout of the reference available")
+    script = textwrap.dedent(
+        """
+        import sys
+        sys.path.insert(0, {root!r}); sys.path.insert(0, {golden!r}); sys.path.insert(0, {tests!r})
+        import _reference_shim
+        _reference_shim.install()
+        from aimet_torch.quantization.affine.backends import _parse_args
+        from aimet_b200 import functional as F
+        from test_boundary_cpu import _CALL_FORMS
+        for args, kwargs, want in _CALL_FORMS:
+            assert tuple(_parse_args(args, kwargs)) == F.parse_grid_arguments(args, kwargs) == want, (args, kwargs)
+        print("PARSE-OK")
+        """
+    ).format(root=ROOT, golden=os.path.join(ROOT, "tests", "golden"), tests=os.path.join(ROOT, "tests"))
+    env = dict(os.environ, AIMET_REFERENCE_ROOT=ref)
+    res = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=env, timeout=600)
+    assert res.returncode == 0 and "PARSE-OK" in res.stdout, res.stdout[-2000:] + res.stderr[-4000:]

@@ -81,3 +81,21 @@ def test_histc_binning_rule():
         b = ((v - lo32) * bins / (hi32 - lo32)).to(torch.int64).clamp(max=bins - 1)
         mine = torch.bincount(b, minlength=bins).to(torch.float32)
         assert torch.equal(ref, mine)
+
+
+LP_CASES = load_golden("lpnorm_cases.pt")
+
+
+@pytest.mark.parametrize("name", sorted(LP_CASES))
+def test_lp_norm_search_matches_reference(name):
+    """Error exponents other than 2 (_LpNormEncodingAnalyzer with p set freely): candidates,
+    per-candidate noise and chosen range against the reference's own evaluation."""
+    case = LP_CASES[name]
+    for (num_steps, sym), want in case["grids"].items():
+        deltas, offsets = OA.sqnr_candidates(case["stats"], num_steps, sym)
+        assert_same(deltas, want["deltas"], "deltas")
+        assert_same(offsets, want["offsets"], "offsets")
+        assert_same(OA.sqnr_noise(case["stats"], deltas, offsets, num_steps, gamma=3.0, p=case["p"]), want["noise"], "noise")
+        mn, mx = OA.sqnr_encodings(case["stats"], case["shape"], num_steps, sym, p=case["p"])
+        assert_same(mn, want["min"], "min")
+        assert_same(mx, want["max"], "max")
