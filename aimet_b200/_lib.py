@@ -178,7 +178,32 @@ def ptr(t: torch.Tensor | None) -> int | None:
 
 
 def stream_ptr(device: torch.device) -> int:
-    return torch.cuda.current_stream(device).cuda_stream
+    """The raw handle of the device's current stream."""
+    index = device.index
+    if index is None:
+        index = torch.cuda.current_device()
+    return torch._C._cuda_getCurrentRawStream(index)  # pylint: disable=protected-access
+
+
+class _Here:
+    """Stands in for ``torch.cuda.device(d)`` when ``d`` already is the current device."""
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_HERE = _Here()
+
+
+def on_device(device: torch.device):
+    """Context in which ``device`` is the current CUDA device (kernels are launched on the current
+    device): nothing to switch, and nothing to pay, in the usual case that it already is."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _HERE
+    return torch.cuda.device(device)
 
 
 class _Scratch:

@@ -245,7 +245,7 @@ def _run_forward(tensor, scale, offset, op, qmin, qmax, zps, block_size, interna
     y = torch.empty_like(x, memory_format=torch.contiguous_format)
     if x.numel() > 0:
         pt = _lib.DTYPE_CODE[plan.pt]
-        with torch.cuda.device(x.device):
+        with _lib.on_device(x.device):
             st = _lib.stream_ptr(x.device)
             if op == "q":
                 rc = lib.aimet_b200_quantize(x.data_ptr(), y.data_ptr(), s.data_ptr(), o.data_ptr(), plan.layout,
@@ -311,7 +311,7 @@ class _AffineFunction(torch.autograd.Function):
             if go is not None:
                 go.zero_()
         else:
-            with torch.cuda.device(x.device):
+            with _lib.on_device(x.device):
                 nbytes = lib.aimet_b200_backward_scratch_bytes(plan.layout, plan.io)
                 _lib.check(nbytes)
                 scratch = _lib.scratch.get(x.device, nbytes) if (need_s or need_o) else None
@@ -483,7 +483,7 @@ def quantize_dequantize_stack(input: torch.Tensor, scale: torch.Tensor, offset: 
         return out
     pt = _lib.DTYPE_CODE[plan.pt]
     step_y, step_p = x.numel() * x.element_size(), s_all[0].numel() * s_all.element_size()
-    with torch.cuda.device(x.device):
+    with _lib.on_device(x.device):
         st = _lib.stream_ptr(x.device)
         for c in range(count):
             if fast:

@@ -216,7 +216,7 @@ def _run_minmax(lay: _StatLayout, finite_only: bool):
     x = lay.x
     mn = torch.empty(lay.count, dtype=x.dtype, device=x.device)
     mx = torch.empty(lay.count, dtype=x.dtype, device=x.device)
-    with torch.cuda.device(x.device):
+    with _lib.on_device(x.device):
         nbytes = lib.aimet_b200_stats_scratch_bytes(lay.layout, lay.io)
         _lib.check(nbytes)
         scratch = _lib.scratch.get(x.device, nbytes)
@@ -238,7 +238,7 @@ def _minmax(lay: _StatLayout, finite_only: bool):
 def _run_histogram(lay: _StatLayout, num_bins: int, lo, hi, below, above):
     x = lay.x
     counts = torch.empty((lay.count, num_bins), dtype=torch.int64, device=x.device)
-    with torch.cuda.device(x.device):
+    with _lib.on_device(x.device):
         nbytes = lib.aimet_b200_stats_scratch_bytes(lay.layout, lay.io)
         _lib.check(nbytes)
         scratch = _lib.scratch.get(x.device, nbytes)
@@ -288,7 +288,7 @@ def _minmax_batches(lays, finite_only: bool):
     x = lay.x
     mn = torch.empty(lay.count, dtype=x.dtype, device=x.device)
     mx = torch.empty(lay.count, dtype=x.dtype, device=x.device)
-    with torch.cuda.device(x.device):
+    with _lib.on_device(x.device):
         nbytes = lib.aimet_b200_stats_scratch_bytes(lay.layout, lay.io)
         _lib.check(nbytes)
         scratch = _lib.scratch.get(x.device, max(nbytes, 1))
@@ -314,7 +314,7 @@ def _range_edges(mn: torch.Tensor, mx: torch.Tensor, num_bins: int, growth_limit
     lo, hi, below, above = (torch.empty(h, dtype=torch.float32, device=dev) for _ in range(4))
     limit = torch.empty((h, 2), dtype=torch.float32, device=dev) if want_limit else None
     a, b = f32(mn), f32(mx)
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         rc = lib.aimet_b200_histogram_edges(a.data_ptr(), b.data_ptr(), h, num_bins, _stat_dtype_code(mn.dtype),
                                             float(growth_limit), edges.data_ptr(), lo.data_ptr(), hi.data_ptr(),
                                             below.data_ptr(), above.data_ptr(), _lib.ptr(limit), _lib.stream_ptr(dev))
@@ -339,7 +339,7 @@ def _histogram_batches(lays, num_bins: int, lo, hi, below, above, counts=None, w
     if want_minmax:
         mn = torch.empty(lay.count, dtype=x.dtype, device=x.device)
         mx = torch.empty(lay.count, dtype=x.dtype, device=x.device)
-    with torch.cuda.device(x.device):
+    with _lib.on_device(x.device):
         nbytes = lib.aimet_b200_stats_scratch_bytes(lay.layout, lay.io)
         _lib.check(nbytes)
         scratch = _lib.scratch.get(x.device, max(nbytes, 1))
@@ -372,7 +372,7 @@ def _merge_histograms(new: "_HistogramList", cur: "_HistogramList", limit: torch
             _f32c(limit)]
     moved = torch.empty(h, dtype=torch.int32, device=dev) if want_moved else None
     rng = torch.empty((h, 4), dtype=torch.float32, device=dev) if want_moved else None
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         rc = lib.aimet_b200_histogram_merge_ex(*[t.data_ptr() for t in args], h, num_bins, out_min.data_ptr(),
                                                out_max.data_ptr(), carry.data_ptr(), edges.data_ptr(), _lib.ptr(moved),
                                                _lib.ptr(rng), _stat_dtype_code(stat_dtype), _lib.stream_ptr(dev))
@@ -428,7 +428,7 @@ class _MinMaxObserver(_Observer):
         cached = self.__dict__.get("_layout_cache")
         if cached is None or cached[0] != key:
             lay = _StatLayout(x, self.shape, self.block_size)
-            with torch.cuda.device(x.device):
+            with _lib.on_device(x.device):
                 nbytes = lib.aimet_b200_stats_scratch_bytes(lay.layout, lay.io)
             _lib.check(nbytes)
             in_place = lay.x.data_ptr() == x.data_ptr()  # a permuted view of x itself (no copy was needed)
@@ -450,11 +450,8 @@ class _MinMaxObserver(_Observer):
                                                  st.min.data_ptr(), st.max.data_ptr(), _lib.ptr(scratch),
                                                  0 if scratch is None else scratch.numel(), _lib.stream_ptr(x.device))
 
-        if x.device.index == torch.cuda.current_device():  # the usual case: no device switch to pay for
+        with _lib.on_device(x.device):
             rc = launch()
-        else:
-            with torch.cuda.device(x.device):
-                rc = launch()
         if rc == _lib.AB_ERR_UNSUPPORTED:
             return self.merge_stats(self.collect_stats(x))
         _lib.check(rc)
@@ -585,7 +582,7 @@ class _HistogramObserver(_Observer):
         redo = torch.zeros_like(counts)
         bin_over(nr[:, 0], nr[:, 1], nr[:, 2], nr[:, 3], counts=redo, run_if=moved)
         hist = torch.empty((counts.shape[0], n), dtype=torch.float32, device=counts.device)
-        with torch.cuda.device(counts.device):
+        with _lib.on_device(counts.device):
             rc = lib.aimet_b200_histogram_combine(counts.data_ptr(), redo.data_ptr(), carry.data_ptr(), moved.data_ptr(),
                                                   counts.shape[0], n, hist.data_ptr(), _lib.stream_ptr(counts.device))
         _lib.check(rc)
@@ -809,7 +806,7 @@ class _LpNormEncodingAnalyzer(_HistogramAnalyzer):
         emin = torch.empty(h, dtype=torch.float32, device=dev)
         emax = torch.empty(h, dtype=torch.float32, device=dev)
         best = torch.empty(h, dtype=torch.int32, device=dev)
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             rc = lib.aimet_b200_sqnr_encodings(hist.data_ptr(), edges.data_ptr(), smin.data_ptr(), smax.data_ptr(),
                                                _lib.ptr(grid), 0 if grid is None else grid.numel(), k, int(symmetric),
                                                _stat_dtype_code(st.min.dtype), h, bins, float(num_steps),
@@ -900,7 +897,7 @@ class _LpNormEncodingAnalyzer(_HistogramAnalyzer):
         ncand = deltas.shape[1]
         noise = torch.empty((h, ncand), dtype=torch.float32, device=dev)
         best = torch.empty(h, dtype=torch.int32, device=dev)
-        with torch.cuda.device(dev):
+        with _lib.on_device(dev):
             rc = lib.aimet_b200_sqnr_sweep(hist.data_ptr(), edge0.data_ptr(), width.data_ptr(), deltas.data_ptr(),
                                            offs.data_ptr(), int(per_hist), h, bins, ncand, float(num_steps),
                                            float(gamma), float(p), noise.data_ptr(), best.data_ptr(),

@@ -166,7 +166,7 @@ def float_quantize_dequantize(input: torch.Tensor, finfo: _finfo, scale: torch.T
         s = scale.detach().to(torch.float32).contiguous()
         io = _lib.DTYPE_CODE[out_dtype]
         flags = (0 if finfo.to_torch_dtype() is not None else 1) | (0 if finfo.finite else 2) | (4 if finfo.unsigned_zero else 0)
-        with torch.cuda.device(x.device):
+        with _lib.on_device(x.device):
             rc = lib.aimet_b200_float_fake_cast(xd.data_ptr(), y.data_ptr(), s.data_ptr(), lay, io, io, finfo.exponent_bits,
                                                 finfo.mantissa_bits, finfo.exponent_bias, float(finfo.max), flags,
                                                 _lib.stream_ptr(x.device))

@@ -152,7 +152,7 @@ def _launch(x, xq, w, wq_all, num_blocks, kind, lowp, has_ref, status_sink):
     nvals = 2 if kind >= 2 else 1
     out = torch.empty((c, n, num_blocks, nvals), dtype=torch.float32, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         nbytes = lib.aimet_b200_seqmse_blocks_scratch_bytes(m, n, k, num_blocks, c)
         _lib.check(nbytes)
         scratch = _lib.scratch.get(dev, nbytes)
