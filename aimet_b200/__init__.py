@@ -22,7 +22,7 @@ __all__ = [
     "quantize", "dequantize", "quantize_dequantize", "register_backend",
 ]
 
-_SUBMODULES = ("_lib", "backend", "functional", "quantizer", "float_quantizer", "encoding_analyzer", "seq_mse", "distributed", "nn",
+_SUBMODULES = ("_lib", "backend", "functional", "pgs", "quantizer", "float_quantizer", "encoding_analyzer", "seq_mse", "distributed", "nn",
                "build")
 _FUNCTIONS = ("quantize", "dequantize", "quantize_dequantize")
 

@@ -91,6 +91,10 @@ SIGNATURES = {
         _i32,
         [_vp, _vp, _vp, _vp, _lay, _i32, _i32, _i32, _i64, _i64, _f64, _vp, _vp, _vp, _vp, _i64, _vp],
     ),
+    "aimet_b200_quantize_dequantize_backward_ex": (
+        _i32,
+        [_vp, _vp, _vp, _vp, _lay, _i32, _i32, _i32, _i64, _i64, _f64, _f64, _f64, _vp, _vp, _vp, _vp, _i64, _vp],
+    ),
     "aimet_b200_fixed_scratch_capacity": (_i64, []),
     "aimet_b200_quantize_dequantize_backward_fixed_scratch": (
         _i32,

@@ -18,7 +18,7 @@ from typing import List, Optional, Sequence, Tuple
 
 import torch
 
-from . import _lib
+from . import _lib, pgs
 from ._lib import lib
 
 __all__ = ["quantize", "dequantize", "quantize_dequantize"]
@@ -289,6 +289,7 @@ class _AffineFunction(torch.autograd.Function):
         y, x, s, o, plan = _run_forward(tensor, scale, offset, op, qmin, qmax, zps, block_size, internal_dtype)
         ctx.plan = plan
         ctx.op, ctx.qmin, ctx.qmax, ctx.zps = op, qmin, qmax, float(zps)
+        ctx.pgs = (pgs.get_pgs_eps(), pgs.get_pgs_multiplier())  # as set when the forward ran, like the reference
         ctx.in_dtype = tensor.dtype
         ctx.scale_meta = (scale.shape, scale.dtype)
         ctx.offset_meta = (offset.shape, offset.dtype)
@@ -329,7 +330,8 @@ class _AffineFunction(torch.autograd.Function):
                 elif ctx.op == "dq":
                     rc = lib.aimet_b200_dequantize_backward(*common, *tail)
                 else:
-                    rc = lib.aimet_b200_quantize_dequantize_backward(*common, ctx.qmin, ctx.qmax, ctx.zps, *tail)
+                    rc = lib.aimet_b200_quantize_dequantize_backward_ex(*common, ctx.qmin, ctx.qmax, ctx.zps, ctx.pgs[0],
+                                                                        ctx.pgs[1], *tail)
             _lib.check(rc)
         if gx is not None:
             gx = _restore(gx, plan, grad).to(ctx.in_dtype)
@@ -435,6 +437,8 @@ def _takes_fake_quantize_path(tensor, scale, offset, block_size, zero_point_shif
     if torch.compiler.is_compiling():
         return False
     if torch.is_grad_enabled() and (scale.requires_grad or offset.requires_grad):
+        return False
+    if tensor.requires_grad and pgs.is_pgs_enabled():  # the fake-quantize arithmetic has no such gradient
         return False
     if tensor.dtype not in (torch.float32, torch.float16, torch.bfloat16):
         return False

@@ -377,7 +377,20 @@ struct BwdArgs {
     int64_t rows, row_len, rows_per_tile;
     double qmin, qmax, zps;
     int exact_edges;
+    double pgs_thr, pgs_mult;  // pgs_mult == 1: off
 };
+
+// the launch's grid of the backward kernels, with the rounding-error threshold in the internal dtype
+template <int CT, typename Args> __device__ __forceinline__ Grid<typename Arith<CT>::T> bwd_grid(const Args &a) {
+    using T = typename Arith<CT>::T;
+    Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0, a.exact_edges};
+    if (a.pgs_mult != 1.0) {
+        g.has_pgs = 1;
+        g.pgs_thr = Arith<CT>::rnd((T)a.pgs_thr);
+        g.pgs_mult = (T)a.pgs_mult;
+    }
+    return g;
+}
 
 template <int CT> __device__ __forceinline__ double finalize(double v) {
     using A = Arith<CT>;
@@ -458,7 +471,7 @@ __global__ void __launch_bounds__(kThreads, 4) k_bwd_seg(BwdArgs a) {
     using C = Cvt<T, E>;
     constexpr int VEC = VECT ? 16 / (int)sizeof(E) : 1;
     constexpr bool kIo16 = IO == AB_BF16 || IO == AB_F16;
-    const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0, a.exact_edges};
+    const Grid<T> g = bwd_grid<CT>(a);
 
     const int G = a.group;
     // index arithmetic needs no memory: it runs while the preceding kernel drains
@@ -574,7 +587,7 @@ __global__ void __launch_bounds__(kThreads) k_bwd_col(BwdArgs a) {
     using T = typename A::T;
     using C = Cvt<T, E>;
     constexpr int VEC = VECT ? 16 / (int)sizeof(E) : 1;
-    const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0, a.exact_edges};
+    const Grid<T> g = bwd_grid<CT>(a);
     const E *__restrict__ xp = static_cast<const E *>(a.x);
     const E *__restrict__ gp = static_cast<const E *>(a.gy);
     E *__restrict__ dxp = static_cast<E *>(a.gx);
@@ -711,6 +724,7 @@ struct BwdGenArgs {
     int64_t box;                   // elements per parameter
     double qmin, qmax, zps;
     int exact_edges;
+    double pgs_thr, pgs_mult;
 };
 
 template <int IO, int CT, int OP, bool WANT_O>
@@ -720,7 +734,7 @@ __global__ void __launch_bounds__(kThreads) k_bwd_gen(BwdGenArgs a) {
     using A = Arith<CT>;
     using T = typename A::T;
     using C = Cvt<T, E>;
-    const Grid<T> g{(T)a.qmin, (T)a.qmax, (T)a.zps, a.zps != 0.0, a.exact_edges};
+    const Grid<T> g = bwd_grid<CT>(a);
     const E *__restrict__ xp = static_cast<const E *>(a.x);
     const E *__restrict__ gp = static_cast<const E *>(a.gy);
     E *__restrict__ dxp = static_cast<E *>(a.gx);
@@ -789,6 +803,7 @@ struct Call {
     void *scratch;
     int64_t scratch_bytes;
     cudaStream_t stream;
+    double pgs_thr = 0.0, pgs_mult = 1.0;  // backward of quantize-dequantize only
 };
 
 int check_common(const Call &c, Canon *canon) {
@@ -906,6 +921,8 @@ template <int IO, int CT, int OP> int launch_backward(const Call &c, const Canon
         a.qmax = (double)c.qmax;
         a.zps = c.zps;
         a.exact_edges = exact_edges(CT, c.qmin, c.qmax);
+        a.pgs_thr = c.pgs_thr;
+        a.pgs_mult = c.pgs_mult;
         int64_t grid = (canon.nparam * 32 + kThreads - 1) / kThreads;
         const int64_t cap = (int64_t)sm_count() * 16;
         if (grid > cap) grid = cap;
@@ -947,6 +964,8 @@ template <int IO, int CT, int OP> int launch_backward(const Call &c, const Canon
     a.qmax = (double)c.qmax;
     a.zps = c.zps;
     a.exact_edges = exact_edges(CT, c.qmin, c.qmax);
+    a.pgs_thr = c.pgs_thr;
+    a.pgs_mult = c.pgs_mult;
 
     if (p.mode == BwdPlan::SEG) {
         const int gpc = kThreads / p.group;
@@ -1111,6 +1130,28 @@ extern "C" int aimet_b200_quantize_dequantize_backward(
     c.gx = grad_x; c.gs = grad_scale; c.go = grad_offset;
     c.scratch = scratch; c.scratch_bytes = scratch_bytes;
     c.stream = static_cast<cudaStream_t>(stream);
+    return ab::dispatch(c, true);
+}
+
+extern "C" int aimet_b200_quantize_dequantize_backward_ex(
+    const void *x, const void *grad_y, const void *scale, const void *offset, const ab_layout *layout,
+    int io_dtype, int compute_dtype, int param_dtype, int64_t qmin, int64_t qmax,
+    double zero_point_shift, double pgs_eps, double pgs_multiplier, void *grad_x, void *grad_scale,
+    void *grad_offset, void *scratch, int64_t scratch_bytes, void *stream) {
+    if (!(pgs_eps >= 0.0 && pgs_eps <= 1.0))
+        return ab::fail(AB_ERR_INVALID, "pgs_eps must be in [0, 1], got %g", pgs_eps);
+    Call c{};
+    c.op = ab::OP_QDQ;
+    c.x = x; c.gy = grad_y; c.scale = scale; c.offset = offset; c.layout = layout;
+    c.io = io_dtype; c.ct = compute_dtype; c.pt = param_dtype;
+    c.qmin = qmin; c.qmax = qmax; c.zps = zero_point_shift;
+    c.gx = grad_x; c.gs = grad_scale; c.go = grad_offset;
+    c.scratch = scratch; c.scratch_bytes = scratch_bytes;
+    c.stream = static_cast<cudaStream_t>(stream);
+    if (pgs_eps > 0.0 && pgs_multiplier != 1.0 && grad_x) {
+        c.pgs_thr = (1.0 - pgs_eps) / 2.0;
+        c.pgs_mult = pgs_multiplier;
+    }
     return ab::dispatch(c, true);
 }
 

@@ -30,6 +30,11 @@ template <typename T> struct Grid {
     // 16-bit internal dtypes only: qmin-1 and qmax+1 are exact in that dtype, so
     // re-rounding an integer difference cannot move it across a grid boundary
     int exact_edges;
+    // backward only: the input gradient of an element whose rounding error exceeds pgs_thr is
+    // multiplied by pgs_mult (QuantDequantFunc.backward with the experimental "pivot gradient
+    // spiking" switched on, torch_builtins.py:779-831); off unless has_pgs
+    int has_pgs = 0;
+    T pgs_thr = (T)0, pgs_mult = (T)1;
 };
 
 // ---------------------------------------------------------------------------
@@ -228,6 +233,11 @@ __device__ __forceinline__ typename Arith<CT>::T bwd_elem(typename Arith<CT>::T 
     if (g.has_zps) xc = A::rnd(op_add(xc, g.zps));
     ds = A::rnd(op_mul(gy, in ? err : xc));
     if (WANT_O) dofs = in ? (T)0 : A::rnd(op_mul(gy, e.s));
+    if (g.has_pgs) {
+        // the product is in the gradient's dtype: the store conversion does that rounding
+        const T mag = err < (T)0 ? -err : err;
+        return in ? (mag > g.pgs_thr ? op_mul(gy, g.pgs_mult) : gy) : (T)0;
+    }
     return in ? gy : (T)0;
 }
 
@@ -310,6 +320,11 @@ __device__ __forceinline__ void bwd_pair(typename Arith<CT>::T &xa, typename Ari
         acc_o += ina ? (T)0 : oa;
         acc_o += inb ? (T)0 : ob;
     }
+    if (g.has_pgs) {
+        const T ea = op_sub(ra, sa), eb = op_sub(rb, sb);
+        if ((ea < (T)0 ? -ea : ea) > g.pgs_thr) ga = op_mul(ga, g.pgs_mult);
+        if ((eb < (T)0 ? -eb : eb) > g.pgs_thr) gb = op_mul(gb, g.pgs_mult);
+    }
     xa = ina ? ga : (T)0;
     xb = inb ? gb : (T)0;
 }
@@ -333,7 +348,7 @@ template <int CT> __device__ __forceinline__ bool vec_fast_ok(const Enc<CT> &e, 
     if (CT == AB_F64) return false;
     const bool int_offset = (float)e.o == rintf((float)e.o);
     const bool lowp_ok = (CT == AB_F32) || e.exact_int;
-    return e.fast && !g.has_zps && int_offset && lowp_ok;
+    return e.fast && !g.has_zps && !g.has_pgs && int_offset && lowp_ok;
 }
 
 // x / s by reciprocal and exact remainder.  GUARD keeps q0 when it is infinite or absurdly large
@@ -482,7 +497,7 @@ template <int CT> __device__ __forceinline__ bool vec_packed_ok(const Enc<CT> &e
     if (CT != AB_BF16 && CT != AB_F16) return false;
     const float lim = CT == AB_BF16 ? 32.0f : 256.0f;
     const float o = (float)e.o;
-    return e.fast && e.exact_int && !g.has_zps && o == rintf(o) && fabsf(o) <= lim &&
+    return e.fast && e.exact_int && !g.has_zps && !g.has_pgs && o == rintf(o) && fabsf(o) <= lim &&
            fabsf((float)e.lo) <= lim && fabsf((float)e.hi) <= lim;
 }
 

@@ -779,6 +779,83 @@ def seqmse_figure(dev, rank, world, m=8192, n=4096, k=4096, cands=20, cpu=True):
     return out
 
 
+def adjacent_rows_figure(dev, cpu=True):
+    """The callers and formats beside the path, each timed with CUDA events and checked against the
+    oracle on a sample: SeqMSE with blockwise weights (all blocks in one launch) and the float
+    fake-cast (fp8 e4m3 per-tensor, MXFP4 blocks of 32)."""
+    from aimet_b200.float_quantizer import FloatQuantizeDequantize, _MXFP4QuantizeDequantize
+    from aimet_b200.seq_mse import block_losses_all_candidates
+    from oracle import float_cast as OF
+    from oracle import seq_mse as OS
+
+    peaks, kind = measured_peaks()
+    gen = torch.Generator(device=dev).manual_seed(6000)
+
+    def timed(fn, reps=5):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    out = {}
+    # --- SeqMSE, blockwise: the q_proj shape with 64-channel blocks (64 blocks), 20 candidates
+    m, n, k, cands, block = 8192, 4096, 4096, 20, 64
+    x = torch.randn((m, k), device=dev, generator=gen).to(torch.bfloat16)
+    w = (torch.randn((n, k), device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+    nb = k // block
+    smax = w.float().reshape(n, nb, block).abs().amax(2, keepdim=True) / 7
+    wq = torch.stack([(torch.clamp(torch.round(w.float().reshape(n, nb, block) / (smax * f)), -8, 7) * (smax * f))
+                      .reshape(n, k).to(torch.bfloat16) for f in torch.linspace(0.5, 1.0, cands).tolist()])
+    ms = timed(lambda: block_losses_all_candidates(x, x, w, wq, nb, "mse"))
+    loss = block_losses_all_candidates(x, x, w, wq, nb, "mse")  # [C, n, nb]
+    rows = 32
+    xd, wd = x.double().cpu(), w[:rows].double().cpu()
+    want = torch.stack([OS.linear_loss(xd, xd, wd, wq[c, :rows].double().cpu(), block) for c in range(cands)])
+    del xd
+    err = float(((loss[:, :rows].double().cpu() - want).abs() / want).max())
+    out["seqmse_blockwise"] = {"shape": {"tokens": m, "out": n, "in": k, "block": block, "candidates": cands},
+                               "ms": ms, "TFLOPs": 2.0 * m * n * k * cands / (ms * 1e-3) / 1e12,
+                               "what": "loss of all candidates and all 64 blocks in one launch",
+                               "parity": {"loss_max_rel_err_vs_float64": err, "rows_checked": rows, "tolerance": 1e-5,
+                                          "ok": err <= 1e-5}}
+    del x, w, wq, loss
+    torch.cuda.empty_cache()
+
+    # --- float fake-cast of the [14336, 4096] bf16 weight: fp8 e4m3 per-tensor, MXFP4 (blocks of 32)
+    wt, _ = make_weight(ROWS, COLS, seed=2000)
+    wt = wt.to(dev)
+    for name, q in (("fp8_e4m3_per_tensor", FloatQuantizeDequantize(dtype=torch.float8_e4m3fn)),
+                    ("mxfp4_block32", _MXFP4QuantizeDequantize((ROWS, COLS // 32), block_size=(1, 32)))):
+        q = q.to(dev)
+        with torch.no_grad():
+            with q.compute_encodings():
+                q(wt)
+            ms = timed(lambda: q(wt))  # pylint: disable=cell-var-from-loop
+            y = q(wt)
+            rows = 256
+            fi = q._finfo  # pylint: disable=protected-access
+            scale = q.get_scale().detach().cpu()
+            if scale.dim() == 2:
+                scale = scale[:rows]
+            want = OF.float_quantize_dequantize(wt[:rows].cpu(), scale, fi.exponent_bits, fi.mantissa_bits, fi.finite,
+                                                fi.unsigned_zero, block_size=q.block_size)
+        exact = bool(torch.equal(y[:rows].cpu().float(), want.float()))
+        nbytes = wt.numel() * (wt.element_size() + y.element_size())
+        out["float_cast_" + name] = {"shape": [ROWS, COLS], "in_dtype": "bfloat16", "out_dtype": str(y.dtype).replace("torch.", ""),
+                                     "us": ms * 1e3, "algorithmic_bytes": nbytes,
+                                     "achieved_GBps": nbytes / (ms * 1e-3) / 1e9,
+                                     "frac_of_" + kind + "_hbm": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                     "timed": "the module call (scale derivation + the cast kernel)",
+                                     "parity": {"bit_exact_vs_oracle": exact, "rows_checked": rows, "ok": exact}}
+    return out
+
+
 def resnet50_figure(dev, batch=256, cpu=True):
     """QuantSim-style forward of a random-init ResNet-50 at batch 256 (224x224 fp32, N(0,1)) with
     per-channel int8 weight quantize-dequantize and per-tensor int8 quantize-dequantize on the input
@@ -1091,6 +1168,8 @@ def run_ours(args):
         if world == 1:  # a model forward does not shard: replicas only
             torch.cuda.empty_cache()
             extras["quantsim_resnet50"] = resnet50_figure(dev, cpu=cpu)
+            torch.cuda.empty_cache()
+            extras["adjacent_rows"] = adjacent_rows_figure(dev, cpu=cpu)
     if rank == 0:
         out.update(extras)
         print(json.dumps(out))

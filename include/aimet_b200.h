@@ -114,6 +114,17 @@ int aimet_b200_quantize_dequantize_backward(const void *x, const void *grad_y, c
                                             int64_t qmin, int64_t qmax, double zero_point_shift,
                                             void *grad_x, void *grad_scale, void *grad_offset,
                                             void *scratch, int64_t scratch_bytes, void *stream);
+/* The same with the reference's experimental "pivot gradient spiking" (experimental/pgs.py,
+ * torch_builtins.py:779-831): where |round(x/s - zps) - (x/s - zps)| > (1 - pgs_eps) / 2 (compared in
+ * the internal dtype) the input gradient is grad_y * pgs_multiplier instead of grad_y.  Off when
+ * pgs_eps == 0, pgs_multiplier == 1 or grad_x == NULL; scale / offset gradients are not affected. */
+int aimet_b200_quantize_dequantize_backward_ex(const void *x, const void *grad_y, const void *scale,
+                                               const void *offset, const ab_layout *layout,
+                                               int io_dtype, int compute_dtype, int param_dtype,
+                                               int64_t qmin, int64_t qmax, double zero_point_shift,
+                                               double pgs_eps, double pgs_multiplier, void *grad_x,
+                                               void *grad_scale, void *grad_offset, void *scratch,
+                                               int64_t scratch_bytes, void *stream);
 /* QuantizeFunc.backward (torch_builtins.py:637-659) */
 int aimet_b200_quantize_backward(const void *x, const void *grad_y, const void *scale,
                                  const void *offset, const ab_layout *layout, int io_dtype,

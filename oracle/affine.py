@@ -111,9 +111,12 @@ def quantize_dequantize(x, scale, offset, qmin, qmax, block_size=None, zero_poin
     return (t * s).to(x.dtype).view(shape)
 
 
-def quantize_dequantize_backward(x, grad, scale, offset, qmin, qmax, block_size=None, zero_point_shift=0.0):
+def quantize_dequantize_backward(x, grad, scale, offset, qmin, qmax, block_size=None, zero_point_shift=0.0,
+                                 pgs_eps=0.0, pgs_multiplier=1.0):
     """QuantDequantFunc.backward (torch_builtins.py:772-831) followed by the sum-to-size autograd
-    applies.  Returns (grad_x in x.dtype, grad_scale, grad_offset in the parameters' dtypes)."""
+    applies.  Returns (grad_x in x.dtype, grad_scale, grad_offset in the parameters' dtypes).
+    ``pgs_eps`` / ``pgs_multiplier``: the experimental gradient multiplier near rounding boundaries
+    (:790-821), applied in the gradient's own dtype."""
     idt = internal_dtype(x.dtype, qmin, qmax)
     shape = x.shape
     xb, s0, o0 = _blocked(x, scale, offset, block_size)
@@ -130,7 +133,13 @@ def quantize_dequantize_backward(x, grad, scale, offset, qmin, qmax, block_size=
         xc = xc + zero_point_shift
     gs_full = gb * torch.where(mask, err, xc)
     go_full = torch.where(mask, torch.zeros((), dtype=idt), gb * s)
-    gx = torch.where(mask, gb, torch.zeros((), dtype=idt)).to(x.dtype).view(shape)
+    if pgs_eps > 0.0 and pgs_multiplier != 1.0:
+        g_in = grad.reshape(xb.shape)
+        near = err.abs() > (1 - pgs_eps) / 2
+        g_in = torch.where(near, g_in * pgs_multiplier, g_in)
+        gx = torch.where(mask, g_in, torch.zeros((), dtype=g_in.dtype)).to(x.dtype).view(shape)
+    else:
+        gx = torch.where(mask, gb, torch.zeros((), dtype=idt)).to(x.dtype).view(shape)
     gs = _sum_to(gs_full, s.shape).to(scale.dtype).view(scale.shape)
     go = _sum_to(go_full, o.shape).to(offset.dtype).view(offset.shape)
     return gx, gs, go

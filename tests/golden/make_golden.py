@@ -133,6 +133,42 @@ def gen_affine():
     _save("affine_cases.pt", out)
 
 
+PGS_CASES = [
+    # affine case it shares inputs with, eps, multiplier, parameter gradients wanted
+    ("fp32_per_tensor_asym8", 0.05, 3.0, True),
+    ("bf16_per_channel_int8", 0.2, 2.0, True),
+    ("bf16_blockwise_int4", 0.5, 0.25, True),
+    ("fp16_per_tensor_int8", 0.05, 3.0, False),
+    ("fp32_zero_point_shift", 1.0, 5.0, True),
+    ("fp32_channel_axis1_4d", 0.1, -1.5, False),
+]
+
+
+def gen_pgs():
+    """quantize_dequantize backward with the experimental gradient multiplier near rounding
+    boundaries switched on (experimental/pgs.py)."""
+    from aimet_torch.experimental import pgs
+
+    cases = {c[0]: (i, c) for i, c in enumerate(AFFINE_CASES)}
+    out = {}
+    for name, eps, mult, param_grads in PGS_CASES:
+        idx, (_, dtype, shape, pshape, block, qmin, qmax, zps, sym, _q) = cases[name]
+        x, grad, scale, offset = _make_affine_inputs(100 + idx, dtype, shape, pshape, qmin, qmax, sym)
+        xi = x.clone().requires_grad_(True)
+        s = scale.clone().requires_grad_(param_grads)
+        o = offset.clone().requires_grad_(param_grads)
+        pgs.enable_pgs(eps, mult)
+        try:
+            y = torch_builtins.quantize_dequantize(xi, s, o, qmin, qmax, block, zps)
+        finally:
+            pgs.disable_pgs()
+        y.backward(grad)  # the switch is read when the forward runs
+        out[name] = dict(dtype=dtype, shape=shape, pshape=pshape, block_size=block, qmin=qmin, qmax=qmax,
+                         zero_point_shift=zps, eps=eps, multiplier=mult, param_grads=param_grads, x=x, grad=grad,
+                         scale=scale, offset=offset, y=y.detach(), gx=xi.grad, gs=s.grad, go=o.grad)
+    _save("pgs_cases.pt", out)
+
+
 # --------------------------------------------------------------------------------------------
 # encoding analyzers: statistics after every update and the encodings computed from them
 # --------------------------------------------------------------------------------------------
@@ -533,6 +569,7 @@ def gen_wire():
 GENERATORS = {
     "backend_vectors": gen_backend_vectors,
     "affine": gen_affine,
+    "pgs": gen_pgs,
     "analyzers": gen_analyzers,
     "lpnorm": gen_lpnorm,
     "quantizers": gen_quantizers,

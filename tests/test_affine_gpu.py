@@ -321,3 +321,63 @@ def test_functional_call_forms():
                 aimet_b200.quantize_dequantize(x, scale, offset, num_steps=15, signed=True)):
         assert_same(got, want)
     assert_same(aimet_b200.dequantize(want_q.cuda(), scale, offset), O.dequantize(want_q, scale.cpu(), offset.cpu()))
+
+
+PGS = load_golden("pgs_cases.pt")
+
+
+@pytest.mark.parametrize("name", sorted(PGS))
+def test_gradient_multiplier_near_rounding_boundaries(name):
+    """The reference's experimental "pivot gradient spiking" (experimental/pgs.py): the input
+    gradient of elements whose rounding error exceeds (1 - eps) / 2 is multiplied.  Bit-exact
+    against the reference's own backward; the switch is read when the forward runs."""
+    from aimet_b200 import pgs
+
+    c = PGS[name]
+    B = _backend()
+    idt = O.internal_dtype(c["dtype"], c["qmin"], c["qmax"])
+    xi = c["x"].clone().cuda().requires_grad_(True)
+    s = c["scale"].clone().cuda().requires_grad_(c["param_grads"])
+    o = c["offset"].clone().cuda().requires_grad_(c["param_grads"])
+    pgs.enable_pgs(c["eps"], c["multiplier"])
+    try:
+        assert pgs.is_pgs_enabled() and pgs.get_pgs_eps() == c["eps"] and pgs.get_pgs_multiplier() == c["multiplier"]
+        y = B.quantize_dequantize(xi, s, o, c["qmin"], c["qmax"], c["block_size"], c["zero_point_shift"])
+    finally:
+        pgs.disable_pgs()
+    assert not pgs.is_pgs_enabled()
+    y.backward(c["grad"].cuda())
+    assert_same(y.detach(), c["y"], "y")
+    assert_same(xi.grad, c["gx"], "grad_x")
+    if c["param_grads"]:
+        _check_param_grad(s.grad, c["gs"], idt, "grad_scale")
+        _check_param_grad(o.grad, c["go"], idt, "grad_offset")
+    with pytest.raises(ValueError):
+        pgs.enable_pgs(0.0, 3.0)
+    with pytest.raises(ValueError):
+        pgs.enable_pgs(0.1, 1.0)
+
+
+def test_gradient_multiplier_at_a_large_size():
+    """The same against the oracle on a tensor that takes the vector kernels (bf16, blockwise)."""
+    from aimet_b200 import pgs
+
+    B = _backend()
+    g = torch.Generator().manual_seed(77)
+    shape, pshape, block, qmin, qmax = (512, 4096), (512, 64), (1, 64), -8, 7
+    x = (torch.randn(shape, generator=g) * 0.02).to(torch.bfloat16)
+    grad = torch.randn(shape, generator=g).to(torch.bfloat16)
+    scale = (x.float().reshape(512, 64, 64).abs().amax(2) / 7).clamp_min(1e-6)
+    offset = torch.zeros(pshape)
+    xi = x.clone().cuda().requires_grad_(True)
+    s = scale.clone().cuda().requires_grad_(True)
+    pgs.enable_pgs(0.1, 3.0)
+    try:
+        y = B.quantize_dequantize(xi, s, offset.cuda(), qmin, qmax, block)
+    finally:
+        pgs.disable_pgs()
+    y.backward(grad.cuda())
+    ogx, ogs, _ = O.quantize_dequantize_backward(x, grad, scale, offset, qmin, qmax, block, 0.0, pgs_eps=0.1,
+                                                 pgs_multiplier=3.0)
+    assert_same(xi.grad, ogx, "grad_x")
+    _check_param_grad(s.grad, ogs, O.internal_dtype(torch.bfloat16, qmin, qmax), "grad_scale")

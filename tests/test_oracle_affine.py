@@ -67,3 +67,21 @@ def test_fake_quantize_formula_is_what_aten_computes(name):
         pytest.skip("reference does not take the fake-quantize path here")
     a = O.fake_quantize(c["x"], c["scale"], c["offset"], c["qmin"], c["qmax"])
     assert_same(O.fake_quantize_formula(c["x"], c["scale"], c["offset"], c["qmin"], c["qmax"]), a, "formula")
+
+
+PGS = load_golden("pgs_cases.pt")
+
+
+@pytest.mark.parametrize("name", sorted(PGS))
+def test_gradient_multiplier_near_rounding_boundaries_matches_reference(name):
+    """quantize_dequantize backward with the reference's experimental "pivot gradient spiking" on."""
+    c = PGS[name]
+    args = (c["scale"], c["offset"], c["qmin"], c["qmax"], c["block_size"], c["zero_point_shift"])
+    assert_same(O.quantize_dequantize(c["x"], *args), c["y"], "y")
+    gx, gs, go = O.quantize_dequantize_backward(c["x"], c["grad"], *args, pgs_eps=c["eps"], pgs_multiplier=c["multiplier"])
+    assert_same(gx, c["gx"], "grad_x")
+    plain, _, _ = O.quantize_dequantize_backward(c["x"], c["grad"], *args)
+    assert not torch.equal(plain, gx)  # the case does exercise the multiplier
+    if c["param_grads"]:
+        assert_same(gs, c["gs"], "grad_scale")
+        assert_same(go, c["go"], "grad_offset")
