@@ -263,6 +263,21 @@ __device__ __forceinline__ float round_lowp(float v, int lowp) {
     return v;
 }
 
+// two values at a time: one packed conversion (full rate; the scalar one runs on the conversion
+// pipe at a quarter of it) and two unpacking bit operations
+__device__ __forceinline__ void round_lowp2(float &a, float &b, int lowp) {
+    if (lowp == 1) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        const uint32_t u = *reinterpret_cast<const uint32_t *>(&h);
+        a = __uint_as_float(u << 16);
+        b = __uint_as_float(u & 0xffff0000u);
+    } else if (lowp == 2) {
+        const float2 f = __half22float2(__floats2half2_rn(a, b));
+        a = f.x;
+        b = f.y;
+    }
+}
+
 // The sequence of passes of one CTA, identical in every role.
 //
 // A unit is (channel tile, token tile, block); an item is (unit, candidate).  Units are dealt out in
@@ -284,6 +299,11 @@ struct PassIter {
     bool has_ref, ref_pending;
     int n_ct, width, rank;
     int64_t G;
+    // the remainder's position as (unit, candidate) and the decoded tile of the current unit: both
+    // advance without divisions (a block of 64 input channels is one short pass, and every thread
+    // of the CTA walks this sequence)
+    int64_t rem_u, dec_unit;
+    int rem_g, dec_ct, dec_tt, dec_blk;
     // `pair`: the workers are pairs of CTAs; a pair's unit spans two channel tiles, one per CTA
     __device__ PassIter(const SeqArgs &a, bool ref, bool pair) {
         width = pair ? 2 : 1;
@@ -298,6 +318,10 @@ struct PassIter {
         const int64_t items = (units - full_units) * a.num_cand;
         i = items * me / G;
         i1 = items * (me + 1) / G;
+        rem_u = i / a.num_cand;
+        rem_g = (int)(i - rem_u * a.num_cand);
+        dec_unit = -1;
+        dec_ct = dec_tt = dec_blk = 0;
         done_unit = -1;
         cur_unit = 0;
         cur_g = 0;
@@ -320,10 +344,13 @@ struct PassIter {
             return true;
         }
         if (i < i1) {
-            const int64_t u = i / num_cand;
-            cur_unit = full_units + u;
-            cur_g = (int)(i - u * num_cand);
+            cur_unit = full_units + rem_u;
+            cur_g = rem_g;
             ++i;
+            if (++rem_g == num_cand) {
+                rem_g = 0;
+                ++rem_u;
+            }
             return true;
         }
         return false;
@@ -337,12 +364,18 @@ struct PassIter {
                 ref_pending = true;
             }
         }
-        const int64_t t = cur_unit / num_blocks;
-        p.blk = (int)(cur_unit - t * num_blocks);
-        // token-tile major: the CTAs of a wave share few token tiles (the larger operand tile) and
-        // spread over the channel tiles (measured: 4 % faster than channel-tile major)
-        p.tt = (int)(t / n_ct);
-        p.ct = (int)(t - (int64_t)p.tt * n_ct) * width + rank;
+        if (cur_unit != dec_unit) {
+            dec_unit = cur_unit;
+            const int64_t t = cur_unit / num_blocks;
+            dec_blk = (int)(cur_unit - t * num_blocks);
+            // token-tile major: the CTAs of a wave share few token tiles (the larger operand tile) and
+            // spread over the channel tiles (measured: 4 % faster than channel-tile major)
+            dec_tt = (int)(t / n_ct);
+            dec_ct = (int)(t - (int64_t)dec_tt * n_ct) * width + rank;
+        }
+        p.blk = dec_blk;
+        p.tt = dec_tt;
+        p.ct = dec_ct;
         if (ref_pending) {
             ref_pending = false;
             p.g = -1;
@@ -355,6 +388,55 @@ struct PassIter {
         return true;
     }
 };
+
+// One thread's share of a candidate pass: its kHalfCols accumulator columns against the values in
+// xw[] (the reference product, or the earlier segments' sum), summed.  KIND / LOWP >= 0 fix the loss
+// and the rounding at compile time, -1 leaves them to the run-time arguments.  Chunks of 16 columns,
+// the next one requested before the current one is used.
+template <bool HAS_REF, int KIND, int LOWP>
+__device__ __forceinline__ void candidate_epilogue(uint32_t t0, const float (&xw)[kHalfCols], bool first_seg, int kind_rt,
+                                                   int lowp_rt, float &s0, float &s1) {
+    const int kind = KIND >= 0 ? KIND : kind_rt;
+    const int lowp = LOWP >= 0 ? LOWP : lowp_rt;
+    constexpr int CW = 16;
+    uint32_t ca[CW], cb[CW];
+    tmem_ld16(t0, ca);
+#pragma unroll
+    for (int ch = 0; ch < kHalfCols / CW; ++ch) {
+        tmem_ld_wait();
+        if (ch + 1 < kHalfCols / CW) {
+            if (ch & 1)
+                tmem_ld16(t0 + (ch + 1) * CW, ca);
+            else
+                tmem_ld16(t0 + (ch + 1) * CW, cb);
+        }
+#pragma unroll
+        for (int j = 0; j < CW; j += 2) {
+            float y0 = __uint_as_float((ch & 1) ? cb[j] : ca[j]);
+            float y1 = __uint_as_float((ch & 1) ? cb[j + 1] : ca[j + 1]);
+            float d0, d1;
+            if (HAS_REF) {
+                if (lowp) round_lowp2(y0, y1, lowp);
+                d0 = xw[ch * CW + j] - y0;
+                d1 = xw[ch * CW + j + 1] - y1;
+            } else {  // the candidate's whole contraction
+                d0 = y0 + (first_seg ? 0.f : xw[ch * CW + j]);
+                d1 = y1 + (first_seg ? 0.f : xw[ch * CW + j + 1]);
+            }
+            float f0 = kind == 1 ? fabsf(d0) : d0 * d0;
+            float f1 = kind == 1 ? fabsf(d1) : d1 * d1;
+            if (lowp) round_lowp2(f0, f1, lowp);
+            s0 += f0;
+            s0 += f1;
+            if (kind == 2) {
+                float q0 = y0 * y0, q1 = y1 * y1;
+                if (lowp) round_lowp2(q0, q1, lowp);
+                s1 += q0;
+                s1 += q1;
+            }
+        }
+    }
+}
 
 template <bool HAS_REF, bool PAIR>
 __global__ void __launch_bounds__(kSeqThreads, 1)
@@ -561,14 +643,21 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
                     tmem_ld16(t0 + ch * 16, r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        float v = __uint_as_float(r[j]);
+                    for (int j = 0; j < 16; j += 2) {
+                        float v0 = __uint_as_float(r[j]), v1 = __uint_as_float(r[j + 1]);
                         if (HAS_REF) {
-                            if (lowp) v = round_lowp(v, lowp);
-                            sref += lowp ? round_lowp(v * v, lowp) : v * v;
-                            xw[ch * 16 + j] = v;
+                            if (lowp) round_lowp2(v0, v1, lowp);
+                            if (kind == 3) {  // the signal power, for the signal-to-noise loss
+                                float q0 = v0 * v0, q1 = v1 * v1;
+                                if (lowp) round_lowp2(q0, q1, lowp);
+                                sref += q0;
+                                sref += q1;
+                            }
+                            xw[ch * 16 + j] = v0;
+                            xw[ch * 16 + j + 1] = v1;
                         } else {
-                            xw[ch * 16 + j] = v + (first_seg ? 0.f : xw[ch * 16 + j]);
+                            xw[ch * 16 + j] = v0 + (first_seg ? 0.f : xw[ch * 16 + j]);
+                            xw[ch * 16 + j + 1] = v1 + (first_seg ? 0.f : xw[ch * 16 + j + 1]);
                         }
                     }
                 }
@@ -580,34 +669,15 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
                 continue;
             }
             float s0 = 0.f, s1 = 0.f;
-            constexpr int CW = 8;  // columns per request: two requests' worth of registers beside xw[]
-            uint32_t ca[CW], cb[CW];
-            tmem_ld8(t0, ca);
-#pragma unroll
-            for (int ch = 0; ch < kHalfCols / CW; ++ch) {
-                tmem_ld_wait();  // chunk ch has arrived; the next one is requested before it is used
-                if (ch + 1 < kHalfCols / CW) {
-                    if (ch & 1)
-                        tmem_ld8(t0 + (ch + 1) * CW, ca);
-                    else
-                        tmem_ld8(t0 + (ch + 1) * CW, cb);
-                }
-#pragma unroll
-                for (int j = 0; j < CW; ++j) {
-                    float y = __uint_as_float((ch & 1) ? cb[j] : ca[j]);
-                    float d;
-                    if (HAS_REF) {
-                        if (lowp) y = round_lowp(y, lowp);
-                        d = xw[ch * CW + j] - y;
-                    } else {
-                        d = y + (first_seg ? 0.f : xw[ch * CW + j]);  // the candidate's whole contraction
-                    }
-                    float f = kind == 1 ? fabsf(d) : d * d;
-                    if (lowp) f = round_lowp(f, lowp);
-                    s0 += f;
-                    if (kind == 2) s1 += lowp ? round_lowp(y * y, lowp) : y * y;
-                }
-            }
+            // the two usual cases (squared error, plain or rounded like bfloat16) as straight-line
+            // code without run-time switches: a pass of a 64-channel block is all epilogue, and the
+            // general form is several times the instructions
+            if (kind == 0 && lowp == 0)
+                candidate_epilogue<HAS_REF, 0, 0>(t0, xw, first_seg, kind, lowp, s0, s1);
+            else if (kind == 0 && lowp == 1)
+                candidate_epilogue<HAS_REF, 0, 1>(t0, xw, first_seg, kind, lowp, s0, s1);
+            else
+                candidate_epilogue<HAS_REF, -1, -1>(t0, xw, first_seg, kind, lowp, s0, s1);
             tc_fence_before();
             if (PAIR)
                 mbar_arrive_cluster(lead_acc_empty + 8 * buf);
@@ -808,11 +878,13 @@ extern "C" int aimet_b200_seqmse_linear_loss_blocks(const void *x, const void *x
     a.seg_len = has_reference ? ((Kb + BK - 1) / BK) * BK : kSegLen;
     a.num_seg = (int)((Kb + a.seg_len - 1) / a.seg_len);
 
-    // With a reference product and at least two channel tiles, pairs of CTAs share a token tile:
-    // each CTA stages half of it and the tensor cores of both SMs read both halves, which takes a
-    // third off the operand bytes an SM has to pull in per pass (the kernel's bound).
+    // With a reference product, at least two channel tiles and long passes, pairs of CTAs share a
+    // token tile: each CTA stages half of it and the tensor cores of both SMs read both halves,
+    // which takes a third off the operand bytes an SM has to pull in per pass.  Short passes (blocks
+    // of fewer than 1024 input channels) are bound by the hand-over between the roles, which costs
+    // twice as much across two CTAs (measured: 1.7 us against 0.85 us per pass), and stay single.
     int pair_clusters = 0;
-    if (has_reference && a.n_ct >= 2) {
+    if (has_reference && a.n_ct >= 2 && Kb >= 1024) {
         int rc2 = pair_cluster_count(&pair_clusters);
         if (rc2 != AB_OK) return rc2;
     }
