@@ -108,7 +108,7 @@ SIGNATURES = {
         _i32,
         [_vp, _vp, _vp, _vp, _lay, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _i64, _vp],
     ),
-    "aimet_b200_float_fake_cast": (_i32, [_vp, _vp, _vp, _lay, _i32, _i32, _i32, _i32, _i32, _f64, _i32, _vp]),
+    "aimet_b200_float_fake_cast": (_i32, [_vp, _vp, _vp, _lay, _i32, _i32, _i32, _i32, _i32, _i32, _f64, _i32, _vp]),
     "aimet_b200_stats_scratch_bytes": (_i64, [_lay, _i32]),
     "aimet_b200_minmax": (_i32, [_vp, _lay, _i32, _i32, _vp, _vp, _vp, _i64, _vp]),
     "aimet_b200_minmax_running": (_i32, [_vp, _lay, _i32, _i32, _vp, _vp, _vp, _i64, _vp]),

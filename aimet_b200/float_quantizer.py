@@ -149,7 +149,9 @@ def float_quantize_dequantize(input: torch.Tensor, finfo: _finfo, scale: torch.T
         block_size = tuple(1 if d > 1 else -1 for d in pshape[:k]) + block_size
     if block_size is None and not _is_expandable(pshape, input.shape):
         raise RuntimeError(f"Scale of shape {pshape} cannot be expanded like input tensor of shape {tuple(input.shape)}.")
-    x = input.detach().to(out_dtype)
+    x = input.detach()
+    if x.dtype not in (torch.float16, torch.bfloat16) or out_dtype != torch.float32:
+        x = x.to(out_dtype)  # (a 16-bit tensor under a float32 result is widened inside the kernel)
     perm = None if block_size else _dense_perm(x)
     blocks = _param_blocks(x.shape, pshape, block_size)
     if perm is not None and list(perm) != list(range(x.dim())):
@@ -160,14 +162,15 @@ def float_quantize_dequantize(input: torch.Tensor, finfo: _finfo, scale: torch.T
         x = x.contiguous()
         perm = tuple(range(x.dim()))
     xd = x.permute(perm)
-    y = torch.empty_like(xd, memory_format=torch.contiguous_format)
+    y = torch.empty_like(xd, dtype=out_dtype, memory_format=torch.contiguous_format)
     if x.numel():
         lay = _lib.make_layout([x.shape[k] for k in perm], [blocks[k] for k in perm])
         s = scale.detach().to(torch.float32).contiguous()
         io = _lib.DTYPE_CODE[out_dtype]
         flags = (0 if finfo.to_torch_dtype() is not None else 1) | (0 if finfo.finite else 2) | (4 if finfo.unsigned_zero else 0)
         with _lib.on_device(x.device):
-            rc = lib.aimet_b200_float_fake_cast(xd.data_ptr(), y.data_ptr(), s.data_ptr(), lay, io, io, finfo.exponent_bits,
+            rc = lib.aimet_b200_float_fake_cast(xd.data_ptr(), y.data_ptr(), s.data_ptr(), lay, _lib.DTYPE_CODE[x.dtype], io, io,
+                                                finfo.exponent_bits,
                                                 finfo.mantissa_bits, finfo.exponent_bias, float(finfo.max), flags,
                                                 _lib.stream_ptr(x.device))
         _lib.check(rc)

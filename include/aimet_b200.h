@@ -158,7 +158,9 @@ int aimet_b200_quantize_dequantize_backward_fixed_scratch(
  * float format with exponent_bits / mantissa_bits on a wider tensor; scale is float32 of the
  * layout's parameter shape (per-tensor, per-channel or blockwise).
  * replaces _float_quantize_dequantize (quantization/float/quantizer.py:619-705).
- *   io_dtype / compute_dtype  AB_F32, AB_F16 or AB_BF16 (equal): the tensor dtype, in which every
+ *   in_dtype       dtype of x: io_dtype, or a 16-bit type with io_dtype AB_F32 (what type promotion
+ *                  makes of a 16-bit tensor divided by a float32 scale with dimensions)
+ *   io_dtype / compute_dtype  AB_F32, AB_F16 or AB_BF16: the dtype of y, in which every
  *                  step is evaluated and rounded as the reference's tensor operations are
  *   exponent_bias  bias of the format's exponent field (smallest normal number 2^(1 - bias))
  *   maxval         largest finite value of the format
@@ -168,7 +170,7 @@ int aimet_b200_quantize_dequantize_backward_fixed_scratch(
  *                  2: the format has infinities: an infinite x / scale passes through (flag 1 only)
  *                  4: the format's zero is unsigned: zero results are +0 */
 int aimet_b200_float_fake_cast(const void *x, void *y, const float *scale, const ab_layout *layout,
-                               int io_dtype, int compute_dtype, int32_t exponent_bits,
+                               int in_dtype, int io_dtype, int compute_dtype, int32_t exponent_bits,
                                int32_t mantissa_bits, int32_t exponent_bias, double maxval,
                                int32_t flags, void *stream);
 
