@@ -498,6 +498,10 @@ def per_tensor_figure(dev, reps=20, cpu=True):
 
     f_med, f_best = timed(fwd)
     b_med, b_best = timed(bwd)
+    # what the same protocol (cold L2, events around one launch) gives for a plain copy (one read,
+    # one write: the forward's traffic) and a plain add (two reads, one write: the backward's)
+    copy_med, _ = timed(lambda: y.copy_(x))
+    add_med, _ = timed(lambda: torch.add(x, dy, out=gx))
     peaks, kind = measured_peaks()
     n = x.numel()
     # parity: calibration, forward, backward against the oracle (whole tensor)
@@ -518,6 +522,7 @@ def per_tensor_figure(dev, reps=20, cpu=True):
            "algorithmic_bytes": {"forward": 8 * n, "backward": 12 * n},
            "forward_us": f_med, "forward_best_us": f_best, "backward_us": b_med, "backward_best_us": b_best,
            "backward_includes": "the finishing kernel that sums the partial scale / offset gradients",
+           "same_protocol_torch_copy_us": copy_med, "same_protocol_torch_add_us": add_med,
            "fwd_bwd_GBps": 20 * n / ((f_med + b_med) * 1e-6) / 1e9,
            "frac_of_" + kind + "_hbm": 20 * n / ((f_med + b_med) * 1e-6) / 1e9 / peaks["hbm_gbs"],
            "l2": "a 256 MB buffer is overwritten between timed iterations (the tensors alone would fit L2)",
