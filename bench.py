@@ -500,8 +500,10 @@ def per_tensor_figure(dev, reps=20, cpu=True):
     b_med, b_best = timed(bwd)
     # what the same protocol (cold L2, events around one launch) gives for a plain copy (one read,
     # one write: the forward's traffic) and a plain add (two reads, one write: the backward's)
-    copy_med, _ = timed(lambda: y.copy_(x))
-    add_med, _ = timed(lambda: torch.add(x, dy, out=gx))
+    tmp = torch.empty_like(x)
+    copy_med, _ = timed(lambda: tmp.copy_(x))
+    add_med, _ = timed(lambda: torch.add(x, dy, out=tmp))
+    del tmp
     peaks, kind = measured_peaks()
     n = x.numel()
     # parity: calibration, forward, backward against the oracle (whole tensor)
