@@ -95,7 +95,9 @@ def compute_encodings(model: nn.Module, group=None):
     (nn/__init__.py:22-84, nn/base.py:331-427): weights are calibrated on entry, activation quantizers
     observe in pass-through mode and get their ranges on exit.
 
-    An observing quantizer costs two kernel launches per forward (the running min / max is updated
+    The weights are quantized once on entry and held for the forwards inside the context (they are
+    taken as fixed while calibration data runs through; forwards with gradients enabled quantize
+    them afresh).  An observing quantizer costs two kernel launches per forward (the running min / max is updated
     on the device, nothing is allocated or copied; the reference clones every observed activation).
     ``group``: a ``torch.distributed`` process group whose ranks each run a share of the calibration
     batches through their replica of the model (data-parallel calibration): on exit the min / max
@@ -112,13 +114,25 @@ def compute_encodings(model: nn.Module, group=None):
                 qw(layer.layer.weight.detach())
                 weight_quantizers.append(qw)
     finish_calibration(weight_quantizers)
+    layers = list(quantized_layers(model))
     with contextlib.ExitStack() as stack:
-        for layer in quantized_layers(model):
+        for layer in layers:
             for q in (*layer.input_quantizers, *layer.output_quantizers):
                 if q is not None and q.is_overwrite_allowed():
                     stack.enter_context(q._compute_encodings(passthrough=True, clone=False, finish=False))  # pylint: disable=protected-access
                     quantizers.append(q)
-        yield
+        # the weights do not change while the calibration data runs through: each is quantized once
+        # here instead of on every forward inside the context (no-grad forwards only)
+        with torch.no_grad():
+            for layer in layers:
+                qw = layer.param_quantizers["weight"]
+                if qw is not None and qw.is_initialized():
+                    layer.__dict__["_held_weight"] = qw(layer.layer.weight).detach()
+        try:
+            yield
+        finally:
+            for layer in layers:
+                layer.__dict__.pop("_held_weight", None)
     if group is not None:
         _allreduce_minmax_statistics(quantizers, group)
     finish_calibration(quantizers)
