@@ -313,6 +313,11 @@ struct PassIter {
         G = gridDim.x / width;
         const int64_t me = blockIdx.x / width;
         full_units = units / G * G;
+        // Left-over units that would fill most of a wave are run as one (some workers idle): walked
+        // in step a pass takes 26 us, against 33 us for workers that start in the middle of
+        // different units and ask for different candidates' weights at the same time, which beats
+        // the even split once the left-over exceeds about three quarters of a wave.
+        if ((units - full_units) * 100 >= 77 * G) full_units = units;
         wave_unit = me;
         wave_g = 0;
         const int64_t items = (units - full_units) * a.num_cand;
