@@ -124,6 +124,7 @@ SIGNATURES = {
     "aimet_b200_histogram_edges": (_i32, [_vp, _vp, _i32, _i32, _i32, _f64, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "aimet_b200_histogram_merge_ex": (_i32, [_vp] * 7 + [_i32, _i32] + [_vp] * 6 + [_i32, _vp]),
     "aimet_b200_histogram_combine": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp]),
+    "aimet_b200_histogram_update": (_i32, [_vp, _lay, _i32, _i32] + [_vp] * 17 + [_vp, _i64, _vp]),
     "aimet_b200_sqnr_encodings": (
         _i32,
         [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _f64, _f64, _f64, _f64, _vp, _vp, _vp, _vp, _vp,

@@ -1200,7 +1200,16 @@ struct MergeArgs {
     int *out_moved;          // [H] or NULL: 1 when the updated range differs from the current edges
     float *out_range;        // [H][4] or NULL: first edge, last edge, and the two rounded to stat_dtype
     int stat_dtype;
+    // the batch's min / max in the tensor's own dtype (new_raw_dtype), used when new_min is NULL
+    const void *new_raw_min = nullptr, *new_raw_max = nullptr;
+    int new_raw_dtype = AB_F32;
 };
+
+__device__ __forceinline__ float load_stat(const void *p, int dt, int64_t i) {
+    if (dt == AB_BF16) return __bfloat162float(static_cast<const __nv_bfloat16 *>(p)[i]);
+    if (dt == AB_F16) return __half2float(static_cast<const __half *>(p)[i]);
+    return static_cast<const float *>(p)[i];
+}
 
 __device__ __forceinline__ float min_prop(float a, float b) {  // torch.minimum: NaN propagates
     return (a != a) ? a : ((b != b) ? b : (a < b ? a : b));
@@ -1214,8 +1223,10 @@ __global__ void __launch_bounds__(kThreads) k_hist_merge(MergeArgs a) {
     const float *edges = a.cur_edges + h * (int64_t)(n + 1);
     const float *hist = a.cur_hist + h * (int64_t)n;
     const float e0 = edges[0], e_last = edges[n];
-    const float umin = clamp_nan(a.new_min[h], a.limit[2 * h], e0);
-    const float umax = clamp_nan(a.new_max[h], e_last, a.limit[2 * h + 1]);
+    const float bmin = a.new_min ? a.new_min[h] : load_stat(a.new_raw_min, a.new_raw_dtype, h);
+    const float bmax = a.new_max ? a.new_max[h] : load_stat(a.new_raw_max, a.new_raw_dtype, h);
+    const float umin = clamp_nan(bmin, a.limit[2 * h], e0);
+    const float umax = clamp_nan(bmax, e_last, a.limit[2 * h + 1]);
     const bool keep = (umin == a.cur_min[h]) && (umax == a.cur_max[h]);
     const float nf = (float)n;
     const float dw = __fdiv_rn(__fsub_rn(umax, umin), nf);
@@ -1699,6 +1710,54 @@ extern "C" int aimet_b200_histogram_merge_ex(const float *new_min, const float *
                    static_cast<cudaStream_t>(stream), a);
     AB_LAUNCH_OK();
     return AB_OK;
+}
+
+extern "C" int aimet_b200_histogram_update(const void *x, const ab_layout *layout, int io_dtype, int32_t num_bins,
+                                           const float *cur_hist, const float *cur_edges, const float *cur_min,
+                                           const float *cur_max, const float *cur_range, const float *range_limit,
+                                           float *new_hist, float *new_edges, float *new_min, float *new_max,
+                                           float *new_range, void *batch_min, void *batch_max, int64_t *counts,
+                                           int64_t *redo, float *carry, int32_t *moved, void *scratch,
+                                           int64_t scratch_bytes, void *stream) {
+    ab::Canon canon;
+    int rc = ab::canonicalize(layout, &canon);
+    if (rc != AB_OK) return rc;
+    if (num_bins <= 0 || num_bins > 8192)
+        return ab::fail(AB_ERR_UNSUPPORTED, "num_bins must be in [1, 8192], got %d", num_bins);
+    if (canon.numel == 0) return ab::fail(AB_ERR_INVALID, "histogram of an empty tensor is undefined");
+    if (!canon.oci || canon.C != 1)
+        return ab::fail(AB_ERR_UNSUPPORTED, "the one-call update serves a single (per-tensor) histogram");
+    if (io_dtype != AB_F32 && io_dtype != AB_F16 && io_dtype != AB_BF16)
+        return ab::fail(AB_ERR_UNSUPPORTED, "the one-call update takes float32, float16 or bfloat16 tensors");
+    if (!x || !cur_hist || !cur_edges || !cur_min || !cur_max || !cur_range || !range_limit || !new_hist || !new_edges ||
+        !new_min || !new_max || !new_range || !batch_min || !batch_max || !counts || !redo || !carry || !moved)
+        return ab::fail(AB_ERR_INVALID, "NULL pointer argument");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // 1. the batch against the current range, and its own finite min / max
+    const void *xs[1] = {x};
+#define AB_BIN(LO, COUNTS, MN, MX, RUN_IF)                                                                              \
+    (io_dtype == AB_F32    ? ab::launch_histogram<AB_F32>(xs, 1, canon, num_bins, (LO), (LO) + 1, (LO) + 2, (LO) + 3,   \
+                                                          (COUNTS), (MN), (MX), 0, (RUN_IF), scratch, scratch_bytes, st) \
+     : io_dtype == AB_F16  ? ab::launch_histogram<AB_F16>(xs, 1, canon, num_bins, (LO), (LO) + 1, (LO) + 2, (LO) + 3,   \
+                                                          (COUNTS), (MN), (MX), 0, (RUN_IF), scratch, scratch_bytes, st) \
+                           : ab::launch_histogram<AB_BF16>(xs, 1, canon, num_bins, (LO), (LO) + 1, (LO) + 2, (LO) + 3,  \
+                                                           (COUNTS), (MN), (MX), 0, (RUN_IF), scratch, scratch_bytes, st))
+    rc = AB_BIN(cur_range, counts, batch_min, batch_max, nullptr);
+    if (rc != AB_OK) return rc;
+    // 2. the accumulated histogram moved into the range that also covers the batch
+    ab::MergeArgs m{nullptr, nullptr, cur_min, cur_max, cur_edges, cur_hist, range_limit,
+                    new_min, new_max, carry, new_edges, num_bins, moved, new_range, io_dtype};
+    m.new_raw_min = batch_min;
+    m.new_raw_max = batch_max;
+    m.new_raw_dtype = io_dtype;
+    ab::launch_pdl(ab::k_hist_merge, 1u, ab::kThreads, sizeof(float) * (size_t)num_bins, st, m);
+    AB_LAUNCH_OK();
+    // 3. if the range moved, the batch again over the new range (skipped on the device otherwise)
+    rc = AB_BIN(new_range, redo, nullptr, nullptr, moved);
+    if (rc != AB_OK) return rc;
+#undef AB_BIN
+    // 4. counts of the batch + carried counts
+    return aimet_b200_histogram_combine(counts, redo, carry, moved, 1, num_bins, new_hist, stream);
 }
 
 extern "C" int aimet_b200_histogram_edges(const float *min, const float *max, int32_t num_hist, int32_t num_bins,

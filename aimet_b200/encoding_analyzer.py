@@ -549,6 +549,10 @@ class _HistogramObserver(_Observer):
             return new
         n = self.num_bins
         cur = self._state
+        if self.num_histograms == 1 and x.dtype in (torch.float32, torch.float16, torch.bfloat16):
+            batch = self._observe_one_call(x, cur, n)
+            if batch is not None:
+                return batch
         lay = _StatLayout(x, self.shape, self.block_size)
         if lay.x.dtype == torch.float64:
             new = self.collect_stats(x)
@@ -588,6 +592,57 @@ class _HistogramObserver(_Observer):
         _lib.check(rc)
         self._state = _HistogramList(hist, edges, umin, umax)
         self._state._range = (nr, lay.x.dtype)  # pylint: disable=protected-access
+        return batch
+
+    def _observe_one_call(self, x: torch.Tensor, cur: "_HistogramList", n: int):
+        """The update of a single (per-tensor) histogram enqueued by one library call
+        (``aimet_b200_histogram_update``: the same launches as the general path below, without the
+        Python between them).  ``None`` when the tensor's layout needs the general path."""
+        key = (tuple(x.shape), x.stride(), x.dtype, x.device)
+        cached = self.__dict__.get("_one_call_cache")
+        if cached is None or cached[0] != key:
+            lay = _StatLayout(x, self.shape, self.block_size)
+            if lay.x.data_ptr() != x.data_ptr():  # a copy was needed: leave it to the general path
+                return None
+            with _lib.on_device(x.device):
+                nbytes = lib.aimet_b200_stats_scratch_bytes(lay.layout, lay.io)
+            _lib.check(nbytes)
+            dev = x.device
+            work = (torch.empty((2, n), dtype=torch.int64, device=dev), torch.empty(n, dtype=torch.float32, device=dev),
+                    torch.empty(1, dtype=torch.int32, device=dev))
+            cached = (key, lay.layout, lay.io, nbytes, work)
+            self.__dict__["_one_call_cache"] = cached
+        _, layout, io, nbytes, (counts, carry, moved) = cached
+        dev = x.device
+        rng = getattr(cur, "_range", None)
+        if rng is None or rng[1] != x.dtype:
+            e0, e1 = cur.bin_edges[:, 0], cur.bin_edges[:, -1]
+            rng = (torch.stack((e0, e1, e0.to(x.dtype).to(torch.float32), e1.to(x.dtype).to(torch.float32)),
+                               dim=1).contiguous(), x.dtype)
+        # the state after the update in one allocation: counts, edges, min, max, range
+        buf = torch.empty(2 * n + 7, dtype=torch.float32, device=dev)
+        hist, edges = buf[:n].view(1, n), buf[n:2 * n + 1].view(1, n + 1)
+        umin, umax, nr = buf[2 * n + 1:2 * n + 2], buf[2 * n + 2:2 * n + 3], buf[2 * n + 3:].view(1, 4)
+        bm = torch.empty(2, dtype=x.dtype, device=dev)
+        bmin, bmax = bm[0:1], bm[1:2]
+        scratch = _lib.scratch.get(dev, max(nbytes, 1))
+        with _lib.on_device(dev):
+            rc = lib.aimet_b200_histogram_update(
+                x.data_ptr(), layout, io, n, _f32c(cur.histogram).data_ptr(), _f32c(cur.bin_edges).data_ptr(),
+                _f32c(cur.min).data_ptr(), _f32c(cur.max).data_ptr(), rng[0].data_ptr(),
+                _f32c(self._histogram_range_limit).data_ptr(), hist.data_ptr(), edges.data_ptr(), umin.data_ptr(),
+                umax.data_ptr(), nr.data_ptr(), bmin.data_ptr(), bmax.data_ptr(), counts[0].data_ptr(),
+                counts[1].data_ptr(), carry.data_ptr(), moved.data_ptr(), _lib.ptr(scratch), scratch.numel(),
+                _lib.stream_ptr(dev))
+        if rc == _lib.AB_ERR_UNSUPPORTED:
+            return None
+        _lib.check(rc)
+        self._state = _HistogramList(hist, edges, umin, umax)
+        self._state._range = (nr, x.dtype)  # pylint: disable=protected-access
+        batch = _LazyHistogramList(None, None, bmin, bmax)
+        batch._edges = lambda: self._create_bin_edges(bmin, bmax)  # pylint: disable=protected-access
+        batch._compute = lambda: _histogram(_StatLayout(x, self.shape, self.block_size), n, batch.bin_edges[:, 0],  # pylint: disable=protected-access
+                                            batch.bin_edges[:, -1])
         return batch
 
     def reset_stats(self):

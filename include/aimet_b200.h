@@ -282,6 +282,26 @@ int aimet_b200_histogram_merge_ex(const float *new_min, const float *new_max, co
                                   float *out_min, float *out_max, float *out_carry, float *out_edges,
                                   int32_t *out_moved, float *out_range, int stat_dtype, void *stream);
 
+/* One update of a single (per-tensor) accumulated histogram with a new batch, everything a call of
+ * _HistogramObserver.collect_stats + merge_stats does (encoding_analyzer.py:194-323), enqueued by
+ * one call: the batch is binned against the current range while its own finite min / max are
+ * found; the accumulated counts move into the range that also covers the batch (growth limit
+ * applied); only if that range differs from the current one is the batch binned again, over the
+ * new range (decided on the device); the two are added.
+ *   cur_hist [num_bins], cur_edges [num_bins + 1], cur_min, cur_max [1]: the state before
+ *   cur_range [4]: first edge, last edge, and the two rounded to the tensor dtype
+ *   range_limit [2]: the growth limits of the range (-inf / +inf when there is none)
+ *   new_*: the state after (must not overlap the state before);  batch_min / batch_max [1] in the
+ *   tensor dtype;  counts, redo int64 [num_bins], carry float32 [num_bins], moved int32 [1]: work
+ *   buffers;  scratch as for aimet_b200_histogram */
+int aimet_b200_histogram_update(const void *x, const ab_layout *layout, int io_dtype, int32_t num_bins,
+                                const float *cur_hist, const float *cur_edges, const float *cur_min,
+                                const float *cur_max, const float *cur_range, const float *range_limit,
+                                float *new_hist, float *new_edges, float *new_min, float *new_max,
+                                float *new_range, void *batch_min, void *batch_max, int64_t *counts,
+                                int64_t *redo, float *carry, int32_t *moved, void *scratch,
+                                int64_t scratch_bytes, void *stream);
+
 /* hist_out[h][b] = carry[h][b] + (moved[h] ? redo : counts)[h][b] as float32: the last step of a
  * sequential update (encoding_analyzer.py:313-323), taking the batch's counts from the pass that is
  * valid for the updated range. */
