@@ -381,3 +381,28 @@ def test_gradient_multiplier_at_a_large_size():
                                                  pgs_multiplier=3.0)
     assert_same(xi.grad, ogx, "grad_x")
     _check_param_grad(s.grad, ogs, O.internal_dtype(torch.bfloat16, qmin, qmax), "grad_scale")
+
+
+def test_stack_of_parameter_sets_equals_separate_calls():
+    """``quantize_dequantize_stack``: one output slice per leading index of the parameters, each what
+    a separate call with that slice's parameters returns, in both arithmetics."""
+    B = _backend()
+    g = torch.Generator().manual_seed(5)
+    w = (torch.randn(96, 256, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    base = w.float().abs().amax(1, keepdim=True) / 7
+    scale = torch.stack([base * f for f in (0.4, 0.7, 1.0)])            # [3, 96, 1]
+    offset = torch.zeros_like(scale)
+    for grads in (False, True):
+        got = B.quantize_dequantize_stack(w, scale, offset, -8, 7, parameter_gradients=grads)
+        assert got.shape == (3, 96, 256) and got.dtype == w.dtype
+        for c in range(3):
+            s = scale[c].clone().requires_grad_(grads)
+            with torch.enable_grad() if grads else torch.no_grad():
+                want = B.quantize_dequantize(w, s, offset[c], -8, 7)
+            assert torch.equal(got[c], want.detach())
+    # blockwise parameters: [candidates, rows, blocks]
+    bscale = torch.stack([w.float().reshape(96, 4, 64).abs().amax(2) / 7 * f for f in (0.5, 1.0)])
+    got = B.quantize_dequantize_stack(w, bscale, torch.zeros_like(bscale), -8, 7, block_size=(1, 64))
+    for c in range(2):
+        want = B.quantize_dequantize(w, bscale[c], torch.zeros_like(bscale[c]), -8, 7, block_size=(1, 64))
+        assert torch.equal(got[c], want)

@@ -54,6 +54,31 @@ def test_layout_errors_and_scratch_queries_without_a_gpu():
         _lib.make_layout([1] * 9, [1] * 9)
 
 
+def test_argument_checks_that_need_no_gpu():
+    """Entry points refuse what they do not cover before anything touches the device."""
+    from aimet_b200 import _lib
+
+    lib = _lib.lib
+    one = 16  # any non-NULL value: the calls below return before a pointer is used
+    per_channel = _lib.make_layout([8, 64], [1, 64])
+    rc = lib.aimet_b200_histogram_update(one, per_channel, _lib.AB_BF16, 64, *([one] * 17), one, 0, None)
+    assert rc == _lib.AB_ERR_UNSUPPORTED and "single" in _lib.last_error()
+    per_tensor = _lib.make_layout([8, 64], [8, 64])
+    rc = lib.aimet_b200_histogram_update(one, per_tensor, _lib.AB_F64, 64, *([one] * 17), one, 0, None)
+    assert rc == _lib.AB_ERR_UNSUPPORTED
+    rc = lib.aimet_b200_histogram_update(one, per_tensor, _lib.AB_BF16, 100000, *([one] * 17), one, 0, None)
+    assert rc == _lib.AB_ERR_UNSUPPORTED and "num_bins" in _lib.last_error()
+    rc = lib.aimet_b200_quantize_dequantize_backward_ex(one, one, one, one, per_tensor, _lib.AB_F32, _lib.AB_F32, 0, 0, 255,
+                                                        0.0, 1.5, 3.0, one, None, None, None, 0, None)
+    assert rc == _lib.AB_ERR_INVALID and "pgs_eps" in _lib.last_error()
+    rc = lib.aimet_b200_sqnr_encodings(one, one, one, one, one, 19, 17, 0, _lib.AB_F32, 1, 64, 255.0, 3.0, 0.0, 1e-9,
+                                       one, None, None, one, one, one, None)
+    assert rc == _lib.AB_ERR_INVALID and "exponent" in _lib.last_error()
+    rc = lib.aimet_b200_float_fake_cast(one * 16, one * 16, one * 16, per_tensor, _lib.AB_F32, _lib.AB_BF16, _lib.AB_BF16, 4, 3,
+                                        7, 448.0, 0, None)
+    assert rc == _lib.AB_ERR_UNSUPPORTED and "in_dtype" in _lib.last_error()
+
+
 def test_cpu_tensors_are_refused():
     from aimet_b200 import backend as B
     from aimet_b200 import encoding_analyzer as EA
