@@ -19,12 +19,21 @@
 // candidates of the tile, so both accumulators are free for candidates: the MMAs of candidate g+1
 // run while the epilogue reads candidate g.
 //
-// Work items are (channel tile, token tile, block, candidate); every CTA takes a contiguous range
-// of them and recomputes the reference pass of a tile it enters in the middle, so that the load
-// balances at the granularity of one candidate pass (a 512-row shard of the weight still fills
-// all SMs).
+// Work items are (channel tile, token tile, block, candidate).  Whole waves of tiles are walked in
+// step, one tile per worker and all its candidates in turn, so that workers which share an operand
+// tile ask for it at the same time (one read from HBM, the rest from L2); what is left over after
+// the last full wave runs as a wave too if it fills most of one, and is otherwise cut at the
+// granularity of one candidate pass, a worker recomputing the reference pass of a tile it enters
+// in the middle.
 //
-// Warp roles (320 threads): warp 0 TMA producer, warp 1 TMEM allocation + MMA issue, warps 2-9
+// A worker is one CTA, or, for long passes with a reference product, a pair of CTAs (cluster of two,
+// cta_group::2, M = 256): each CTA stages its own channel tile and half of the token tile, the leader
+// issues the MMAs for both, tcgen05.commit with cluster multicast signals the barriers of both, the
+// partner's epilogue arrives on the leader's barrier through the cluster's shared window.  No TMA
+// load uses multicast.
+//
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 TMEM allocation + MMA issue (the warp walks
+// its loop uniformly, one elected lane issues a whole stage as straight-line code), warps 2-9
 // epilogue (two per TMEM lane quadrant, one per half of the columns).  Every wait is bounded: on a
 // time-out the kernel raises the status word, all roles leave their loops, TMEM is freed and the
 // kernel returns.
@@ -220,24 +229,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr)
         : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr)
-                 : "memory");
-}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 struct SeqArgs {
@@ -256,12 +247,6 @@ struct SeqArgs {
     int *status;
     unsigned long long timeout_ns;
 };
-
-__device__ __forceinline__ float round_lowp(float v, int lowp) {
-    if (lowp == 1) return __bfloat162float(__float2bfloat16_rn(v));
-    if (lowp == 2) return __half2float(__float2half_rn(v));
-    return v;
-}
 
 // two values at a time: one packed conversion (full rate; the scalar one runs on the conversion
 // pipe at a quarter of it) and two unpacking bit operations
