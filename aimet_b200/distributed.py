@@ -208,9 +208,9 @@ def calibrate_histogram(analyzer, batches: Sequence[torch.Tensor], group=None, *
     minmax_fn, counts_fn = minmax_fn or _default_minmax, counts_fn or _default_counts
     lays = None
     if batches and fast:
-        from .encoding_analyzer import _check_input, _minmax_batches, _same_layout, _StatLayout
+        from .encoding_analyzer import _layouts_of, _minmax_batches, _same_layout
 
-        lays = [_StatLayout(_check_input(x), tuple(shape), block) for x in batches]
+        lays = _layouts_of(batches, tuple(shape), block)
         if not _same_layout(lays):
             lays = None
     if lays is not None:

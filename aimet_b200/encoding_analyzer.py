@@ -188,15 +188,31 @@ class _StatLayout:
             pdims = [k for k in perm if x.shape[k] // blocks[k] > 1]
             if pdims != sorted(pdims):
                 perm = None
+        self._key = (tuple(x.shape), x.stride(), x.dtype, x.device)
+        self._copied = perm is None
         if perm is None:
             x = x.contiguous()
             perm = tuple(range(x.dim()))
+        self._perm = perm
+        self._identity = list(perm) == list(range(x.dim()))
         self.x = x.permute(perm)
         self.size = [x.shape[k] for k in perm]
         self.block = [blocks[k] for k in perm]
         self.layout = _lib.make_layout(self.size, self.block)
         self.count = int(np.prod(shape, dtype=np.int64)) if len(shape) else 1
         self.io = _lib.DTYPE_CODE[self.x.dtype]
+
+    def like(self, x: torch.Tensor) -> "_StatLayout":
+        """The layout of another tensor of the same shape, strides, dtype and device (a list of
+        calibration batches): nothing is derived again.  ``None`` if ``x`` differs in any of them."""
+        if (tuple(x.shape), x.stride(), x.dtype, x.device) != self._key:
+            return None
+        other = _StatLayout.__new__(_StatLayout)
+        other.__dict__.update(self.__dict__)
+        if self._copied:
+            x = x.contiguous()
+        other.x = x if self._identity else x.permute(self._perm)
+        return other
 
     def densify(self):
         """Fallback for layouts the kernels cannot walk in place: copy to [count, rest]."""
@@ -271,6 +287,16 @@ def _histogram_counts(lay: _StatLayout, num_bins: int, lo: torch.Tensor, hi: tor
 def _histogram(lay: _StatLayout, num_bins: int, lo: torch.Tensor, hi: torch.Tensor) -> torch.Tensor:
     """The same as float32, the dtype the reference keeps histograms in (exact below 2^24)."""
     return _histogram_counts(lay, num_bins, lo, hi).to(torch.float32)
+
+
+def _layouts_of(tensors, shape, block_size):
+    """A ``_StatLayout`` per tensor of a list; tensors shaped like the first share its derivation."""
+    first = _StatLayout(_check_input(tensors[0]), shape, block_size)
+    lays = [first]
+    for x in tensors[1:]:
+        x = _check_input(x)
+        lays.append(first.like(x) or _StatLayout(x, shape, block_size))
+    return lays
 
 
 def _same_layout(lays) -> bool:
