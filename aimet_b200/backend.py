@@ -169,7 +169,8 @@ class _Plan:
 
 def _prepare(tensor, scale, offset, block_size, internal_dtype):
     """Returns (x_dense_view, plan).  ``x_dense_view`` is a contiguous permuted view (or copy)."""
-    pshape = torch.broadcast_shapes(scale.shape, offset.shape)
+    # (torch.broadcast_shapes costs as much as the rest of this function; the shapes are nearly always equal)
+    pshape = scale.shape if scale.shape == offset.shape else torch.broadcast_shapes(scale.shape, offset.shape)
     perm = None if block_size else _dense_perm(tensor)
     if perm is None:
         x = tensor.contiguous()

@@ -106,15 +106,15 @@ def compute_encodings(model: nn.Module, group=None):
     from .quantizer import finish_calibration
 
     quantizers, weight_quantizers = [], []
+    layers = list(quantized_layers(model))
     with torch.no_grad(), contextlib.ExitStack() as stack:  # weights: observed once, in pass-through mode
-        for layer in quantized_layers(model):
+        for layer in layers:
             qw = layer.param_quantizers["weight"]
             if qw is not None and qw.is_overwrite_allowed():
                 stack.enter_context(qw._compute_encodings(passthrough=True, clone=False, finish=False))  # pylint: disable=protected-access
                 qw(layer.layer.weight.detach())
                 weight_quantizers.append(qw)
     finish_calibration(weight_quantizers)
-    layers = list(quantized_layers(model))
     with contextlib.ExitStack() as stack:
         for layer in layers:
             for q in (*layer.input_quantizers, *layer.output_quantizers):
@@ -123,11 +123,7 @@ def compute_encodings(model: nn.Module, group=None):
                     quantizers.append(q)
         # the weights do not change while the calibration data runs through: each is quantized once
         # here instead of on every forward inside the context (no-grad forwards only)
-        with torch.no_grad():
-            for layer in layers:
-                qw = layer.param_quantizers["weight"]
-                if qw is not None and qw.is_initialized():
-                    layer.__dict__["_held_weight"] = qw(layer.layer.weight).detach()
+        _hold_quantized_weights(layers)
         try:
             yield
         finally:
@@ -136,6 +132,20 @@ def compute_encodings(model: nn.Module, group=None):
     if group is not None:
         _allreduce_minmax_statistics(quantizers, group)
     finish_calibration(quantizers)
+
+
+def _hold_quantized_weights(layers):
+    """Quantize the weight of every layer once and keep it on the layer (popped by the caller).  The
+    scales and offsets of all weight quantizers come from one batched derivation: one by one, the
+    few small tensor operations per quantizer cost more than quantizing the weights."""
+    from .quantizer import derive_encodings
+
+    pairs = [(layer, layer.param_quantizers["weight"]) for layer in layers]
+    pairs = [(layer, qw) for layer, qw in pairs if qw is not None and qw.is_initialized()]
+    with torch.no_grad():
+        for (layer, qw), enc in zip(pairs, derive_encodings([qw for _, qw in pairs])):
+            with qw._set_encodings(enc):  # pylint: disable=protected-access
+                layer.__dict__["_held_weight"] = qw(layer.layer.weight).detach()
 
 
 def _allreduce_minmax_statistics(quantizers, group):
@@ -179,12 +189,15 @@ def precomputed(model: nn.Module):
     every forward (what the reference's ``fold_param_quantizers`` achieves, nn/base.py:1103-1155,
     without giving up the quantizers).  Nothing is cached outside the context, so weights and
     ranges may be edited freely (in place, through ``.data``, by re-assignment) between contexts."""
+    from .quantizer import derive_encodings
+
     with contextlib.ExitStack() as stack, torch.no_grad():
         layers = list(quantized_layers(model))
-        for layer in layers:
-            for q in (*layer.input_quantizers, *layer.output_quantizers, layer.param_quantizers["weight"]):
-                if q is not None and q.is_initialized():
-                    stack.enter_context(q._precompute_encodings())  # pylint: disable=protected-access
+        frozen = [q for layer in layers
+                  for q in (*layer.input_quantizers, *layer.output_quantizers, layer.param_quantizers["weight"])
+                  if q is not None and q.is_initialized()]
+        for q, enc in zip(frozen, derive_encodings(frozen)):
+            stack.enter_context(q._set_encodings(enc))  # pylint: disable=protected-access
         for layer in layers:
             qw = layer.param_quantizers["weight"]
             if qw is not None and qw.is_initialized():

@@ -34,6 +34,7 @@ from .encoding_analyzer import (
 
 __all__ = [
     "finish_calibration",
+    "derive_encodings",
     "AffineEncoding",
     "AffineQuantizerBase",
     "Quantize",
@@ -316,6 +317,18 @@ def _get_symmetric_offset(qmin, qmax, shape, dtype, device):
     return offset
 
 
+def _scale_of_range(min, max, num_steps, dtype):  # pylint: disable=redefined-builtin
+    """``|max - min| / num_steps``, never below the minimum scale (quantizer.py:319-342).  Elementwise,
+    so the ranges of many quantizers laid end to end give each quantizer's own values."""
+    scale = (max.to(dtype) - min.to(dtype)) / _scalar(num_steps, dtype, min.device)
+    return scale.abs().clamp_min(_get_minimum_scale(num_steps)).to(dtype)
+
+
+def _offset_of_range(min, scale, qmin, qmax, dtype):  # pylint: disable=redefined-builtin
+    """Offset of an asymmetric grid (quantizer.py:357-376); elementwise like :func:`_scale_of_range`."""
+    return torch.clamp(ste_round(min / scale) - qmin, -qmax, -qmin).to(dtype)
+
+
 def _get_scale_offset(min, max, qmin, qmax, symmetric):  # pylint: disable=redefined-builtin
     """float32 (scale, offset) of a range (quantizer.py:869-900)."""
     num_steps = qmax - qmin
@@ -496,10 +509,7 @@ class AffineQuantizerBase(QuantizerBase):
             return self._pinned_encoding.scale.to(dtype or torch.float32)
         if not self.is_initialized():
             return None
-        dtype = dtype or torch.float32
-        num_steps = self.qmax - self.qmin
-        scale = (self.max.to(dtype) - self.min.to(dtype)) / _scalar(num_steps, dtype, self.min.device)
-        return scale.abs().clamp_min(_get_minimum_scale(num_steps)).to(dtype)
+        return _scale_of_range(self.min, self.max, self.qmax - self.qmin, dtype or torch.float32)
 
     def get_offset(self, dtype=None) -> Optional[torch.Tensor]:
         return self._get_offset(dtype=dtype)
@@ -513,8 +523,7 @@ class AffineQuantizerBase(QuantizerBase):
         if self.symmetric:
             return _get_symmetric_offset(self.qmin, self.qmax, self.shape, dtype, self.min.device)
         scale = scale if scale is not None else self.get_scale(dtype)
-        offset = torch.clamp(ste_round(self.min / scale) - self.qmin, -self.qmax, -self.qmin)
-        return offset.to(dtype)
+        return _offset_of_range(self.min, scale, self.qmin, self.qmax, dtype)
 
     def get_min(self, dtype=None) -> Optional[torch.Tensor]:
         if self.get_scale(dtype) is None:
@@ -725,14 +734,61 @@ def finish_calibration(quantizers) -> None:
         mins = torch.cat([st.min.reshape(-1) for _, st in members])
         maxs = torch.cat([st.max.reshape(-1) for _, st in members])
         lo, hi = MinMaxEncodingAnalyzer(()).compute_encodings_from_stats(_MinMaxRange(mins, maxs), steps, symmetric)
-        _flag_extreme_min_max(lo, hi)
         sizes = [st.min.numel() for _, st in members]
+        dst, src = [], []
+        for (q, _), a, b in zip(members, lo.split(sizes), hi.split(sizes)):
+            if q._is_overwrite_allowed["min"]:  # pylint: disable=protected-access
+                dst.append(q.min)
+                src.append(a.view(q.shape))
+            if q._is_overwrite_allowed["max"]:  # pylint: disable=protected-access
+                dst.append(q.max)
+                src.append(b.view(q.shape))
         with torch.no_grad():
-            for (q, _), a, b in zip(members, lo.split(sizes), hi.split(sizes)):
-                if q._is_overwrite_allowed["min"]:  # pylint: disable=protected-access
-                    q.min.copy_(a.view(q.shape))
-                if q._is_overwrite_allowed["max"]:  # pylint: disable=protected-access
-                    q.max.copy_(b.view(q.shape))
+            if all(d.dtype == s.dtype for d, s in zip(dst, src)):
+                torch._foreach_copy_(dst, src)  # pylint: disable=protected-access  (all the copies in a launch or two)
+            else:
+                for d, s in zip(dst, src):
+                    d.copy_(s)
+        _flag_extreme_min_max(lo, hi)  # reads the device: last, so that the copies are queued behind the forward passes
+
+
+def derive_encodings(quantizers):
+    """``get_encodings()`` of many quantizers with a handful of launches: the ranges of all quantizers
+    that share a grid (qmin, qmax, symmetry, dtype) are laid end to end and the scale / offset
+    rules, which are elementwise, are evaluated once over all of them; each quantizer gets views of
+    the result, with the values its own ``get_encodings()`` would have computed.  Quantizers that
+    define their own rules, hold a pinned encoding or are not initialised are asked one by one.
+    Returns the encodings in the order of ``quantizers``, detached from the ranges."""
+    out, groups = {}, {}
+    plain = (AffineQuantizerBase.get_scale, AffineQuantizerBase._get_offset, AffineQuantizerBase.get_encodings)  # pylint: disable=protected-access
+    for i, q in enumerate(quantizers):
+        cls = type(q)
+        if (cls.get_scale, cls._get_offset, cls.get_encodings) != plain or q._pinned_encoding is not None \
+                or not q.is_initialized() or q.min.shape != q.max.shape:  # pylint: disable=protected-access
+            with torch.no_grad():
+                out[i] = q.get_encodings()
+            continue
+        key = (q.qmin, q.qmax, q._symmetric, q.min.dtype, q.max.dtype, q.min.device)  # pylint: disable=protected-access
+        groups.setdefault(key, []).append(i)
+    with torch.no_grad():
+        for (qmin, qmax, symmetric, _, _, device), members in groups.items():
+            qs = [quantizers[i] for i in members]
+            mins = torch.cat([q.min.reshape(-1) for q in qs])
+            maxs = torch.cat([q.max.reshape(-1) for q in qs])
+            scales = _scale_of_range(mins, maxs, qmax - qmin, torch.float32)
+            if symmetric:
+                offsets = _get_symmetric_offset(qmin, qmax, scales.shape, torch.float32, device)
+                constant = offsets._b200_constant  # pylint: disable=protected-access
+            else:
+                offsets, constant = _offset_of_range(mins, scales, qmin, qmax, torch.float32), None
+            sizes = [q.min.numel() for q in qs]
+            for i, q, s, o in zip(members, qs, scales.split(sizes), offsets.split(sizes)):
+                o = o.view(q.shape)
+                if constant is not None:
+                    o._b200_constant = constant  # pylint: disable=protected-access
+                out[i] = AffineEncoding(s.view(q.shape), o, q.qmin, q.qmax, q._symmetric, q.block_size,  # pylint: disable=protected-access
+                                        q.zero_point_shift, producer=q)
+    return [out[i] for i in range(len(quantizers))]
 
 
 class Quantize(AffineQuantizerBase):

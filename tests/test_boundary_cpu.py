@@ -153,3 +153,12 @@ def test_call_forms_agree_with_the_reference_parser():
     env = dict(os.environ, AIMET_REFERENCE_ROOT=ref)
     res = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True, env=env, timeout=600)
     assert res.returncode == 0 and "PARSE-OK" in res.stdout, res.stdout[-2000:] + res.stderr[-4000:]
+
+
+def test_batched_derivation_of_encodings_host_arithmetic():
+    """``derive_encodings`` (scale / offset of many quantizers from a handful of tensor operations)
+    gives each quantizer what its own ``get_encodings()`` gives; the CUDA run of the same check is
+    in test_quantizer_gpu.py."""
+    from test_quantizer_gpu import check_batched_derivation
+
+    check_batched_derivation("cpu")

@@ -100,3 +100,47 @@ def test_learning_moves_the_range():
         loss.backward()
         opt.step()
     assert loss.item() < before
+
+
+def _mixed_quantizers(device):
+    from aimet_b200 import quantizer as Q
+
+    torch.manual_seed(0)
+    qs = []
+    for i, (shape, bw, sym) in enumerate([((8, 1), 8, True), ((), 8, False), ((4, 1, 1, 1), 4, True), ((), 8, False),
+                                          ((3,), 16, False), ((8, 1), 8, True), ((5, 1), 8, False)]):
+        q = Q.QuantizeDequantize(shape, bw, sym)
+        lo, hi = -torch.rand(shape) * 3, torch.rand(shape) * 2
+        q.set_range(lo, lo.clone() if i == 3 else hi)  # one empty range: the minimum scale applies
+        qs.append(q)
+    qs.append(Q.QuantizeDequantize((2,), 8, True))  # never initialised: no encoding
+    lpbq = Q.GroupedBlockQuantizeDequantize((4, 2), 4, True, 8, block_size=(1, 8), block_grouping=(1, -1))
+    lpbq.set_range(-torch.rand(4, 2) - 0.1, torch.rand(4, 2) + 0.1)
+    if device == "cuda":
+        qs.append(lpbq)  # a quantizer with rules of its own is asked directly (its scale runs a kernel)
+    return [q.to(device) for q in qs]
+
+
+def check_batched_derivation(device):
+    from aimet_b200 import quantizer as Q
+
+    qs = _mixed_quantizers(device)
+    encs = Q.derive_encodings(qs)
+    assert len(encs) == len(qs)
+    for q, got in zip(qs, encs):
+        want = q.get_encodings()
+        if want is None:
+            assert got is None
+            continue
+        assert type(got) is type(want)
+        assert_same(got.scale, want.scale, "scale")
+        assert_same(got.offset, want.offset, "offset")
+        assert got.scale.shape == want.scale.shape and got.offset.shape == want.offset.shape
+        assert (got.qmin, got.qmax, got.symmetry, got.block_size, got.zero_point_shift) == \
+            (want.qmin, want.qmax, want.symmetry, want.block_size, want.zero_point_shift)
+        assert getattr(got.offset, "_b200_constant", None) == getattr(want.offset, "_b200_constant", None)
+        assert not got.scale.requires_grad and not got.offset.requires_grad
+
+
+def test_batched_derivation_of_encodings():
+    check_batched_derivation("cuda")
