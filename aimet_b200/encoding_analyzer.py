@@ -464,22 +464,23 @@ class _MinMaxObserver(_Observer):
         if not in_place:
             lay = _StatLayout(x, self.shape, self.block_size)
         st = self.stats
-        if st.min is None or st.min.dtype != x.dtype or st.min.device != x.device:
-            if st.min is not None:  # statistics of another dtype exist: fall back to the general path
+        first = st.min is None
+        if first or st.min.dtype != x.dtype or st.min.device != x.device:
+            if not first:  # statistics of another dtype exist: fall back to the general path
                 return self.merge_stats(self.collect_stats(x))
-            st = _MinMaxRange(torch.full(self.shape, float("inf"), dtype=x.dtype, device=x.device),
-                              torch.full(self.shape, float("-inf"), dtype=x.dtype, device=x.device))
-            self.stats = st
-        def launch():
-            scratch = _lib.scratch.get(x.device, nbytes)
-            return lib.aimet_b200_minmax_running(x.data_ptr() if in_place else lay.x.data_ptr(), lay.layout, lay.io, 0,
-                                                 st.min.data_ptr(), st.max.data_ptr(), _lib.ptr(scratch),
-                                                 0 if scratch is None else scratch.numel(), _lib.stream_ptr(x.device))
-
+            # the first tensor's min / max are the running ones: written, not merged into +-inf
+            st = _MinMaxRange(torch.empty(self.shape, dtype=x.dtype, device=x.device),
+                              torch.empty(self.shape, dtype=x.dtype, device=x.device))
+        entry = lib.aimet_b200_minmax if first else lib.aimet_b200_minmax_running
         with _lib.on_device(x.device):
-            rc = launch()
+            scratch = _lib.scratch.get(x.device, nbytes)
+            rc = entry(x.data_ptr() if in_place else lay.x.data_ptr(), lay.layout, lay.io, 0, st.min.data_ptr(),
+                       st.max.data_ptr(), _lib.ptr(scratch), 0 if scratch is None else scratch.numel(),
+                       _lib.stream_ptr(x.device))
         if rc == _lib.AB_ERR_UNSUPPORTED:
             return self.merge_stats(self.collect_stats(x))
+        if first and rc == 0:
+            self.stats = st
         _lib.check(rc)
         return None
 
