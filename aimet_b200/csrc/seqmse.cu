@@ -32,11 +32,15 @@
 // partner's epilogue arrives on the leader's barrier through the cluster's shared window.  No TMA
 // load uses multicast.
 //
-// Warp roles (320 threads): warp 0 TMA producer, warp 1 TMEM allocation + MMA issue (the warp walks
-// its loop uniformly, one elected lane issues a whole stage as straight-line code), warps 2-9
-// epilogue (two per TMEM lane quadrant, one per half of the columns).  Every wait is bounded: on a
-// time-out the kernel raises the status word, all roles leave their loops, TMEM is freed and the
-// kernel returns.
+// Warp roles (384 threads, three groups of four warps): warp 0 TMA producer, warp 1 TMEM allocation
+// + MMA issue (the warp walks its loop uniformly, one elected lane issues a whole stage as
+// straight-line code), warps 2-3 idle, warps 4-11 epilogue (two per TMEM lane quadrant, one per half
+// of the columns).  The first group gives registers up (setmaxnreg 56) and the epilogue groups take
+// them (224): an epilogue thread holds 128 values of the reference product, and at the 168 registers
+// a thread of this CTA gets by default its loop spilled (23 local-memory loads per pass and warp,
+// which a pass of a 64-channel block, four MMAs and a whole epilogue, cannot hide).  Every wait is
+// bounded: on a time-out the kernel raises the status word, all roles leave their loops, TMEM is
+// freed and the kernel returns.
 #include <cuda.h>
 
 #include <mutex>
@@ -51,7 +55,10 @@ constexpr int BN = 256;      // tokens per tile (MMA N, TMEM columns per accumul
 constexpr int BK = 64;       // K elements per pipeline stage: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;   // K elements per tcgen05.mma (16-bit operands)
 constexpr int kEpiWarps = 8;                 // two per TMEM lane quadrant
-constexpr int kSeqThreads = 64 + 32 * kEpiWarps;
+// Three groups of four warps: producer, MMA issue and two idle warps; then the epilogue warps.
+// Registers can only be moved between warps in such groups of four.
+constexpr int kSeqThreads = 128 + 32 * kEpiWarps;
+constexpr int kRegsFew = 56, kRegsMany = 224;  // 4 * 56 + 8 * 224 = 12 * 168, the compiled allocation
 constexpr int kHalfCols = BN / 2;            // columns of one epilogue thread
 constexpr uint32_t A_BYTES = BM * BK * 2;
 constexpr uint32_t TMEM_COLS = 512;          // two accumulators of BN columns
@@ -278,16 +285,18 @@ struct Pass {
     int ct, tt, blk, g, seg;
 };
 struct PassIter {
-    int64_t wave_unit, full_units, i, i1, done_unit, cur_unit;
+    // 32-bit throughout (the host refuses problems with 2^31 items or more): every thread of the
+    // CTA walks this sequence, and in the epilogue warps its state competes for registers with the
+    // reference product
+    int wave_unit, full_units, i, i1, done_unit, cur_unit;
     int wave_g, cur_g, seg_left;
     int num_cand, n_tt, num_blocks, num_seg;
     bool has_ref, ref_pending;
     int n_ct, width, rank;
-    int64_t G;
+    int G;
     // the remainder's position as (unit, candidate) and the decoded tile of the current unit: both
-    // advance without divisions (a block of 64 input channels is one short pass, and every thread
-    // of the CTA walks this sequence)
-    int64_t rem_u, dec_unit;
+    // advance without divisions (a block of 64 input channels is one short pass)
+    int rem_u, dec_unit;
     int rem_g, dec_ct, dec_tt, dec_blk;
     // `pair`: the workers are pairs of CTAs; a pair's unit spans two channel tiles, one per CTA
     __device__ PassIter(const SeqArgs &a, bool ref, bool pair) {
@@ -295,21 +304,22 @@ struct PassIter {
         rank = pair ? (int)(blockIdx.x & 1u) : 0;
         n_ct = (a.n_ct + width - 1) / width;
         const int64_t units = (int64_t)n_ct * a.n_tt * a.num_blocks;
-        G = gridDim.x / width;
+        G = (int)(gridDim.x / width);
         const int64_t me = blockIdx.x / width;
-        full_units = units / G * G;
+        int64_t full = units / G * G;
         // Left-over units that would fill most of a wave are run as one (some workers idle): walked
         // in step a pass takes 26 us, against 33 us for workers that start in the middle of
         // different units and ask for different candidates' weights at the same time, which beats
         // the even split once the left-over exceeds about three quarters of a wave.
-        if ((units - full_units) * 100 >= 77 * G) full_units = units;
-        wave_unit = me;
+        if ((units - full) * 100 >= 77 * (int64_t)G) full = units;
+        full_units = (int)full;
+        wave_unit = (int)me;
         wave_g = 0;
-        const int64_t items = (units - full_units) * a.num_cand;
-        i = items * me / G;
-        i1 = items * (me + 1) / G;
+        const int64_t items = (units - full) * a.num_cand;
+        i = (int)(items * me / G);
+        i1 = (int)(items * (me + 1) / G);
         rem_u = i / a.num_cand;
-        rem_g = (int)(i - rem_u * a.num_cand);
+        rem_g = i - rem_u * a.num_cand;
         dec_unit = -1;
         dec_ct = dec_tt = dec_blk = 0;
         done_unit = -1;
@@ -356,12 +366,12 @@ struct PassIter {
         }
         if (cur_unit != dec_unit) {
             dec_unit = cur_unit;
-            const int64_t t = cur_unit / num_blocks;
-            dec_blk = (int)(cur_unit - t * num_blocks);
+            const int t = cur_unit / num_blocks;
+            dec_blk = cur_unit - t * num_blocks;
             // token-tile major: the CTAs of a wave share few token tiles (the larger operand tile) and
             // spread over the channel tiles (measured: 4 % faster than channel-tile major)
-            dec_tt = (int)(t / n_ct);
-            dec_ct = (int)(t - (int64_t)dec_tt * n_ct) * width + rank;
+            dec_tt = t / n_ct;
+            dec_ct = (t - dec_tt * n_ct) * width + rank;
         }
         p.blk = dec_blk;
         p.tt = dec_tt;
@@ -491,7 +501,14 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const unsigned long long limit = a.timeout_ns;
+    // The epilogue threads keep 128 values of the reference product in registers and want as many
+    // accumulator columns in flight from TMEM as they can get; the producer and the MMA warp need
+    // little.  The first group of four warps hands registers over to the other two.
+    // (Each of the two instructions is executed by whole groups of four warps and dominates the
+    // code of its roles, which is how the compiler knows each role's allowance.)
 
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsFew));
     if (warp == 0) {
         // ---------------- TMA producer (in a pair: each CTA loads its own channel tile and its half
         // of the token tile) ----------------
@@ -598,12 +615,14 @@ k_seqmse(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUten
                 ++pass;
             }
         }
+    }
     } else {
-        // ---------------- epilogue: warps 2..9 ----------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsMany));
+        // ---------------- epilogue: warps 4..11 ----------------
         // a warp may only read the TMEM lanes of its quadrant (warp index mod 4); the two warps of a
         // quadrant take one half of the accumulator's columns each
         const int quad = warp & 3;
-        const int half = (warp - 2) >> 2;
+        const int half = (warp - 4) >> 2;
         const uint32_t lane_base = ((uint32_t)(quad * 32) << 16) + (uint32_t)(half * kHalfCols);
         const int nvals = a.loss_kind >= 2 ? 2 : 1;
         const int lowp = a.lowp, kind = a.loss_kind;
@@ -842,6 +861,8 @@ extern "C" int aimet_b200_seqmse_linear_loss_blocks(const void *x, const void *x
         if (!aligned16(p)) return fail(AB_ERR_INVALID, "operands must be 16-byte aligned");
     if ((int64_t)num_cand * N >= ((int64_t)1 << 31) || M >= ((int64_t)1 << 31) || K >= ((int64_t)1 << 31))
         return fail(AB_ERR_UNSUPPORTED, "row and column counts must fit 31 bits");
+    if (((N + BM - 1) / BM) * ((M + BN - 1) / BN) * num_blocks * num_cand >= ((int64_t)1 << 31))
+        return fail(AB_ERR_UNSUPPORTED, "tiles x blocks x candidates must fit 31 bits");
     const int64_t need = blocks_scratch_bytes(M, N, num_blocks, num_cand);
     if (!scratch || scratch_bytes < need)
         return fail(AB_ERR_SCRATCH, "seqmse needs %lld bytes of scratch, got %lld", (long long)need, (long long)scratch_bytes);
