@@ -1232,20 +1232,26 @@ def run_kernels_only(steps, case):
     """A few eager resident steps and nothing else: the small, fixed launch sequence that the ncu
     captures under ``profiles/`` are taken from (``qdq``: 8 launches per step, see
     ResidentStep.run; ``calibration``: a two-phase SQNR calibration over 4 config-3 batches;
-    ``seqmse``: the loss kernel on 4096 tokens of the q_proj shape, 20 candidates)."""
+    ``seqmse``: the loss kernel on 4096 tokens of the q_proj shape, 20 candidates;
+    ``seqmse_blockwise``: the same on 2048 tokens with the weight cut into 64 blocks of 64 input
+    channels)."""
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
-    if case == "seqmse":
-        from aimet_b200.seq_mse import linear_loss_all_candidates
+    if case in ("seqmse", "seqmse_blockwise"):
+        from aimet_b200.seq_mse import block_losses_all_candidates, linear_loss_all_candidates
 
         gen = torch.Generator(device=dev).manual_seed(5000)
-        x = torch.randn((4096, 4096), device=dev, generator=gen).to(torch.bfloat16)
+        tokens = 4096 if case == "seqmse" else 2048
+        x = torch.randn((tokens, 4096), device=dev, generator=gen).to(torch.bfloat16)
         w = (torch.randn((4096, 4096), device=dev, generator=gen) * 0.02).to(torch.bfloat16)
         smax = w.float().abs().amax(1, keepdim=True) / 7
         wq = torch.stack([(torch.clamp(torch.round(w.float() / (smax * f)), -8, 7) * (smax * f)).to(torch.bfloat16)
                           for f in torch.linspace(0.5, 1.0, 20).tolist()])
         for _ in range(steps):
-            linear_loss_all_candidates(x, x, w, wq, "mse")
+            if case == "seqmse":
+                linear_loss_all_candidates(x, x, w, wq, "mse")
+            else:
+                block_losses_all_candidates(x, x, w, wq, 64, "mse")
         torch.cuda.synchronize()
         print(json.dumps({"kernels_only_steps": steps, "case": case}))
         return
@@ -1281,7 +1287,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the calibration and SeqMSE figures")
     ap.add_argument("--kernels-only", type=int, default=0, metavar="STEPS",
                     help="run STEPS eager resident steps and exit (for profiler captures)")
-    ap.add_argument("--kernels-case", default="qdq", choices=["qdq", "calibration", "seqmse"])
+    ap.add_argument("--kernels-case", default="qdq", choices=["qdq", "calibration", "seqmse", "seqmse_blockwise"])
     args = ap.parse_args()
     if args.kernels_only:
         run_kernels_only(args.kernels_only, args.kernels_case)
