@@ -305,18 +305,23 @@ def optimize_module_sharded(quant_module, x, xq, params, group=None):
         raise PeerFailure(f"rank {rank} received no output channel ({out_ch} channels over {world} ranks)")
 
     # a view of the layer restricted to this rank's rows, with a quantizer of the matching shape
-    part = QuantizedLinear(quant_module.in_features, hi - lo, bias=False, device=quant_module.weight.device,
-                           dtype=quant_module.weight.dtype)
-    with torch.no_grad():
-        part.weight.copy_(quant_module.weight[lo:hi])
-    pq = type(qtz)((hi - lo, *qtz.shape[1:]), qtz.bitwidth, qtz.symmetric, block_size=qtz.block_size,
-                   zero_point_shift=qtz.zero_point_shift).to(quant_module.weight.device)
+    # (built without initialising a weight of its own: its weight is this rank's rows of the layer's)
+    dev = quant_module.weight.device
+    part = QuantizedLinear(quant_module.in_features, hi - lo, bias=False, device="meta", dtype=quant_module.weight.dtype)
+    part.weight = torch.nn.Parameter(quant_module.weight.detach()[lo:hi], requires_grad=False)
+    with torch.device(dev):  # parameters are created where they will live: no host-to-device copies
+        pq = type(qtz)((hi - lo, *qtz.shape[1:]), qtz.bitwidth, qtz.symmetric, block_size=qtz.block_size,
+                       zero_point_shift=qtz.zero_point_shift)
     pq.set_range(qtz.min.detach()[lo:hi], qtz.max.detach()[lo:hi])
     part.param_quantizers["weight"] = pq
     best = SequentialMse.optimize_module(part, x, xq, params)
 
-    new_min = gather_rows(pq.min.detach(), out_ch, group)
-    new_max = gather_rows(pq.max.detach(), out_ch, group)
-    qtz.set_range(new_min, new_max)
+    # ranges and winners travel together: one all-gather of [rows, min | max | winner] (the winners are
+    # small integers, exact in the parameters' float type)
+    rows = hi - lo
+    pmin, pmax = pq.min.detach().reshape(rows, -1), pq.max.detach().reshape(rows, -1)
+    ncol = pmin.shape[1]
+    packed = gather_rows(torch.cat([pmin, pmax, best.reshape(rows, -1).to(pmin.dtype)], dim=1), out_ch, group)
+    qtz.set_range(packed[:, :ncol].reshape(qtz.shape), packed[:, ncol:2 * ncol].reshape(qtz.shape))
     SequentialMse._freeze_quantizer_encoding(qtz)  # pylint: disable=protected-access
-    return gather_rows(best.reshape(hi - lo, -1), out_ch, group)
+    return packed[:, 2 * ncol:].to(best.dtype)

@@ -526,14 +526,23 @@ class AffineQuantizerBase(QuantizerBase):
         return _offset_of_range(self.min, scale, self.qmin, self.qmax, dtype)
 
     def get_min(self, dtype=None) -> Optional[torch.Tensor]:
-        if self.get_scale(dtype) is None:
+        scale = self.get_scale(dtype)  # derived once: the offset below is formed from the same values
+        if scale is None:
             return None
-        return self.get_scale(dtype) * (self.get_offset(dtype) + self.qmin + self.zero_point_shift)
+        return scale * (self._scale_and_offset(scale, dtype) + self.qmin + self.zero_point_shift)
 
     def get_max(self, dtype=None) -> Optional[torch.Tensor]:
-        if self.get_scale(dtype) is None:
+        scale = self.get_scale(dtype)
+        if scale is None:
             return None
-        return self.get_scale(dtype) * (self.get_offset(dtype) + self.qmax + self.zero_point_shift)
+        return scale * (self._scale_and_offset(scale, dtype) + self.qmax + self.zero_point_shift)
+
+    def _scale_and_offset(self, scale, dtype):
+        """``get_offset(dtype)`` given the already derived ``get_scale(dtype)`` (a subclass with its own
+        ``get_offset`` is asked directly)."""
+        if type(self).get_offset is not AffineQuantizerBase.get_offset:
+            return self.get_offset(dtype)
+        return self._get_offset(scale=scale, dtype=dtype)
 
     @torch.no_grad()
     def set_range(self, min, max):  # pylint: disable=redefined-builtin

@@ -294,12 +294,17 @@ class SequentialMse:
         lo, hi = lo.reshape(wide), hi.reshape(wide)
         steps = quantizer.qmax - quantizer.qmin - (1 if quantizer.zero_point_shift == 0.5 else 0)
         lo, hi = MinMaxEncodingAnalyzer(wide).compute_encodings_from_stats(_MinMaxRange(lo, hi), steps, quantizer.symmetric)
-        probe = QuantizeDequantize(wide, quantizer.bitwidth, quantizer.symmetric,
-                                   zero_point_shift=quantizer.zero_point_shift).to(w.device)
-        probe.signed = quantizer.signed
-        probe.set_range(lo, hi)
+        # scale and offset as a quantizer of shape (C, *shape) holding these ranges would derive them
+        # (float32 parameters, the quantizer's own grid), without building one
+        from .quantizer import _get_symmetric_offset, _offset_of_range, _scale_of_range
+
         with torch.no_grad():
-            scale, offset = probe.get_scale(), probe.get_offset()
+            lo32, hi32 = lo.to(torch.float32), hi.to(torch.float32)
+            scale = _scale_of_range(lo32, hi32, quantizer.qmax - quantizer.qmin, torch.float32)
+            if quantizer.symmetric:
+                offset = _get_symmetric_offset(quantizer.qmin, quantizer.qmax, wide, torch.float32, w.device)
+            else:
+                offset = _offset_of_range(lo32, scale, quantizer.qmin, quantizer.qmax, torch.float32)
         pshape = (c,) + shape  # per candidate: the quantizer's own parameter shape
         wants_grad = torch.is_grad_enabled() and any(p.requires_grad for p in quantizer.parameters())
         offsets = offset.reshape(pshape)
