@@ -828,8 +828,8 @@ def seqmse_figure(dev, rank, world, m=8192, n=4096, k=4096, cands=20, cpu=True):
 
 def adjacent_rows_figure(dev, cpu=True):
     """The callers and formats beside the path, each timed with CUDA events and checked against the
-    oracle on a sample: SeqMSE with blockwise weights (all blocks in one launch) and the float
-    fake-cast (fp8 e4m3 per-tensor, MXFP4 blocks of 32)."""
+    oracle on a sample: SeqMSE with blockwise weights (all blocks in one launch), SeqMSE of a Conv2d
+    layer and the float fake-cast (fp8 e4m3 per-tensor, MXFP4 blocks of 32)."""
     from aimet_b200.float_quantizer import FloatQuantizeDequantize, _MXFP4QuantizeDequantize
     from aimet_b200.seq_mse import block_losses_all_candidates
     from oracle import float_cast as OF
@@ -873,6 +873,62 @@ def adjacent_rows_figure(dev, cpu=True):
                                "parity": {"loss_max_rel_err_vs_float64": err, "rows_checked": rows, "tolerance": 1e-5,
                                           "ok": err <= 1e-5}}
     del x, w, wq, loss
+    torch.cuda.empty_cache()
+
+    # --- SeqMSE of a Conv2d layer (a ResNet-50 stage-3 3x3 convolution, 256 -> 256 channels, 14 x 14
+    # positions, 64 images): the whole search through the module API, per-channel int4 weights
+    from aimet_b200.quantizer import QuantizeDequantize
+    from aimet_b200.seq_mse import QuantizedConv2d, SeqMseParams, SequentialMse
+
+    cin, cout, hw, imgs = 256, 256, 14, 64
+    xc = torch.randn((1, imgs, cin, hw, hw), device=dev, generator=gen).to(torch.bfloat16)
+    wc = (torch.randn((cout, cin, 3, 3), device=dev, generator=gen) * 0.02).to(torch.bfloat16)
+
+    def conv_layer():
+        mod = QuantizedConv2d(cin, cout, 3, padding=1, bias=False).to(torch.bfloat16).to(dev)
+        with torch.no_grad():
+            mod.weight.copy_(wc)
+        q = QuantizeDequantize((cout, 1, 1, 1), 4, True).to(dev)
+        mod.param_quantizers["weight"] = q
+        with q.compute_encodings():
+            q(mod.weight.data)
+        return mod, q
+
+    params = SeqMseParams(num_batches=None, num_candidates=cands, loss_fn="mse")
+    times = []
+    for it in range(5):
+        mod, q = conv_layer()
+        if it == 4:
+            lo_before, hi_before = q.get_min().detach().clone(), q.get_max().detach().clone()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        SequentialMse.optimize_module(mod, xc, xc, params)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    ms = statistics.median(times[2:])
+    losses = SequentialMse.last_losses.double().cpu()  # [C, out, 1]
+    rows = 16
+    xd, wd = xc[0].double().cpu(), wc[:rows].double().cpu()
+    want = []
+    for i in range(cands):
+        cmin, cmax = OS.candidate(i, cands, lo_before[:rows].cpu(), hi_before[:rows].cpu())
+        emin, emax = OS.encodings_for_candidate(cmin, cmax, (rows, 1, 1, 1), -8, 7, True)
+        wqd = OS.quantized_weight(wc[:rows].cpu(), emin, emax, -8, 7, True, None).double()
+        want.append(OS.conv_loss(xd, xd, wd, wqd, cin, "mse", stride=1, padding=1))
+    want = torch.stack(want)
+    err = float(((losses[:, :rows] - want).abs() / want).max())
+    positions = imgs * hw * hw
+    out["seqmse_conv3x3"] = {"shape": {"images": imgs, "in": cin, "out": cout, "kernel": 3, "positions": hw * hw,
+                                       "candidates": cands},
+                             "ms": ms, "TFLOPs": 2.0 * positions * cout * cin * 9 * cands / (ms * 1e-3) / 1e12,
+                             "what": "SequentialMse.optimize_module of the layer: candidate weights, the unfolded "
+                                     "input, the loss kernel, arg-min and the final encodings (float32 loss terms)",
+                             "parity": {"loss_max_rel_err_vs_float64": err, "rows_checked": rows, "tolerance": 1e-4,
+                                        "tolerance_note": "bf16 operands, K = 2304: accumulator truncation of the "
+                                                          "tensor core", "ok": err <= 1e-4}}
+    del xc, wc
     torch.cuda.empty_cache()
 
     # --- float fake-cast of the [14336, 4096] bf16 weight: fp8 e4m3 per-tensor, MXFP4 (blocks of 32)
