@@ -780,7 +780,7 @@ int make_map(CUtensorMap *map, const void *ptr, int64_t rows, int64_t K, int box
 // The kernel moves registers between its warp groups: 4 x kRegsFew + 8 x kRegsMany must not exceed
 // what the CTA was given at launch (12 warps x the compiled register count), or the warps asking for
 // more would wait for registers that never come.  Checked once per kernel, before its first launch.
-template <auto kernel> int check_register_budget() {
+template <auto kernel> int check_register_allowance() {
     static std::mutex mu;
     static int state = 0;  // 0 unknown, 1 fine, -1 refused
     std::lock_guard<std::mutex> lock(mu);
@@ -947,14 +947,14 @@ extern "C" int aimet_b200_seqmse_linear_loss_blocks(const void *x, const void *x
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        if ((rc = check_register_budget<k_seqmse<true, true>>()) != AB_OK) return rc;
+        if ((rc = check_register_allowance<k_seqmse<true, true>>()) != AB_OK) return rc;
         AB_CUDA_OK(cudaLaunchKernelEx(&cfg, k_seqmse<true, true>, tm_w, tm_wq, tm_x, tm_xq, a));
     } else {
         // the opt-in to more than 48 KB of shared memory is a per-device attribute of the kernel
         if ((rc = opt_in_smem<k_seqmse<true, false>>(Ring<false>::kSmemBytes)) != AB_OK) return rc;
         if ((rc = opt_in_smem<k_seqmse<false, false>>(Ring<false>::kSmemBytes)) != AB_OK) return rc;
-        if ((rc = check_register_budget<k_seqmse<true, false>>()) != AB_OK) return rc;
-        if ((rc = check_register_budget<k_seqmse<false, false>>()) != AB_OK) return rc;
+        if ((rc = check_register_allowance<k_seqmse<true, false>>()) != AB_OK) return rc;
+        if ((rc = check_register_allowance<k_seqmse<false, false>>()) != AB_OK) return rc;
         const int64_t items = (int64_t)a.n_ct * a.n_tt * num_blocks * num_cand;
         int grid = sm_count();
         if (items < grid) grid = (int)items;
