@@ -337,6 +337,13 @@ class SequentialMse:
     @classmethod
     def get_min_and_max_for_candidate_selection(cls, quant_module) -> Tuple[torch.Tensor, torch.Tensor]:
         q = quant_module.param_quantizers["weight"]
+        if type(q).get_min is AffineQuantizerBase.get_min and type(q).get_max is AffineQuantizerBase.get_max:
+            # get_min() and get_max() with the scale and offset they share derived once
+            scale = q.get_scale()
+            if scale is not None:
+                offset = q._scale_and_offset(scale, None)  # pylint: disable=protected-access
+                return (scale * (offset + q.qmin + q.zero_point_shift),
+                        scale * (offset + q.qmax + q.zero_point_shift))
         return q.get_min(), q.get_max()
 
     @classmethod
