@@ -908,11 +908,12 @@ extern "C" int aimet_b200_seqmse_linear_loss_blocks(const void *x, const void *x
 
     // With a reference product, at least two channel tiles and long passes, pairs of CTAs share a
     // token tile: each CTA stages half of it and the tensor cores of both SMs read both halves,
-    // which takes a third off the operand bytes an SM has to pull in per pass.  Short passes (blocks
-    // of fewer than 1024 input channels) are bound by the hand-over between the roles, which costs
-    // twice as much across two CTAs (measured: 1.7 us against 0.85 us per pass), and stay single.
+    // which takes a third off the operand bytes an SM has to pull in per pass.  Short passes are
+    // bound by the epilogue and the hand-over between the roles, which costs twice as much across
+    // two CTAs, and stay single.  Measured on the 4096-channel layer cut into blocks: 512 channels
+    // per block 5.3 ms paired against 6.1-6.6 ms single, 256 channels 7.3-7.8 ms against 5.8 ms.
     int pair_clusters = 0;
-    if (has_reference && a.n_ct >= 2 && Kb >= 1024) {
+    if (has_reference && a.n_ct >= 2 && Kb >= 512) {
         int rc2 = pair_cluster_count(&pair_clusters);
         if (rc2 != AB_OK) return rc2;
     }
