@@ -143,7 +143,8 @@ def test_loss_kernel_shapes():
 
     g = torch.Generator().manual_seed(11)
     shapes = ((300, 130, 72, 3, 1), (1000, 260, 200, 2, 1), (17, 8, 64, 1, 1), (513, 384, 1024, 5, 1),
-              (600, 200, 256, 3, 8), (300, 130, 192, 4, 2), (257, 129, 96, 7, 6), (2100, 1000, 128, 20, 2))
+              (600, 200, 256, 3, 8), (300, 130, 192, 4, 2), (257, 129, 96, 7, 6), (2100, 1000, 128, 20, 2),
+              (700, 300, 1024, 3, 2), (520, 512, 2048, 2, 4))  # blocks long enough for CTA pairs (odd / even tile counts)
     for m, n, k, c, nb in shapes:
         x = torch.randn(m, k, generator=g).to(torch.bfloat16)
         xq = (x.float() + 0.02 * torch.randn(m, k, generator=g)).to(torch.bfloat16)
